@@ -1,0 +1,618 @@
+// Host engine behind the C handle: the B200 counterpart of class QWen3AWQInfer
+// (Inference.cu:356-415).  Same weight directory, same per-layer flow (runOneLayer,
+// Inference.cu:1029-1230), same generateResponse contract (Inference.cu:1297-1408), but:
+//   * no fp16 copies of the weights (d_dq) and no cuBLAS: five fused kernels per layer;
+//   * position, step counter and sampled token live on the device, so a token pass is a fixed
+//     launch sequence that is captured once into a CUDA graph and replayed, and the host never
+//     waits inside the loops (the reference synchronises six times per token);
+//   * the 2-GPU layer split (Inference.cu:43-47) is a list of 1..8 stages; the hidden state and
+//     the sampled id move between stages with event-ordered peer copies (the reference's copy is
+//     not ordered after the producing stream, Inference.cu:1013-1023).
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace qw3 {
+
+int gemv_launch(const W4Desc* d, const Qw3GemvArgs* a, const Workspace* ws, bool pdl, cudaStream_t st);
+int attn_decode_launch(const void* q, const void* kc, const void* vc, int heads, int head_dim, long long max_pos,
+                       const int* d_pos, int pos, void* ctx, const Workspace* ws, bool pdl, cudaStream_t st);
+int embed_gather_launch(const void* packed, const void* scale, const void* zp, long long n_alloc, long long hidden,
+                        long long vocab, const int* d_token, const int* d_index, const int* d_skip, int token, void* out,
+                        bool pdl, cudaStream_t st);
+int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, bool pdl, cudaStream_t st);
+const W4Desc* w4_desc(qw3_w4_t w);
+const Workspace* ws_struct(qw3_ws_t ws);
+
+#define QW3_TRY(expr)                     \
+    do {                                  \
+        int rc__ = (expr);                \
+        if (rc__ != QW3_OK) return rc__;  \
+    } while (0)
+
+struct W4Dev {  // AWQWeight (Inference.cu:318-325) minus d_dq
+    void* packed = nullptr;
+    void* scale = nullptr;
+    void* zp = nullptr;
+    qw3_w4_t desc = nullptr;
+    int64_t out_dim = 0, in_dim = 0, n_alloc = 0;
+};
+
+struct LayerDev {
+    W4Dev wqkv, wo, w1, w2;
+    void* gamma = nullptr;
+    void* kc = nullptr;
+    void* vc = nullptr;
+};
+
+struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
+    int device = 0;
+    int l0 = 0, l1 = 0;
+    cudaStream_t stream = nullptr;
+    qw3_ws_t ws = nullptr;
+    std::vector<LayerDev> layers;
+    void *hidden = nullptr, *q = nullptr, *ctx = nullptr, *mlp = nullptr;
+    void *cos_t = nullptr, *sin_t = nullptr;
+    int *d_pos = nullptr, *d_step = nullptr, *d_token = nullptr, *d_skip = nullptr;
+    int *d_prompt = nullptr, *d_out_ids = nullptr;
+    W4Dev emb, unemb;                  // first / last stage only
+    void* logits16 = nullptr;          // last stage
+    float* logits32 = nullptr;         // last stage, keep_logits
+    cudaEvent_t done = nullptr;        // recorded after each token pass of this stage
+    cudaEvent_t taken = nullptr;       // recorded after this stage has copied its input from a peer
+    cudaGraphExec_t g_prompt = nullptr, g_decode = nullptr;
+    int launches_prompt = 0, launches_decode = 0;
+};
+
+}  // namespace qw3
+
+using namespace qw3;
+
+struct qw3_engine {
+    Qw3Config cfg;
+    std::vector<Stage> st;
+    std::vector<void*> allocs;          // every cudaMalloc, with its device
+    std::vector<int> alloc_dev;
+    void* pinned = nullptr;
+    size_t pinned_bytes = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;  // on stage 0's device
+    float prompt_ms = 0.f, decode_ms = 0.f;
+    int64_t launches = 0;
+    int out_cap = 0;
+};
+
+namespace qw3 {
+
+static int dev_alloc(qw3_engine* e, int dev, void** p, size_t bytes) {
+    QW3_CUDA(cudaSetDevice(dev));
+    cudaError_t r = cudaMalloc(p, bytes);
+    if (r != cudaSuccess) {
+        set_last_error("cudaMalloc(%zu bytes) on device %d -> %s", bytes, dev, cudaGetErrorString(r));
+        return r == cudaErrorMemoryAllocation ? QW3_ERR_NOMEM : QW3_ERR_CUDA;
+    }
+    e->allocs.push_back(*p);
+    e->alloc_dev.push_back(dev);
+    return QW3_OK;
+}
+
+// readBinaryFileToDevice (Inference.cu:297-311): the file must hold at least `bytes`; excess is ignored.
+static int read_to_device(qw3_engine* e, const std::string& fn, void* d_ptr, size_t bytes, cudaStream_t st,
+                          std::vector<uint16_t>* keep_host = nullptr) {
+    FILE* f = std::fopen(fn.c_str(), "rb");
+    if (!f) {
+        set_last_error("could not open %s", fn.c_str());
+        return QW3_ERR_IO;
+    }
+    if (bytes > e->pinned_bytes) {
+        if (e->pinned) cudaFreeHost(e->pinned);
+        e->pinned = nullptr;
+        e->pinned_bytes = 0;
+        QW3_CUDA(cudaMallocHost(&e->pinned, bytes));
+        e->pinned_bytes = bytes;
+    }
+    const size_t got = std::fread(e->pinned, 1, bytes, f);
+    std::fclose(f);
+    if (got != bytes) {
+        set_last_error("read failed for %s: wanted %zu bytes, got %zu", fn.c_str(), bytes, got);
+        return QW3_ERR_IO;
+    }
+    if (keep_host) {
+        keep_host->resize(bytes / 2);
+        std::memcpy(keep_host->data(), e->pinned, bytes);
+    }
+    QW3_CUDA(cudaMemcpyAsync(d_ptr, e->pinned, bytes, cudaMemcpyHostToDevice, st));
+    QW3_CUDA(cudaStreamSynchronize(st));  // the staging buffer is reused by the next file
+    return QW3_OK;
+}
+
+static float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (h >> 15) & 1u, ex = (h >> 10) & 31u, man = h & 1023u;
+    float v;
+    if (ex == 0) v = std::ldexp((float)man, -24);
+    else if (ex == 31) v = man ? NAN : INFINITY;
+    else v = std::ldexp((float)(man | 1024u), (int)ex - 25);
+    return sign ? -v : v;
+}
+
+// Every zero-point an integer of magnitude <= 1023: 1024 + zp and 64 + zp are then exact in fp16.
+static int zp_all_integral(const std::vector<uint16_t>& zp) {
+    for (uint16_t h : zp) {
+        const float v = half_bits_to_float(h);
+        if (!(std::fabs(v) <= 1023.0f) || v != std::floor(v)) return 0;
+    }
+    return 1;
+}
+
+// One AWQ matrix: allocation sizes as Inference.cu:616-626, file names as Inference.cu:780-900.
+static int load_w4(qw3_engine* e, Stage& s, W4Dev& w, int64_t out_dim, int64_t in_dim, const std::string& fp,
+                   const std::string& fs, const std::string& fz, bool make_desc) {
+    w.out_dim = out_dim; w.in_dim = in_dim; w.n_alloc = out_dim / 128;
+    const size_t pbytes = (size_t)out_dim * ((in_dim + 1) / 2), gbytes = (size_t)w.n_alloc * 2;
+    QW3_TRY(dev_alloc(e, s.device, &w.packed, pbytes));
+    QW3_TRY(dev_alloc(e, s.device, &w.scale, gbytes));
+    QW3_TRY(dev_alloc(e, s.device, &w.zp, gbytes));
+    std::vector<uint16_t> zp_host;
+    QW3_TRY(read_to_device(e, fp, w.packed, pbytes, s.stream));
+    QW3_TRY(read_to_device(e, fs, w.scale, gbytes, s.stream));
+    QW3_TRY(read_to_device(e, fz, w.zp, gbytes, s.stream, &zp_host));
+    if (make_desc)
+        QW3_TRY(qw3_w4_create(w.packed, w.scale, w.zp, w.n_alloc, out_dim, in_dim, zp_all_integral(zp_host), &w.desc));
+    return QW3_OK;
+}
+
+static int validate_config(Qw3Config& c) {
+    QW3_REQUIRE(c.head_dim == 128, "config: head_dim must be 128");
+    QW3_REQUIRE(c.hidden == c.heads * c.head_dim, "config: hidden must equal heads*head_dim");
+    QW3_REQUIRE(c.hidden % 128 == 0 && c.inter % 128 == 0 && c.vocab % 128 == 0, "config: hidden, inter and vocab must be multiples of 128");
+    QW3_REQUIRE(c.layers >= 1 && c.max_pos >= 2, "config: layers >= 1 and max_pos >= 2 required");
+    QW3_REQUIRE(c.n_stages >= 1 && c.n_stages <= QW3_MAX_STAGES && c.n_stages <= c.layers, "config: n_stages must be in 1..min(8, layers)");
+    QW3_REQUIRE(c.world >= 1 && c.rank >= 0 && c.rank < c.world, "config: bad rank/world");
+    bool any = false;
+    for (int s = 0; s <= c.n_stages; ++s) any |= c.first_layer[s] != 0;
+    if (!any) {  // even split, remainder on the leading stages: 36 layers on 8 stages -> 5,5,5,5,4,4,4,4
+        const int base = c.layers / c.n_stages, rem = c.layers % c.n_stages;
+        int l = 0;
+        for (int s = 0; s < c.n_stages; ++s) {
+            c.first_layer[s] = l;
+            l += base + (s < rem ? 1 : 0);
+        }
+        c.first_layer[c.n_stages] = c.layers;
+    }
+    QW3_REQUIRE(c.first_layer[0] == 0 && c.first_layer[c.n_stages] == c.layers, "config: stage split must cover all layers");
+    for (int s = 0; s < c.n_stages; ++s)
+        QW3_REQUIRE(c.first_layer[s] < c.first_layer[s + 1], "config: every stage needs at least one layer");
+    return QW3_OK;
+}
+
+// One decoder layer for one token, five launches (runOneLayer, Inference.cu:1029-1230).
+static int enqueue_layer(qw3_engine* e, Stage& s, int li, bool pdl, int* launches) {
+    const Qw3Config& c = e->cfg;
+    LayerDev& L = s.layers[li];
+    const Workspace* ws = ws_struct(s.ws);
+    Qw3GemvArgs a;
+    // RMSNorm + Wqkv + split + RoPE + KV append (Inference.cu:1036-1103)
+    std::memset(&a, 0, sizeof(a));
+    a.d_x = s.hidden; a.d_gamma = L.gamma; a.eps = c.eps; a.epilogue = QW3_EPI_ROPE_KV; a.d_y = s.q;
+    a.d_k_cache = L.kc; a.d_v_cache = L.vc; a.d_cos = s.cos_t; a.d_sin = s.sin_t;
+    a.heads = c.heads; a.head_dim = c.head_dim; a.max_pos = c.max_pos; a.d_pos = s.d_pos;
+    QW3_TRY(gemv_launch(w4_desc(L.wqkv.desc), &a, ws, pdl, s.stream));
+    // attention over rows 0..pos (Inference.cu:1106-1120, length repaired to pos+1 in every layer)
+    QW3_TRY(attn_decode_launch(s.q, L.kc, L.vc, c.heads, c.head_dim, c.max_pos, s.d_pos, 0, s.ctx, ws, pdl, s.stream));
+    // Wo + residual (Inference.cu:1122-1156; reads ctx, never in place)
+    std::memset(&a, 0, sizeof(a));
+    a.d_x = s.ctx; a.epilogue = QW3_EPI_RESIDUAL; a.d_y = s.hidden;
+    QW3_TRY(gemv_launch(w4_desc(L.wo.desc), &a, ws, pdl, s.stream));
+    // RMSNorm (same gamma) + W1 + GeLU (Inference.cu:1158-1197)
+    std::memset(&a, 0, sizeof(a));
+    a.d_x = s.hidden; a.d_gamma = L.gamma; a.eps = c.eps; a.epilogue = QW3_EPI_GELU; a.d_y = s.mlp;
+    QW3_TRY(gemv_launch(w4_desc(L.w1.desc), &a, ws, pdl, s.stream));
+    // W2 + residual (Inference.cu:1198-1228)
+    std::memset(&a, 0, sizeof(a));
+    a.d_x = s.mlp; a.epilogue = QW3_EPI_RESIDUAL; a.d_y = s.hidden;
+    QW3_TRY(gemv_launch(w4_desc(L.w2.desc), &a, ws, pdl, s.stream));
+    *launches += 5;
+    return QW3_OK;
+}
+
+// Final norm with the last layer's gamma + unembed + arg-max (sampleNextToken, Inference.cu:1235-1292).
+static int enqueue_sample(qw3_engine* e, Stage& s, bool pdl, int* launches) {
+    const Qw3Config& c = e->cfg;
+    Qw3GemvArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.d_x = s.hidden; a.d_gamma = s.layers.back().gamma; a.eps = c.eps; a.epilogue = QW3_EPI_ARGMAX;
+    a.d_y = s.logits16; a.d_token = s.d_token; a.d_logits_f32 = s.logits32;
+    QW3_TRY(gemv_launch(w4_desc(s.unemb.desc), &a, ws_struct(s.ws), pdl, s.stream));
+    *launches += 1;
+    return QW3_OK;
+}
+
+// The launch sequence of one token pass on one stage.
+static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, bool pdl, int* launches) {
+    const Qw3Config& c = e->cfg;
+    Stage& s = e->st[si];
+    const bool first = si == 0, last = si == c.n_stages - 1;
+    QW3_CUDA(cudaSetDevice(s.device));
+    if (layers) {
+        if (first) {
+            if (decode)
+                QW3_TRY(embed_gather_launch(s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, c.hidden, c.vocab, s.d_token,
+                                            nullptr, s.d_skip, 0, s.hidden, pdl, s.stream));
+            else
+                QW3_TRY(embed_gather_launch(s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, c.hidden, c.vocab, s.d_prompt,
+                                            s.d_pos, nullptr, 0, s.hidden, pdl, s.stream));
+            *launches += 1;
+        }
+        for (int li = 0; li < (int)s.layers.size(); ++li) QW3_TRY(enqueue_layer(e, s, li, pdl, launches));
+    }
+    if (decode && last) QW3_TRY(enqueue_sample(e, s, pdl, launches));
+    QW3_TRY(step_tail_launch(layers ? s.d_pos : nullptr, (decode && last) ? s.d_step : nullptr, s.d_token,
+                             (decode && last) ? s.d_out_ids : nullptr, first ? s.d_skip : nullptr, pdl, s.stream));
+    *launches += 1;
+    return QW3_OK;
+}
+
+static int capture_stage_graph(qw3_engine* e, int si, bool decode, cudaGraphExec_t* out, int* launches) {
+    Stage& s = e->st[si];
+    QW3_CUDA(cudaSetDevice(s.device));
+    QW3_CUDA(cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeThreadLocal));
+    *launches = 0;
+    int rc = enqueue_stage_pass(e, si, decode, true, e->cfg.use_pdl != 0, launches);
+    cudaGraph_t g = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(s.stream, &g);
+    if (rc != QW3_OK) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    QW3_CUDA(ce);
+    ce = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    QW3_CUDA(ce);
+    return QW3_OK;
+}
+
+// Hidden state (and, towards stage 0, the sampled id) from stage `from` to stage `to`, ordered
+// after the producer's pass by an event (copyHiddenBetweenGPUs, Inference.cu:1013-1023).
+static int handoff(qw3_engine* e, int from, int to, bool hidden, bool token) {
+    Stage &a = e->st[from], &b = e->st[to];
+    QW3_CUDA(cudaSetDevice(b.device));
+    QW3_CUDA(cudaStreamWaitEvent(b.stream, a.done, 0));
+    if (hidden)
+        QW3_CUDA(cudaMemcpyPeerAsync(b.hidden, b.device, a.hidden, a.device, (size_t)e->cfg.hidden * 2, b.stream));
+    if (token) QW3_CUDA(cudaMemcpyPeerAsync(b.d_token, b.device, a.d_token, a.device, 4, b.stream));
+    // The producer may not overwrite what is being copied: its next pass waits for the copy.
+    QW3_CUDA(cudaEventRecord(b.taken, b.stream));
+    QW3_CUDA(cudaSetDevice(a.device));
+    QW3_CUDA(cudaStreamWaitEvent(a.stream, b.taken, 0));
+    return QW3_OK;
+}
+
+static int run_pass(qw3_engine* e, bool decode, bool layers) {
+    const Qw3Config& c = e->cfg;
+    const int N = c.n_stages;
+    for (int si = 0; si < N; ++si) {
+        Stage& s = e->st[si];
+        if (si > 0 && layers) QW3_TRY(handoff(e, si - 1, si, true, false));
+        if (!layers && si != N - 1) continue;  // sample-only pass touches the last stage alone
+        QW3_CUDA(cudaSetDevice(s.device));
+        cudaGraphExec_t g = decode ? s.g_decode : s.g_prompt;
+        if (layers && g) {
+            QW3_CUDA(cudaGraphLaunch(g, s.stream));
+            e->launches += decode ? s.launches_decode : s.launches_prompt;
+        } else {
+            int n = 0;
+            QW3_TRY(enqueue_stage_pass(e, si, decode, layers, false, &n));
+            e->launches += n;
+        }
+        QW3_CUDA(cudaEventRecord(s.done, s.stream));
+    }
+    return QW3_OK;
+}
+
+}  // namespace qw3
+
+extern "C" {
+
+int qw3_config_default(Qw3Config* c) {
+    QW3_REQUIRE(c, "qw3_config_default: null pointer");
+    std::memset(c, 0, sizeof(*c));
+    c->hidden = 4096; c->inter = 12288; c->heads = 32; c->head_dim = 128; c->layers = 36; c->vocab = 151936;
+    c->max_pos = 40960; c->eps = 1e-6f; c->rope_base = 10000.0f; c->sample_first = 0;
+    c->n_stages = 1; c->rank = 0; c->world = 1; c->use_graph = 1; c->use_pdl = 1; c->keep_logits = 0;
+    return QW3_OK;
+}
+
+int qw3_destroy(qw3_handle e) {
+    if (!e) return QW3_OK;
+    for (Stage& s : e->st) {
+        cudaSetDevice(s.device);
+        if (s.stream) cudaStreamSynchronize(s.stream);
+        if (s.g_prompt) cudaGraphExecDestroy(s.g_prompt);
+        if (s.g_decode) cudaGraphExecDestroy(s.g_decode);
+        for (LayerDev& L : s.layers) {
+            qw3_w4_destroy(L.wqkv.desc); qw3_w4_destroy(L.wo.desc); qw3_w4_destroy(L.w1.desc); qw3_w4_destroy(L.w2.desc);
+        }
+        qw3_w4_destroy(s.unemb.desc);
+        if (s.ws) qw3_ws_destroy(s.ws);
+        if (s.done) cudaEventDestroy(s.done);
+        if (s.taken) cudaEventDestroy(s.taken);
+        if (s.stream) cudaStreamDestroy(s.stream);
+    }
+    if (!e->st.empty()) cudaSetDevice(e->st[0].device);
+    if (e->ev0) cudaEventDestroy(e->ev0);
+    if (e->ev1) cudaEventDestroy(e->ev1);
+    if (e->ev2) cudaEventDestroy(e->ev2);
+    for (size_t i = 0; i < e->allocs.size(); ++i) {
+        cudaSetDevice(e->alloc_dev[i]);
+        cudaFree(e->allocs[i]);
+    }
+    if (e->pinned) cudaFreeHost(e->pinned);
+    delete e;
+    return QW3_OK;
+}
+
+static int create_impl(const char* weight_dir, qw3_engine* e) {
+    Qw3Config& c = e->cfg;
+    QW3_TRY(validate_config(c));
+    QW3_REQUIRE(c.world == 1, "qw3_create: one process per GPU (world > 1) is not enabled in this build");
+    int ndev = 0;
+    QW3_CUDA(cudaGetDeviceCount(&ndev));
+    for (int s = 0; s < c.n_stages; ++s) {
+        if (c.device[s] < 0 || c.device[s] >= ndev) {   // Inference.cu:566-569
+            set_last_error("stage %d wants device %d but only %d device(s) are visible", s, c.device[s], ndev);
+            return QW3_ERR_DEVICE;
+        }
+    }
+    const std::string dir(weight_dir);
+    const int H = c.hidden, I = c.inter, V = c.vocab, N = c.n_stages;
+    e->st.resize(N);
+    // initMultiGPU (Inference.cu:563-596): peer access between every pair of devices in use.
+    for (int a = 0; a < N; ++a)
+        for (int b = 0; b < N; ++b) {
+            const int da = c.device[a], db = c.device[b];
+            if (da == db) continue;
+            int can = 0;
+            QW3_CUDA(cudaDeviceCanAccessPeer(&can, da, db));
+            if (!can) {
+                set_last_error("P2P not supported between device %d and device %d", da, db);
+                return QW3_ERR_DEVICE;
+            }
+            QW3_CUDA(cudaSetDevice(da));
+            cudaError_t pe = cudaDeviceEnablePeerAccess(db, 0);
+            if (pe == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else QW3_CUDA(pe);
+        }
+    std::vector<uint16_t> h_cos((size_t)c.max_pos * 64), h_sin((size_t)c.max_pos * 64);
+    for (int pos = 0; pos < c.max_pos; ++pos)           // Inference.cu:444-454 (fp16 tables, host libm)
+        for (int i = 0; i < 64; ++i) {
+            const float inv_freq = 1.0f / powf(c.rope_base, float(2 * i) / float(c.head_dim));
+            const float angle = float(pos) * inv_freq;
+            const __half hc = __float2half_rn(cosf(angle)), hs = __float2half_rn(sinf(angle));
+            std::memcpy(&h_cos[(size_t)pos * 64 + i], &hc, 2);
+            std::memcpy(&h_sin[(size_t)pos * 64 + i], &hs, 2);
+        }
+    for (int si = 0; si < N; ++si) {
+        Stage& s = e->st[si];
+        s.device = c.device[si]; s.l0 = c.first_layer[si]; s.l1 = c.first_layer[si + 1];
+        QW3_CUDA(cudaSetDevice(s.device));
+        QW3_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+        QW3_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+        QW3_CUDA(cudaEventCreateWithFlags(&s.taken, cudaEventDisableTiming));
+        QW3_TRY(qw3_ws_create(&s.ws));
+        qw3_ws_set_pdl(s.ws, c.use_pdl);
+        QW3_TRY(dev_alloc(e, s.device, &s.hidden, (size_t)H * 2));
+        QW3_TRY(dev_alloc(e, s.device, &s.q, (size_t)H * 2));
+        QW3_TRY(dev_alloc(e, s.device, &s.ctx, (size_t)H * 2));
+        QW3_TRY(dev_alloc(e, s.device, &s.mlp, (size_t)I * 2));
+        QW3_TRY(dev_alloc(e, s.device, &s.cos_t, h_cos.size() * 2));
+        QW3_TRY(dev_alloc(e, s.device, &s.sin_t, h_sin.size() * 2));
+        QW3_CUDA(cudaMemcpyAsync(s.cos_t, h_cos.data(), h_cos.size() * 2, cudaMemcpyHostToDevice, s.stream));
+        QW3_CUDA(cudaMemcpyAsync(s.sin_t, h_sin.data(), h_sin.size() * 2, cudaMemcpyHostToDevice, s.stream));
+        void* ints = nullptr;
+        QW3_TRY(dev_alloc(e, s.device, &ints, 256));
+        QW3_CUDA(cudaMemsetAsync(ints, 0, 256, s.stream));
+        s.d_pos = static_cast<int*>(ints); s.d_step = s.d_pos + 1; s.d_token = s.d_pos + 2; s.d_skip = s.d_pos + 3;
+        QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_prompt), (size_t)c.max_pos * 4));
+        QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_out_ids), (size_t)c.max_pos * 4));
+        QW3_CUDA(cudaMemsetAsync(s.hidden, 0, (size_t)H * 2, s.stream));
+        s.layers.resize(s.l1 - s.l0);
+        const size_t kv_bytes = (size_t)c.heads * c.max_pos * c.head_dim * 2;   // Inference.cu:676
+        for (int l = s.l0; l < s.l1; ++l) {
+            LayerDev& L = s.layers[l - s.l0];
+            const std::string p = dir + "/layer_" + std::to_string(l) + "_";
+            QW3_TRY(load_w4(e, s, L.wqkv, 3 * (int64_t)H, H, p + "wqkv.bin", p + "bqkv_scale.bin", p + "bqkv_zp.bin", true));
+            QW3_TRY(load_w4(e, s, L.wo, H, H, p + "wo.bin", p + "wo_scale.bin", p + "wo_zp.bin", true));
+            QW3_TRY(load_w4(e, s, L.w1, I, H, p + "w1.bin", p + "w1_scale.bin", p + "w1_zp.bin", true));
+            QW3_TRY(load_w4(e, s, L.w2, H, I, p + "w2.bin", p + "w2_scale.bin", p + "w2_zp.bin", true));
+            QW3_TRY(dev_alloc(e, s.device, &L.gamma, (size_t)H * 2));
+            QW3_TRY(read_to_device(e, dir + "/rms_norm_gamma_" + std::to_string(l) + ".bin", L.gamma, (size_t)H * 2, s.stream));
+            QW3_TRY(dev_alloc(e, s.device, &L.kc, kv_bytes));
+            QW3_TRY(dev_alloc(e, s.device, &L.vc, kv_bytes));
+            QW3_CUDA(cudaMemsetAsync(L.kc, 0, kv_bytes, s.stream));             // Inference.cu:431-437
+            QW3_CUDA(cudaMemsetAsync(L.vc, 0, kv_bytes, s.stream));
+        }
+        if (si == 0)
+            QW3_TRY(load_w4(e, s, s.emb, H, V, dir + "/word_embedding.bin", dir + "/word_embed_scale.bin",
+                            dir + "/word_embed_zp.bin", false));
+        if (si == N - 1) {
+            QW3_TRY(load_w4(e, s, s.unemb, V, H, dir + "/unembed.bin", dir + "/unembed_scale.bin", dir + "/unembed_zp.bin", true));
+            QW3_TRY(dev_alloc(e, s.device, &s.logits16, (size_t)V * 2));
+            if (c.keep_logits) QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.logits32), (size_t)V * 4));
+        }
+        QW3_CUDA(cudaStreamSynchronize(s.stream));
+    }
+    QW3_CUDA(cudaSetDevice(e->st[0].device));
+    QW3_CUDA(cudaEventCreate(&e->ev0));
+    QW3_CUDA(cudaEventCreate(&e->ev1));
+    QW3_CUDA(cudaEventCreate(&e->ev2));
+    if (e->pinned) {
+        cudaFreeHost(e->pinned);
+        e->pinned = nullptr;
+        e->pinned_bytes = 0;
+    }
+    if (c.use_graph) {
+        for (int si = 0; si < N; ++si) {
+            QW3_TRY(capture_stage_graph(e, si, false, &e->st[si].g_prompt, &e->st[si].launches_prompt));
+            QW3_TRY(capture_stage_graph(e, si, true, &e->st[si].g_decode, &e->st[si].launches_decode));
+        }
+    }
+    return QW3_OK;
+}
+
+int qw3_create(const char* weight_dir, const Qw3Config* cfg, qw3_handle* out) {
+    QW3_REQUIRE(weight_dir && out, "qw3_create: null pointer");
+    qw3_engine* e = new (std::nothrow) qw3_engine();
+    if (!e) return QW3_ERR_NOMEM;
+    if (cfg) e->cfg = *cfg; else qw3_config_default(&e->cfg);
+    int rc = create_impl(weight_dir, e);
+    if (rc != QW3_OK) {
+        qw3_destroy(e);
+        return rc;
+    }
+    *out = e;
+    return QW3_OK;
+}
+
+int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_ids, int32_t* n_out) {
+    QW3_REQUIRE(e && prompt && (out_ids || max_new == 0), "qw3_generate: null pointer");
+    const Qw3Config& c = e->cfg;
+    if (n_prompt < 1 || max_new < 0 || (int64_t)n_prompt + max_new > c.max_pos) {   // Inference.cu:1301, plus the new tokens
+        set_last_error("qw3_generate: prompt of %d plus %d new tokens does not fit max_pos=%d", n_prompt, max_new, c.max_pos);
+        return QW3_ERR_RANGE;
+    }
+    for (int t = 0; t < n_prompt; ++t)
+        if (prompt[t] < 0 || prompt[t] >= c.vocab) {
+            set_last_error("qw3_generate: token id %d at %d is outside [0, %d)", prompt[t], t, c.vocab);
+            return QW3_ERR_RANGE;
+        }
+    const int N = c.n_stages;
+    Stage &s0 = e->st[0], &sl = e->st[N - 1];
+    e->launches = 0;
+    // The object is reusable: position and step restart for every call.
+    for (int si = 0; si < N; ++si) {
+        Stage& s = e->st[si];
+        QW3_CUDA(cudaSetDevice(s.device));
+        QW3_CUDA(cudaMemsetAsync(s.d_pos, 0, 16, s.stream));
+    }
+    QW3_CUDA(cudaSetDevice(s0.device));
+    QW3_CUDA(cudaMemcpyAsync(s0.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s0.stream));
+    QW3_CUDA(cudaEventRecord(e->ev0, s0.stream));
+    for (int t = 0; t < n_prompt; ++t) QW3_TRY(run_pass(e, false, true));            // Inference.cu:1304-1343
+    QW3_CUDA(cudaSetDevice(s0.device));
+    QW3_CUDA(cudaStreamWaitEvent(s0.stream, sl.done, 0));
+    QW3_CUDA(cudaEventRecord(e->ev1, s0.stream));
+    for (int step = 0; step < max_new; ++step) {                                     // Inference.cu:1352-1405
+        bool layers = true;
+        if (c.sample_first && step == 0) layers = false;
+        if (layers) {
+            if (step == 0) {
+                // Reference flow: step 0 re-enters layer 0 with the final hidden state of the last
+                // prompt token (Inference.cu:1357): move it back to stage 0 and skip the gather.
+                if (N > 1) QW3_TRY(handoff(e, N - 1, 0, true, false));
+                const int one = 1;
+                QW3_CUDA(cudaSetDevice(s0.device));
+                QW3_CUDA(cudaMemcpyAsync(s0.d_skip, &one, 4, cudaMemcpyHostToDevice, s0.stream));
+            } else if (N > 1) {
+                QW3_TRY(handoff(e, N - 1, 0, false, true));                           // sampled id -> stage 0
+            }
+        }
+        QW3_TRY(run_pass(e, true, layers));
+    }
+    QW3_CUDA(cudaSetDevice(s0.device));
+    QW3_CUDA(cudaStreamWaitEvent(s0.stream, sl.done, 0));
+    QW3_CUDA(cudaEventRecord(e->ev2, s0.stream));
+    QW3_CUDA(cudaStreamSynchronize(s0.stream));
+    QW3_CUDA(cudaSetDevice(sl.device));
+    QW3_CUDA(cudaStreamSynchronize(sl.stream));
+    if (max_new > 0) QW3_CUDA(cudaMemcpy(out_ids, sl.d_out_ids, (size_t)max_new * 4, cudaMemcpyDeviceToHost));
+    if (n_out) *n_out = max_new;
+    QW3_CUDA(cudaEventElapsedTime(&e->prompt_ms, e->ev0, e->ev1));
+    QW3_CUDA(cudaEventElapsedTime(&e->decode_ms, e->ev1, e->ev2));
+    for (int si = 0; si < N; ++si) {
+        QW3_CUDA(cudaSetDevice(e->st[si].device));
+        QW3_TRY(qw3_ws_check(e->st[si].ws, e->st[si].stream));
+    }
+    return QW3_OK;
+}
+
+int qw3_last_logits(qw3_handle e, float* out_vocab) {
+    QW3_REQUIRE(e && out_vocab, "qw3_last_logits: null pointer");
+    Stage& sl = e->st.back();
+    if (!sl.logits32) {
+        set_last_error("qw3_last_logits: the handle was created with keep_logits = 0");
+        return QW3_ERR_STATE;
+    }
+    QW3_CUDA(cudaSetDevice(sl.device));
+    QW3_CUDA(cudaStreamSynchronize(sl.stream));
+    QW3_CUDA(cudaMemcpy(out_vocab, sl.logits32, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost));
+    return QW3_OK;
+}
+
+int qw3_last_timing(qw3_handle e, float* prompt_ms, float* decode_ms) {
+    QW3_REQUIRE(e, "qw3_last_timing: null handle");
+    if (prompt_ms) *prompt_ms = e->prompt_ms;
+    if (decode_ms) *decode_ms = e->decode_ms;
+    return QW3_OK;
+}
+
+int qw3_last_launches(qw3_handle e, int64_t* n) {
+    QW3_REQUIRE(e && n, "qw3_last_launches: null pointer");
+    *n = e->launches;
+    return QW3_OK;
+}
+
+static Stage* stage_of_layer(qw3_engine* e, int layer) {
+    for (Stage& s : e->st)
+        if (layer >= s.l0 && layer < s.l1) return &s;
+    return nullptr;
+}
+
+int qw3_kv_upload(qw3_handle e, int32_t layer, int32_t which, const void* host_f16, int64_t upto) {
+    QW3_REQUIRE(e && host_f16, "qw3_kv_upload: null pointer");
+    Stage* s = stage_of_layer(e, layer);
+    QW3_REQUIRE(s && upto >= 0 && upto <= e->cfg.max_pos, "qw3_kv_upload: layer or row count out of range");
+    const Qw3Config& c = e->cfg;
+    LayerDev& L = s->layers[layer - s->l0];
+    QW3_CUDA(cudaSetDevice(s->device));
+    __half* dst = static_cast<__half*>(which ? L.vc : L.kc);
+    const __half* src = static_cast<const __half*>(host_f16);
+    for (int h = 0; h < c.heads; ++h)
+        QW3_CUDA(cudaMemcpyAsync(dst + (size_t)h * c.max_pos * 128, src + (size_t)h * upto * 128, (size_t)upto * 256,
+                                 cudaMemcpyHostToDevice, s->stream));
+    QW3_CUDA(cudaStreamSynchronize(s->stream));
+    return QW3_OK;
+}
+
+int qw3_layer_decode(qw3_handle e, int32_t layer, int32_t pos, void* host_hidden) {
+    QW3_REQUIRE(e && host_hidden, "qw3_layer_decode: null pointer");
+    Stage* s = stage_of_layer(e, layer);
+    QW3_REQUIRE(s && pos >= 0 && pos < e->cfg.max_pos, "qw3_layer_decode: layer or pos out of range");
+    QW3_CUDA(cudaSetDevice(s->device));
+    QW3_CUDA(cudaMemcpyAsync(s->hidden, host_hidden, (size_t)e->cfg.hidden * 2, cudaMemcpyHostToDevice, s->stream));
+    QW3_CUDA(cudaMemcpyAsync(s->d_pos, &pos, 4, cudaMemcpyHostToDevice, s->stream));
+    int n = 0;
+    QW3_TRY(enqueue_layer(e, *s, layer - s->l0, false, &n));
+    QW3_CUDA(cudaMemcpyAsync(host_hidden, s->hidden, (size_t)e->cfg.hidden * 2, cudaMemcpyDeviceToHost, s->stream));
+    QW3_CUDA(cudaStreamSynchronize(s->stream));
+    return qw3_ws_check(s->ws, s->stream);
+}
+
+int qw3_stage_export(qw3_handle, void*) {
+    set_last_error("qw3_stage_export: one process per GPU is not enabled in this build");
+    return QW3_ERR_STATE;
+}
+
+int qw3_stage_connect(qw3_handle, const void*) {
+    set_last_error("qw3_stage_connect: one process per GPU is not enabled in this build");
+    return QW3_ERR_STATE;
+}
+
+int qw3_gemm_w4a16(qw3_w4_t, const void*, int64_t, void*, qw3_ws_t, void*) {
+    set_last_error("qw3_gemm_w4a16: not built yet");
+    return QW3_ERR_STATE;
+}
+
+}  // extern "C"

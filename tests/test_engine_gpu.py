@@ -1,0 +1,155 @@
+"""GPU parity of the engine (QWen3AWQInfer over the C ABI) against the CPU oracle: one decoder
+layer, whole-model greedy decoding, stage-split invariance, error behaviour."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from test_gemv_gpu import _ulp_diff
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLDEN = json.load(open(os.path.join(HERE, "golden", "golden.json")))
+SMALL = dict(hidden=512, inter=1536, heads=4, head_dim=128, layers=4, vocab=2176, max_pos=64, rope_base=10000.0)
+
+
+@pytest.fixture(scope="module")
+def small_dir(orc, tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("w_small"))
+    orc.write_weight_dir(orc.default_config(**SMALL), 0, d)
+    return d
+
+
+def _oracle_generate(orc, cfg_kw, seed, weight_dir, prompt, max_new, sample_first=0):
+    m = orc.Model(orc.default_config(sample_first=sample_first, **cfg_kw))
+    assert m.load_dir(weight_dir) == 0
+    out = m.generate(prompt, max_new)
+    m.close()
+    return out
+
+
+def _logits_close(got32, want16):
+    want = want16.astype(np.float32)
+    return (np.abs(got32 - want) <= 2e-2 * np.abs(want) + 2e-2 * np.abs(want).mean()).all()
+
+
+@pytest.mark.parametrize("use_graph,use_pdl", [(0, 0), (1, 0), (0, 1), (1, 1)])
+def test_small_model_tokens_match_oracle(pkg, orc, cuda, small_dir, use_graph, use_pdl):
+    prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
+    ids, logits, margins = _oracle_generate(orc, SMALL, 0, small_dir, prompt, 10)
+    assert [int(t) for t in ids] == GOLDEN["small_model"]["ids"]          # the oracle itself is pinned
+    inf = pkg.QWen3AWQInfer(small_dir, use_graph=use_graph, use_pdl=use_pdl, keep_logits=1, **SMALL)
+    got = inf.generateResponse(prompt, 10)
+    assert got == [int(t) for t in ids], f"margins {margins}"
+    assert _logits_close(inf.last_logits(), logits)
+    assert inf.generateResponse(prompt, 10) == got                         # the object is reusable
+    assert inf.last_launches() > 0
+    inf.close()
+
+
+def test_small_model_sample_first(pkg, orc, cuda, small_dir):
+    prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
+    ids, _, _ = _oracle_generate(orc, SMALL, 0, small_dir, prompt, 10, sample_first=1)
+    assert [int(t) for t in ids] == GOLDEN["small_model_sample_first"]["ids"]
+    inf = pkg.QWen3AWQInfer(small_dir, sample_first=1, **SMALL)
+    assert inf.generateResponse(prompt, 10) == [int(t) for t in ids]
+    inf.close()
+
+
+@pytest.mark.parametrize("n_stages", [2, 3, 4])
+def test_stage_split_does_not_change_tokens(pkg, orc, cuda, small_dir, n_stages):
+    """Layer pipeline with several logical stages mapped onto one device: the hand-off is a local
+    copy, the results must equal the single-stage run."""
+    prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
+    inf = pkg.QWen3AWQInfer(small_dir, n_stages=n_stages, device=[0] * n_stages, keep_logits=1, **SMALL)
+    got = inf.generateResponse(prompt, 10)
+    assert got == GOLDEN["small_model"]["ids"]
+    inf.close()
+
+
+def test_one_decoder_layer_full_width(pkg, orc, cuda, tmp_path):
+    """One Qwen3-8B-shape layer at batch 1: hidden 4096, 32 heads, wqkv 12288x4096, wo 4096x4096,
+    w1/w2 at 12288, RoPE base 1e6, KV rows 0..511 pre-filled N(0,1), decode at position 512."""
+    cfg_kw = dict(hidden=4096, inter=12288, heads=32, head_dim=128, layers=1, vocab=1024, max_pos=1024, rope_base=1e6)
+    d = str(tmp_path)
+    cfg = orc.default_config(**cfg_kw)
+    orc.write_weight_dir(cfg, 0, d)
+    m = orc.Model(cfg)
+    assert m.load_dir(d) == 0
+    m.fill_kv(0, 512)
+    hidden = orc.gen_normal_f16(0, orc.ACT, 4096)
+    want = m.layer(0, 512, hidden)
+    inf = pkg.QWen3AWQInfer(d, **cfg_kw)
+    for which in (0, 1):
+        kv = m.kv(0, which).reshape(32, 1024, 128)[:, :512].copy()
+        inf.kv_upload(0, which, kv, 512)
+    got = inf.layer_decode(0, 512, hidden)
+    inf.close()
+    m.close()
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert (err <= 2e-2 * np.abs(want.astype(np.float32)) + 2e-2 * np.abs(want.astype(np.float32)).mean()).all()
+    d_ulp = _ulp_diff(got, want)
+    assert (d_ulp > 1).mean() < 0.02, f"{(d_ulp > 1).mean():.4f} of the hidden state is more than one ulp off"
+
+
+def test_full_model_tokens_match_golden(pkg, orc, cuda, tmp_path):
+    """Full 36-layer model, prompt 128, 20 greedy tokens, one GPU; expected ids were produced by the
+    CPU oracle (tests/golden/make_golden.py --full) from the same seeded weights."""
+    g = GOLDEN.get("full_model")
+    if g is None:
+        pytest.skip("golden.json has no full-size entry")
+    d = str(tmp_path)
+    cfg = orc.default_config(**g["config"])
+    orc.write_weight_dir(cfg, g["seed"], d)
+    prompt = orc.gen_tokens(g["seed"], orc.TOKENS, g["n_prompt"], cfg.vocab)
+    assert [int(t) for t in prompt[:8]] == g["prompt_head"]
+    inf = pkg.QWen3AWQInfer(d, keep_logits=1, **g["config"])
+    got = inf.generateResponse(prompt, g["max_new"])
+    logits = inf.last_logits()
+    inf.close()
+    assert got == g["ids"], f"oracle top-1/top-2 margins per step: {g['margins']}"
+    top = np.array(g["last_logits_top8_idx"])
+    want = np.array(g["last_logits_top8"], np.float32)
+    assert (np.abs(logits[top] - want) <= 2e-2 * np.abs(want)).all()
+
+
+def test_errors_are_status_codes(pkg, orc, cuda, small_dir, tmp_path):
+    cabi = pkg.cabi
+    with pytest.raises(cabi.Qw3Error) as e:   # missing directory
+        pkg.QWen3AWQInfer(str(tmp_path / "nowhere"), **SMALL)
+    assert e.value.status == cabi.QW3_ERR_IO
+    d = str(tmp_path / "short")
+    subprocess.check_call(["cp", "-r", small_dir, d])
+    with open(os.path.join(d, "layer_2_w1.bin"), "r+b") as f:   # short file (Inference.cu:305-308)
+        f.truncate(100)
+    with pytest.raises(cabi.Qw3Error) as e:
+        pkg.QWen3AWQInfer(d, **SMALL)
+    assert e.value.status == cabi.QW3_ERR_IO
+    with pytest.raises(cabi.Qw3Error) as e:   # more stages than devices
+        pkg.QWen3AWQInfer(small_dir, n_stages=2, device=[0, 99], **SMALL)
+    assert e.value.status == cabi.QW3_ERR_DEVICE
+    inf = pkg.QWen3AWQInfer(small_dir, **SMALL)
+    with pytest.raises(cabi.Qw3Error) as e:   # prompt + new tokens beyond the KV capacity
+        inf.generateResponse([1] * 60, 10)
+    assert e.value.status == cabi.QW3_ERR_RANGE
+    with pytest.raises(cabi.Qw3Error) as e:   # token id outside the vocabulary
+        inf.generateResponse([5, 999999], 2)
+    assert e.value.status == cabi.QW3_ERR_RANGE
+    with pytest.raises(cabi.Qw3Error) as e:   # empty prompt
+        inf.generateResponse([], 2)
+    assert e.value.status == cabi.QW3_ERR_RANGE
+    assert inf.generateResponse([5, 6], 0) == []
+    assert len(inf.generateResponse([5, 6], 3)) == 3            # still usable after the errors
+    inf.close()
+
+
+def test_example_binary_prints_oracle_tokens(pkg, orc, cuda, small_dir):
+    """The reference's main (Inference.cu:1413-1433): single-token prompt, 20 new tokens."""
+    exe = os.path.join(os.path.dirname(pkg.cabi.LIB_PATH), "qwen3_awq_infer")
+    out = subprocess.run([exe, small_dir, "20", "1", "4", "512", "1536", "2176", "64"], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    ids, _, _ = _oracle_generate(orc, SMALL, 0, small_dir, np.array([0], np.int32), 20)
+    assert out.stdout.split(":")[1].split() == [str(int(t)) for t in ids]

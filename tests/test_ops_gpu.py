@@ -1,0 +1,76 @@
+"""GPU parity of the small operators (RMSNorm, RoPE + KV append, decode attention, embedding
+gather, arg-max) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from test_gemv_gpu import _to_dev, _ulp_diff
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [128, 512, 4096, 12288])
+def test_rmsnorm_bit_exact(ops, orc, cuda, n):
+    x = orc.gen_normal_f16(21, orc.ACT, n, 0.0, 3.0)
+    g = orc.gen_normal_f16(21, orc.GAMMA, n, 1.0, 0.02)
+    want = orc.rmsnorm(x, g)
+    got = ops.rmsnorm(_to_dev(x, cuda), _to_dev(g, cuda)).cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_rope_kv_append_bit_exact(ops, orc, cuda):
+    heads, max_pos = 8, 128
+    H = heads * 128
+    qkv = orc.gen_normal_f16(22, orc.ACT, 3 * H)
+    cos_t, sin_t = orc.rope_tables(max_pos, 128, 10000.0)
+    for pos in (0, 1, 77, 127):
+        q = torch.zeros(H, dtype=torch.float16, device=cuda)
+        kc = torch.zeros(heads, max_pos, 128, dtype=torch.float16, device=cuda)
+        vc = torch.zeros_like(kc)
+        ops.rope_kv_append(_to_dev(qkv, cuda), q, kc, vc, _to_dev(cos_t, cuda), _to_dev(sin_t, cuda), heads, max_pos, pos)
+        assert np.array_equal(q.cpu().numpy().view(np.uint16), orc.rope(qkv[:H], heads, 128, cos_t, sin_t, pos).view(np.uint16))
+        assert np.array_equal(kc[:, pos].reshape(-1).cpu().numpy().view(np.uint16),
+                              orc.rope(qkv[H:2 * H], heads, 128, cos_t, sin_t, pos).view(np.uint16))
+        assert np.array_equal(vc[:, pos].reshape(-1).cpu().numpy().view(np.uint16), qkv[2 * H:].view(np.uint16))
+
+
+@pytest.mark.parametrize("heads,max_pos,length", [(4, 64, 1), (4, 64, 2), (8, 600, 513), (32, 1024, 512), (32, 2048, 2048), (2, 4096, 3000)])
+def test_attention_decode(ops, orc, cuda, heads, max_pos, length):
+    q = orc.gen_normal_f16(23, orc.ACT, heads * 128)
+    kc = orc.gen_normal_f16(23, orc.KV_K, heads * max_pos * 128)
+    vc = orc.gen_normal_f16(23, orc.KV_V, heads * max_pos * 128)
+    want = orc.attention(q, kc, vc, heads, 128, max_pos, length)
+    ws = ops.Workspace()
+    for _ in range(2):
+        got = ops.attn_decode(_to_dev(q, cuda), _to_dev(kc, cuda), _to_dev(vc, cuda), heads, max_pos, length - 1, ws).cpu().numpy()
+    ws.check()
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert (err <= 2e-2 * np.abs(want.astype(np.float32)) + 2e-3).all()
+    d = _ulp_diff(got, want)
+    assert (d > 1).mean() < 0.01
+
+
+def test_embed_gather_bit_exact(ops, orc, cuda):
+    H, V = 512, 4096 + 256
+    p, s, z = orc.gen_linear(24, H, V, kind=orc.EMB)
+    pd, sd, zd = _to_dev(p, cuda), _to_dev(s, cuda), _to_dev(z, cuda)
+    for tok in (0, 1, 127, 128, 4095, 4096, V - 1):
+        want = orc.embed_gather(p, s, z, H, V, tok)
+        got = ops.embed_gather_w4(pd, sd, zd, H, V, tok).cpu().numpy()
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), tok
+    d_tok = torch.tensor([777], dtype=torch.int32, device=cuda)
+    got = ops.embed_gather_w4(pd, sd, zd, H, V, 0, d_token=d_tok).cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), orc.embed_gather(p, s, z, H, V, 777).view(np.uint16))
+
+
+def test_argmax_first_max_wins(ops, orc, cuda):
+    n = 151936
+    logits = orc.gen_normal_f16(25, orc.ACT, n)
+    ws = ops.Workspace()
+    assert int(ops.argmax_f16(_to_dev(logits, cuda), ws).item()) == orc.argmax_f16(logits)
+    logits[:] = np.float16(1.5)   # all equal: index 0
+    assert int(ops.argmax_f16(_to_dev(logits, cuda), ws).item()) == 0
+    logits[100000] = np.float16(2.0)
+    logits[140000] = np.float16(2.0)   # tie between two maxima: the lower index
+    assert int(ops.argmax_f16(_to_dev(logits, cuda), ws).item()) == 100000
+    ws.check()
