@@ -22,7 +22,7 @@ EXPORTS = [
     "qw3_strerror", "qw3_last_error", "qw3_dequant_w4", "qw3_w4_create", "qw3_w4_destroy", "qw3_ws_create",
     "qw3_ws_destroy", "qw3_ws_set_pdl", "qw3_ws_check", "qw3_gemv_w4a16", "qw3_gemm_w4a16", "qw3_rmsnorm",
     "qw3_rope_kv_append", "qw3_attn_decode", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
-    "qw3_create", "qw3_destroy", "qw3_generate", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
+    "qw3_create", "qw3_destroy", "qw3_generate", "qw3_decode_more", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
     "qw3_kv_upload", "qw3_layer_decode", "qw3_stage_export", "qw3_stage_connect",
 ]
 
@@ -95,6 +95,7 @@ def lib():
         "qw3_create": [C.c_char_p, C.POINTER(Config), C.POINTER(vp)],
         "qw3_destroy": [vp],
         "qw3_generate": [vp, vp, i32, i32, vp, C.POINTER(i32)],
+        "qw3_decode_more": [vp, i32, vp, C.POINTER(i32)],
         "qw3_last_logits": [vp, vp],
         "qw3_last_timing": [vp, C.POINTER(f32), C.POINTER(f32)],
         "qw3_last_launches": [vp, C.POINTER(i64)],

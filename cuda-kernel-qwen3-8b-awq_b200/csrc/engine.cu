@@ -82,7 +82,8 @@ struct qw3_engine {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;  // on stage 0's device
     float prompt_ms = 0.f, decode_ms = 0.f;
     int64_t launches = 0;
-    int out_cap = 0;
+    int seq_len = 0;                    // token passes through the layers so far (next position)
+    int sampled = 0;                    // ids sampled since the last prompt
 };
 
 namespace qw3 {
@@ -476,6 +477,49 @@ int qw3_create(const char* weight_dir, const Qw3Config* cfg, qw3_handle* out) {
     return QW3_OK;
 }
 
+// The decode loop of generateResponse (Inference.cu:1352-1405), continuing from the current
+// sequence state; max_new ids are read back at the end (the host never waits inside the loop).
+static int decode_loop(qw3_engine* e, int max_new, int32_t* out_ids) {
+    const Qw3Config& c = e->cfg;
+    const int N = c.n_stages;
+    Stage &s0 = e->st[0], &sl = e->st[N - 1];
+    QW3_CUDA(cudaSetDevice(sl.device));
+    QW3_CUDA(cudaMemsetAsync(sl.d_step, 0, 4, sl.stream));
+    for (int step = 0; step < max_new; ++step) {
+        const bool very_first = (e->sampled == 0);
+        bool layers = true;
+        if (c.sample_first && very_first) layers = false;
+        if (layers) {
+            if (very_first) {
+                // Reference flow: step 0 re-enters layer 0 with the final hidden state of the last
+                // prompt token (Inference.cu:1357): move it back to stage 0 and skip the gather.
+                if (N > 1) QW3_TRY(handoff(e, N - 1, 0, true, false));
+                const int one = 1;
+                QW3_CUDA(cudaSetDevice(s0.device));
+                QW3_CUDA(cudaMemcpyAsync(s0.d_skip, &one, 4, cudaMemcpyHostToDevice, s0.stream));
+            } else if (N > 1) {
+                QW3_TRY(handoff(e, N - 1, 0, false, true));                           // sampled id -> stage 0
+            }
+        }
+        QW3_TRY(run_pass(e, true, layers));
+        if (layers) e->seq_len += 1;
+        e->sampled += 1;
+    }
+    QW3_CUDA(cudaSetDevice(s0.device));
+    QW3_CUDA(cudaStreamWaitEvent(s0.stream, sl.done, 0));
+    QW3_CUDA(cudaEventRecord(e->ev2, s0.stream));
+    QW3_CUDA(cudaStreamSynchronize(s0.stream));
+    QW3_CUDA(cudaSetDevice(sl.device));
+    QW3_CUDA(cudaStreamSynchronize(sl.stream));
+    if (max_new > 0) QW3_CUDA(cudaMemcpy(out_ids, sl.d_out_ids, (size_t)max_new * 4, cudaMemcpyDeviceToHost));
+    QW3_CUDA(cudaEventElapsedTime(&e->decode_ms, e->ev1, e->ev2));
+    for (int si = 0; si < N; ++si) {
+        QW3_CUDA(cudaSetDevice(e->st[si].device));
+        QW3_TRY(qw3_ws_check(e->st[si].ws, e->st[si].stream));
+    }
+    return QW3_OK;
+}
+
 int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_ids, int32_t* n_out) {
     QW3_REQUIRE(e && prompt && (out_ids || max_new == 0), "qw3_generate: null pointer");
     const Qw3Config& c = e->cfg;
@@ -491,6 +535,7 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
     const int N = c.n_stages;
     Stage &s0 = e->st[0], &sl = e->st[N - 1];
     e->launches = 0;
+    e->seq_len = 0;
     // The object is reusable: position and step restart for every call.
     for (int si = 0; si < N; ++si) {
         Stage& s = e->st[si];
@@ -504,37 +549,31 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaStreamWaitEvent(s0.stream, sl.done, 0));
     QW3_CUDA(cudaEventRecord(e->ev1, s0.stream));
-    for (int step = 0; step < max_new; ++step) {                                     // Inference.cu:1352-1405
-        bool layers = true;
-        if (c.sample_first && step == 0) layers = false;
-        if (layers) {
-            if (step == 0) {
-                // Reference flow: step 0 re-enters layer 0 with the final hidden state of the last
-                // prompt token (Inference.cu:1357): move it back to stage 0 and skip the gather.
-                if (N > 1) QW3_TRY(handoff(e, N - 1, 0, true, false));
-                const int one = 1;
-                QW3_CUDA(cudaSetDevice(s0.device));
-                QW3_CUDA(cudaMemcpyAsync(s0.d_skip, &one, 4, cudaMemcpyHostToDevice, s0.stream));
-            } else if (N > 1) {
-                QW3_TRY(handoff(e, N - 1, 0, false, true));                           // sampled id -> stage 0
-            }
-        }
-        QW3_TRY(run_pass(e, true, layers));
-    }
-    QW3_CUDA(cudaSetDevice(s0.device));
-    QW3_CUDA(cudaStreamWaitEvent(s0.stream, sl.done, 0));
-    QW3_CUDA(cudaEventRecord(e->ev2, s0.stream));
-    QW3_CUDA(cudaStreamSynchronize(s0.stream));
-    QW3_CUDA(cudaSetDevice(sl.device));
-    QW3_CUDA(cudaStreamSynchronize(sl.stream));
-    if (max_new > 0) QW3_CUDA(cudaMemcpy(out_ids, sl.d_out_ids, (size_t)max_new * 4, cudaMemcpyDeviceToHost));
+    e->seq_len = n_prompt;
+    e->sampled = 0;
+    QW3_TRY(decode_loop(e, max_new, out_ids));
     if (n_out) *n_out = max_new;
     QW3_CUDA(cudaEventElapsedTime(&e->prompt_ms, e->ev0, e->ev1));
-    QW3_CUDA(cudaEventElapsedTime(&e->decode_ms, e->ev1, e->ev2));
-    for (int si = 0; si < N; ++si) {
-        QW3_CUDA(cudaSetDevice(e->st[si].device));
-        QW3_TRY(qw3_ws_check(e->st[si].ws, e->st[si].stream));
+    return QW3_OK;
+}
+
+int qw3_decode_more(qw3_handle e, int32_t max_new, int32_t* out_ids, int32_t* n_out) {
+    QW3_REQUIRE(e && (out_ids || max_new == 0), "qw3_decode_more: null pointer");
+    if (e->seq_len < 1 || e->sampled < 1) {
+        set_last_error("qw3_decode_more: nothing to continue; call qw3_generate with max_new >= 1 first");
+        return QW3_ERR_STATE;
     }
+    if (max_new < 0 || (int64_t)e->seq_len + max_new > e->cfg.max_pos) {
+        set_last_error("qw3_decode_more: %d more tokens after %d do not fit max_pos=%d", max_new, e->seq_len, e->cfg.max_pos);
+        return QW3_ERR_RANGE;
+    }
+    Stage& s0 = e->st[0];
+    e->launches = 0;
+    e->prompt_ms = 0.f;
+    QW3_CUDA(cudaSetDevice(s0.device));
+    QW3_CUDA(cudaEventRecord(e->ev1, s0.stream));
+    QW3_TRY(decode_loop(e, max_new, out_ids));
+    if (n_out) *n_out = max_new;
     return QW3_OK;
 }
 

@@ -36,6 +36,13 @@ class QWen3AWQInfer:
         cabi.check(self._lib.qw3_generate(self._h, prompt, n, max_new_tokens, out, C.byref(n_out)), "qw3_generate")
         return [int(out[i]) for i in range(n_out.value)]
 
+    def decode_more(self, max_new_tokens):
+        """Continue the last generateResponse call for max_new_tokens more ids (same KV state)."""
+        out = (C.c_int32 * max(max_new_tokens, 1))()
+        n_out = C.c_int32(0)
+        cabi.check(self._lib.qw3_decode_more(self._h, max_new_tokens, out, C.byref(n_out)), "qw3_decode_more")
+        return [int(out[i]) for i in range(n_out.value)]
+
     def last_logits(self):
         """fp32 logits of the last decode step (needs keep_logits=1)."""
         import numpy as np

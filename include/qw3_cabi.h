@@ -183,6 +183,11 @@ int qw3_destroy(qw3_handle h);
 int qw3_generate(qw3_handle h, const int32_t* prompt, int32_t n_prompt, int32_t max_new,
                  int32_t* out_ids, int32_t* n_out);
 
+/* Continues the decode loop of the last qw3_generate call for max_new more ids (same KV state,
+ * positions carry on).  No counterpart in the reference, whose object is single-shot; it lets a
+ * caller stream a long generation in pieces and lets a benchmark time decode steps alone. */
+int qw3_decode_more(qw3_handle h, int32_t max_new, int32_t* out_ids, int32_t* n_out);
+
 /* fp32 logits of the last decode step (keep_logits = 1), vocab floats to host memory. */
 int qw3_last_logits(qw3_handle h, float* out_vocab);
 /* Device time of the last call's prompt loop and decode loop (CUDA events, milliseconds). */

@@ -159,7 +159,11 @@ def test_gemv_epilogues(ops, orc, cuda):
     y = torch.zeros(M, dtype=torch.float16, device=cuda)
     ops.gemv_w4a16(w, ws, ops.gemv_args(xd, epilogue=ops.cabi.EPI_GELU, y=y, gamma=gd))
     got = y.cpu().numpy()
-    assert _ulp_diff(got, want).max() <= 2 and (_ulp_diff(got, want) > 0).mean() < 0.02
+    # a one-ulp difference of the GEMV result may move the GeLU output by a few ulps where GeLU is
+    # steep relative to its value (negative tail); judge those on absolute error
+    d = _ulp_diff(got, want)
+    near = np.abs(got.astype(np.float32) - want.astype(np.float32)) <= 1e-3 * np.abs(want.astype(np.float32)).mean()
+    assert ((d <= 2) | near).all() and (d > 0).mean() < 0.02
     # residual epilogue, no prologue
     res = orc.gen_normal_f16(10, orc.ACT, M)
     _, y16 = orc.gemm_w4a16(p, s, z, M, K, x)
