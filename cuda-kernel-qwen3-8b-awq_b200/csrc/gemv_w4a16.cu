@@ -737,3 +737,106 @@ extern "C" int qw3_gemv_w4a16(qw3_w4_t w, const Qw3GemvArgs* args, qw3_ws_t ws, 
     QW3_REQUIRE(w && ws, "qw3_gemv_w4a16: null descriptor or workspace");
     return gemv_launch(&w->d, args, &ws->h.ws, ws->h.use_pdl != 0, static_cast<cudaStream_t>(stream));
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the fused dequant-GEMV
+// ------------------------------------------------------------------------------------------------
+// Some callers must not allocate device memory when they run an operator: a serving process that
+// reserved its whole memory budget at start-up and hands out slices from its own pool, a plug-in
+// called from inside another framework's execution step (where cudaMalloc would synchronise the
+// device and stall every other stream), or code that is simply forbidden to grow the process.
+// qw3_gemv_w4a16 needs a qw3_ws_t workspace (one cudaMalloc) and a qw3_w4_t descriptor (host
+// memory).  The entry point below needs neither: its split-K scratch lives in a fixed array that is
+// part of the library image on every GPU that loads it, and the matrix is described by plain
+// arguments.  The price is a size limit and one shared scratch area per GPU.
+namespace qw3 {
+
+constexpr int NOALLOC_MAX_DIM = 16384;                          // largest out_dim and in_dim accepted
+constexpr int NOALLOC_MAX_TILES = NOALLOC_MAX_DIM / TI;         // 16
+constexpr size_t NOALLOC_PARTIAL_BYTES = (size_t)(WS_MAX_CTAS + NOALLOC_MAX_TILES) * TI * 4;   // 1,114,112
+constexpr size_t NOALLOC_TAIL_BYTES = 1024;                     // arrival counters, error word
+constexpr size_t NOALLOC_BYTES = NOALLOC_PARTIAL_BYTES + NOALLOC_TAIL_BYTES;                   // ~1.06 MiB per GPU
+
+// Held by every GPU that loads the library, until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+struct NoAllocDevice {
+    void* base = nullptr;   // device address of g_noalloc_scratch on this device
+    int sm_count = 0;
+    bool ready = false;
+};
+static NoAllocDevice g_noalloc_dev[64];
+static std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: in host code the array's name is only a handle, the
+// address a kernel can use comes from cudaGetSymbolAddress.
+static int noalloc_setup(int dev, NoAllocDevice** out) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocDevice& d = g_noalloc_dev[dev];
+    if (!d.ready) {
+        void* ptr = nullptr;
+        QW3_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        QW3_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        const int rc = gemv_init_device();   // shared-memory opt-in of the kernel: an attribute, not an allocation
+        if (rc != QW3_OK) return rc;
+        d.base = ptr;
+        d.ready = true;
+    }
+    *out = &d;
+    return QW3_OK;
+}
+
+}  // namespace qw3
+
+extern "C" int qw3_gemv_w4a16_noalloc(const void* d_packed, const void* d_scale, const void* d_zp, int64_t n_groups_alloc,
+                                      int64_t out_dim, int64_t in_dim, int zp_integral, const void* d_x, void* d_y,
+                                      void* stream) {
+    QW3_REQUIRE(d_packed && d_scale && d_zp && d_x && d_y, "qw3_gemv_w4a16_noalloc: null pointer");
+    QW3_REQUIRE(out_dim > 0 && in_dim > 0 && out_dim % 128 == 0 && in_dim % 128 == 0,
+                "qw3_gemv_w4a16_noalloc: out_dim=%lld and in_dim=%lld must be positive multiples of 128",
+                (long long)out_dim, (long long)in_dim);
+    QW3_REQUIRE(out_dim <= NOALLOC_MAX_DIM && in_dim <= NOALLOC_MAX_DIM,
+                "qw3_gemv_w4a16_noalloc: out_dim=%lld, in_dim=%lld exceed the fixed scratch (at most %d each); "
+                "use qw3_gemv_w4a16 with a workspace for larger matrices",
+                (long long)out_dim, (long long)in_dim, NOALLOC_MAX_DIM);
+    QW3_REQUIRE(n_groups_alloc > 0 && n_groups_alloc <= 0x7fffffff, "qw3_gemv_w4a16_noalloc: n_groups_alloc out of range");
+    QW3_REQUIRE((reinterpret_cast<uintptr_t>(d_packed) & 15) == 0, "qw3_gemv_w4a16_noalloc: packed pointer must be 16-byte aligned");
+    int dev = 0;
+    QW3_CUDA(cudaGetDevice(&dev));
+    QW3_REQUIRE(dev >= 0 && dev < 64, "qw3_gemv_w4a16_noalloc: device index %d not supported", dev);
+    NoAllocDevice* nd = nullptr;
+    {
+        const int rc = noalloc_setup(dev, &nd);
+        if (rc != QW3_OK) return rc;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    W4Desc d = {};
+    d.packed = static_cast<const uint8_t*>(d_packed);
+    d.scale = static_cast<const __half*>(d_scale);
+    d.zp = static_cast<const __half*>(d_zp);
+    d.n_alloc = n_groups_alloc; d.M = out_dim; d.K = in_dim; d.zp_integral = zp_integral ? 1 : 0;
+    const int64_t Mb = out_dim / 128, Kb = in_dim / 128;
+    d.uniform = (Mb % Kb == 0) || (Kb % n_groups_alloc == 0 && Mb % n_groups_alloc == 0);
+    {
+        const int rc = encode_2d_u32(&d.tmap, d_packed, (uint64_t)out_dim / 8, (uint64_t)in_dim, (uint64_t)out_dim / 2,
+                                     TI / 8, UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != QW3_OK) return rc;
+    }
+    uint8_t* base = static_cast<uint8_t*>(nd->base);
+    Workspace ws = {};
+    ws.partials = reinterpret_cast<float*>(base);
+    ws.counters = reinterpret_cast<int32_t*>(base + NOALLOC_PARTIAL_BYTES);          // [NOALLOC_MAX_TILES]
+    ws.tiles_done = reinterpret_cast<int32_t*>(base + NOALLOC_PARTIAL_BYTES + 256);
+    ws.err = reinterpret_cast<int32_t*>(base + NOALLOC_PARTIAL_BYTES + 512);
+    ws.device = dev;
+    ws.sm_count = nd->sm_count;
+    // The array keeps whatever the previous call left: the counters and the error word must start at
+    // zero (the partial sums are always written before they are read).
+    QW3_CUDA(cudaMemsetAsync(base + NOALLOC_PARTIAL_BYTES, 0, NOALLOC_TAIL_BYTES, st));
+    Qw3GemvArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.d_x = d_x;
+    a.d_y = d_y;
+    a.epilogue = QW3_EPI_STORE;
+    return gemv_launch(&d, &a, &ws, false, st);
+}

@@ -107,6 +107,26 @@ typedef struct Qw3GemvArgs {
  * at n = 1 (Inference.cu:1052, 1128, 1176, 1201, 1260) and the kernels the epilogue names. */
 int qw3_gemv_w4a16(qw3_w4_t w, const Qw3GemvArgs* args, qw3_ws_t ws, void* stream);
 
+/* The same product, y = half(sum_j W[i + j*out_dim] * x[j]), for callers that may not allocate: a
+ * server that carved up all device memory at start-up, or a plug-in running inside another
+ * framework's step, where cudaMalloc would stall the whole device.  It takes no workspace and no
+ * descriptor: the split-K scratch is a fixed array inside the library (about 1.06 MiB, held by every
+ * GPU that loads the library until the process exits) and the matrix is given by plain arguments.
+ * It has no counterpart in the reference, which allocates everything in its constructor.
+ * Limits and rules:
+ *   - out_dim and in_dim are multiples of 128 and at most 16384 each; larger sizes are refused with
+ *     QW3_ERR_ARG (use qw3_gemv_w4a16 with a workspace instead);
+ *   - the first call on a device looks up the device address of the array and opts the kernel in to
+ *     its shared-memory size; make that first call before any stream capture;
+ *   - all calls on a GPU share the one array, so two calls that can overlap on that GPU (different
+ *     streams) race; calls ordered on one stream are safe, and each call clears the counters it
+ *     needs itself;
+ *   - no cudaMalloc, cudaFree or other allocating routine is called.
+ * zp_integral as in qw3_w4_create. */
+int qw3_gemv_w4a16_noalloc(const void* d_packed, const void* d_scale, const void* d_zp, int64_t n_groups_alloc,
+                           int64_t out_dim, int64_t in_dim, int zp_integral, const void* d_x, void* d_y,
+                           void* stream);
+
 /* Tensor-core W4A16 contraction for `rows` activations (prefill / batched rows): Y[r][i] =
  * sum_j W[i + j*out_dim] * X[r][j], fp16 in, fp32 accumulate, fp16 out.  The reference has no
  * batched path; row r of Y equals qw3_gemv_w4a16 on row r of X within fp32 summation order.
