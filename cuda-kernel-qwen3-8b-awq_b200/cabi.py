@@ -23,7 +23,7 @@ EXPORTS = [
     "qw3_ws_destroy", "qw3_ws_set_pdl", "qw3_ws_check", "qw3_gemv_w4a16", "qw3_gemv_w4a16_noalloc", "qw3_gemm_w4a16", "qw3_rmsnorm",
     "qw3_rope_kv_append", "qw3_attn_decode", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
     "qw3_create", "qw3_destroy", "qw3_generate", "qw3_decode_more", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
-    "qw3_kv_upload", "qw3_layer_decode", "qw3_stage_export", "qw3_stage_connect",
+    "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect",
 ]
 
 
@@ -46,7 +46,7 @@ class Config(C.Structure):
                 ("rope_base", C.c_float), ("sample_first", C.c_int32), ("n_stages", C.c_int32),
                 ("first_layer", C.c_int32 * (MAX_STAGES + 1)), ("device", C.c_int32 * MAX_STAGES),
                 ("rank", C.c_int32), ("world", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32),
-                ("keep_logits", C.c_int32)]
+                ("keep_logits", C.c_int32), ("persistent", C.c_int32)]
 
 
 def build(force=False, verbose=False):
@@ -102,6 +102,7 @@ def lib():
         "qw3_last_launches": [vp, C.POINTER(i64)],
         "qw3_kv_upload": [vp, i32, i32, vp, i64],
         "qw3_layer_decode": [vp, i32, i32, vp],
+        "qw3_debug_trace": [vp, i32, vp, i32, C.POINTER(i32)],
         "qw3_stage_export": [vp, vp],
         "qw3_stage_connect": [vp, vp],
     }

@@ -118,6 +118,52 @@ __device__ __forceinline__ __half dequant_one(uint32_t q, __half z, __half s) {
     return h_mul(h_sub(__int2half_rn((int)q), z), s);
 }
 
+// ---- AWQ unpack shared by the GEMV kernels -----------------------------------------------------
+struct DqConst {  // per-group constants, duplicated into both halves
+    uint32_t z;   // exact path: 1024 + zp;  generic path: zp
+    uint32_t hz;  // exact path: -(64 + zp)
+    uint32_t s;
+};
+
+template <bool EXACT>
+__device__ __forceinline__ DqConst make_const(__half z, __half s) {
+    DqConst c;
+    if (EXACT) {
+        c.z = dup_h2(h_add(__ushort_as_half(0x6400), z));   // 1024 + zp, exact for integral zp
+        c.hz = dup_h2(h_sub(__ushort_as_half(0xD400), z));  // -64 - zp, exact
+    } else {
+        c.z = dup_h2(z);
+        c.hz = 0;
+    }
+    c.s = dup_h2(s);
+    return c;
+}
+
+// Eight nibbles of one row -> after `u = w` / `u = w >> 8`: two registers of dequantised pairs.
+//   lo: nibbles (0,4) resp. (2,6);  hi: nibbles (1,5) resp. (3,7).
+// Both roundings of the reference are kept: d = RN(q - zp), w = RN(d * scale).
+template <bool EXACT>
+__device__ __forceinline__ void dq_pair(uint32_t u, const DqConst& c, uint32_t& wlo, uint32_t& whi) {
+    const uint32_t lo = lop3_and_or(u, 0x000f000fu, 0x64006400u);  // (1024 + q) x2
+    const uint32_t hi = lop3_and_or(u, 0x00f000f0u, 0x64006400u);  // (1024 + 16 q) x2
+    uint32_t dlo, dhi;
+    if (EXACT) {
+        dlo = h2_sub(lo, c.z);                     // (1024+q) - (1024+zp): exact operands, one rounding
+        dhi = h2_fma(hi, 0x2C002C00u, c.hz);       // (1024+16q)/16 - (64+zp), one rounding
+    } else {
+        dlo = h2_sub(h2_sub(lo, 0x64006400u), c.z);                  // q exactly, then RN(q - zp)
+        dhi = h2_sub(h2_fma(hi, 0x2C002C00u, 0xD400D400u), c.z);
+    }
+    wlo = h2_mul(dlo, c.s);
+    whi = h2_mul(dhi, c.s);
+}
+
+// CTA that owns unit u when U units are cut into G equal contiguous ranges [c*U/G, (c+1)*U/G).
+__device__ __forceinline__ int owner_of(long long u, int G, long long U) { return (int)(((u + 1) * G - 1) / U); }
+
+// Arg-max order: larger value wins, equal values go to the lower index (first maximum).
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
 // ---- shared-memory barriers and bulk tensor copies ---------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -1,0 +1,944 @@
+// One persistent kernel per token pass of a pipeline stage (sm_100a).
+//
+// The reference runs a token through a stage as 12 launches + 68 memcpys per layer with the host
+// in the loop (runOneLayer, Inference.cu:1029-1230; generateResponse, Inference.cu:1304-1405).  At
+// batch 1 every operator of the path moves a few tens of MB, which HBM delivers in 1-4 us: launch
+// boundaries, not bytes, set the pace.  Here a whole pass -- embedding gather, then per layer
+// RMSNorm+Wqkv+RoPE+KV append, attention, Wo+residual, RMSNorm+W1+GeLU, W2+residual, and on the
+// last stage final norm + unembed + arg-max -- is one cooperative launch of one CTA per SM that
+// walks a list of operator descriptors:
+//   * the packed weights of ALL operators, in order, flow through one ring of 4 KB TMA boxes
+//     (32 units, 128 KB per SM).  There is no producer warp: each of the 16 warps owns two ring
+//     slots and, as soon as it has consumed a unit, issues the TMA load of the unit that will
+//     land in the same slot 32 units later -- possibly a unit of a later operator, since weights
+//     never depend on activations.  The ring is therefore full again by the time the warps have
+//     crossed an operator boundary, and no empty-slot barrier exists;
+//   * the warps take units round-robin (no stage-wide lock-step), unpack and accumulate exactly
+//     as the stand-alone GEMV does, and finish a tile with the same deterministic fix-up
+//     (partials in CTA order, last arriver runs the epilogue);
+//   * operators are chained by arrival counters in global memory: the CTA that finalises a tile
+//     (or an attention head) publishes it with a fence + atomic, consumers of the next operator
+//     wait with a bounded acquire-poll.  All CTAs are co-resident (cooperative launch), so the
+//     waits cannot deadlock; every wait gives up after about a second and reports an error.
+// Activations written inside the kernel are read with ld.global.cg (L1 is not coherent across SMs).
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace qw3 {
+
+constexpr int P_TI = WS_TILE;            // outputs per tile
+constexpr int P_ROW_BYTES = P_TI / 2;    // 512
+constexpr int P_UNIT_ROWS = 8;
+constexpr int P_UNIT_BYTES = P_UNIT_ROWS * P_ROW_BYTES;   // 4096
+constexpr int P_NCW = 16;                // 4 warps per scheduler: 128 registers per thread
+constexpr int P_NCONS = P_NCW * 32;
+constexpr int P_NTHREADS = P_NCONS;
+constexpr int P_RING = 32;               // units in flight per SM (128 KB): two slots per warp
+constexpr int P_MAXK = 12288;            // largest in_dim (activation vector kept in shared memory)
+constexpr int P_MAXK_NU = 4096;          // largest in_dim of an operator with j-dependent groups
+constexpr int P_MAX_GROUPS = 256;
+constexpr int P_RED_BYTES = 32768;       // cross-warp reduction (8 slots x 4 KB) / 32 attention states (16.9 KB)
+constexpr int P_OPW = 32;                // 32-bit words of a descriptor after its tensor map
+
+constexpr size_t P_OFF_RED = (size_t)P_RING * P_UNIT_BYTES;
+constexpr size_t P_OFF_XS = P_OFF_RED + P_RED_BYTES;
+constexpr size_t P_OFF_GIDX = P_OFF_XS + (size_t)P_MAXK * 2;
+constexpr size_t P_OFF_GTAB = P_OFF_GIDX + (size_t)P_MAXK_NU * 2;
+constexpr size_t P_OFF_MISC = P_OFF_GTAB + (size_t)P_MAX_GROUPS * 16;
+constexpr size_t P_SMEM_BYTES = P_OFF_MISC + 2048;
+
+enum PassOpKind { PASS_EMBED = 0, PASS_GEMV = 1, PASS_ATTN = 2 };
+
+struct PassOpBody {          // 128 bytes, copied to shared memory per operator
+    int32_t kind, uniform, exact, epilogue;
+    int32_t M, K, Mb, Kb;
+    int32_t n_alloc, n_tiles, upt, done_target;
+    long long U;
+    const __half* scale;
+    const __half* zp;
+    const __half* x;
+    const __half* gamma;
+    __half* y;
+    __half* kc;
+    __half* vc;
+    const uint8_t* packed;   // embedding only
+    float eps;
+    int32_t pad;
+};
+static_assert(sizeof(PassOpBody) == 128, "descriptor body must be 128 bytes");
+
+struct alignas(128) PassOp {
+    CUtensorMap tmap;
+    PassOpBody b;
+};
+static_assert(sizeof(PassOp) == 256, "descriptor must be 256 bytes");
+
+struct PassParams {
+    const PassOp* ops;
+    int n_ops;
+    int* done;                // [n_ops], zeroed before the launch
+    const int* d_pos;
+    const int* d_token;       // sampled id of the previous step (decode pass)
+    const int* d_skip;        // non-zero: keep the hidden state, skip the gather
+    const int* d_prompt;      // prompt ids (prompt pass)
+    int decode;
+    const __half* cos_t;
+    const __half* sin_t;
+    int heads, hidden;
+    long long max_pos, vocab;
+    int* d_token_out;
+    float* logits_f32;
+    int skip_math;               // debug: wait for the weights but do not unpack or multiply
+    unsigned long long* trace2;  // optional [grid][n_ops][8]: per-CTA event times inside each operator (debug)
+    unsigned long long* trace;   // optional [n_ops + 1]: global timer when CTA 0 enters each operator
+    Workspace ws;
+};
+
+__device__ __forceinline__ void trace_event(const PassParams& p, int o, int ev) {
+    if (p.trace2 != nullptr && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.trace2[((size_t)blockIdx.x * p.n_ops + o) * 8 + ev] = t;
+    }
+}
+
+__device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
+    int old;   // release: the CTA's earlier writes (ordered before by the CTA barrier) are published; acquire: the
+               // writes published by the other arrivals are visible to this CTA after its next barrier
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void red_add_release(int* p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Share of one operator's units for CTA c: a contiguous range [ub, ub + n) of absolute units
+// (tile * upt + row unit).  With fewer tiles than CTAs every CTA works inside ONE tile (tile t is cut
+// evenly among CTAs [t*G/nt, (t+1)*G/nt)), so it reduces across warps and CTAs once per operator;
+// otherwise the flattened unit space is cut into G equal ranges.  cf..cl are the CTAs that
+// contribute to tile `tile_q`.
+__device__ __forceinline__ void cta_range(long long U, int upt, int n_tiles, int c, int& ub, int& n) {
+    const int Gf = gridDim.x;
+    if (n_tiles < Gf) {
+        const int t = (int)(((long long)(c + 1) * n_tiles - 1) / Gf);
+        const int cb = (int)((long long)t * Gf / n_tiles), cb1 = (int)((long long)(t + 1) * Gf / n_tiles);
+        const int cnt = min(cb1 - cb, upt), idx = c - cb;
+        if (idx < cnt) {
+            const int lo = (int)((long long)idx * upt / cnt), hi = (int)((long long)(idx + 1) * upt / cnt);
+            ub = t * upt + lo;
+            n = hi - lo;
+        } else {
+            ub = 0;
+            n = 0;
+        }
+    } else {
+        const int G = (long long)Gf < U ? Gf : (int)U;
+        if (c < G) {
+            const long long u0 = (long long)c * U / G, u1 = (long long)(c + 1) * U / G;
+            ub = (int)u0;
+            n = (int)(u1 - u0);
+        } else {
+            ub = 0;
+            n = 0;
+        }
+    }
+}
+__device__ __forceinline__ void tile_contributors(long long U, int upt, int n_tiles, int tile, int& cf, int& cl) {
+    const int Gf = gridDim.x;
+    if (n_tiles < Gf) {
+        const int cb = (int)((long long)tile * Gf / n_tiles), cb1 = (int)((long long)(tile + 1) * Gf / n_tiles);
+        cf = cb;
+        cl = cb + min(cb1 - cb, upt) - 1;
+    } else {
+        const int G = (long long)Gf < U ? Gf : (int)U;
+        const long long ut0 = (long long)tile * upt;
+        cf = owner_of(ut0, G, U);
+        cl = owner_of(ut0 + upt - 1, G, U);
+    }
+}
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct PassSmem {
+    uint8_t* ring;
+    float* red;
+    __half* xs;
+    uint16_t* gidx;
+    uint4* gtab;
+    uint32_t full0;           // shared address of the ring barriers
+    double* dsum;
+    float* s_argv;
+    int* s_argi;
+    int* s_flag;
+    int* s_dead;
+    uint32_t* s_op;           // [2][P_OPW]
+};
+
+// Per-warp prefetch cursor over the units this warp will consume (global unit counter uc = warp
+// mod 16), walking through the operator list ahead of the computation.
+struct Prefetch {
+    int op;      // operator the cursor is in (-1 before the first)
+    int uc;      // global unit counter of the last unit issued
+    int base;    // global unit counter of the first unit of `op` for this CTA
+    int n;       // units of `op` for this CTA
+    int ub;      // first unit of this CTA in `op` (tile * upt + row unit)
+    int upt;
+    int next_u, tile, r;   // last unit issued in `op` and its (tile, row unit)
+    bool end;
+};
+
+__device__ __forceinline__ void prefetch_next(Prefetch& pf, const PassParams& p, const PassSmem& sm) {
+    if (pf.end) return;
+    pf.uc += P_NCW;
+    while (pf.uc - pf.base >= pf.n) {
+        pf.base += pf.n;
+        pf.n = 0;
+        do {
+            ++pf.op;
+        } while (pf.op < p.n_ops && p.ops[pf.op].b.kind != PASS_GEMV);
+        if (pf.op >= p.n_ops) {
+            pf.end = true;
+            return;
+        }
+        pf.upt = p.ops[pf.op].b.upt;
+        cta_range(p.ops[pf.op].b.U, pf.upt, p.ops[pf.op].b.n_tiles, blockIdx.x, pf.ub, pf.n);
+        pf.next_u = pf.ub;
+        pf.tile = pf.ub / pf.upt;
+        pf.r = pf.ub - pf.tile * pf.upt;
+    }
+    // (tile, r) of unit ub + (uc - base), advanced incrementally from the last unit issued in this operator
+    const int u = pf.ub + (pf.uc - pf.base);
+    pf.r += u - pf.next_u;
+    pf.next_u = u;
+    while (pf.r >= pf.upt) {
+        pf.r -= pf.upt;
+        ++pf.tile;
+    }
+    const int tile = pf.tile, r = pf.r;
+    if ((threadIdx.x & 31) == 0) {
+        const int slot = pf.uc & (P_RING - 1);
+        const uint32_t bar = sm.full0 + 8 * slot;
+        // the slot was read by this warp with ordinary loads: order them before the bulk write
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, P_UNIT_BYTES);
+        tma_load_2d(smem_u32(sm.ring + slot * P_UNIT_BYTES), &p.ops[pf.op].tmap, tile * (P_TI / 8), r * P_UNIT_ROWS, bar);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused dequantise + matrix-vector product of one operator, for this CTA's share of its units.
+// ---------------------------------------------------------------------------------------------
+template <bool UNIFORM, bool EXACT>
+__device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody& op, const int o, const PassSmem& sm,
+                                            int& uc_base, const int pos, Prefetch& pf) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int c = blockIdx.x;
+    const long long U = op.U;
+    const int upt = op.upt, K = op.K;
+    int u_begin, n_units;
+    cta_range(U, upt, op.n_tiles, c, u_begin, n_units);
+    const int t0 = u_begin / upt, r0 = u_begin - t0 * upt;
+    __half* xs = sm.xs;
+
+    // ---- loads that depend on nothing computed here are issued first, so that their latencies overlap:
+    // group constants of the first tile, and what the epilogue of that tile will need
+    DqConst ku_first = {0u, 0u, 0u};
+    if (UNIFORM) {
+        int ib = t0 * (P_TI / 128) + (lane >> 2);
+        if (ib >= op.Mb) ib = 0;
+        const int g = (ib % op.Kb) % op.n_alloc;
+        ku_first = make_const<EXACT>(op.zp[g], op.scale[g]);
+    }
+    uint32_t pre_a = 0u, pre_b = 0u;   // RESIDUAL: y[i], y[i+1];  ROPE_KV: cos, sin of this thread's pair
+    {
+        const int i = t0 * P_TI + 2 * tid;
+        if (i < op.M) {
+            if (op.epilogue == QW3_EPI_RESIDUAL) {
+                pre_a = __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+            } else if (op.epilogue == QW3_EPI_ROPE_KV && i < 2 * p.hidden) {
+                const int d = i & 127;
+                pre_a = __half_as_ushort(p.cos_t[(size_t)pos * 64 + (d >> 1)]);
+                pre_b = __half_as_ushort(p.sin_t[(size_t)pos * 64 + (d >> 1)]);
+            }
+        }
+    }
+
+    // ---- prologue: (RMS-normalised) input vector -> shared memory -------------------------------
+    const int n_chunks = K >> 3;   // 16-byte chunks of 8 halves
+    if (op.gamma != nullptr) {
+        uint4 xv[3], gvv[3];
+        double s = 0.0;
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            const int ch = tid + e * P_NCONS;
+            gvv[e] = make_uint4(0u, 0u, 0u, 0u);
+            if (ch < n_chunks) gvv[e] = *(reinterpret_cast<const uint4*>(op.gamma) + ch);
+        }
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            const int ch = tid + e * P_NCONS;
+            xv[e] = make_uint4(0u, 0u, 0u, 0u);
+            if (ch < n_chunks) {
+                xv[e] = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+                const __half2* h = reinterpret_cast<const __half2*>(&xv[e]);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float2 f = __half22float2(h[t]);
+                    s += (double)(f.x * f.x);
+                    s += (double)(f.y * f.y);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) s += shfl_xor_double(s, m);
+        if (lane == 0) sm.dsum[warp] = s;
+        named_barrier(1, P_NCONS);
+        double tot = 0.0;
+#pragma unroll
+        for (int w = 0; w < P_NCW; ++w) tot += sm.dsum[w];
+        const float mean_sq = __fdiv_rn((float)tot, (float)K);                         // Inference.cu:136
+        const float denom = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, op.eps)));    // Inference.cu:137
+        const __half nscale = __float2half_rn(denom);                                  // Inference.cu:138
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            const int ch = tid + e * P_NCONS;
+            if (ch < n_chunks) {
+                const uint4 gv = gvv[e];
+                const __half* xh = reinterpret_cast<const __half*>(&xv[e]);
+                const __half* gh = reinterpret_cast<const __half*>(&gv);
+                uint4 ov;
+                __half* oh = reinterpret_cast<__half*>(&ov);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) oh[t] = h_mul(h_mul(xh[t], nscale), gh[t]);  // Inference.cu:142-143
+                *(reinterpret_cast<uint4*>(xs) + ch) = ov;
+            }
+        }
+    } else if (n_units >= upt || K <= 4096) {
+        for (int ch = tid; ch < n_chunks; ch += P_NCONS)
+            *(reinterpret_cast<uint4*>(xs) + ch) = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+    } else {
+        // only the rows this CTA multiplies: [r0, r0 + n_units) units, wrapping once into the next tile
+        const int a0 = r0, a1 = min(r0 + n_units, upt), b1 = r0 + n_units - upt;   // unit (= 16-byte chunk) ranges
+        for (int ch = a0 + tid; ch < a1; ch += P_NCONS)
+            *(reinterpret_cast<uint4*>(xs) + ch) = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+        for (int ch = tid; ch < b1; ch += P_NCONS)
+            *(reinterpret_cast<uint4*>(xs) + ch) = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+    }
+    if (!UNIFORM) {
+        for (int j = tid; j < K; j += P_NCONS) sm.gidx[j] = (uint16_t)(((long long)j * op.Mb) % op.Kb);
+        const int n_used = op.Kb < op.n_alloc ? op.Kb : op.n_alloc;
+        for (int g = tid; g < n_used; g += P_NCONS) {
+            const DqConst k = make_const<EXACT>(op.zp[g], op.scale[g]);
+            sm.gtab[g] = make_uint4(k.z, k.hz, k.s, 0u);
+        }
+    }
+    named_barrier(1, P_NCONS);
+    trace_event(p, o, 2);
+
+    float acc[4][2][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int d = 0; d < 4; ++d) acc[a][b][d] = 0.0f;
+
+    const int q4 = lane >> 2, t4 = lane & 3;
+    const bool is_b = (t4 == (q4 >> 1));
+    const int bshift = (q4 & 1) * 16;
+
+    int k = 0, tile = t0, r = r0;
+    while (k < n_units) {
+        const int seg = min(upt - r, n_units - k);
+        DqConst ku = {0u, 0u, 0u};
+        int ib = tile * (P_TI / 128) + (lane >> 2);
+        if (ib >= op.Mb) ib = 0;               // columns past out_dim: zero-filled by TMA, results discarded
+        const int ibk = ib % op.Kb;
+        if (UNIFORM) {
+            if (tile == t0) {
+                ku = ku_first;
+            } else {
+                const int g = ibk % op.n_alloc;
+                ku = make_const<EXACT>(op.zp[g], op.scale[g]);
+            }
+        }
+        // ---- my units of this segment: those whose global counter is this warp's (mod 16)
+        for (int kk = k + ((warp - uc_base - k) & (P_NCW - 1)); kk < k + seg; kk += P_NCW) {
+            const int uc = uc_base + kk;
+            const int slot = uc & (P_RING - 1);
+            const uint32_t ph = (uc / P_RING) & 1;
+            if (*sm.s_dead == 0 && !mbar_wait(sm.full0 + 8 * slot, ph)) {
+                if (lane == 0) {
+                    atomicCAS(p.ws.err, 0, 0x10000 | o);   // weights of operator o never arrived
+                    *sm.s_dead = 1;
+                }
+            }
+            const int row0 = (r + (kk - k)) * P_UNIT_ROWS;
+            const uint8_t* ubase = sm.ring + slot * P_UNIT_BYTES + lane * 16;
+#pragma unroll
+            for (int half = 0; half < (p.skip_math ? 0 : 2); ++half) {
+                const int jrow = row0 + half * 4;
+                const uint8_t* src = ubase + half * 4 * P_ROW_BYTES;
+                const uint4 ra = *reinterpret_cast<const uint4*>(src);
+                const uint4 rb = *reinterpret_cast<const uint4*>(src + P_ROW_BYTES);
+                const uint4 rc = *reinterpret_cast<const uint4*>(src + 2 * P_ROW_BYTES);
+                const uint4 rd = *reinterpret_cast<const uint4*>(src + 3 * P_ROW_BYTES);
+                const uint2 xv = *reinterpret_cast<const uint2*>(xs + jrow);
+                const uint32_t bac0 = is_b ? ((xv.x & 0xffffu) << bshift) : 0u;
+                const uint32_t bbd0 = is_b ? ((xv.x >> 16) << bshift) : 0u;
+                const uint32_t bac1 = is_b ? ((xv.y & 0xffffu) << bshift) : 0u;
+                const uint32_t bbd1 = is_b ? ((xv.y >> 16) << bshift) : 0u;
+                DqConst ka = ku, kb = ku, kc = ku, kd = ku;
+                if (!UNIFORM) {
+                    const uint2 gv = *reinterpret_cast<const uint2*>(sm.gidx + jrow);
+                    int g0 = ibk + (int)(gv.x & 0xffffu), g1 = ibk + (int)(gv.x >> 16);
+                    int g2 = ibk + (int)(gv.y & 0xffffu), g3 = ibk + (int)(gv.y >> 16);
+                    g0 -= g0 >= op.Kb ? op.Kb : 0; g1 -= g1 >= op.Kb ? op.Kb : 0;
+                    g2 -= g2 >= op.Kb ? op.Kb : 0; g3 -= g3 >= op.Kb ? op.Kb : 0;
+                    if (op.Kb > op.n_alloc) { g0 %= op.n_alloc; g1 %= op.n_alloc; g2 %= op.n_alloc; g3 %= op.n_alloc; }
+                    uint4 t;
+                    t = sm.gtab[g0]; ka = {t.x, t.y, t.z};
+                    t = sm.gtab[g1]; kb = {t.x, t.y, t.z};
+                    t = sm.gtab[g2]; kc = {t.x, t.y, t.z};
+                    t = sm.gtab[g3]; kd = {t.x, t.y, t.z};
+                }
+                const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wb[4] = {rb.x, rb.y, rb.z, rb.w};
+                const uint32_t wc[4] = {rc.x, rc.y, rc.z, rc.w}, wdd[4] = {rd.x, rd.y, rd.z, rd.w};
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t alo, ahi, blo, bhi, clo, chi, dlo, dhi;
+                        dq_pair<EXACT>(h ? wa[wd] >> 8 : wa[wd], ka, alo, ahi);
+                        dq_pair<EXACT>(h ? wc[wd] >> 8 : wc[wd], kc, clo, chi);
+                        mma_16816(acc[wd][h], alo, ahi, clo, chi, bac0, bac1);
+                        dq_pair<EXACT>(h ? wb[wd] >> 8 : wb[wd], kb, blo, bhi);
+                        dq_pair<EXACT>(h ? wdd[wd] >> 8 : wdd[wd], kd, dlo, dhi);
+                        mma_16816(acc[wd][h], blo, bhi, dlo, dhi, bbd0, bbd1);
+                    }
+                }
+            }
+            __syncwarp();
+            prefetch_next(pf, p, sm);   // refill the slot just consumed with this warp's unit 32 units ahead
+        }
+
+        trace_event(p, o, 3);
+        // ---- flush the tile: cross-warp reduction in a fixed order ------------------------------
+        // red[slot][lane][32 floats], 16-byte chunks rotated by the lane index (conflict-free 128-bit
+        // accesses).  Warps 0-7 store, warps 8-15 add on top, then every thread sums the 8 slots.
+        {
+            float4* mine = reinterpret_cast<float4*>(sm.red) + (warp & 7) * (P_TI / 4) + lane * 8;
+            float4 v[8];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {   // outputs 4*ch .. 4*ch+3 of this lane's 32
+                const int wd = ch >> 1, d0 = ch & 1;   // nibbles 4*d0 + {0,1,2,3} = (h0,d0) (h0,d0+2) (h1,d0) (h1,d0+2)
+                v[ch] = make_float4(acc[wd][0][d0], acc[wd][0][d0 + 2], acc[wd][1][d0], acc[wd][1][d0 + 2]);
+            }
+            if (warp >= 8) named_barrier(2, P_NCONS);          // wait for the stores of warps 0-7
+            if (warp >= 8) {
+                float4 w[8];
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) w[ch] = mine[(ch + lane) & 7];
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    v[ch].x += w[ch].x; v[ch].y += w[ch].y; v[ch].z += w[ch].z; v[ch].w += w[ch].w;
+                }
+            }
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) mine[(ch + lane) & 7] = v[ch];
+            if (warp < 8) named_barrier(2, P_NCONS);
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) acc[a][b][d] = 0.0f;
+        }
+        named_barrier(1, P_NCONS);
+        float tot[2];
+        {
+            const int il = 2 * tid, ln = il >> 5, off = il & 31;
+            const int fidx = ln * 32 + ((((off >> 2) + ln) & 7) << 2) + (off & 3);
+            tot[0] = 0.0f;
+            tot[1] = 0.0f;
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                const float2 t2 = *reinterpret_cast<const float2*>(sm.red + sl * P_TI + fidx);
+                tot[0] += t2.x;
+                tot[1] += t2.y;
+            }
+        }
+        named_barrier(1, P_NCONS);
+        trace_event(p, o, 4);
+
+        // ---- cross-CTA fix-up --------------------------------------------------------------------
+        int cf, cl;
+        tile_contributors(U, upt, op.n_tiles, tile, cf, cl);
+        bool finalise = true;
+        if (cf != cl) {
+            float* part = p.ws.partials + (size_t)(c + tile) * P_TI;
+            *reinterpret_cast<float2*>(part + 2 * tid) = make_float2(tot[0], tot[1]);
+            named_barrier(1, P_NCONS);
+            if (tid == 0) {
+                const int old = atom_add_acq_rel(&p.ws.counters[tile], 1);
+                const int last = (old == cl - cf);
+                if (last) p.ws.counters[tile] = 0;
+                *sm.s_flag = last;
+            }
+            named_barrier(1, P_NCONS);
+            finalise = *sm.s_flag != 0;
+            named_barrier(1, P_NCONS);
+            trace_event(p, o, 5);
+            if (finalise) {
+                tot[0] = 0.0f;
+                tot[1] = 0.0f;
+                for (int cc = cf; cc <= cl; cc += 16) {   // sixteen loads in flight, summed in CTA order
+                    float2 v[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        v[e] = cc + e <= cl ? __ldcg(reinterpret_cast<const float2*>(p.ws.partials + (size_t)(cc + e + tile) * P_TI + 2 * tid))
+                                            : make_float2(0.0f, 0.0f);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        tot[0] += v[e].x;
+                        tot[1] += v[e].y;
+                    }
+                }
+            }
+        }
+        if (finalise) {
+            const int i = tile * P_TI + 2 * tid;
+            const bool valid = i < op.M;
+            const __half h0 = __float2half_rn(tot[0]), h1 = __float2half_rn(tot[1]);
+            if (op.epilogue == QW3_EPI_STORE) {
+                if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
+            } else if (op.epilogue == QW3_EPI_RESIDUAL) {
+                if (valid) {
+                    const uint32_t rv = tile == t0 ? pre_a : __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+                    const __half r0h = __ushort_as_half((unsigned short)(rv & 0xffffu)), r1h = __ushort_as_half((unsigned short)(rv >> 16));
+                    *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h_add(r0h, h0), h_add(r1h, h1));
+                }
+            } else if (op.epilogue == QW3_EPI_GELU) {
+                if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(gelu_h(h0), gelu_h(h1));
+            } else if (op.epilogue == QW3_EPI_ROPE_KV) {
+                if (valid) {
+                    const int sec = i / p.hidden, idx = i - sec * p.hidden;
+                    const int head = idx >> 7, d = idx & 127;
+                    __half o0 = h0, o1 = h1;
+                    if (sec < 2) {
+                        const __half cs = tile == t0 ? __ushort_as_half((unsigned short)pre_a) : p.cos_t[(size_t)pos * 64 + (d >> 1)];
+                        const __half sn = tile == t0 ? __ushort_as_half((unsigned short)pre_b) : p.sin_t[(size_t)pos * 64 + (d >> 1)];
+                        o0 = h_sub(h_mul(h0, cs), h_mul(h1, sn));
+                        o1 = h_add(h_mul(h0, sn), h_mul(h1, cs));
+                    }
+                    __half* dst = sec == 0 ? op.y + idx : (sec == 1 ? op.kc : op.vc) + ((size_t)head * p.max_pos + pos) * 128 + d;
+                    *reinterpret_cast<__half2*>(dst) = __halves2half2(o0, o1);
+                }
+            } else {  // QW3_EPI_ARGMAX
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                if (valid) {
+                    if (op.y) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
+                    const float f0 = __half2float(h0), f1 = __half2float(h1);
+                    if (p.logits_f32) *reinterpret_cast<float2*>(p.logits_f32 + i) = make_float2(f0, f1);
+                    bv = f0; bi = i;
+                    if (f1 > f0) { bv = f1; bi = i + 1; }
+                }
+#pragma unroll
+                for (int m = 16; m > 0; m >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                }
+                if (lane == 0) { sm.s_argv[warp] = bv; sm.s_argi[warp] = bi; }
+                named_barrier(1, P_NCONS);
+                if (warp == 0) {
+                    bv = lane < P_NCW ? sm.s_argv[lane] : -INFINITY;
+                    bi = lane < P_NCW ? sm.s_argi[lane] : 0x7fffffff;
+#pragma unroll
+                    for (int m = 8; m > 0; m >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+                        const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                    }
+                    int last = 0;
+                    if (lane == 0) {
+                        p.ws.arg_val[tile] = bv;
+                        p.ws.arg_idx[tile] = bi;
+                        __threadfence();
+                        const int old = atomicAdd(p.ws.tiles_done, 1);
+                        last = (old == op.n_tiles - 1);
+                        if (last) *p.ws.tiles_done = 0;
+                    }
+                    last = __shfl_sync(0xffffffffu, last, 0);
+                    if (last) {
+                        __threadfence();
+                        bv = -INFINITY; bi = 0x7fffffff;
+                        for (int t = lane; t < op.n_tiles; t += 32) {
+                            const float ov = __ldcg(p.ws.arg_val + t);
+                            const int oi = __ldcg(p.ws.arg_idx + t);
+                            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                        }
+#pragma unroll
+                        for (int m = 16; m > 0; m >>= 1) {
+                            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+                            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                        }
+                        if (lane == 0 && p.d_token_out) *p.d_token_out = bi;
+                    }
+                }
+            }
+            // publish the tile: one cumulative fence after the CTA barrier, then the arrival
+            trace_event(p, o, 6);
+            named_barrier(1, P_NCONS);
+            if (tid == 0) red_add_release(&p.done[o], 1);
+            trace_event(p, o, 7);
+        }
+        k += seg;
+        r = 0;
+        ++tile;
+    }
+    uc_base += n_units;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention of one layer (attentionKernel, Inference.cu:182-266, intended math): work items
+// (head, split of the KV length) are dealt round-robin to the CTAs; 32 half-warps of a CTA keep an
+// online-softmax state each; the last CTA of a head merges its splits in a fixed order.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void att_merge_states(const float* st, int n, int i, float& M, float& L, float& O) {
+    M = -INFINITY;
+    for (int g = 0; g < n; ++g) M = fmaxf(M, st[g * WS_ATT_STRIDE + 128]);
+    L = 0.0f;
+    O = 0.0f;
+    for (int g = 0; g < n; ++g) {
+        const float m = st[g * WS_ATT_STRIDE + 128];
+        const float w = (m == -INFINITY) ? 0.0f : expf(m - M);
+        L += st[g * WS_ATT_STRIDE + 129] * w;
+        O += st[g * WS_ATT_STRIDE + i] * w;
+    }
+}
+
+__device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody& op, const int o, const PassSmem& sm, const int pos) {
+    const int tid = threadIdx.x, grp = tid >> 4, sl = tid & 15;
+    const int G = gridDim.x, c = blockIdx.x, heads = p.heads;
+    int S = G / heads;   // one (head, split) item per CTA
+    S = S < 1 ? 1 : (S > WS_ATT_MAX_SPLITS ? WS_ATT_MAX_SPLITS : S);
+    const int len = pos + 1;
+    const int chunk = (len + S - 1) / S;
+    const float scale = 1.0f / sqrtf(128.0f);
+    float* st = sm.red;
+    constexpr int NG = P_NCONS / 16;   // 32 half-warps
+    for (int item = c; item < heads * S; item += G) {
+        const int head = item / S, split = item - head * S;
+        const int p0 = split * chunk, p1 = min(len, p0 + chunk);
+        float qf[8];
+        {
+            const uint4 qv = __ldcg(reinterpret_cast<const uint4*>(op.x + head * 128 + sl * 8));
+            const __half2* h = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                qf[2 * e] = f.x;
+                qf[2 * e + 1] = f.y;
+            }
+        }
+        const __half* kh = op.kc + (size_t)head * p.max_pos * 128 + sl * 8;
+        const __half* vh = op.vc + (size_t)head * p.max_pos * 128 + sl * 8;
+        float m = -INFINITY, l = 0.0f, ov[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ov[e] = 0.0f;
+        constexpr int UN = 2;
+        for (int kb = p0; kb < p1; kb += NG * UN) {   // trip count uniform across the CTA
+            uint4 kv[UN], vv[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int kp = kb + grp + u * NG;
+                kv[u] = make_uint4(0u, 0u, 0u, 0u);
+                vv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (kp < p1) {
+                    kv[u] = __ldcg(reinterpret_cast<const uint4*>(kh + (size_t)kp * 128));
+                    vv[u] = __ldcg(reinterpret_cast<const uint4*>(vh + (size_t)kp * 128));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int kp = kb + grp + u * NG;
+                const __half2* kh2 = reinterpret_cast<const __half2*>(&kv[u]);
+                float dot = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(kh2[e]);
+                    dot = fmaf(qf[2 * e], f.x, dot);
+                    dot = fmaf(qf[2 * e + 1], f.y, dot);
+                }
+#pragma unroll
+                for (int msk = 8; msk > 0; msk >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, msk);
+                if (kp < p1) {
+                    const float s = dot * scale;
+                    const float mn = fmaxf(m, s);
+                    const float corr = (m == -INFINITY) ? 0.0f : expf(m - mn);
+                    const float pr = expf(s - mn);
+                    l = l * corr + pr;
+                    const __half2* vh2 = reinterpret_cast<const __half2*>(&vv[u]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __half22float2(vh2[e]);
+                        ov[2 * e] = fmaf(pr, f.x, ov[2 * e] * corr);
+                        ov[2 * e + 1] = fmaf(pr, f.y, ov[2 * e + 1] * corr);
+                    }
+                    m = mn;
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) st[grp * WS_ATT_STRIDE + sl * 8 + e] = ov[e];
+        if (sl == 0) {
+            st[grp * WS_ATT_STRIDE + 128] = m;
+            st[grp * WS_ATT_STRIDE + 129] = l;
+        }
+        named_barrier(1, P_NCONS);
+        float M = 0.f, L = 1.f, O = 0.f;
+        if (tid < 128) att_merge_states(st, NG, tid, M, L, O);
+        bool finalise = true;
+        if (S > 1) {
+            float* mine = p.ws.att_part + ((size_t)head * WS_ATT_MAX_SPLITS + split) * WS_ATT_STRIDE;
+            if (tid < 128) mine[tid] = O;
+            if (tid == 0) {
+                mine[128] = M;
+                mine[129] = L;
+            }
+            named_barrier(1, P_NCONS);
+            if (tid == 0) {
+                const int old = atom_add_acq_rel(&p.ws.att_count[head], 1);
+                const int last = (old == S - 1);
+                if (last) p.ws.att_count[head] = 0;
+                *sm.s_flag = last;
+            }
+            named_barrier(1, P_NCONS);
+            finalise = *sm.s_flag != 0;
+            if (finalise) {
+                const float* all = p.ws.att_part + (size_t)head * WS_ATT_MAX_SPLITS * WS_ATT_STRIDE;
+                for (int t = tid; t < S * WS_ATT_STRIDE; t += P_NCONS) st[t] = __ldcg(all + t);
+                named_barrier(1, P_NCONS);
+                if (tid < 128) att_merge_states(st, S, tid, M, L, O);
+            }
+        }
+        if (finalise) {
+            if (tid < 128) op.y[head * 128 + tid] = __float2half_rn(O / L);
+            named_barrier(1, P_NCONS);
+            if (tid == 0) red_add_release(&p.done[o], 1);
+        }
+        named_barrier(1, P_NCONS);   // st and s_flag are reused by the next item
+    }
+}
+
+// Embedding gather straight from the packed [hidden][vocab] matrix (Inference.cu:1310-1315).
+__device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBody& op, const int o, const int pos) {
+    const int tid = threadIdx.x, c = blockIdx.x;
+    const int nblk = (p.hidden + P_NCONS - 1) / P_NCONS;
+    if (c >= nblk) return;
+    const int idx = c * P_NCONS + tid;
+    const bool skip = p.d_skip != nullptr && __ldcg(p.d_skip) != 0;
+    if (idx < p.hidden && !skip) {
+        long long tok = p.decode ? __ldcg(p.d_token) : __ldcg(p.d_prompt + pos);
+        if (tok < 0 || tok >= p.vocab) tok = 0;
+        const long long pc = (p.vocab + 1) / 2;
+        const uint32_t byte = op.packed[(long long)idx * pc + (tok >> 1)];
+        const uint32_t q = (tok & 1) ? (byte >> 4) : (byte & 15u);
+        const long long g = (tok / 128) % op.n_alloc;
+        op.y[idx] = dequant_one(q, op.zp[g], op.scale[g]);
+    }
+    named_barrier(1, P_NCONS);
+    if (tid == 0) red_add_release(&p.done[o], 1);
+}
+
+__global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    PassSmem sm;
+    sm.ring = smem;
+    sm.red = reinterpret_cast<float*>(smem + P_OFF_RED);
+    sm.xs = reinterpret_cast<__half*>(smem + P_OFF_XS);
+    sm.gidx = reinterpret_cast<uint16_t*>(smem + P_OFF_GIDX);
+    sm.gtab = reinterpret_cast<uint4*>(smem + P_OFF_GTAB);
+    uint8_t* misc = smem + P_OFF_MISC;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(misc);              // full[P_RING]: 256 bytes
+    sm.full0 = smem_u32(bars);
+    sm.dsum = reinterpret_cast<double*>(misc + 640);                 // 128
+    sm.s_argv = reinterpret_cast<float*>(misc + 768);                // 64
+    sm.s_argi = reinterpret_cast<int*>(misc + 832);                  // 64
+    sm.s_flag = reinterpret_cast<int*>(misc + 896);
+    sm.s_dead = reinterpret_cast<int*>(misc + 900);
+    sm.s_op = reinterpret_cast<uint32_t*>(misc + 1024);              // 2 x 128 bytes
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < P_RING; ++s) mbar_init(sm.full0 + 8 * s, 1);
+        *sm.s_dead = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // prime the ring: the first two units of this warp (weights do not depend on activations)
+    Prefetch pf;
+    pf.op = -1; pf.uc = warp - P_NCW; pf.base = 0; pf.n = 0; pf.ub = 0; pf.upt = 1; pf.next_u = 0; pf.tile = 0; pf.r = 0; pf.end = false;
+    prefetch_next(pf, p, sm);
+    prefetch_next(pf, p, sm);
+
+    // ---------------- consumers ----------------------------------------------------------------
+    const int pos = __ldcg(p.d_pos);
+    if (tid < P_OPW) sm.s_op[tid] = reinterpret_cast<const uint32_t*>(&p.ops[0].b)[tid];
+    int uc_base = 0;
+    int prev_target = 0;
+    for (int o = 0; o < p.n_ops; ++o) {
+        trace_event(p, o, 0);
+        if (o > 0 && tid == 0 && *sm.s_dead == 0) {
+            // the operator before this one must be complete: bounded acquire-poll of its counter
+            const long long t0 = clock64();
+            while (ld_acquire(p.done + o - 1) < prev_target) {
+                if (clock64() - t0 > (1ll << 31)) {
+                    atomicCAS(p.ws.err, 0, 0x20000 | o);   // operator o-1 never completed
+                    *sm.s_dead = 1;
+                    break;
+                }
+            }
+        }
+        named_barrier(1, P_NCONS);
+        trace_event(p, o, 1);
+        if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            p.trace[o] = t;
+        }
+        const PassOpBody& op = *reinterpret_cast<const PassOpBody*>(sm.s_op + (o & 1) * P_OPW);
+        if (o + 1 < p.n_ops && tid < P_OPW)   // next descriptor, visible after the barriers of this operator
+            sm.s_op[((o + 1) & 1) * P_OPW + tid] = reinterpret_cast<const uint32_t*>(&p.ops[o + 1].b)[tid];
+        prev_target = op.done_target;
+        if (op.kind == PASS_GEMV) {
+            if (op.uniform) {
+                if (op.exact) gemv_phase<true, true>(p, op, o, sm, uc_base, pos, pf);
+                else gemv_phase<true, false>(p, op, o, sm, uc_base, pos, pf);
+            } else {
+                if (op.exact) gemv_phase<false, true>(p, op, o, sm, uc_base, pos, pf);
+                else gemv_phase<false, false>(p, op, o, sm, uc_base, pos, pf);
+            }
+        } else if (op.kind == PASS_ATTN) {
+            attn_phase(p, op, o, sm, pos);
+        } else {
+            embed_phase(p, op, o, pos);
+        }
+    }
+    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.trace[p.n_ops] = t;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+int encode_2d_u32(CUtensorMap* map, const void* base, uint64_t inner_elems, uint64_t rows, uint64_t pitch_bytes,
+                  uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz);
+
+int pass_init_device() {
+    QW3_CUDA(cudaFuncSetAttribute(decode_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM_BYTES));
+    int nb = 0;
+    QW3_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, decode_pass_kernel, P_NTHREADS, P_SMEM_BYTES));
+    if (nb < 1) {
+        set_last_error("decode_pass_kernel does not fit on an SM (%zu bytes of shared memory)", P_SMEM_BYTES);
+        return QW3_ERR_CUDA;
+    }
+    return QW3_OK;
+}
+
+// Whether a matrix can be an operator of the persistent pass (else the per-operator path is used).
+bool pass_supports(const W4Desc* d) {
+    if (d->K > P_MAXK) return false;
+    if (!d->uniform) {
+        const long long Kb = d->K / 128, used = Kb < d->n_alloc ? Kb : d->n_alloc;
+        if (d->K > P_MAXK_NU || used > P_MAX_GROUPS) return false;
+    }
+    return true;
+}
+
+void pass_fill_gemv(PassOp* op, const W4Desc* d, const void* x, const void* gamma, float eps, int epilogue, void* y,
+                    void* kc, void* vc) {
+    std::memset(op, 0, sizeof(*op));
+    op->tmap = d->tmap;
+    PassOpBody& b = op->b;
+    b.kind = PASS_GEMV;
+    b.uniform = d->uniform; b.exact = d->zp_integral; b.epilogue = epilogue;
+    b.M = (int)d->M; b.K = (int)d->K; b.Mb = b.M / 128; b.Kb = b.K / 128;
+    b.n_alloc = (int)d->n_alloc;
+    b.n_tiles = (b.M + P_TI - 1) / P_TI;
+    b.upt = b.K / P_UNIT_ROWS;
+    b.done_target = b.n_tiles;
+    b.U = (long long)b.n_tiles * b.upt;
+    b.scale = d->scale; b.zp = d->zp;
+    b.x = static_cast<const __half*>(x); b.gamma = static_cast<const __half*>(gamma);
+    b.y = static_cast<__half*>(y); b.kc = static_cast<__half*>(kc); b.vc = static_cast<__half*>(vc);
+    b.eps = eps;
+}
+
+void pass_fill_attn(PassOp* op, const void* q, void* kc, void* vc, void* ctx, int heads) {
+    std::memset(op, 0, sizeof(*op));
+    PassOpBody& b = op->b;
+    b.kind = PASS_ATTN;
+    b.done_target = heads;
+    b.x = static_cast<const __half*>(q);
+    b.kc = static_cast<__half*>(kc); b.vc = static_cast<__half*>(vc);
+    b.y = static_cast<__half*>(ctx);
+}
+
+void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const void* zp, long long n_alloc, void* hidden_out,
+                     int hidden) {
+    std::memset(op, 0, sizeof(*op));
+    PassOpBody& b = op->b;
+    b.kind = PASS_EMBED;
+    b.done_target = (hidden + P_NCONS - 1) / P_NCONS;
+    b.packed = static_cast<const uint8_t*>(packed);
+    b.scale = static_cast<const __half*>(scale); b.zp = static_cast<const __half*>(zp);
+    b.n_alloc = (int)n_alloc;
+    b.y = static_cast<__half*>(hidden_out);
+}
+
+size_t pass_op_bytes() { return sizeof(PassOp); }
+
+struct PassLaunch {
+    PassParams p;
+};
+
+// Enqueues one pass: clears the arrival counters, then the cooperative launch.
+int pass_launch(const void* d_ops, int n_ops, int* d_done, const int* d_pos, const int* d_token, const int* d_skip,
+                const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
+                long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
+                unsigned long long* trace2, const Workspace* ws, cudaStream_t st) {
+    PassParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.ops = static_cast<const PassOp*>(d_ops);
+    p.n_ops = n_ops;
+    p.done = d_done;
+    p.d_pos = d_pos; p.d_token = d_token; p.d_skip = d_skip; p.d_prompt = d_prompt;
+    p.decode = decode;
+    p.cos_t = static_cast<const __half*>(cos_t); p.sin_t = static_cast<const __half*>(sin_t);
+    p.heads = heads; p.hidden = hidden; p.max_pos = max_pos; p.vocab = vocab;
+    p.d_token_out = d_token_out; p.logits_f32 = logits_f32; p.trace = trace; p.trace2 = trace2;
+    p.skip_math = std::getenv("QW3_DEBUG_SKIP_MATH") != nullptr;
+    p.ws = *ws;
+    QW3_CUDA(cudaMemsetAsync(d_done, 0, (size_t)n_ops * 4, st));
+    int grid = ws->sm_count < WS_MAX_CTAS ? ws->sm_count : WS_MAX_CTAS;
+    void* args[] = {&p};
+    QW3_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_pass_kernel), dim3(grid), dim3(P_NTHREADS), args,
+                                         P_SMEM_BYTES, st));
+    return QW3_OK;
+}
+
+}  // namespace qw3

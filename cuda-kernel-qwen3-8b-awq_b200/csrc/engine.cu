@@ -10,6 +10,7 @@
 //     not ordered after the producing stream, Inference.cu:1013-1023).
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -27,6 +28,20 @@ int embed_gather_launch(const void* packed, const void* scale, const void* zp, l
 int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, bool pdl, cudaStream_t st);
 const W4Desc* w4_desc(qw3_w4_t w);
 const Workspace* ws_struct(qw3_ws_t ws);
+// persistent token-pass kernel (decode_pass.cu)
+struct PassOp;
+int pass_init_device();
+bool pass_supports(const W4Desc* d);
+size_t pass_op_bytes();
+void pass_fill_gemv(PassOp* op, const W4Desc* d, const void* x, const void* gamma, float eps, int epilogue, void* y,
+                    void* kc, void* vc);
+void pass_fill_attn(PassOp* op, const void* q, void* kc, void* vc, void* ctx, int heads);
+void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const void* zp, long long n_alloc, void* hidden_out,
+                     int hidden);
+int pass_launch(const void* d_ops, int n_ops, int* d_done, const int* d_pos, const int* d_token, const int* d_skip,
+                const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
+                long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
+                unsigned long long* trace2, const Workspace* ws, cudaStream_t st);
 
 #define QW3_TRY(expr)                     \
     do {                                  \
@@ -66,6 +81,14 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     cudaEvent_t taken = nullptr;       // recorded after this stage has copied its input from a peer
     cudaGraphExec_t g_prompt = nullptr, g_decode = nullptr;
     int launches_prompt = 0, launches_decode = 0;
+    // persistent pass: operator lists (device) of the prompt pass and of the decode pass
+    void* ops_prompt = nullptr;
+    void* ops_decode = nullptr;
+    int n_ops_prompt = 0, n_ops_decode = 0;
+    int* d_done = nullptr;
+    unsigned long long* d_trace = nullptr;   // per-operator entry times of the last pass (debug)
+    unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
+    bool persistent = false;
 };
 
 }  // namespace qw3
@@ -237,7 +260,13 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
     Stage& s = e->st[si];
     const bool first = si == 0, last = si == c.n_stages - 1;
     QW3_CUDA(cudaSetDevice(s.device));
-    if (layers) {
+    if (layers && s.persistent) {
+        // the whole pass of this stage is one cooperative launch
+        QW3_TRY(pass_launch(decode ? s.ops_decode : s.ops_prompt, decode ? s.n_ops_decode : s.n_ops_prompt, s.d_done, s.d_pos,
+                            s.d_token, first ? s.d_skip : nullptr, s.d_prompt, decode ? 1 : 0, s.cos_t, s.sin_t, c.heads,
+                            c.hidden, c.max_pos, c.vocab, s.d_token, s.logits32, s.d_trace, s.d_trace2, ws_struct(s.ws), s.stream));
+        *launches += 1;
+    } else if (layers) {
         if (first) {
             if (decode)
                 QW3_TRY(embed_gather_launch(s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, c.hidden, c.vocab, s.d_token,
@@ -249,10 +278,39 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
         }
         for (int li = 0; li < (int)s.layers.size(); ++li) QW3_TRY(enqueue_layer(e, s, li, pdl, launches));
     }
-    if (decode && last) QW3_TRY(enqueue_sample(e, s, pdl, launches));
+    if (decode && last && !(layers && s.persistent)) QW3_TRY(enqueue_sample(e, s, pdl, launches));
     QW3_TRY(step_tail_launch(layers ? s.d_pos : nullptr, (decode && last) ? s.d_step : nullptr, s.d_token,
                              (decode && last) ? s.d_out_ids : nullptr, first ? s.d_skip : nullptr, pdl, s.stream));
     *launches += 1;
+    return QW3_OK;
+}
+
+// Operator list of one pass of a stage, uploaded once (runOneLayer's sequence, Inference.cu:1029-1230).
+static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, int* n_ops) {
+    const Qw3Config& c = e->cfg;
+    Stage& s = e->st[si];
+    const bool first = si == 0, last = si == c.n_stages - 1;
+    const size_t ob = pass_op_bytes();
+    const int n = (first ? 1 : 0) + 5 * (int)s.layers.size() + ((decode && last) ? 1 : 0);
+    std::vector<uint8_t> host((size_t)n * ob + 256);
+    uint8_t* base = host.data();
+    base += (256 - (reinterpret_cast<uintptr_t>(base) & 255)) & 255;   // descriptors hold 64-byte aligned tensor maps
+    int k = 0;
+    auto at = [&](int i) { return reinterpret_cast<PassOp*>(base + (size_t)i * ob); };
+    if (first) pass_fill_embed(at(k++), s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, s.hidden, c.hidden);
+    for (LayerDev& L : s.layers) {
+        pass_fill_gemv(at(k++), w4_desc(L.wqkv.desc), s.hidden, L.gamma, c.eps, QW3_EPI_ROPE_KV, s.q, L.kc, L.vc);
+        pass_fill_attn(at(k++), s.q, L.kc, L.vc, s.ctx, c.heads);
+        pass_fill_gemv(at(k++), w4_desc(L.wo.desc), s.ctx, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
+        pass_fill_gemv(at(k++), w4_desc(L.w1.desc), s.hidden, L.gamma, c.eps, QW3_EPI_GELU, s.mlp, nullptr, nullptr);
+        pass_fill_gemv(at(k++), w4_desc(L.w2.desc), s.mlp, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
+    }
+    if (decode && last)
+        pass_fill_gemv(at(k++), w4_desc(s.unemb.desc), s.hidden, s.layers.back().gamma, c.eps, QW3_EPI_ARGMAX, s.logits16,
+                       nullptr, nullptr);
+    QW3_TRY(dev_alloc(e, s.device, d_ops, (size_t)n * ob));
+    QW3_CUDA(cudaMemcpy(*d_ops, base, (size_t)n * ob, cudaMemcpyHostToDevice));
+    *n_ops = n;
     return QW3_OK;
 }
 
@@ -322,7 +380,7 @@ int qw3_config_default(Qw3Config* c) {
     std::memset(c, 0, sizeof(*c));
     c->hidden = 4096; c->inter = 12288; c->heads = 32; c->head_dim = 128; c->layers = 36; c->vocab = 151936;
     c->max_pos = 40960; c->eps = 1e-6f; c->rope_base = 10000.0f; c->sample_first = 0;
-    c->n_stages = 1; c->rank = 0; c->world = 1; c->use_graph = 1; c->use_pdl = 1; c->keep_logits = 0;
+    c->n_stages = 1; c->rank = 0; c->world = 1; c->use_graph = 1; c->use_pdl = 1; c->keep_logits = 0; c->persistent = 1;
     return QW3_OK;
 }
 
@@ -444,6 +502,30 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
             if (c.keep_logits) QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.logits32), (size_t)V * 4));
         }
         QW3_CUDA(cudaStreamSynchronize(s.stream));
+    }
+    if (c.persistent) {
+        for (int si = 0; si < N; ++si) {
+            Stage& s = e->st[si];
+            bool ok = c.heads <= WS_ATT_MAX_HEADS;
+            for (LayerDev& L : s.layers)
+                ok = ok && pass_supports(w4_desc(L.wqkv.desc)) && pass_supports(w4_desc(L.wo.desc)) &&
+                     pass_supports(w4_desc(L.w1.desc)) && pass_supports(w4_desc(L.w2.desc));
+            if (si == N - 1) ok = ok && pass_supports(w4_desc(s.unemb.desc));
+            if (!ok) continue;   // shapes outside the persistent kernel's limits: per-operator launches
+            QW3_CUDA(cudaSetDevice(s.device));
+            QW3_TRY(pass_init_device());
+            QW3_TRY(build_pass_program(e, si, false, &s.ops_prompt, &s.n_ops_prompt));
+            QW3_TRY(build_pass_program(e, si, true, &s.ops_decode, &s.n_ops_decode));
+            QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_done), (size_t)(s.n_ops_decode + 1) * 4));
+            if (std::getenv("QW3_TRACE")) {
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_trace), (size_t)(s.n_ops_decode + 1) * 8));
+                QW3_CUDA(cudaMemset(s.d_trace, 0, (size_t)(s.n_ops_decode + 1) * 8));
+                const size_t t2 = (size_t)256 * s.n_ops_decode * 8 * 8;
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_trace2), t2));
+                QW3_CUDA(cudaMemset(s.d_trace2, 0, t2));
+            }
+            s.persistent = true;
+        }
     }
     QW3_CUDA(cudaSetDevice(e->st[0].device));
     QW3_CUDA(cudaEventCreate(&e->ev0));
@@ -637,6 +719,28 @@ int qw3_layer_decode(qw3_handle e, int32_t layer, int32_t pos, void* host_hidden
     QW3_CUDA(cudaMemcpyAsync(host_hidden, s->hidden, (size_t)e->cfg.hidden * 2, cudaMemcpyDeviceToHost, s->stream));
     QW3_CUDA(cudaStreamSynchronize(s->stream));
     return qw3_ws_check(s->ws, s->stream);
+}
+
+int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries) {
+    QW3_REQUIRE(e && out && n_entries && stage >= 0 && stage < (int)e->st.size(), "qw3_debug_trace: bad argument");
+    Stage& s = e->st[stage];
+    if (!s.d_trace) {
+        set_last_error("qw3_debug_trace: create the handle with QW3_TRACE set in the environment and persistent = 1");
+        return QW3_ERR_STATE;
+    }
+    QW3_CUDA(cudaSetDevice(s.device));
+    QW3_CUDA(cudaStreamSynchronize(s.stream));
+    if (max_entries < 0) {   // detailed form: -max_entries values of [grid][n_ops][8] per-CTA event times
+        const size_t total = (size_t)256 * s.n_ops_decode * 8;
+        const size_t m = (size_t)(-max_entries) < total ? (size_t)(-max_entries) : total;
+        QW3_CUDA(cudaMemcpy(out, s.d_trace2, m * 8, cudaMemcpyDeviceToHost));
+        *n_entries = s.n_ops_decode;
+        return QW3_OK;
+    }
+    const int n = s.n_ops_decode + 1 < max_entries ? s.n_ops_decode + 1 : max_entries;
+    QW3_CUDA(cudaMemcpy(out, s.d_trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
+    *n_entries = n;
+    return QW3_OK;
 }
 
 int qw3_stage_export(qw3_handle, void*) {

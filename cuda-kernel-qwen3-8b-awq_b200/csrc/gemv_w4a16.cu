@@ -68,49 +68,6 @@ struct GemvParams {
     Workspace ws;
 };
 
-struct DqConst {  // per-group constants, duplicated into both halves
-    uint32_t z;   // exact path: 1024 + zp;  generic path: zp
-    uint32_t hz;  // exact path: -(64 + zp)
-    uint32_t s;
-};
-
-template <bool EXACT>
-__device__ __forceinline__ DqConst make_const(__half z, __half s) {
-    DqConst c;
-    if (EXACT) {
-        c.z = dup_h2(h_add(__ushort_as_half(0x6400), z));   // 1024 + zp, exact for integral zp
-        c.hz = dup_h2(h_sub(__ushort_as_half(0xD400), z));  // -64 - zp, exact
-    } else {
-        c.z = dup_h2(z);
-        c.hz = 0;
-    }
-    c.s = dup_h2(s);
-    return c;
-}
-
-// Eight nibbles of one row -> after `u = w` / `u = w >> 8`: two registers of dequantised pairs.
-//   lo: nibbles (0,4) resp. (2,6);  hi: nibbles (1,5) resp. (3,7).
-// Both roundings of the reference are kept: d = RN(q - zp), w = RN(d * scale).
-template <bool EXACT>
-__device__ __forceinline__ void dq_pair(uint32_t u, const DqConst& c, uint32_t& wlo, uint32_t& whi) {
-    const uint32_t lo = lop3_and_or(u, 0x000f000fu, 0x64006400u);  // (1024 + q) x2
-    const uint32_t hi = lop3_and_or(u, 0x00f000f0u, 0x64006400u);  // (1024 + 16 q) x2
-    uint32_t dlo, dhi;
-    if (EXACT) {
-        dlo = h2_sub(lo, c.z);                     // (1024+q) - (1024+zp): exact operands, one rounding
-        dhi = h2_fma(hi, 0x2C002C00u, c.hz);       // (1024+16q)/16 - (64+zp), one rounding
-    } else {
-        dlo = h2_sub(h2_sub(lo, 0x64006400u), c.z);                  // q exactly, then RN(q - zp)
-        dhi = h2_sub(h2_fma(hi, 0x2C002C00u, 0xD400D400u), c.z);
-    }
-    wlo = h2_mul(dlo, c.s);
-    whi = h2_mul(dhi, c.s);
-}
-
-__device__ __forceinline__ int owner_of(long long u, int G, long long U) { return (int)(((u + 1) * G - 1) / U); }
-
-__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
-
 template <bool UNIFORM, bool EXACT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemv_w4a16_kernel(const __grid_constant__ CUtensorMap tmap, const GemvParams p) {
@@ -669,7 +626,7 @@ int qw3_ws_check(qw3_ws_t ws, void* stream) {
         if (base) QW3_CUDA(cudaMemsetAsync(base + workspace_zero_from(), 0, workspace_bytes() - workspace_zero_from(), st));
         else QW3_CUDA(cudaMemsetAsync(ws->h.ws.err, 0, 4, st));
         QW3_CUDA(cudaStreamSynchronize(st));
-        set_last_error("a bounded device-side wait gave up (device error word = %d)", err);
+        set_last_error("a bounded device-side wait gave up (device error word = 0x%x)", err);
         return QW3_ERR_TIMEOUT;
     }
     return QW3_OK;

@@ -187,6 +187,7 @@ typedef struct Qw3Config {
     int32_t use_graph;     /* replay one captured decode step per token */
     int32_t use_pdl;       /* programmatic dependent launch between the step's kernels */
     int32_t keep_logits;   /* keep an fp32 copy of the last step's logits (test hook) */
+    int32_t persistent;    /* 1: a token pass of a stage is one persistent cooperative kernel; 0: one launch per operator */
 } Qw3Config;
 
 typedef struct qw3_engine* qw3_handle;
@@ -220,6 +221,10 @@ int qw3_last_launches(qw3_handle h, int64_t* n);
  * with host hidden state in/out. */
 int qw3_kv_upload(qw3_handle h, int32_t layer, int32_t which, const void* host_f16, int64_t upto);
 int qw3_layer_decode(qw3_handle h, int32_t layer, int32_t pos, void* host_hidden_f16);
+
+/* Debug: global-timer value (ns) at which CTA 0 entered each operator of the last decode pass of a
+ * stage, plus the end of the pass; needs QW3_TRACE set in the environment when the handle is made. */
+int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries);
 
 /* One process per GPU: 64-byte CUDA IPC handles of this stage's inbox; connect to the next
  * stage's (and, from the last stage, the first stage's) inbox. */

@@ -36,12 +36,12 @@ def _logits_close(got32, want16):
     return (np.abs(got32 - want) <= 2e-2 * np.abs(want) + 2e-2 * np.abs(want).mean()).all()
 
 
-@pytest.mark.parametrize("use_graph,use_pdl", [(0, 0), (1, 0), (0, 1), (1, 1)])
-def test_small_model_tokens_match_oracle(pkg, orc, cuda, small_dir, use_graph, use_pdl):
+@pytest.mark.parametrize("persistent,use_graph,use_pdl", [(1, 0, 0), (1, 1, 0), (0, 0, 0), (0, 1, 0), (0, 0, 1), (0, 1, 1)])
+def test_small_model_tokens_match_oracle(pkg, orc, cuda, small_dir, persistent, use_graph, use_pdl):
     prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
     ids, logits, margins = _oracle_generate(orc, SMALL, 0, small_dir, prompt, 10)
     assert [int(t) for t in ids] == GOLDEN["small_model"]["ids"]          # the oracle itself is pinned
-    inf = pkg.QWen3AWQInfer(small_dir, use_graph=use_graph, use_pdl=use_pdl, keep_logits=1, **SMALL)
+    inf = pkg.QWen3AWQInfer(small_dir, persistent=persistent, use_graph=use_graph, use_pdl=use_pdl, keep_logits=1, **SMALL)
     got = inf.generateResponse(prompt, 10)
     assert got == [int(t) for t in ids], f"margins {margins}"
     assert _logits_close(inf.last_logits(), logits)
@@ -59,12 +59,13 @@ def test_small_model_sample_first(pkg, orc, cuda, small_dir):
     inf.close()
 
 
+@pytest.mark.parametrize("persistent", [1, 0])
 @pytest.mark.parametrize("n_stages", [2, 3, 4])
-def test_stage_split_does_not_change_tokens(pkg, orc, cuda, small_dir, n_stages):
+def test_stage_split_does_not_change_tokens(pkg, orc, cuda, small_dir, n_stages, persistent):
     """Layer pipeline with several logical stages mapped onto one device: the hand-off is a local
     copy, the results must equal the single-stage run."""
     prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
-    inf = pkg.QWen3AWQInfer(small_dir, n_stages=n_stages, device=[0] * n_stages, keep_logits=1, **SMALL)
+    inf = pkg.QWen3AWQInfer(small_dir, n_stages=n_stages, device=[0] * n_stages, keep_logits=1, persistent=persistent, **SMALL)
     got = inf.generateResponse(prompt, 10)
     assert got == GOLDEN["small_model"]["ids"]
     inf.close()
