@@ -753,9 +753,4 @@ int qw3_stage_connect(qw3_handle, const void*) {
     return QW3_ERR_STATE;
 }
 
-int qw3_gemm_w4a16(qw3_w4_t, const void*, int64_t, void*, qw3_ws_t, void*) {
-    set_last_error("qw3_gemm_w4a16: not built yet");
-    return QW3_ERR_STATE;
-}
-
 }  // extern "C"

@@ -1,0 +1,348 @@
+// Tensor-core W4A16 contraction for several activation rows (prefill / batched rows) on sm_100a:
+//   Y[r][i] = sum_j W(i, j) * X[r][j],   W(i, j) = hmul(hsub(half(q), zp[g]), scale[g])  (bit-exact),
+// with tcgen05.mma (fp16 x fp16 -> fp32 in tensor memory).  The reference has no batched path: it
+// feeds prompts token by token through cublasGemmEx at n = 1 (Inference.cu:1304-1343, 1052-1065);
+// this is the same product for `rows` tokens at once.
+//
+// One CTA computes a tile of 128 outputs x N rows of X (N = 16..256).  Six warps:
+//   warp 0      TMA producer: per 64-deep K block one box of packed nibbles [64 rows][64 B] and one
+//               box of activations [N][64] (128-byte swizzle, K-major operand B)
+//   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
+//   warps 2..5  unpack the nibbles to fp16 with the reference's two roundings and write operand A
+//               to shared memory in the MN-major 128-byte-swizzled canonical layout (outputs are
+//               contiguous in the packed stream, so MN-major needs no transposition); afterwards the
+//               same four warps read the accumulators back (tcgen05.ld) and store Y as fp16.
+// Within every group of 8 outputs the rows of A are stored in the order the lop3 unpack yields them
+// (0,4,1,5,2,6,3,7); the epilogue undoes that permutation when it computes the output index.
+// All mbarrier waits are bounded; a wait that gives up sets the workspace error word.
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace qw3 {
+
+const Workspace* ws_struct(qw3_ws_t ws);
+const W4Desc* w4_desc(qw3_w4_t w);
+
+constexpr int GM_TILE_M = 128;                 // outputs per CTA
+constexpr int GM_BK = 64;                      // K per pipeline stage
+constexpr int GM_PACKED_BYTES = GM_BK * GM_TILE_M / 2;   // 4096
+constexpr int GM_A_BYTES = GM_TILE_M * GM_BK * 2;        // 16384
+constexpr int GM_LD_STAGES = 4;
+constexpr int GM_A_STAGES = 3;
+constexpr int GM_THREADS = 192;
+
+struct GemmParams {
+    const __half* scale;
+    const __half* zp;
+    int n_alloc, M, K, Mb, Kb;
+    int uniform, exact;
+    int rows;          // rows of X / Y
+    int n_tile;        // UMMA N: 16..256, multiple of 16
+    int tmem_cols;     // power of two >= max(32, n_tile)
+    __half* y;         // [rows][M]
+    int* err;
+    int a_lbo, a_sbo, a_kstep;   // operand A descriptor: byte offsets between 64-output blocks, between 8-deep K blocks, per K=16 step
+};
+
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred;
+}
+
+// Shared-memory matrix descriptor (tcgen05): start >> 4 in bits 0-13, leading byte offset >> 4 in
+// bits 16-29, stride byte offset >> 4 in bits 32-45, version 1 in bits 46-47, swizzle mode in bits 61-63
+// (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int x_bytes = p.n_tile * 128;                                   // [n_tile][64] fp16
+    uint8_t* a_st = smem;                                                 // GM_A_STAGES x 16 KB (1024-aligned)
+    uint8_t* x_st = smem + GM_A_STAGES * GM_A_BYTES;                      // GM_LD_STAGES x x_bytes (multiple of 1024)
+    uint8_t* w_st = x_st + GM_LD_STAGES * x_bytes;                        // GM_LD_STAGES x 4 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_st + GM_LD_STAGES * GM_PACKED_BYTES);
+    const uint32_t ld_full = smem_u32(bars), ld_empty = smem_u32(bars + GM_LD_STAGES);
+    const uint32_t a_full = smem_u32(bars + 2 * GM_LD_STAGES), a_empty = smem_u32(bars + 2 * GM_LD_STAGES + GM_A_STAGES);
+    const uint32_t acc_full = smem_u32(bars + 2 * GM_LD_STAGES + 2 * GM_A_STAGES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GM_LD_STAGES + 2 * GM_A_STAGES + 1);
+    int* s_dead = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile_m = blockIdx.x, tile_n = blockIdx.y;
+    const int n_kb = p.K / GM_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < GM_LD_STAGES; ++s) {
+            mbar_init(ld_full + 8 * s, 1);
+            mbar_init(ld_empty + 8 * s, 5);     // 4 unpack warps + 1 commit of the MMAs that read X
+        }
+        for (int s = 0; s < GM_A_STAGES; ++s) {
+            mbar_init(a_full + 8 * s, 4);       // 4 unpack warps
+            mbar_init(a_empty + 8 * s, 1);      // commit of the MMAs that read A
+        }
+        mbar_init(acc_full, 1);
+        *s_dead = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {   // tensor memory for the accumulators: 128 lanes x tmem_cols 32-bit columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------------------------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_w);
+            tma_prefetch_desc(&tmap_x);
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int s = kb % GM_LD_STAGES;
+                if (kb >= GM_LD_STAGES && !mbar_wait(ld_empty + 8 * s, ((kb / GM_LD_STAGES) - 1) & 1)) {
+                    atomicCAS(p.err, 0, 0x30001);
+                    *s_dead = 1;
+                    break;
+                }
+                mbar_expect_tx(ld_full + 8 * s, (uint32_t)(GM_PACKED_BYTES + x_bytes));
+                tma_load_2d(smem_u32(w_st + s * GM_PACKED_BYTES), &tmap_w, tile_m * (GM_TILE_M / 2), kb * GM_BK, ld_full + 8 * s);
+                tma_load_2d(smem_u32(x_st + s * x_bytes), &tmap_x, kb * GM_BK, tile_n * p.n_tile, ld_full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer -------------------------------------------------------------
+        // instruction descriptor: D = f32, A = B = f16, A MN-major (bit 15), B K-major, N >> 3, M >> 4
+        const uint32_t idesc = (1u << 4) | (1u << 15) | ((uint32_t)(p.n_tile >> 3) << 17) | ((uint32_t)(GM_TILE_M >> 4) << 24);
+        for (int kb = 0; kb < n_kb; ++kb) {
+            const int s = kb % GM_LD_STAGES, t = kb % GM_A_STAGES;
+            bool ok = true;
+            if (*s_dead == 0) {
+                ok = mbar_wait(ld_full + 8 * s, (kb / GM_LD_STAGES) & 1) && mbar_wait(a_full + 8 * t, (kb / GM_A_STAGES) & 1);
+                if (!ok && lane == 0) {
+                    atomicCAS(p.err, 0, 0x30002);
+                    *s_dead = 1;
+                }
+            }
+            __syncwarp();
+            if (*s_dead != 0) break;
+            tc_fence_after();
+            if (elect_one()) {
+                const uint32_t a_addr = smem_u32(a_st + t * GM_A_BYTES), b_addr = smem_u32(x_st + s * x_bytes);
+#pragma unroll
+                for (int ks = 0; ks < GM_BK / 16; ++ks) {
+                    // A (MN-major): 64-output blocks 8 KB apart (LBO), 8-deep K blocks 1 KB apart (SBO); K=16 = 2 blocks
+                    const uint64_t adesc = make_smem_desc(a_addr + ks * p.a_kstep, p.a_lbo, p.a_sbo);
+                    // B (K-major): 8-row groups 1 KB apart (SBO); K=16 = 32 bytes inside the swizzled row
+                    const uint64_t bdesc = make_smem_desc(b_addr + ks * 32, 16, 1024);
+                    umma_f16(tmem_base, adesc, bdesc, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(a_empty + 8 * t);    // A stage free once these MMAs have read it
+                umma_commit(ld_empty + 8 * s);   // X stage likewise
+                if (kb == n_kb - 1) umma_commit(acc_full);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---------------- unpack warps (2..5), then epilogue ------------------------------------
+        const int ut = tid - 64;                  // 0..127
+        const int c4 = ut & 3, krow = ut >> 2;    // 16-byte chunk (32 outputs) of a row; row 0..31 (+32)
+        const int ib = tile_m;                    // the tile is exactly one block of 128 outputs
+        const int ibk = ib % p.Kb;
+        DqConst ku = {0u, 0u, 0u};
+        if (p.uniform) {
+            const int g = ibk % p.n_alloc;
+            ku = p.exact ? make_const<true>(p.zp[g], p.scale[g]) : make_const<false>(p.zp[g], p.scale[g]);
+        }
+        bool dead = false;
+        for (int kb = 0; kb < n_kb && !dead; ++kb) {
+            const int s = kb % GM_LD_STAGES, t = kb % GM_A_STAGES;
+            if (!mbar_wait(ld_full + 8 * s, (kb / GM_LD_STAGES) & 1) ||
+                (kb >= GM_A_STAGES && !mbar_wait(a_empty + 8 * t, ((kb / GM_A_STAGES) - 1) & 1))) {
+                if (lane == 0) atomicCAS(p.err, 0, 0x30003);
+                *s_dead = 1;
+                dead = true;
+                break;
+            }
+            const uint8_t* wsrc = w_st + s * GM_PACKED_BYTES;
+            uint8_t* adst = a_st + t * GM_A_BYTES + (c4 >> 1) * 8192;
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                const int k = krow + pass * 32;
+                const uint4 raw = *reinterpret_cast<const uint4*>(wsrc + k * 64 + c4 * 16);
+                DqConst kc = ku;
+                if (!p.uniform) {
+                    const long long j = (long long)kb * GM_BK + k;
+                    int g = ibk + (int)((j * p.Mb) % p.Kb);
+                    g -= g >= p.Kb ? p.Kb : 0;
+                    g %= p.n_alloc;
+                    kc = p.exact ? make_const<true>(p.zp[g], p.scale[g]) : make_const<false>(p.zp[g], p.scale[g]);
+                }
+                const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+                uint8_t* rowp = adst + (k >> 3) * 1024 + (k & 7) * 128;
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) {
+                    uint32_t lo0, hi0, lo1, hi1;
+                    if (p.exact) {
+                        dq_pair<true>(w4[wd], kc, lo0, hi0);
+                        dq_pair<true>(w4[wd] >> 8, kc, lo1, hi1);
+                    } else {
+                        dq_pair<false>(w4[wd], kc, lo0, hi0);
+                        dq_pair<false>(w4[wd] >> 8, kc, lo1, hi1);
+                    }
+                    const int chunk = 4 * (c4 & 1) + wd;   // 8 outputs, stored in unpack order (0,4,1,5,2,6,3,7)
+                    *reinterpret_cast<uint4*>(rowp + ((chunk ^ (k & 7)) << 4)) = make_uint4(lo0, hi0, lo1, hi1);
+                }
+            }
+            // generic-proxy writes of A must be visible to the tensor core (async proxy) before the arrive
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(a_full + 8 * t);
+                mbar_arrive(ld_empty + 8 * s);
+            }
+        }
+        // ---------------- epilogue: accumulators -> fp16 Y ----------------------------------------
+        if (!dead && *s_dead == 0 && !mbar_wait(acc_full, 0)) {
+            if (lane == 0) atomicCAS(p.err, 0, 0x30004);
+            *s_dead = 1;
+            dead = true;
+        }
+        if (!dead && *s_dead == 0) {
+            tc_fence_after();
+            const int q = warp & 3;                           // TMEM lanes 32q..32q+31 belong to this warp
+            const int m = 32 * q + lane;                      // row of A = TMEM lane
+            const int pos = m & 7;                            // position inside the 8-group, in unpack order
+            const int nib = (pos >> 1) + ((pos & 1) << 2);    // 0,4,1,5,2,6,3,7
+            const int i = tile_m * GM_TILE_M + (m & ~7) + nib;
+            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int r = tile_n * p.n_tile + c0 + e;
+                    if (r < p.rows) p.y[(size_t)r * p.M + i] = __float2half_rn(__uint_as_float(v[e]));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                     uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(f);
+    });
+    if (!fn) {
+        set_last_error("cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+        return QW3_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return QW3_ERR_CUDA;
+    }
+    return QW3_OK;
+}
+
+}  // namespace qw3
+
+using namespace qw3;
+
+extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d_y, qw3_ws_t ws, void* stream) {
+    QW3_REQUIRE(w && d_x && d_y && ws, "qw3_gemm_w4a16: null argument");
+    QW3_REQUIRE(rows >= 1 && rows <= (1 << 20), "qw3_gemm_w4a16: rows out of range");
+    QW3_REQUIRE((reinterpret_cast<uintptr_t>(d_x) & 15) == 0, "qw3_gemm_w4a16: X must be 16-byte aligned");
+    const W4Desc* d = w4_desc(w);
+    GemmParams p = {};
+    p.scale = d->scale; p.zp = d->zp; p.n_alloc = (int)d->n_alloc;
+    p.M = (int)d->M; p.K = (int)d->K; p.Mb = p.M / 128; p.Kb = p.K / 128;
+    p.uniform = d->uniform; p.exact = d->zp_integral;
+    p.rows = (int)rows;
+    p.n_tile = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+    p.tmem_cols = p.n_tile < 32 ? 32 : p.n_tile;
+    p.y = static_cast<__half*>(d_y);
+    p.err = ws_struct(ws)->err;
+    p.a_lbo = 8192; p.a_sbo = 1024; p.a_kstep = 2048;
+    if (const char* e = std::getenv("QW3_GEMM_A_LBO")) p.a_lbo = std::atoi(e);
+    if (const char* e = std::getenv("QW3_GEMM_A_SBO")) p.a_sbo = std::atoi(e);
+    CUtensorMap tmap_w, tmap_x;
+    int rc = encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->packed, (uint64_t)d->M / 2, (uint64_t)d->K, (uint64_t)d->M / 2,
+                       GM_TILE_M / 2, GM_BK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != QW3_OK) return rc;
+    rc = encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d_x, (uint64_t)d->K, (uint64_t)rows, (uint64_t)d->K * 2, GM_BK,
+                   (uint32_t)p.n_tile, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != QW3_OK) return rc;
+    const size_t smem = (size_t)GM_A_STAGES * GM_A_BYTES + (size_t)GM_LD_STAGES * (p.n_tile * 128 + GM_PACKED_BYTES) + 256;
+    static std::once_flag attr_once[16];
+    int dev = 0;
+    QW3_CUDA(cudaGetDevice(&dev));
+    if (dev < 16)
+        std::call_once(attr_once[dev], [] {
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        });
+    dim3 grid((unsigned)(d->M / GM_TILE_M), (unsigned)((rows + p.n_tile - 1) / p.n_tile));
+    gemm_w4a16_tc_kernel<<<grid, GM_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmap_w, tmap_x, p);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
