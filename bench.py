@@ -187,6 +187,54 @@ def roofline_gemv(pkg, torch, M, K, n_mats, reps):
     return us, n, us_pdl
 
 
+def gemm_sweep(pkg, torch, shapes, rows_list, reps=10):
+    """Batched-row sweep of the tcgen05 W4A16 contraction: one CUDA graph of `reps` launches per
+    configuration, CUDA events on the launching stream.  Rows <= 64 are HBM-bound, above that the
+    contraction is tensor-bound; each line carries both fractions against the measured peaks."""
+    import importlib
+    ops = importlib.import_module("qw3awq_b200.ops")
+    dev = torch.device("cuda:0")
+    peaks, peak_kind = measured_peaks()
+    g = torch.Generator(device=dev)
+    g.manual_seed(SEED)
+    out = []
+    for (M, K) in shapes:
+        packed = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device=dev, generator=g)
+        scale = (torch.randn(M // 128, device=dev, generator=g).abs() * 0.02).half()
+        zp = torch.randint(6, 10, (M // 128,), device=dev, generator=g).half()
+        w = ops.W4Linear(packed, scale, zp, M, K)
+        for R in rows_list:
+            x = torch.randn(R, K, device=dev, generator=g).half()
+            y = torch.zeros(R, M, dtype=torch.float16, device=dev)
+            ws = ops.Workspace()
+            ops.gemm_w4a16(w, ws, x, y)
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(reps):
+                        ops.gemm_w4a16(w, ws, x, y)
+                graph.replay()
+                side.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(side)
+                graph.replay()
+                graph.replay()
+                e1.record(side)
+                side.synchronize()
+                ws.check()
+            us = e0.elapsed_time(e1) * 1e3 / (2 * reps)
+            flops = 2.0 * R * M * K
+            nbytes = M * K // 2 + 2 * R * K + 2 * R * M
+            tf, gbs = flops / us / 1e6, nbytes / us / 1e3
+            out.append({"shape": [M, K], "rows": R, "us": us, "TFLOP/s": tf, "GB/s": gbs,
+                        "bound": "hbm" if R <= 64 else "tensor",
+                        "frac_tensor": tf / peaks["bf16_tflops"], "frac_hbm": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind})
+        w.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -200,6 +248,9 @@ def main():
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)
     ap.add_argument("--roofline-shape", default="12288x4096")
+    ap.add_argument("--only-gemm", action="store_true", help="batched-row sweep of the tensor-core W4A16 contraction")
+    ap.add_argument("--gemm-shapes", default="12288x4096,4096x4096,4096x12288,151936x4096")
+    ap.add_argument("--gemm-rows", default="16,64,256,2048")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -222,6 +273,11 @@ def main():
         us, n, us_pdl = roofline_gemv(pkg, torch, M, K, args.roofline_mats, args.roofline_reps)
         print(json.dumps({"kernel": "gemv_w4a16_kernel", "shape": [M, K], "avg_launch_us": us, "avg_launch_us_pdl": us_pdl,
                           "launches": n, "GBps": gemv_bytes(M, K) / us / 1e3}))
+        return
+    if args.only_gemm:
+        shapes = [tuple(int(v) for v in t.split("x")) for t in args.gemm_shapes.split(",")]
+        for line in gemm_sweep(pkg, torch, shapes, [int(v) for v in args.gemm_rows.split(",")]):
+            print(json.dumps(line))
         return
     orc = load_oracle()   # weight generator + CPU baseline leg only
 

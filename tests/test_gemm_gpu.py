@@ -71,6 +71,8 @@ def test_gemm_sweep_rows_equal_gemv(ops, orc, cuda, M, K, R):
     y = torch.zeros(M, dtype=torch.float16, device=cuda)
     for r in rows:
         ops.gemv_w4a16(w, ws, ops.gemv_args(_to_dev(X[r], cuda), y=y))
-        d = _ulp_diff(got[r], y.cpu().numpy())
-        assert (d > 1).mean() < 1e-3 and (d > 0).mean() < 0.05
+        yv = y.cpu().numpy()
+        d = _ulp_diff(got[r], yv)
+        near = np.abs(got[r].astype(np.float32) - yv.astype(np.float32)) <= 1e-4 * np.abs(yv.astype(np.float32)).mean()
+        assert ((d <= 1) | near).all() and (d > 0).mean() < 0.05
     ws.check()
