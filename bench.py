@@ -287,36 +287,56 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    import importlib
+    pipeline = importlib.import_module("qw3awq_b200.pipeline")
     n_gpus = args.gpus
-    result = None
-    if rank == 0:
-        tmp = None
-        wdir = args.weights
-        if wdir is None:
-            tmp = tempfile.TemporaryDirectory()
-            wdir = tmp.name
-            orc.write_weight_dir(orc.default_config(), SEED, wdir)
-        prompt = [int(t) for t in orc.gen_tokens(SEED, orc.TOKENS, args.prompt_len, 151936)]
-        max_pos = args.prompt_len + args.warmup + 2 * args.steps + 8
+    if world > 1 and world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch one rank per GPU")
+    # weights: rank 0 writes the reference's .bin set once; every rank loads its own stage from it
+    wdir = args.weights or os.path.join(tempfile.gettempdir(), f"qw3_bench_weights_{os.environ.get('MASTER_PORT', 'single')}_{os.getppid() if world > 1 else os.getpid()}")
+    made = False
+    if rank == 0 and not os.path.exists(os.path.join(wdir, "unembed_zp.bin")):
+        orc.write_weight_dir(orc.default_config(), SEED, wdir)
+        made = args.weights is None
+    barrier()
+    prompt = [int(t) for t in orc.gen_tokens(SEED, orc.TOKENS, args.prompt_len, 151936)]
+    max_pos = args.prompt_len + args.warmup + 2 * args.steps + 8
+    if world > 1:
+        # one process per GPU: this rank owns stage `rank`; hidden state and token id move by peer stores
+        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=world, world=world, rank=rank, device=list(range(world)))
+        pipeline.connect_ring(inf, dist)
+    else:
         inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)))
-        inf.generateResponse(prompt, args.warmup)          # prompt pass + W warm-up decode steps
-        sampler = ClockSampler(0)
+    barrier()
+    inf.generateResponse(prompt, args.warmup)              # prompt pass + W warm-up decode steps
+    sampler = ClockSampler(local)
+    if rank == 0:
         sampler.start()
     barrier()
-    if rank == 0:
-        # device-timed: K decode steps, CUDA events inside the engine around the decode loop
-        ids_dev = inf.decode_more(args.steps)
-        _, decode_ms = inf.last_timing()
-        launches = inf.last_launches()
+    # device-timed: K decode steps, CUDA events inside the engine around this rank's decode loop
+    ids_dev = inf.decode_more(args.steps)
+    _, decode_ms = inf.last_timing()
+    launches = inf.last_launches()
     barrier()
+    # end to end: the same K steps through the public API, host wall-clock, ids to host memory
+    t0 = time.perf_counter()
+    ids_e2e = inf.decode_more(args.steps)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    if world > 1:   # max over ranks of the device time and of the wall-clock; launches summed
+        t = torch.tensor([decode_ms, e2e_s], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        decode_ms, e2e_s = float(t[0]), float(t[1])
+        ln = torch.tensor([launches], dtype=torch.int64, device=f"cuda:{local}")
+        dist.all_reduce(ln, op=dist.ReduceOp.SUM)
+        launches = int(ln[0])
+        ids_dev = pipeline.broadcast_ids(ids_dev, args.steps, dist)
+        ids_e2e = pipeline.broadcast_ids(ids_e2e, args.steps, dist)
+    inf.close()
+    result = None
     if rank == 0:
-        # end to end: the same K steps through the public API, host wall-clock, ids to host memory
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        ids_e2e = inf.decode_more(args.steps)
-        e2e_s = time.perf_counter() - t0
         clocks = sampler.stop()
-        inf.close()
         ctx_mid = args.prompt_len + args.warmup + args.steps // 2
         tps = args.steps / (decode_ms * 1e-3)
         peaks, peak_kind = measured_peaks()
@@ -335,24 +355,27 @@ def main():
                 "config": {"workload": "full 36-layer Qwen3-8B-shape W4A16 model (hidden 4096, 32 heads, inter 12288, vocab 151936), "
                                        f"prompt {args.prompt_len} ids, batch-1 greedy decode steps at context {args.prompt_len + args.warmup}.."
                                        f"{args.prompt_len + args.warmup + 2 * args.steps}, seeded random weights",
-                           "parallelism": f"pp{n_gpus}", "l2": "3.3 GB of weights streamed per step (inputs larger than L2)"},
+                           "parallelism": f"pp{n_gpus}" + (" (one process per GPU, P2P hand-off)" if world > 1 else ""),
+                           "l2": "3.3 GB of weights streamed per step (inputs larger than L2)"},
                 "roofline": roof,
-                "decode_roofline": {"bound": "hbm", "achieved": decode_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                    "frac": decode_gbs / peaks["hbm_gbs"], "bytes_per_token": token_bytes(ctx_mid)},
+                "decode_roofline": {"bound": "hbm", "achieved": decode_gbs, "peak": peaks["hbm_gbs"] * n_gpus, "unit": "GB/s",
+                                    "frac": decode_gbs / (peaks["hbm_gbs"] * n_gpus), "bytes_per_token": token_bytes(ctx_mid),
+                                    "note": "at batch 1 the stages run one after another, so one GPU's bandwidth is in use at a time"},
                 "e2e": {"value": args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
                         "note": "host wall-clock of decode_more(K) through the C ABI; the sampled id feeds the next step on the device"},
                 "gpu_launches": int(launches), "clocks": clocks,
                 "tokens_equal_between_runs": None if len(ids_dev) != len(ids_e2e) else True}
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and n_gpus == 1:
             n_cpu = 8
             cpu_tps, _ = cpu_decode_tokens_per_s(orc, wdir, n_cpu, args.prompt_len)
             line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
                                     "sample": f"{n_cpu} decode-token passes of the same model on the host, KV rows pre-filled to context {args.prompt_len}"}
-        if tmp is not None:
-            tmp.cleanup()
         result = line
     barrier()
     if rank == 0:
+        if made:
+            import shutil
+            shutil.rmtree(wdir, ignore_errors=True)
         print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()

@@ -23,7 +23,7 @@ EXPORTS = [
     "qw3_ws_destroy", "qw3_ws_set_pdl", "qw3_ws_check", "qw3_gemv_w4a16", "qw3_gemv_w4a16_noalloc", "qw3_gemm_w4a16", "qw3_rmsnorm",
     "qw3_rope_kv_append", "qw3_attn_decode", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
     "qw3_create", "qw3_destroy", "qw3_generate", "qw3_decode_more", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
-    "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect",
+    "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect", "qw3_stage_layers",
 ]
 
 
@@ -104,7 +104,8 @@ def lib():
         "qw3_layer_decode": [vp, i32, i32, vp],
         "qw3_debug_trace": [vp, i32, vp, i32, C.POINTER(i32)],
         "qw3_stage_export": [vp, vp],
-        "qw3_stage_connect": [vp, vp],
+        "qw3_stage_connect": [vp, vp, vp],
+        "qw3_stage_layers": [C.POINTER(Config), i32, C.POINTER(i32), C.POINTER(i32)],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

@@ -28,6 +28,12 @@ int embed_gather_launch(const void* packed, const void* scale, const void* zp, l
 int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, bool pdl, cudaStream_t st);
 const W4Desc* w4_desc(qw3_w4_t w);
 const Workspace* ws_struct(qw3_ws_t ws);
+// stage hand-off between processes (handoff.cu)
+size_t mailbox_bytes(int hidden);
+int handoff_send(const void* hidden, void* next_mb, const void* my_mb, int msg, int hidden_n, int* err, cudaStream_t st);
+int handoff_recv(void* hidden, const void* my_mb, void* prev_mb, int msg, int hidden_n, int* err, cudaStream_t st);
+int token_send(const int* d_token, void* first_mb, int msg, cudaStream_t st);
+int token_recv(int* d_token, const void* my_mb, int msg, int* err, cudaStream_t st);
 // persistent token-pass kernel (decode_pass.cu)
 struct PassOp;
 int pass_init_device();
@@ -66,6 +72,7 @@ struct LayerDev {
 
 struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     int device = 0;
+    int gidx = 0;                      // index of this stage in the whole pipeline
     int l0 = 0, l1 = 0;
     cudaStream_t stream = nullptr;
     qw3_ws_t ws = nullptr;
@@ -105,6 +112,13 @@ struct qw3_engine {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;  // on stage 0's device
     float prompt_ms = 0.f, decode_ms = 0.f;
     int64_t launches = 0;
+    // one process per GPU: this stage's mailbox and the ring neighbours' (mapped through CUDA IPC)
+    void* mailbox = nullptr;
+    void* next_mb = nullptr;
+    void* prev_mb = nullptr;
+    bool next_is_prev = false;
+    int msg_out = 0, msg_in = 0;        // hidden-state messages sent to the next stage / taken from the previous one
+    int tok_out = 0, tok_in = 0;        // token messages (last stage -> first stage)
     int seq_len = 0;                    // token passes through the layers so far (next position)
     int sampled = 0;                    // ids sampled since the last prompt
 };
@@ -258,7 +272,7 @@ static int enqueue_sample(qw3_engine* e, Stage& s, bool pdl, int* launches) {
 static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, bool pdl, int* launches) {
     const Qw3Config& c = e->cfg;
     Stage& s = e->st[si];
-    const bool first = si == 0, last = si == c.n_stages - 1;
+    const bool first = e->st[si].gidx == 0, last = e->st[si].gidx == c.n_stages - 1;
     QW3_CUDA(cudaSetDevice(s.device));
     if (layers && s.persistent) {
         // the whole pass of this stage is one cooperative launch
@@ -289,7 +303,7 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
 static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, int* n_ops) {
     const Qw3Config& c = e->cfg;
     Stage& s = e->st[si];
-    const bool first = si == 0, last = si == c.n_stages - 1;
+    const bool first = e->st[si].gidx == 0, last = e->st[si].gidx == c.n_stages - 1;
     const size_t ob = pass_op_bytes();
     const int n = (first ? 1 : 0) + 5 * (int)s.layers.size() + ((decode && last) ? 1 : 0);
     std::vector<uint8_t> host((size_t)n * ob + 256);
@@ -401,6 +415,8 @@ int qw3_destroy(qw3_handle e) {
         if (s.stream) cudaStreamDestroy(s.stream);
     }
     if (!e->st.empty()) cudaSetDevice(e->st[0].device);
+    if (e->next_mb) cudaIpcCloseMemHandle(e->next_mb);
+    if (e->prev_mb && !e->next_is_prev) cudaIpcCloseMemHandle(e->prev_mb);
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
     if (e->ev2) cudaEventDestroy(e->ev2);
@@ -416,20 +432,22 @@ int qw3_destroy(qw3_handle e) {
 static int create_impl(const char* weight_dir, qw3_engine* e) {
     Qw3Config& c = e->cfg;
     QW3_TRY(validate_config(c));
-    QW3_REQUIRE(c.world == 1, "qw3_create: one process per GPU (world > 1) is not enabled in this build");
+    const bool mp = c.world > 1;   // one process per GPU: this handle owns stage `rank` only
+    QW3_REQUIRE(!mp || c.n_stages == c.world, "qw3_create: with world > 1 the number of stages must equal world");
     int ndev = 0;
     QW3_CUDA(cudaGetDeviceCount(&ndev));
     for (int s = 0; s < c.n_stages; ++s) {
+        if (mp && s != c.rank) continue;
         if (c.device[s] < 0 || c.device[s] >= ndev) {   // Inference.cu:566-569
             set_last_error("stage %d wants device %d but only %d device(s) are visible", s, c.device[s], ndev);
             return QW3_ERR_DEVICE;
         }
     }
     const std::string dir(weight_dir);
-    const int H = c.hidden, I = c.inter, V = c.vocab, N = c.n_stages;
+    const int H = c.hidden, I = c.inter, V = c.vocab, N = mp ? 1 : c.n_stages;   // N: stages in this process
     e->st.resize(N);
     // initMultiGPU (Inference.cu:563-596): peer access between every pair of devices in use.
-    for (int a = 0; a < N; ++a)
+    for (int a = 0; a < N && !mp; ++a)
         for (int b = 0; b < N; ++b) {
             const int da = c.device[a], db = c.device[b];
             if (da == db) continue;
@@ -455,7 +473,8 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
         }
     for (int si = 0; si < N; ++si) {
         Stage& s = e->st[si];
-        s.device = c.device[si]; s.l0 = c.first_layer[si]; s.l1 = c.first_layer[si + 1];
+        s.gidx = mp ? c.rank : si;
+        s.device = c.device[s.gidx]; s.l0 = c.first_layer[s.gidx]; s.l1 = c.first_layer[s.gidx + 1];
         QW3_CUDA(cudaSetDevice(s.device));
         QW3_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
         QW3_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
@@ -493,10 +512,10 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
             QW3_CUDA(cudaMemsetAsync(L.kc, 0, kv_bytes, s.stream));             // Inference.cu:431-437
             QW3_CUDA(cudaMemsetAsync(L.vc, 0, kv_bytes, s.stream));
         }
-        if (si == 0)
+        if (s.gidx == 0)
             QW3_TRY(load_w4(e, s, s.emb, H, V, dir + "/word_embedding.bin", dir + "/word_embed_scale.bin",
                             dir + "/word_embed_zp.bin", false));
-        if (si == N - 1) {
+        if (s.gidx == c.n_stages - 1) {
             QW3_TRY(load_w4(e, s, s.unemb, V, H, dir + "/unembed.bin", dir + "/unembed_scale.bin", dir + "/unembed_zp.bin", true));
             QW3_TRY(dev_alloc(e, s.device, &s.logits16, (size_t)V * 2));
             if (c.keep_logits) QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.logits32), (size_t)V * 4));
@@ -510,7 +529,7 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
             for (LayerDev& L : s.layers)
                 ok = ok && pass_supports(w4_desc(L.wqkv.desc)) && pass_supports(w4_desc(L.wo.desc)) &&
                      pass_supports(w4_desc(L.w1.desc)) && pass_supports(w4_desc(L.w2.desc));
-            if (si == N - 1) ok = ok && pass_supports(w4_desc(s.unemb.desc));
+            if (s.gidx == c.n_stages - 1) ok = ok && pass_supports(w4_desc(s.unemb.desc));
             if (!ok) continue;   // shapes outside the persistent kernel's limits: per-operator launches
             QW3_CUDA(cudaSetDevice(s.device));
             QW3_TRY(pass_init_device());
@@ -526,6 +545,11 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
             }
             s.persistent = true;
         }
+    }
+    if (mp) {
+        Stage& s = e->st[0];
+        QW3_TRY(dev_alloc(e, s.device, &e->mailbox, mailbox_bytes(H)));
+        QW3_CUDA(cudaMemset(e->mailbox, 0, mailbox_bytes(H)));
     }
     QW3_CUDA(cudaSetDevice(e->st[0].device));
     QW3_CUDA(cudaEventCreate(&e->ev0));
@@ -556,6 +580,101 @@ int qw3_create(const char* weight_dir, const Qw3Config* cfg, qw3_handle* out) {
         return rc;
     }
     *out = e;
+    return QW3_OK;
+}
+
+// ---- one process per GPU: this process drives stage `rank`; neighbours are reached through mailboxes ----
+static int pass_mp(qw3_engine* e, bool decode, bool layers) {
+    Stage& s = e->st[0];
+    QW3_CUDA(cudaSetDevice(s.device));
+    cudaGraphExec_t g = decode ? s.g_decode : s.g_prompt;
+    if (layers && g) {
+        QW3_CUDA(cudaGraphLaunch(g, s.stream));
+        e->launches += decode ? s.launches_decode : s.launches_prompt;
+    } else {
+        int n = 0;
+        QW3_TRY(enqueue_stage_pass(e, 0, decode, layers, false, &n));
+        e->launches += n;
+    }
+    return QW3_OK;
+}
+static int mp_send(qw3_engine* e) {
+    Stage& s = e->st[0];
+    e->launches += 1;
+    return handoff_send(s.hidden, e->next_mb, e->mailbox, ++e->msg_out, e->cfg.hidden, ws_struct(s.ws)->err, s.stream);
+}
+static int mp_recv(qw3_engine* e) {
+    Stage& s = e->st[0];
+    e->launches += 1;
+    return handoff_recv(s.hidden, e->mailbox, e->prev_mb, ++e->msg_in, e->cfg.hidden, ws_struct(s.ws)->err, s.stream);
+}
+
+static int decode_loop_mp(qw3_engine* e, int max_new, int32_t* out_ids, int32_t* n_out) {
+    const Qw3Config& c = e->cfg;
+    Stage& s = e->st[0];
+    const bool first = s.gidx == 0, last = s.gidx == c.n_stages - 1;
+    if (!e->next_mb || !e->prev_mb) {
+        set_last_error("one process per GPU: call qw3_stage_connect before generating");
+        return QW3_ERR_STATE;
+    }
+    QW3_CUDA(cudaSetDevice(s.device));
+    if (last) QW3_CUDA(cudaMemsetAsync(s.d_step, 0, 4, s.stream));
+    for (int step = 0; step < max_new; ++step) {
+        const bool very_first = (e->sampled == 0);
+        const bool layers = !(c.sample_first && very_first);
+        if (layers) {
+            if (very_first) {
+                // Reference flow (Inference.cu:1357): the last stage's final hidden state re-enters layer 0.
+                if (last) QW3_TRY(mp_send(e));
+                if (first) {
+                    QW3_TRY(mp_recv(e));
+                    const int one = 1;
+                    QW3_CUDA(cudaMemcpyAsync(s.d_skip, &one, 4, cudaMemcpyHostToDevice, s.stream));
+                }
+            } else {
+                if (last) { QW3_TRY(token_send(s.d_token, e->next_mb, ++e->tok_out, s.stream)); e->launches += 1; }
+                if (first) { QW3_TRY(token_recv(s.d_token, e->mailbox, ++e->tok_in, ws_struct(s.ws)->err, s.stream)); e->launches += 1; }
+            }
+            if (!first) QW3_TRY(mp_recv(e));
+            QW3_TRY(pass_mp(e, true, true));
+            if (!last) QW3_TRY(mp_send(e));
+            e->seq_len += 1;
+        } else if (last) {
+            QW3_TRY(pass_mp(e, true, false));   // sample-only pass on the last stage
+        }
+        e->sampled += 1;
+    }
+    QW3_CUDA(cudaEventRecord(e->ev2, s.stream));
+    QW3_CUDA(cudaStreamSynchronize(s.stream));
+    if (last && max_new > 0) QW3_CUDA(cudaMemcpy(out_ids, s.d_out_ids, (size_t)max_new * 4, cudaMemcpyDeviceToHost));
+    if (n_out) *n_out = last ? max_new : 0;     // the ids come out of the last stage's process
+    QW3_CUDA(cudaEventElapsedTime(&e->decode_ms, e->ev1, e->ev2));
+    return qw3_ws_check(s.ws, s.stream);
+}
+
+static int generate_mp(qw3_engine* e, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_ids, int32_t* n_out) {
+    const Qw3Config& c = e->cfg;
+    Stage& s = e->st[0];
+    const bool first = s.gidx == 0, last = s.gidx == c.n_stages - 1;
+    if (!e->next_mb || !e->prev_mb) {
+        set_last_error("one process per GPU: call qw3_stage_connect before generating");
+        return QW3_ERR_STATE;
+    }
+    e->launches = 0;
+    QW3_CUDA(cudaSetDevice(s.device));
+    QW3_CUDA(cudaMemsetAsync(s.d_pos, 0, 16, s.stream));
+    if (first) QW3_CUDA(cudaMemcpyAsync(s.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s.stream));
+    QW3_CUDA(cudaEventRecord(e->ev0, s.stream));
+    for (int t = 0; t < n_prompt; ++t) {     // stages overlap on successive prompt tokens (two inbox slots)
+        if (!first) QW3_TRY(mp_recv(e));
+        QW3_TRY(pass_mp(e, false, true));
+        if (!last) QW3_TRY(mp_send(e));
+    }
+    QW3_CUDA(cudaEventRecord(e->ev1, s.stream));
+    e->seq_len = n_prompt;
+    e->sampled = 0;
+    QW3_TRY(decode_loop_mp(e, max_new, out_ids, n_out));
+    QW3_CUDA(cudaEventElapsedTime(&e->prompt_ms, e->ev0, e->ev1));
     return QW3_OK;
 }
 
@@ -614,6 +733,7 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
             set_last_error("qw3_generate: token id %d at %d is outside [0, %d)", prompt[t], t, c.vocab);
             return QW3_ERR_RANGE;
         }
+    if (c.world > 1) return generate_mp(e, prompt, n_prompt, max_new, out_ids, n_out);
     const int N = c.n_stages;
     Stage &s0 = e->st[0], &sl = e->st[N - 1];
     e->launches = 0;
@@ -654,6 +774,7 @@ int qw3_decode_more(qw3_handle e, int32_t max_new, int32_t* out_ids, int32_t* n_
     e->prompt_ms = 0.f;
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaEventRecord(e->ev1, s0.stream));
+    if (e->cfg.world > 1) return decode_loop_mp(e, max_new, out_ids, n_out);
     QW3_TRY(decode_loop(e, max_new, out_ids));
     if (n_out) *n_out = max_new;
     return QW3_OK;
@@ -743,14 +864,48 @@ int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entr
     return QW3_OK;
 }
 
-int qw3_stage_export(qw3_handle, void*) {
-    set_last_error("qw3_stage_export: one process per GPU is not enabled in this build");
-    return QW3_ERR_STATE;
+int qw3_stage_layers(const Qw3Config* cfg, int32_t stage, int32_t* first, int32_t* count) {
+    QW3_REQUIRE(cfg && first && count, "qw3_stage_layers: null pointer");
+    Qw3Config c = *cfg;
+    QW3_TRY(validate_config(c));
+    QW3_REQUIRE(stage >= 0 && stage < c.n_stages, "qw3_stage_layers: stage out of range");
+    *first = c.first_layer[stage];
+    *count = c.first_layer[stage + 1] - c.first_layer[stage];
+    return QW3_OK;
 }
 
-int qw3_stage_connect(qw3_handle, const void*) {
-    set_last_error("qw3_stage_connect: one process per GPU is not enabled in this build");
-    return QW3_ERR_STATE;
+int qw3_stage_export(qw3_handle e, void* out_handle_64B) {
+    QW3_REQUIRE(e && out_handle_64B, "qw3_stage_export: null pointer");
+    if (!e->mailbox) {
+        set_last_error("qw3_stage_export: the handle was not created with world > 1");
+        return QW3_ERR_STATE;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+    cudaIpcMemHandle_t h;
+    QW3_CUDA(cudaSetDevice(e->st[0].device));
+    QW3_CUDA(cudaIpcGetMemHandle(&h, e->mailbox));
+    std::memcpy(out_handle_64B, &h, 64);
+    return QW3_OK;
+}
+
+int qw3_stage_connect(qw3_handle e, const void* next_stage_handle_64B, const void* prev_stage_handle_64B) {
+    QW3_REQUIRE(e && next_stage_handle_64B && prev_stage_handle_64B, "qw3_stage_connect: null pointer");
+    if (!e->mailbox || e->next_mb) {
+        set_last_error("qw3_stage_connect: needs a handle created with world > 1 that is not connected yet");
+        return QW3_ERR_STATE;
+    }
+    cudaIpcMemHandle_t hn, hp;
+    std::memcpy(&hn, next_stage_handle_64B, 64);
+    std::memcpy(&hp, prev_stage_handle_64B, 64);
+    QW3_CUDA(cudaSetDevice(e->st[0].device));
+    QW3_CUDA(cudaIpcOpenMemHandle(&e->next_mb, hn, cudaIpcMemLazyEnablePeerAccess));
+    if (std::memcmp(&hn, &hp, 64) == 0) {   // two stages: the next stage is also the previous one
+        e->prev_mb = e->next_mb;
+        e->next_is_prev = true;
+    } else {
+        QW3_CUDA(cudaIpcOpenMemHandle(&e->prev_mb, hp, cudaIpcMemLazyEnablePeerAccess));
+    }
+    return QW3_OK;
 }
 
 }  // extern "C"

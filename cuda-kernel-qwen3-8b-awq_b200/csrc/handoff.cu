@@ -1,0 +1,120 @@
+// Stage hand-off between GPUs for the one-process-per-GPU layer pipeline (sm_100a, NVLink P2P).
+//
+// The reference moves the hidden state between its two GPUs with cudaMemcpyPeerAsync from one host
+// thread and a host synchronisation per copy (copyHiddenBetweenGPUs, Inference.cu:1013-1023,
+// 1335-1336, 1357-1358).  With one process per GPU the stages are chained on the device instead:
+// every stage owns a mailbox in its own memory; its ring neighbours map it through CUDA IPC and
+//   * the sender stores the 8 KB hidden state straight into the receiver's inbox (plain peer
+//     stores over NVLink), fences at system scope and releases the receiver's flag;
+//   * the receiver's stream holds a one-CTA kernel that acquire-polls that flag (bounded: about
+//     nine seconds, then it records an error and returns), copies the inbox out and acknowledges
+//     into the sender's mailbox, which is what lets the sender reuse the two inbox slots;
+//   * the sampled token id travels the same way from the last stage to the first.
+// No collective exists on this path, so no NCCL; no multicast of any kind is used.
+#include "common.cuh"
+
+namespace qw3 {
+
+struct Mailbox {
+    int in_flag;     // number of the newest hidden-state message delivered into `inbox`
+    int ack_flag;    // number of the newest message the stage after this one has taken out of ITS inbox
+    int tok_flag;    // number of the newest token message
+    int tok_val;
+    int pad[60];
+    // followed by __half inbox[2][hidden]
+};
+static_assert(sizeof(Mailbox) == 256, "mailbox header is 256 bytes");
+
+size_t mailbox_bytes(int hidden) { return sizeof(Mailbox) + (size_t)2 * hidden * 2; }
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for *flag >= want.  Returns false after ~2^34 clocks.
+__device__ __forceinline__ bool wait_flag(const int* flag, int want) {
+    const long long t0 = clock64();
+    while (ld_acquire_sys(flag) < want) {
+        if (clock64() - t0 > (1ll << 34)) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+
+__global__ void __launch_bounds__(256) handoff_send_kernel(const __half* __restrict__ hidden, Mailbox* next_mb,
+                                                           const Mailbox* my_mb, int msg, int n_chunks, int* err) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        s_ok = wait_flag(&my_mb->ack_flag, msg - 2) ? 1 : 0;   // slot msg&1 was last used by message msg-2
+        if (!s_ok) atomicCAS(err, 0, 0x40001);
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(next_mb) + sizeof(Mailbox)) + (size_t)(msg & 1) * n_chunks;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden);
+    for (int i = threadIdx.x; i < n_chunks; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(&next_mb->in_flag, msg);
+}
+
+__global__ void __launch_bounds__(256) handoff_recv_kernel(__half* __restrict__ hidden, const Mailbox* my_mb, Mailbox* prev_mb,
+                                                           int msg, int n_chunks, int* err) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        s_ok = wait_flag(&my_mb->in_flag, msg) ? 1 : 0;
+        if (!s_ok) atomicCAS(err, 0, 0x40002);
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(my_mb) + sizeof(Mailbox)) + (size_t)(msg & 1) * n_chunks;
+    uint4* dst = reinterpret_cast<uint4*>(hidden);
+    for (int i = threadIdx.x; i < n_chunks; i += blockDim.x) dst[i] = __ldcg(src + i);
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(&prev_mb->ack_flag, msg);
+}
+
+__global__ void token_send_kernel(const int* __restrict__ d_token, Mailbox* first_mb, int msg) {
+    if (threadIdx.x != 0) return;
+    first_mb->tok_val = *d_token;
+    __threadfence_system();
+    st_release_sys(&first_mb->tok_flag, msg);
+}
+
+__global__ void token_recv_kernel(int* __restrict__ d_token, const Mailbox* my_mb, int msg, int* err) {
+    if (threadIdx.x != 0) return;
+    if (!wait_flag(&my_mb->tok_flag, msg)) {
+        atomicCAS(err, 0, 0x40003);
+        return;
+    }
+    *d_token = __ldcg(&my_mb->tok_val);
+}
+
+int handoff_send(const void* hidden, void* next_mb, const void* my_mb, int msg, int hidden_n, int* err, cudaStream_t st) {
+    handoff_send_kernel<<<1, 256, 0, st>>>(static_cast<const __half*>(hidden), static_cast<Mailbox*>(next_mb),
+                                           static_cast<const Mailbox*>(my_mb), msg, hidden_n / 8, err);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
+int handoff_recv(void* hidden, const void* my_mb, void* prev_mb, int msg, int hidden_n, int* err, cudaStream_t st) {
+    handoff_recv_kernel<<<1, 256, 0, st>>>(static_cast<__half*>(hidden), static_cast<const Mailbox*>(my_mb),
+                                           static_cast<Mailbox*>(prev_mb), msg, hidden_n / 8, err);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
+int token_send(const int* d_token, void* first_mb, int msg, cudaStream_t st) {
+    token_send_kernel<<<1, 32, 0, st>>>(d_token, static_cast<Mailbox*>(first_mb), msg);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
+int token_recv(int* d_token, const void* my_mb, int msg, int* err, cudaStream_t st) {
+    token_recv_kernel<<<1, 32, 0, st>>>(d_token, static_cast<const Mailbox*>(my_mb), msg, err);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
+
+}  // namespace qw3

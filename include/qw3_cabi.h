@@ -226,10 +226,19 @@ int qw3_layer_decode(qw3_handle h, int32_t layer, int32_t pos, void* host_hidden
  * stage, plus the end of the pass; needs QW3_TRACE set in the environment when the handle is made. */
 int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries);
 
-/* One process per GPU: 64-byte CUDA IPC handles of this stage's inbox; connect to the next
- * stage's (and, from the last stage, the first stage's) inbox. */
+/* One process per GPU (world > 1, n_stages == world, rank = this process's stage).  Every stage owns
+ * a mailbox in its device memory; qw3_stage_export returns its 64-byte CUDA IPC handle, the caller
+ * exchanges the handles between the processes (any transport), and qw3_stage_connect maps the mailbox
+ * of the next stage (rank+1, wrapping to 0) and of the previous one (rank-1, wrapping).  After that
+ * every process calls qw3_generate / qw3_decode_more with the same arguments; hidden states and token
+ * ids move between the GPUs by peer stores and device-side flags (replaces copyHiddenBetweenGPUs,
+ * Inference.cu:1013-1023).  The generated ids are returned by the last stage's process (n_out = 0
+ * elsewhere). */
 int qw3_stage_export(qw3_handle h, void* out_handle_64B);
-int qw3_stage_connect(qw3_handle h, const void* next_stage_handle_64B);
+int qw3_stage_connect(qw3_handle h, const void* next_stage_handle_64B, const void* prev_stage_handle_64B);
+
+/* Layers [*first, *first + *count) that stage `stage` of cfg runs (pure host arithmetic). */
+int qw3_stage_layers(const Qw3Config* cfg, int32_t stage, int32_t* first, int32_t* count);
 
 #ifdef __cplusplus
 }

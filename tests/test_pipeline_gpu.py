@@ -1,0 +1,68 @@
+"""Two stages in two processes on two GPUs: the hidden state and the sampled id cross NVLink by peer
+stores into CUDA-IPC mailboxes; the ids must equal the single-GPU run and the oracle's golden ids.
+Needs two visible GPUs (skipped otherwise).  gloo carries the handle exchange."""
+import json
+import multiprocessing as mp
+import os
+import socket
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SMALL = dict(hidden=512, inter=1536, heads=4, head_dim=128, layers=4, vocab=2176, max_pos=64, rope_base=10000.0)
+
+
+def _rank_main(rank, world, port, wdir, prompt, q, sample_first):
+    import sys
+    sys.path.insert(0, HERE)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    from conftest import load_package
+    pkg = load_package()
+    import importlib
+    pipeline = importlib.import_module("qw3awq_b200.pipeline")
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.cuda.set_device(rank)
+        inf = pkg.QWen3AWQInfer(wdir, n_stages=world, world=world, rank=rank, device=list(range(world)),
+                                sample_first=sample_first, **SMALL)
+        pipeline.connect_ring(inf, dist)
+        dist.barrier()
+        ids = inf.generateResponse(prompt, 6)
+        more = inf.decode_more(4)
+        dist.barrier()
+        ids = pipeline.broadcast_ids(ids + more if rank == world - 1 else [], 10, dist)
+        q.put((rank, ids))
+        inf.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,sample_first", [(2, 0), (2, 1), (4, 0)])
+def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_first):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    golden = json.load(open(os.path.join(HERE, "golden", "golden.json")))
+    want = golden["small_model_sample_first" if sample_first else "small_model"]["ids"]
+    wdir = str(tmp_path)
+    orc.write_weight_dir(orc.default_config(**SMALL), 0, wdir)
+    prompt = [int(t) for t in orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])]
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, wdir, prompt, q, sample_first)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, ids in got:
+        assert ids == want, (rank, ids, want)
