@@ -41,6 +41,9 @@ constexpr int P_MAXK_NU = 4096;          // largest in_dim of an operator with j
 constexpr int P_MAX_GROUPS = 256;
 constexpr int P_RED_BYTES = 32768;       // cross-warp reduction (8 slots x 4 KB) / 32 attention states (16.9 KB)
 constexpr int P_OPW = 32;                // 32-bit words of a descriptor after its tensor map
+constexpr int P_DONE = 256;              // largest number of tiles / heads of an operator
+constexpr int P_TAG_OPS = 1024;          // tags: launch epoch * P_TAG_OPS + operator index
+constexpr int P_PSLOTS = WS_MAX_CTAS + P_DONE;   // partial-sum slots (CTA + tile) of an operator
 
 constexpr size_t P_OFF_RED = (size_t)P_RING * P_UNIT_BYTES;
 constexpr size_t P_OFF_XS = P_OFF_RED + P_RED_BYTES;
@@ -54,7 +57,7 @@ enum PassOpKind { PASS_EMBED = 0, PASS_GEMV = 1, PASS_ATTN = 2 };
 struct PassOpBody {          // 128 bytes, copied to shared memory per operator
     int32_t kind, uniform, exact, epilogue;
     int32_t M, K, Mb, Kb;
-    int32_t n_alloc, n_tiles, upt, done_target;
+    int32_t n_alloc, n_tiles, upt, reserved0;
     long long U;
     const __half* scale;
     const __half* zp;
@@ -78,7 +81,10 @@ static_assert(sizeof(PassOp) == 256, "descriptor must be 256 bytes");
 struct PassParams {
     const PassOp* ops;
     int n_ops;
-    int* done;                // [n_ops], zeroed before the launch
+    int* done;                // [n_ops] arrival counters (one arrival per CTA and operator), zeroed before the launch
+    unsigned long long* xchg; // [P_PSLOTS][1024] tagged partial sums of (CTA, tile) slot c + tile
+    const int* d_epoch;       // launches completed on this stage so far (incremented after each pass); this launch
+                              // writes *d_epoch + 1 into its flags, so flags never need clearing
     const int* d_pos;
     const int* d_token;       // sampled id of the previous step (decode pass)
     const int* d_skip;        // non-zero: keep the hidden state, skip the gather
@@ -90,7 +96,6 @@ struct PassParams {
     long long max_pos, vocab;
     int* d_token_out;
     float* logits_f32;
-    int skip_math;               // debug: wait for the weights but do not unpack or multiply
     unsigned long long* trace2;  // optional [grid][n_ops][8]: per-CTA event times inside each operator (debug)
     unsigned long long* trace;   // optional [n_ops + 1]: global timer when CTA 0 enters each operator
     Workspace ws;
@@ -112,6 +117,39 @@ __device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
 }
 __device__ __forceinline__ void red_add_release(int* p, int v) {
     asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Publishing is a plain release store (no read-modify-write round trip): after the CTA barrier it
+// orders every write of the CTA before the flag.
+__device__ __forceinline__ void st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Partial sums cross CTAs as (value, tag) words: the tag names the launch and the operator, value and tag
+// travel in ONE aligned 64-bit store, so a reader that sees the tag has the value.
+__device__ __forceinline__ unsigned long long pack_tagged(float v, uint32_t tag) {
+    return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+}
+__device__ __forceinline__ void st_relaxed_v2(unsigned long long* p, unsigned long long a, unsigned long long b) {
+    asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_v2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long a) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long a;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return a;
+}
+// Output pairs of a tile shared by CTAs cf..cl are dealt evenly: CTA c finalises pairs [pb, pe) of the
+// 512; thread t of it takes pair pb + t.  Returns whether thread t has a pair.
+__device__ __forceinline__ bool slice_pair(int cf, int cl, int c, int t, int& pp) {
+    const int n = cl - cf + 1, k = c - cf;
+    const int pb = (P_TI / 2) * k / n, pe = (P_TI / 2) * (k + 1) / n;
+    pp = pb + t;
+    return t < pe - pb;
 }
 
 // Share of one operator's units for CTA c: a contiguous range [ub, ub + n) of absolute units
@@ -166,6 +204,7 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
 }
 
 struct PassSmem {
+    int* s_epoch;   // value this launch writes into its flags
     uint8_t* ring;
     float* red;
     __half* xs;
@@ -175,10 +214,31 @@ struct PassSmem {
     double* dsum;
     float* s_argv;
     int* s_argi;
-    int* s_flag;
     int* s_dead;
     uint32_t* s_op;           // [2][P_OPW]
 };
+
+// The operator before `o` must be complete before its outputs are read: every CTA arrives once per
+// operator on its counter; thread 0 acquire-polls it (bounded), the CTA barrier hands the result on.
+__device__ __forceinline__ void wait_for_previous(const PassParams& p, const PassSmem& sm, int o) {
+    if (o > 0 && threadIdx.x == 0 && *sm.s_dead == 0) {
+        const long long t0 = clock64();
+        while (ld_acquire(p.done + o - 1) < (int)gridDim.x) {
+            if (clock64() - t0 > (1ll << 31)) {
+                atomicCAS(p.ws.err, 0, 0x20000 | o);   // operator o-1 never completed
+                *sm.s_dead = 1;
+                break;
+            }
+        }
+    }
+    named_barrier(1, P_NCONS);
+    trace_event(p, o, 1);
+}
+// This CTA's part of operator o is written: one cumulative release after the CTA barrier.
+__device__ __forceinline__ void publish(const PassParams& p, int o) {
+    named_barrier(1, P_NCONS);
+    if (threadIdx.x == 0) red_add_release(&p.done[o], 1);
+}
 
 // Per-warp prefetch cursor over the units this warp will consume (global unit counter uc = warp
 // mod 16), walking through the operator list ahead of the computation.
@@ -246,8 +306,9 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
     const int t0 = u_begin / upt, r0 = u_begin - t0 * upt;
     __half* xs = sm.xs;
 
-    // ---- loads that depend on nothing computed here are issued first, so that their latencies overlap:
-    // group constants of the first tile, and what the epilogue of that tile will need
+    // ---- loads that do not depend on the previous operator are issued before waiting for it:
+    // group constants of the first tile
+    const int n_chunks = K >> 3;   // 16-byte chunks of 8 halves
     DqConst ku_first = {0u, 0u, 0u};
     if (UNIFORM) {
         int ib = t0 * (P_TI / 128) + (lane >> 2);
@@ -255,10 +316,16 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         const int g = (ib % op.Kb) % op.n_alloc;
         ku_first = make_const<EXACT>(op.zp[g], op.scale[g]);
     }
+    wait_for_previous(p, sm, o);
+    // what the epilogue of the first tile will need (written by operators that are complete now)
+    const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
     uint32_t pre_a = 0u, pre_b = 0u;   // RESIDUAL: y[i], y[i+1];  ROPE_KV: cos, sin of this thread's pair
-    {
-        const int i = t0 * P_TI + 2 * tid;
-        if (i < op.M) {
+    if (n_units > 0) {
+        int cf, cl, pp = tid;
+        tile_contributors(U, upt, op.n_tiles, t0, cf, cl);
+        const bool active = cf == cl ? true : slice_pair(cf, cl, c, tid, pp);
+        const int i = t0 * P_TI + 2 * pp;
+        if (active && i < op.M) {
             if (op.epilogue == QW3_EPI_RESIDUAL) {
                 pre_a = __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
             } else if (op.epilogue == QW3_EPI_ROPE_KV && i < 2 * p.hidden) {
@@ -269,8 +336,73 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         }
     }
 
+    // ---- epilogue of one output pair (outputs tile_e * 1024 + 2 * pp, + 1), called by all threads of the CTA
+    auto epilogue = [&](const int tile_e, const int pp, const float v0, const float v1, const bool active) {
+        const int i = tile_e * P_TI + 2 * pp;
+        const bool valid = active && i < op.M;
+        const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+        if (op.epilogue == QW3_EPI_STORE) {
+            if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
+        } else if (op.epilogue == QW3_EPI_RESIDUAL) {
+            if (valid) {
+                const uint32_t rv = tile_e == t0 ? pre_a : __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+                const __half r0h = __ushort_as_half((unsigned short)(rv & 0xffffu)), r1h = __ushort_as_half((unsigned short)(rv >> 16));
+                *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h_add(r0h, h0), h_add(r1h, h1));
+            }
+        } else if (op.epilogue == QW3_EPI_GELU) {
+            if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(gelu_h(h0), gelu_h(h1));
+        } else if (op.epilogue == QW3_EPI_ROPE_KV) {
+            if (valid) {
+                const int sec = i / p.hidden, idx = i - sec * p.hidden;
+                const int head = idx >> 7, d = idx & 127;
+                __half o0 = h0, o1 = h1;
+                if (sec < 2) {
+                    const __half cs = tile_e == t0 ? __ushort_as_half((unsigned short)pre_a) : p.cos_t[(size_t)pos * 64 + (d >> 1)];
+                    const __half sn = tile_e == t0 ? __ushort_as_half((unsigned short)pre_b) : p.sin_t[(size_t)pos * 64 + (d >> 1)];
+                    o0 = h_sub(h_mul(h0, cs), h_mul(h1, sn));
+                    o1 = h_add(h_mul(h0, sn), h_mul(h1, cs));
+                }
+                __half* dst = sec == 0 ? op.y + idx : (sec == 1 ? op.kc : op.vc) + ((size_t)head * p.max_pos + pos) * 128 + d;
+                *reinterpret_cast<__half2*>(dst) = __halves2half2(o0, o1);
+            }
+        } else {  // QW3_EPI_ARGMAX: winner of this CTA's outputs of the tile -> slot c + tile_e
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            if (valid) {
+                if (op.y) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
+                const float f0 = __half2float(h0), f1 = __half2float(h1);
+                if (p.logits_f32) *reinterpret_cast<float2*>(p.logits_f32 + i) = make_float2(f0, f1);
+                bv = f0; bi = i;
+                if (f1 > f0) { bv = f1; bi = i + 1; }
+            }
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+            named_barrier(1, P_NCONS);   // the previous use of s_argv / s_argi is over
+            if (lane == 0) { sm.s_argv[warp] = bv; sm.s_argi[warp] = bi; }
+            named_barrier(1, P_NCONS);
+            if (warp == 0) {
+                bv = lane < P_NCW ? sm.s_argv[lane] : -INFINITY;
+                bi = lane < P_NCW ? sm.s_argi[lane] : 0x7fffffff;
+#pragma unroll
+                for (int m = 8; m > 0; m >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+                }
+                if (lane == 0) {
+                    p.ws.arg_val[c + tile_e] = bv;
+                    p.ws.arg_idx[c + tile_e] = bi;
+                }
+            }
+        }
+    };
+    int n_shared = 0, sh_tile0 = 0, sh_tile1 = 0;
+
     // ---- prologue: (RMS-normalised) input vector -> shared memory -------------------------------
-    const int n_chunks = K >> 3;   // 16-byte chunks of 8 halves
     if (op.gamma != nullptr) {
         uint4 xv[3], gvv[3];
         double s = 0.0;
@@ -381,8 +513,8 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             }
             const int row0 = (r + (kk - k)) * P_UNIT_ROWS;
             const uint8_t* ubase = sm.ring + slot * P_UNIT_BYTES + lane * 16;
-#pragma unroll
-            for (int half = 0; half < (p.skip_math ? 0 : 2); ++half) {
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
                 const int jrow = row0 + half * 4;
                 const uint8_t* src = ubase + half * 4 * P_ROW_BYTES;
                 const uint4 ra = *reinterpret_cast<const uint4*>(src);
@@ -480,130 +612,104 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         // ---- cross-CTA fix-up --------------------------------------------------------------------
         int cf, cl;
         tile_contributors(U, upt, op.n_tiles, tile, cf, cl);
-        bool finalise = true;
-        if (cf != cl) {
-            float* part = p.ws.partials + (size_t)(c + tile) * P_TI;
-            *reinterpret_cast<float2*>(part + 2 * tid) = make_float2(tot[0], tot[1]);
-            named_barrier(1, P_NCONS);
-            if (tid == 0) {
-                const int old = atom_add_acq_rel(&p.ws.counters[tile], 1);
-                const int last = (old == cl - cf);
-                if (last) p.ws.counters[tile] = 0;
-                *sm.s_flag = last;
-            }
-            named_barrier(1, P_NCONS);
-            finalise = *sm.s_flag != 0;
-            named_barrier(1, P_NCONS);
-            trace_event(p, o, 5);
-            if (finalise) {
-                tot[0] = 0.0f;
-                tot[1] = 0.0f;
-                for (int cc = cf; cc <= cl; cc += 16) {   // sixteen loads in flight, summed in CTA order
-                    float2 v[16];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e)
-                        v[e] = cc + e <= cl ? __ldcg(reinterpret_cast<const float2*>(p.ws.partials + (size_t)(cc + e + tile) * P_TI + 2 * tid))
-                                            : make_float2(0.0f, 0.0f);
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        tot[0] += v[e].x;
-                        tot[1] += v[e].y;
-                    }
-                }
-            }
-        }
-        if (finalise) {
-            const int i = tile * P_TI + 2 * tid;
-            const bool valid = i < op.M;
-            const __half h0 = __float2half_rn(tot[0]), h1 = __float2half_rn(tot[1]);
-            if (op.epilogue == QW3_EPI_STORE) {
-                if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
-            } else if (op.epilogue == QW3_EPI_RESIDUAL) {
-                if (valid) {
-                    const uint32_t rv = tile == t0 ? pre_a : __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
-                    const __half r0h = __ushort_as_half((unsigned short)(rv & 0xffffu)), r1h = __ushort_as_half((unsigned short)(rv >> 16));
-                    *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h_add(r0h, h0), h_add(r1h, h1));
-                }
-            } else if (op.epilogue == QW3_EPI_GELU) {
-                if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(gelu_h(h0), gelu_h(h1));
-            } else if (op.epilogue == QW3_EPI_ROPE_KV) {
-                if (valid) {
-                    const int sec = i / p.hidden, idx = i - sec * p.hidden;
-                    const int head = idx >> 7, d = idx & 127;
-                    __half o0 = h0, o1 = h1;
-                    if (sec < 2) {
-                        const __half cs = tile == t0 ? __ushort_as_half((unsigned short)pre_a) : p.cos_t[(size_t)pos * 64 + (d >> 1)];
-                        const __half sn = tile == t0 ? __ushort_as_half((unsigned short)pre_b) : p.sin_t[(size_t)pos * 64 + (d >> 1)];
-                        o0 = h_sub(h_mul(h0, cs), h_mul(h1, sn));
-                        o1 = h_add(h_mul(h0, sn), h_mul(h1, cs));
-                    }
-                    __half* dst = sec == 0 ? op.y + idx : (sec == 1 ? op.kc : op.vc) + ((size_t)head * p.max_pos + pos) * 128 + d;
-                    *reinterpret_cast<__half2*>(dst) = __halves2half2(o0, o1);
-                }
-            } else {  // QW3_EPI_ARGMAX
-                float bv = -INFINITY;
-                int bi = 0x7fffffff;
-                if (valid) {
-                    if (op.y) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
-                    const float f0 = __half2float(h0), f1 = __half2float(h1);
-                    if (p.logits_f32) *reinterpret_cast<float2*>(p.logits_f32 + i) = make_float2(f0, f1);
-                    bv = f0; bi = i;
-                    if (f1 > f0) { bv = f1; bi = i + 1; }
-                }
-#pragma unroll
-                for (int m = 16; m > 0; m >>= 1) {
-                    const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-                    const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-                    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-                }
-                if (lane == 0) { sm.s_argv[warp] = bv; sm.s_argi[warp] = bi; }
-                named_barrier(1, P_NCONS);
-                if (warp == 0) {
-                    bv = lane < P_NCW ? sm.s_argv[lane] : -INFINITY;
-                    bi = lane < P_NCW ? sm.s_argi[lane] : 0x7fffffff;
-#pragma unroll
-                    for (int m = 8; m > 0; m >>= 1) {
-                        const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-                        const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-                        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-                    }
-                    int last = 0;
-                    if (lane == 0) {
-                        p.ws.arg_val[tile] = bv;
-                        p.ws.arg_idx[tile] = bi;
-                        __threadfence();
-                        const int old = atomicAdd(p.ws.tiles_done, 1);
-                        last = (old == op.n_tiles - 1);
-                        if (last) *p.ws.tiles_done = 0;
-                    }
-                    last = __shfl_sync(0xffffffffu, last, 0);
-                    if (last) {
-                        __threadfence();
-                        bv = -INFINITY; bi = 0x7fffffff;
-                        for (int t = lane; t < op.n_tiles; t += 32) {
-                            const float ov = __ldcg(p.ws.arg_val + t);
-                            const int oi = __ldcg(p.ws.arg_idx + t);
-                            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-                        }
-#pragma unroll
-                        for (int m = 16; m > 0; m >>= 1) {
-                            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-                            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-                            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-                        }
-                        if (lane == 0 && p.d_token_out) *p.d_token_out = bi;
-                    }
-                }
-            }
-            // publish the tile: one cumulative fence after the CTA barrier, then the arrival
-            trace_event(p, o, 6);
-            named_barrier(1, P_NCONS);
-            if (tid == 0) red_add_release(&p.done[o], 1);
-            trace_event(p, o, 7);
+        if (cf == cl) {
+            epilogue(tile, tid, tot[0], tot[1], true);   // the tile is this CTA's alone
+        } else {
+            // Shared tile: every contributor stores its sums as (value, tag) words and moves on; the sums are
+            // gathered after the unit loop, so that no CTA waits for another while it still owes partial sums.
+            unsigned long long* slot = p.xchg + (size_t)(c + tile) * P_TI;
+            st_relaxed_v2(slot + 2 * tid, pack_tagged(tot[0], tag), pack_tagged(tot[1], tag));
+            if (n_shared == 0) sh_tile0 = tile;
+            else sh_tile1 = tile;
+            ++n_shared;
         }
         k += seg;
         r = 0;
         ++tile;
+    }
+    // ---- shared tiles: the outputs of a tile are dealt evenly to its contributors; each sums, in CTA order,
+    // the tagged partial sums of all of them for its own outputs (a word is valid once it carries this
+    // operator's tag: value and tag travel in one 64-bit store, so no flag, fence or second round trip)
+    for (int sidx = 0; sidx < n_shared; ++sidx) {
+        const int tile_s = sidx == 0 ? sh_tile0 : sh_tile1;
+        int cf, cl, pp;
+        tile_contributors(U, upt, op.n_tiles, tile_s, cf, cl);
+        const bool active = slice_pair(cf, cl, c, tid, pp);
+        const int n = cl - cf + 1, pb = pp - tid;
+        const int cnt = (P_TI / 2) * (c - cf + 1) / n - pb, total = n * cnt;   // (contributor, pair) words to fetch
+        // all threads fetch: word idx = contributor * cnt + pair, so that every load is in flight at once
+        float2* stage = reinterpret_cast<float2*>(sm.red);
+        for (int base = 0; base < total; base += 2 * P_NCONS) {
+            const int i0 = base + tid, i1 = i0 + P_NCONS;
+            const bool h0 = i0 < total, h1 = i1 < total;
+            const int c0 = i0 / cnt, c1 = i1 / cnt;
+            const unsigned long long* s0p = p.xchg + (size_t)(cf + c0 + tile_s) * P_TI + 2 * (pb + i0 - c0 * cnt);
+            const unsigned long long* s1p = p.xchg + (size_t)(cf + c1 + tile_s) * P_TI + 2 * (pb + i1 - c1 * cnt);
+            unsigned long long a0 = 0, b0 = 0, a1 = 0, b1 = 0;
+            const long long t_begin = clock64();
+            for (;;) {
+                if (h0) ld_relaxed_v2(s0p, a0, b0);
+                if (h1) ld_relaxed_v2(s1p, a1, b1);
+                const bool ok0 = !h0 || ((uint32_t)(a0 >> 32) == tag && (uint32_t)(b0 >> 32) == tag);
+                const bool ok1 = !h1 || ((uint32_t)(a1 >> 32) == tag && (uint32_t)(b1 >> 32) == tag);
+                if ((ok0 && ok1) || *sm.s_dead != 0) break;
+                if (clock64() - t_begin > (1ll << 31)) {
+                    atomicCAS(p.ws.err, 0, 0x50000 | o);   // a contributor's partial sums never arrived
+                    *sm.s_dead = 1;
+                    break;
+                }
+            }
+            if (h0) stage[i0] = make_float2(__uint_as_float((uint32_t)a0), __uint_as_float((uint32_t)b0));
+            if (h1) stage[i1] = make_float2(__uint_as_float((uint32_t)a1), __uint_as_float((uint32_t)b1));
+        }
+        named_barrier(1, P_NCONS);
+        float s0 = 0.0f, s1 = 0.0f;
+        if (active) {
+            for (int cc = 0; cc < n; ++cc) {   // CTA order
+                const float2 v = stage[cc * cnt + tid];
+                s0 += v.x;
+                s1 += v.y;
+            }
+        }
+        trace_event(p, o, 5);
+        epilogue(tile_s, pp, s0, s1, active);
+        named_barrier(1, P_NCONS);   // stage is reused by the next shared tile
+    }
+    trace_event(p, o, 6);
+    publish(p, o);   // this CTA's outputs of the operator are written
+    trace_event(p, o, 7);
+    if (op.epilogue == QW3_EPI_ARGMAX && c == 0 && warp == 0) {
+        // whole-vocabulary winner (lowest index among equal maxima): CTA 0 waits for every CTA and reduces the
+        // winners of all (CTA, tile) slices
+        if (lane == 0 && *sm.s_dead == 0) {
+            const long long t_begin = clock64();
+            while (ld_acquire(p.done + o) < (int)gridDim.x) {
+                if (clock64() - t_begin > (1ll << 31)) {
+                    atomicCAS(p.ws.err, 0, 0x60000 | o);
+                    *sm.s_dead = 1;
+                    break;
+                }
+            }
+        }
+        __syncwarp();
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int t = lane; t < op.n_tiles; t += 32) {
+            int cf, cl;
+            tile_contributors(U, upt, op.n_tiles, t, cf, cl);
+            for (int cc = cf; cc <= cl; ++cc) {
+                const float ov = __ldcg(p.ws.arg_val + cc + t);
+                const int oi = __ldcg(p.ws.arg_idx + cc + t);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0 && p.d_token_out) *p.d_token_out = bi;
     }
     uc_base += n_units;
 }
@@ -709,42 +815,54 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
         if (tid < 128) att_merge_states(st, NG, tid, M, L, O);
         bool finalise = true;
         if (S > 1) {
-            float* mine = p.ws.att_part + ((size_t)head * WS_ATT_MAX_SPLITS + split) * WS_ATT_STRIDE;
-            if (tid < 128) mine[tid] = O;
-            if (tid == 0) {
-                mine[128] = M;
-                mine[129] = L;
-            }
-            named_barrier(1, P_NCONS);
-            if (tid == 0) {
-                const int old = atom_add_acq_rel(&p.ws.att_count[head], 1);
-                const int last = (old == S - 1);
-                if (last) p.ws.att_count[head] = 0;
-                *sm.s_flag = last;
-            }
-            named_barrier(1, P_NCONS);
-            finalise = *sm.s_flag != 0;
-            if (finalise) {
-                const float* all = p.ws.att_part + (size_t)head * WS_ATT_MAX_SPLITS * WS_ATT_STRIDE;
-                for (int t = tid; t < S * WS_ATT_STRIDE; t += P_NCONS) st[t] = __ldcg(all + t);
+            // split 0 of the head finalises; the other splits hand over their state (128 outputs, max, sum) as
+            // tagged words, which split 0 polls: no flag, fence or second round trip
+            const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
+            if (split != 0) {
+                unsigned long long* mine = p.xchg + (size_t)item * P_TI;
+                if (tid < 128) st_relaxed_u64(mine + tid, pack_tagged(O, tag));
+                if (tid == 0) {   // M and L are the same in all threads below 128
+                    st_relaxed_u64(mine + 128, pack_tagged(M, tag));
+                    st_relaxed_u64(mine + 129, pack_tagged(L, tag));
+                }
+                finalise = false;
+            } else {
+                named_barrier(1, P_NCONS);   // everybody has read st
+                if (tid < 128) st[tid] = O;  // own state becomes row 0 of the merge table
+                if (tid == 0) {
+                    st[128] = M;
+                    st[129] = L;
+                }
+                if (tid < 130) {
+                    for (int sp = 1; sp < S; ++sp) {
+                        const unsigned long long* src = p.xchg + (size_t)(item + sp) * P_TI + tid;
+                        unsigned long long w;
+                        const long long t_begin = clock64();
+                        for (;;) {
+                            w = ld_relaxed_u64(src);
+                            if ((uint32_t)(w >> 32) == tag || *sm.s_dead != 0) break;
+                            if (clock64() - t_begin > (1ll << 31)) {
+                                atomicCAS(p.ws.err, 0, 0x70000 | o);   // a split's state never arrived
+                                *sm.s_dead = 1;
+                                break;
+                            }
+                        }
+                        st[sp * WS_ATT_STRIDE + tid] = __uint_as_float((uint32_t)w);
+                    }
+                }
                 named_barrier(1, P_NCONS);
                 if (tid < 128) att_merge_states(st, S, tid, M, L, O);
             }
         }
-        if (finalise) {
-            if (tid < 128) op.y[head * 128 + tid] = __float2half_rn(O / L);
-            named_barrier(1, P_NCONS);
-            if (tid == 0) red_add_release(&p.done[o], 1);
-        }
-        named_barrier(1, P_NCONS);   // st and s_flag are reused by the next item
+        if (finalise && tid < 128) op.y[head * 128 + tid] = __float2half_rn(O / L);
+        named_barrier(1, P_NCONS);   // st is reused by the next item
     }
+    publish(p, o);
 }
 
 // Embedding gather straight from the packed [hidden][vocab] matrix (Inference.cu:1310-1315).
 __device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBody& op, const int o, const int pos) {
     const int tid = threadIdx.x, c = blockIdx.x;
-    const int nblk = (p.hidden + P_NCONS - 1) / P_NCONS;
-    if (c >= nblk) return;
     const int idx = c * P_NCONS + tid;
     const bool skip = p.d_skip != nullptr && __ldcg(p.d_skip) != 0;
     if (idx < p.hidden && !skip) {
@@ -756,8 +874,7 @@ __device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBod
         const long long g = (tok / 128) % op.n_alloc;
         op.y[idx] = dequant_one(q, op.zp[g], op.scale[g]);
     }
-    named_barrier(1, P_NCONS);
-    if (tid == 0) red_add_release(&p.done[o], 1);
+    publish(p, o);
 }
 
 __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassParams p) {
@@ -774,14 +891,15 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
     sm.dsum = reinterpret_cast<double*>(misc + 640);                 // 128
     sm.s_argv = reinterpret_cast<float*>(misc + 768);                // 64
     sm.s_argi = reinterpret_cast<int*>(misc + 832);                  // 64
-    sm.s_flag = reinterpret_cast<int*>(misc + 896);
     sm.s_dead = reinterpret_cast<int*>(misc + 900);
+    sm.s_epoch = reinterpret_cast<int*>(misc + 904);
     sm.s_op = reinterpret_cast<uint32_t*>(misc + 1024);              // 2 x 128 bytes
 
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) {
         for (int s = 0; s < P_RING; ++s) mbar_init(sm.full0 + 8 * s, 1);
         *sm.s_dead = 0;
+        *sm.s_epoch = __ldcg(p.d_epoch) + 1;
         mbar_fence_init();
     }
     __syncthreads();
@@ -796,22 +914,9 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
     const int pos = __ldcg(p.d_pos);
     if (tid < P_OPW) sm.s_op[tid] = reinterpret_cast<const uint32_t*>(&p.ops[0].b)[tid];
     int uc_base = 0;
-    int prev_target = 0;
     for (int o = 0; o < p.n_ops; ++o) {
         trace_event(p, o, 0);
-        if (o > 0 && tid == 0 && *sm.s_dead == 0) {
-            // the operator before this one must be complete: bounded acquire-poll of its counter
-            const long long t0 = clock64();
-            while (ld_acquire(p.done + o - 1) < prev_target) {
-                if (clock64() - t0 > (1ll << 31)) {
-                    atomicCAS(p.ws.err, 0, 0x20000 | o);   // operator o-1 never completed
-                    *sm.s_dead = 1;
-                    break;
-                }
-            }
-        }
-        named_barrier(1, P_NCONS);
-        trace_event(p, o, 1);
+        named_barrier(1, P_NCONS);   // the descriptor of this operator (copied during the previous one) is visible
         if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -820,7 +925,6 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
         const PassOpBody& op = *reinterpret_cast<const PassOpBody*>(sm.s_op + (o & 1) * P_OPW);
         if (o + 1 < p.n_ops && tid < P_OPW)   // next descriptor, visible after the barriers of this operator
             sm.s_op[((o + 1) & 1) * P_OPW + tid] = reinterpret_cast<const uint32_t*>(&p.ops[o + 1].b)[tid];
-        prev_target = op.done_target;
         if (op.kind == PASS_GEMV) {
             if (op.uniform) {
                 if (op.exact) gemv_phase<true, true>(p, op, o, sm, uc_base, pos, pf);
@@ -830,8 +934,10 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
                 else gemv_phase<false, false>(p, op, o, sm, uc_base, pos, pf);
             }
         } else if (op.kind == PASS_ATTN) {
+            wait_for_previous(p, sm, o);
             attn_phase(p, op, o, sm, pos);
         } else {
+            wait_for_previous(p, sm, o);
             embed_phase(p, op, o, pos);
         }
     }
@@ -861,7 +967,7 @@ int pass_init_device() {
 
 // Whether a matrix can be an operator of the persistent pass (else the per-operator path is used).
 bool pass_supports(const W4Desc* d) {
-    if (d->K > P_MAXK) return false;
+    if (d->K > P_MAXK || d->M > (long long)P_DONE * P_TI) return false;
     if (!d->uniform) {
         const long long Kb = d->K / 128, used = Kb < d->n_alloc ? Kb : d->n_alloc;
         if (d->K > P_MAXK_NU || used > P_MAX_GROUPS) return false;
@@ -880,7 +986,6 @@ void pass_fill_gemv(PassOp* op, const W4Desc* d, const void* x, const void* gamm
     b.n_alloc = (int)d->n_alloc;
     b.n_tiles = (b.M + P_TI - 1) / P_TI;
     b.upt = b.K / P_UNIT_ROWS;
-    b.done_target = b.n_tiles;
     b.U = (long long)b.n_tiles * b.upt;
     b.scale = d->scale; b.zp = d->zp;
     b.x = static_cast<const __half*>(x); b.gamma = static_cast<const __half*>(gamma);
@@ -892,7 +997,6 @@ void pass_fill_attn(PassOp* op, const void* q, void* kc, void* vc, void* ctx, in
     std::memset(op, 0, sizeof(*op));
     PassOpBody& b = op->b;
     b.kind = PASS_ATTN;
-    b.done_target = heads;
     b.x = static_cast<const __half*>(q);
     b.kc = static_cast<__half*>(kc); b.vc = static_cast<__half*>(vc);
     b.y = static_cast<__half*>(ctx);
@@ -903,7 +1007,6 @@ void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const vo
     std::memset(op, 0, sizeof(*op));
     PassOpBody& b = op->b;
     b.kind = PASS_EMBED;
-    b.done_target = (hidden + P_NCONS - 1) / P_NCONS;
     b.packed = static_cast<const uint8_t*>(packed);
     b.scale = static_cast<const __half*>(scale); b.zp = static_cast<const __half*>(zp);
     b.n_alloc = (int)n_alloc;
@@ -911,30 +1014,35 @@ void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const vo
 }
 
 size_t pass_op_bytes() { return sizeof(PassOp); }
+// Exchange buffer of tagged partial sums: one 1024-word slot per (CTA, tile) pair c + tile.
+size_t pass_xchg_bytes() { return (size_t)P_PSLOTS * P_TI * sizeof(unsigned long long); }
 
 struct PassLaunch {
     PassParams p;
 };
 
-// Enqueues one pass: clears the arrival counters, then the cooperative launch.
-int pass_launch(const void* d_ops, int n_ops, int* d_done, const int* d_pos, const int* d_token, const int* d_skip,
+// Enqueues one pass: clears the arrival counters, then one cooperative launch.  The caller increments
+// *d_epoch on the same stream afterwards.
+int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d_xchg, const int* d_epoch, const int* d_pos, const int* d_token, const int* d_skip,
                 const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
                 long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
                 unsigned long long* trace2, const Workspace* ws, cudaStream_t st) {
+    QW3_REQUIRE(n_ops <= P_TAG_OPS, "pass_launch: too many operators in one pass");
     PassParams p;
     std::memset(&p, 0, sizeof(p));
     p.ops = static_cast<const PassOp*>(d_ops);
     p.n_ops = n_ops;
     p.done = d_done;
+    p.xchg = d_xchg;
+    p.d_epoch = d_epoch;
     p.d_pos = d_pos; p.d_token = d_token; p.d_skip = d_skip; p.d_prompt = d_prompt;
     p.decode = decode;
     p.cos_t = static_cast<const __half*>(cos_t); p.sin_t = static_cast<const __half*>(sin_t);
     p.heads = heads; p.hidden = hidden; p.max_pos = max_pos; p.vocab = vocab;
     p.d_token_out = d_token_out; p.logits_f32 = logits_f32; p.trace = trace; p.trace2 = trace2;
-    p.skip_math = std::getenv("QW3_DEBUG_SKIP_MATH") != nullptr;
     p.ws = *ws;
-    QW3_CUDA(cudaMemsetAsync(d_done, 0, (size_t)n_ops * 4, st));
     int grid = ws->sm_count < WS_MAX_CTAS ? ws->sm_count : WS_MAX_CTAS;
+    QW3_CUDA(cudaMemsetAsync(d_done, 0, (size_t)n_ops * sizeof(int), st));
     void* args[] = {&p};
     QW3_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_pass_kernel), dim3(grid), dim3(P_NTHREADS), args,
                                          P_SMEM_BYTES, st));

@@ -25,7 +25,8 @@ int attn_decode_launch(const void* q, const void* kc, const void* vc, int heads,
 int embed_gather_launch(const void* packed, const void* scale, const void* zp, long long n_alloc, long long hidden,
                         long long vocab, const int* d_token, const int* d_index, const int* d_skip, int token, void* out,
                         bool pdl, cudaStream_t st);
-int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, bool pdl, cudaStream_t st);
+int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, int* d_epoch, bool pdl,
+                     cudaStream_t st);
 const W4Desc* w4_desc(qw3_w4_t w);
 const Workspace* ws_struct(qw3_ws_t ws);
 // stage hand-off between processes (handoff.cu)
@@ -44,7 +45,8 @@ void pass_fill_gemv(PassOp* op, const W4Desc* d, const void* x, const void* gamm
 void pass_fill_attn(PassOp* op, const void* q, void* kc, void* vc, void* ctx, int heads);
 void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const void* zp, long long n_alloc, void* hidden_out,
                      int hidden);
-int pass_launch(const void* d_ops, int n_ops, int* d_done, const int* d_pos, const int* d_token, const int* d_skip,
+size_t pass_xchg_bytes();
+int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d_xchg, const int* d_epoch, const int* d_pos, const int* d_token, const int* d_skip,
                 const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
                 long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
                 unsigned long long* trace2, const Workspace* ws, cudaStream_t st);
@@ -92,7 +94,9 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     void* ops_prompt = nullptr;
     void* ops_decode = nullptr;
     int n_ops_prompt = 0, n_ops_decode = 0;
-    int* d_done = nullptr;
+    int* d_done = nullptr;    // persistent pass: per-operator arrival counters + the launch epoch word behind them
+    int* d_epoch = nullptr;
+    unsigned long long* d_xchg = nullptr;   // tagged partial sums exchanged between CTAs
     unsigned long long* d_trace = nullptr;   // per-operator entry times of the last pass (debug)
     unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
     bool persistent = false;
@@ -276,7 +280,7 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
     QW3_CUDA(cudaSetDevice(s.device));
     if (layers && s.persistent) {
         // the whole pass of this stage is one cooperative launch
-        QW3_TRY(pass_launch(decode ? s.ops_decode : s.ops_prompt, decode ? s.n_ops_decode : s.n_ops_prompt, s.d_done, s.d_pos,
+        QW3_TRY(pass_launch(decode ? s.ops_decode : s.ops_prompt, decode ? s.n_ops_decode : s.n_ops_prompt, s.d_done, s.d_xchg, s.d_epoch, s.d_pos,
                             s.d_token, first ? s.d_skip : nullptr, s.d_prompt, decode ? 1 : 0, s.cos_t, s.sin_t, c.heads,
                             c.hidden, c.max_pos, c.vocab, s.d_token, s.logits32, s.d_trace, s.d_trace2, ws_struct(s.ws), s.stream));
         *launches += 1;
@@ -294,7 +298,8 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
     }
     if (decode && last && !(layers && s.persistent)) QW3_TRY(enqueue_sample(e, s, pdl, launches));
     QW3_TRY(step_tail_launch(layers ? s.d_pos : nullptr, (decode && last) ? s.d_step : nullptr, s.d_token,
-                             (decode && last) ? s.d_out_ids : nullptr, first ? s.d_skip : nullptr, pdl, s.stream));
+                             (decode && last) ? s.d_out_ids : nullptr, first ? s.d_skip : nullptr,
+                             (layers && s.persistent) ? s.d_epoch : nullptr, pdl, s.stream));
     *launches += 1;
     return QW3_OK;
 }
@@ -535,7 +540,14 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
             QW3_TRY(pass_init_device());
             QW3_TRY(build_pass_program(e, si, false, &s.ops_prompt, &s.n_ops_prompt));
             QW3_TRY(build_pass_program(e, si, true, &s.ops_decode, &s.n_ops_decode));
-            QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_done), (size_t)(s.n_ops_decode + 1) * 4));
+            {
+                const int n_max = s.n_ops_decode > s.n_ops_prompt ? s.n_ops_decode : s.n_ops_prompt;
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_done), (size_t)(n_max + 64) * sizeof(int)));
+                QW3_CUDA(cudaMemset(s.d_done, 0, (size_t)(n_max + 64) * sizeof(int)));
+                s.d_epoch = s.d_done + n_max + 32;
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_xchg), pass_xchg_bytes()));
+                QW3_CUDA(cudaMemset(s.d_xchg, 0, pass_xchg_bytes()));
+            }
             if (std::getenv("QW3_TRACE")) {
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_trace), (size_t)(s.n_ops_decode + 1) * 8));
                 QW3_CUDA(cudaMemset(s.d_trace, 0, (size_t)(s.n_ops_decode + 1) * 8));

@@ -108,7 +108,7 @@ __global__ void embed_gather_kernel(const uint8_t* __restrict__ packed, const __
 }
 
 // End of one token pass: publish the sampled id, advance the device-side position and step.
-__global__ void step_tail_kernel(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip) {
+__global__ void step_tail_kernel(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, int* d_epoch) {
     pdl_launch_dependents();
     pdl_wait();
     if (threadIdx.x != 0) return;
@@ -118,6 +118,7 @@ __global__ void step_tail_kernel(int* d_pos, int* d_step, const int* d_token, in
     }
     if (d_pos) *d_pos += 1;
     if (d_skip) *d_skip = 0;
+    if (d_epoch) *d_epoch += 1;   // the persistent pass before this kernel used epoch *d_epoch + 1
 }
 
 // ---- attentionKernel (Inference.cu:182-266), intended math, split over the KV length --------------
@@ -345,8 +346,9 @@ int embed_gather_launch(const void* packed, const void* scale, const void* zp, l
     return QW3_OK;
 }
 
-int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, bool pdl, cudaStream_t st) {
-    QW3_CUDA(launch(step_tail_kernel, dim3(1), dim3(32), 0, st, pdl, d_pos, d_step, d_token, d_out_ids, d_skip));
+int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, int* d_epoch, bool pdl,
+                     cudaStream_t st) {
+    QW3_CUDA(launch(step_tail_kernel, dim3(1), dim3(32), 0, st, pdl, d_pos, d_step, d_token, d_out_ids, d_skip, d_epoch));
     return QW3_OK;
 }
 
