@@ -40,7 +40,7 @@ constexpr int P_MAXK = 12288;            // largest in_dim (activation vector ke
 constexpr int P_MAXK_NU = 4096;          // largest in_dim of an operator with j-dependent groups
 constexpr int P_MAX_GROUPS = 256;
 constexpr int P_RED_BYTES = 32768;       // cross-warp reduction (8 slots x 4 KB) / 32 attention states (16.9 KB)
-constexpr int P_OPW = 32;                // 32-bit words of a descriptor after its tensor map
+constexpr int P_OPW = 48;                // 32-bit words of a descriptor after its tensor map
 constexpr int P_DONE = 256;              // largest number of tiles / heads of an operator
 constexpr int P_TAG_OPS = 1024;          // tags: launch epoch * P_TAG_OPS + operator index
 constexpr int P_PSLOTS = WS_MAX_CTAS + P_DONE;   // partial-sum slots (CTA + tile) of an operator
@@ -54,35 +54,48 @@ constexpr size_t P_SMEM_BYTES = P_OFF_MISC + 2048;
 
 enum PassOpKind { PASS_EMBED = 0, PASS_GEMV = 1, PASS_ATTN = 2 };
 
-struct PassOpBody {          // 128 bytes, copied to shared memory per operator
+enum PassOpFlags {
+    PASS_WAIT_PREV = 1,   // inputs are plain memory written by the operator before: wait for its arrival counter
+    PASS_PUBLISH = 2,     // the operator after (or the final arg-max) waits on this operator's arrival counter
+};
+
+struct PassOpBody {          // 192 bytes, copied to shared memory per operator
     int32_t kind, uniform, exact, epilogue;
     int32_t M, K, Mb, Kb;
-    int32_t n_alloc, n_tiles, upt, reserved0;
+    int32_t n_alloc, n_tiles, upt, flags;
     long long U;
     const __half* scale;
     const __half* zp;
-    const __half* x;
+    const __half* x;         // plain input (used when xt is null)
     const __half* gamma;
     __half* y;
     __half* kc;
     __half* vc;
     const uint8_t* packed;   // embedding only
     float eps;
-    int32_t pad;
+    int32_t src;             // operator that writes xt in this launch (its tag is expected in every word)
+    // Activations between operators of one launch travel as tagged words: (two halves, tag) in one 64-bit
+    // word per output pair, polled by the consumer, so no flag, fence or arrival counter sits between them.
+    const unsigned long long* xt;   // tagged input, K/2 words (null: plain x)
+    unsigned long long* yt;         // tagged copy of the output (null: none)
+    const unsigned long long* rt;   // RESIDUAL: tagged words holding the value to add to (null: plain y)
+    int32_t rsrc;                   // operator that wrote rt in this launch
+    int32_t reserved1;
+    long long reserved[4];
 };
-static_assert(sizeof(PassOpBody) == 128, "descriptor body must be 128 bytes");
+static_assert(sizeof(PassOpBody) == 192, "descriptor body must be 192 bytes");
 
 struct alignas(128) PassOp {
     CUtensorMap tmap;
     PassOpBody b;
 };
-static_assert(sizeof(PassOp) == 256, "descriptor must be 256 bytes");
+static_assert(sizeof(PassOp) == 384, "descriptor must be 384 bytes");
 
 struct PassParams {
     const PassOp* ops;
     int n_ops;
     int* done;                // [n_ops] arrival counters (one arrival per CTA and operator), zeroed before the launch
-    unsigned long long* xchg; // [P_PSLOTS][1024] tagged partial sums of (CTA, tile) slot c + tile
+    unsigned long long* xchg; // [2][P_PSLOTS][1024] tagged partial sums: operator parity, (CTA, tile) slot c + tile
     const int* d_epoch;       // launches completed on this stage so far (incremented after each pass); this launch
                               // writes *d_epoch + 1 into its flags, so flags never need clearing
     const int* d_pos;
@@ -240,6 +253,65 @@ __device__ __forceinline__ void publish(const PassParams& p, int o) {
     if (threadIdx.x == 0) red_add_release(&p.done[o], 1);
 }
 
+// Up to three 16-byte chunks (8 halves each) of an operator's input vector for this thread: chunk indices
+// first, first + 512, first + 1024 below `limit`.  Plain input: ordinary L2 loads.  Tagged input: every
+// chunk is four (two halves, tag) words; all loads are in flight together and are repeated until every word
+// carries the producer's tag (bounded).  A cheap one-word poll per warp comes first, so that CTAs that are
+// early do not flood the L2 with full-vector polls while the producers still work.
+__device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm, const PassOpBody& op, const int o,
+                                         const uint32_t xtag, const int first, const int limit, uint4 (&xv)[3]) {
+#pragma unroll
+    for (int e = 0; e < 3; ++e) xv[e] = make_uint4(0u, 0u, 0u, 0u);
+    if (op.xt == nullptr) {
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            const int ch = first + e * P_NCONS;
+            if (ch < limit) xv[e] = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+        }
+        return;
+    }
+    const long long t_begin = clock64();
+    if ((threadIdx.x & 31) == 0 && first < limit) {
+        while ((uint32_t)(ld_relaxed_u64(op.xt + 4 * (size_t)first) >> 32) != xtag && *sm.s_dead == 0) {
+            if (clock64() - t_begin > (1ll << 31)) {
+                atomicCAS(p.ws.err, 0, 0x20000 | o);   // the input of operator o never arrived
+                *sm.s_dead = 1;
+                break;
+            }
+            __nanosleep(40);
+        }
+    }
+    __syncwarp();
+    unsigned long long w[3][4] = {{0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}};
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            const int ch = first + e * P_NCONS;
+            if (ch < limit) {
+                ld_relaxed_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
+                ld_relaxed_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            if (first + e * P_NCONS < limit) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) ok = ok && (uint32_t)(w[e][q] >> 32) == xtag;
+            }
+        }
+        if (ok || *sm.s_dead != 0) break;
+        if (clock64() - t_begin > (1ll << 31)) {
+            atomicCAS(p.ws.err, 0, 0x20000 | o);
+            *sm.s_dead = 1;
+            break;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 3; ++e)
+        if (first + e * P_NCONS < limit) xv[e] = make_uint4((uint32_t)w[e][0], (uint32_t)w[e][1], (uint32_t)w[e][2], (uint32_t)w[e][3]);
+}
+
 // Per-warp prefetch cursor over the units this warp will consume (global unit counter uc = warp
 // mod 16), walking through the operator list ahead of the computation.
 struct Prefetch {
@@ -316,8 +388,10 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         const int g = (ib % op.Kb) % op.n_alloc;
         ku_first = make_const<EXACT>(op.zp[g], op.scale[g]);
     }
-    wait_for_previous(p, sm, o);
-    // what the epilogue of the first tile will need (written by operators that are complete now)
+    if (op.flags & PASS_WAIT_PREV) wait_for_previous(p, sm, o);
+    else trace_event(p, o, 1);
+    const uint32_t xtag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.src;
+    // what the epilogue of the first tile will need (written two or more operators ago)
     const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
     uint32_t pre_a = 0u, pre_b = 0u;   // RESIDUAL: y[i], y[i+1];  ROPE_KV: cos, sin of this thread's pair
     if (n_units > 0) {
@@ -327,7 +401,13 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         const int i = t0 * P_TI + 2 * pp;
         if (active && i < op.M) {
             if (op.epilogue == QW3_EPI_RESIDUAL) {
-                pre_a = __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+                if (op.rt != nullptr) {   // value and tag; the tag is checked when the value is used
+                    const unsigned long long w = ld_relaxed_u64(op.rt + (i >> 1));
+                    pre_a = (uint32_t)w;
+                    pre_b = (uint32_t)(w >> 32);
+                } else {
+                    pre_a = __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+                }
             } else if (op.epilogue == QW3_EPI_ROPE_KV && i < 2 * p.hidden) {
                 const int d = i & 127;
                 pre_a = __half_as_ushort(p.cos_t[(size_t)pos * 64 + (d >> 1)]);
@@ -341,16 +421,41 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         const int i = tile_e * P_TI + 2 * pp;
         const bool valid = active && i < op.M;
         const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+        // plain store for readers after this launch; tagged copy for the next operator of this launch
+        auto store_pair = [&](const __half a, const __half b) {
+            const __half2 v = __halves2half2(a, b);
+            *reinterpret_cast<__half2*>(op.y + i) = v;
+            if (op.yt != nullptr)
+                st_relaxed_u64(op.yt + (i >> 1), ((unsigned long long)tag << 32) | *reinterpret_cast<const uint32_t*>(&v));
+        };
         if (op.epilogue == QW3_EPI_STORE) {
-            if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h0, h1);
+            if (valid) store_pair(h0, h1);
         } else if (op.epilogue == QW3_EPI_RESIDUAL) {
             if (valid) {
-                const uint32_t rv = tile_e == t0 ? pre_a : __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+                uint32_t rv;
+                if (op.rt != nullptr) {
+                    // the word must carry the tag of the operator that wrote the residual stream last: a CTA that
+                    // had no part in the operators in between may be here before that word is written
+                    const uint32_t rtag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.rsrc;
+                    unsigned long long w = tile_e == t0 ? (((unsigned long long)pre_b << 32) | pre_a) : ld_relaxed_u64(op.rt + (i >> 1));
+                    const long long t_begin = clock64();
+                    while ((uint32_t)(w >> 32) != rtag && *sm.s_dead == 0) {
+                        if (clock64() - t_begin > (1ll << 31)) {
+                            atomicCAS(p.ws.err, 0, 0x80000 | o);   // the residual stream was never written
+                            *sm.s_dead = 1;
+                            break;
+                        }
+                        w = ld_relaxed_u64(op.rt + (i >> 1));
+                    }
+                    rv = (uint32_t)w;
+                } else {
+                    rv = tile_e == t0 ? pre_a : __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));
+                }
                 const __half r0h = __ushort_as_half((unsigned short)(rv & 0xffffu)), r1h = __ushort_as_half((unsigned short)(rv >> 16));
-                *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(h_add(r0h, h0), h_add(r1h, h1));
+                store_pair(h_add(r0h, h0), h_add(r1h, h1));
             }
         } else if (op.epilogue == QW3_EPI_GELU) {
-            if (valid) *reinterpret_cast<__half2*>(op.y + i) = __halves2half2(gelu_h(h0), gelu_h(h1));
+            if (valid) store_pair(gelu_h(h0), gelu_h(h1));
         } else if (op.epilogue == QW3_EPI_ROPE_KV) {
             if (valid) {
                 const int sec = i / p.hidden, idx = i - sec * p.hidden;
@@ -401,9 +506,15 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         }
     };
     int n_shared = 0, sh_tile0 = 0, sh_tile1 = 0;
+    // Exchange slots alternate between two halves by operator parity: a slot is rewritten two operators later,
+    // when every reader of this operator's words has provably finished.
+    unsigned long long* const xchg_o = p.xchg + (size_t)(o & 1) * P_PSLOTS * P_TI;
 
     // ---- prologue: (RMS-normalised) input vector -> shared memory -------------------------------
-    if (op.gamma != nullptr) {
+    if (n_units == 0) {
+        // nothing to multiply: the input is not read (a CTA that reads an input must also contribute to the
+        // operator, so that nobody can run ahead and overwrite what it still reads)
+    } else if (op.gamma != nullptr) {
         uint4 xv[3], gvv[3];
         double s = 0.0;
 #pragma unroll
@@ -412,19 +523,15 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             gvv[e] = make_uint4(0u, 0u, 0u, 0u);
             if (ch < n_chunks) gvv[e] = *(reinterpret_cast<const uint4*>(op.gamma) + ch);
         }
+        fetch_x3(p, sm, op, o, xtag, tid, n_chunks, xv);
 #pragma unroll
         for (int e = 0; e < 3; ++e) {
-            const int ch = tid + e * P_NCONS;
-            xv[e] = make_uint4(0u, 0u, 0u, 0u);
-            if (ch < n_chunks) {
-                xv[e] = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
-                const __half2* h = reinterpret_cast<const __half2*>(&xv[e]);
+            const __half2* h = reinterpret_cast<const __half2*>(&xv[e]);
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const float2 f = __half22float2(h[t]);
-                    s += (double)(f.x * f.x);
-                    s += (double)(f.y * f.y);
-                }
+            for (int t = 0; t < 4; ++t) {   // chunks past the end are zero
+                const float2 f = __half22float2(h[t]);
+                s += (double)(f.x * f.x);
+                s += (double)(f.y * f.y);
             }
         }
 #pragma unroll
@@ -452,15 +559,30 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             }
         }
     } else if (n_units >= upt || K <= 4096) {
-        for (int ch = tid; ch < n_chunks; ch += P_NCONS)
-            *(reinterpret_cast<uint4*>(xs) + ch) = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+        for (int base = 0; base < n_chunks; base += 3 * P_NCONS) {
+            uint4 xv[3];
+            fetch_x3(p, sm, op, o, xtag, base + tid, n_chunks, xv);
+#pragma unroll
+            for (int e = 0; e < 3; ++e)
+                if (base + tid + e * P_NCONS < n_chunks) *(reinterpret_cast<uint4*>(xs) + base + tid + e * P_NCONS) = xv[e];
+        }
     } else {
         // only the rows this CTA multiplies: [r0, r0 + n_units) units, wrapping once into the next tile
         const int a0 = r0, a1 = min(r0 + n_units, upt), b1 = r0 + n_units - upt;   // unit (= 16-byte chunk) ranges
-        for (int ch = a0 + tid; ch < a1; ch += P_NCONS)
-            *(reinterpret_cast<uint4*>(xs) + ch) = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
-        for (int ch = tid; ch < b1; ch += P_NCONS)
-            *(reinterpret_cast<uint4*>(xs) + ch) = __ldcg(reinterpret_cast<const uint4*>(op.x) + ch);
+        for (int base = a0; base < a1; base += 3 * P_NCONS) {
+            uint4 xv[3];
+            fetch_x3(p, sm, op, o, xtag, base + tid, a1, xv);
+#pragma unroll
+            for (int e = 0; e < 3; ++e)
+                if (base + tid + e * P_NCONS < a1) *(reinterpret_cast<uint4*>(xs) + base + tid + e * P_NCONS) = xv[e];
+        }
+        for (int base = 0; base < b1; base += 3 * P_NCONS) {
+            uint4 xv[3];
+            fetch_x3(p, sm, op, o, xtag, base + tid, b1, xv);
+#pragma unroll
+            for (int e = 0; e < 3; ++e)
+                if (base + tid + e * P_NCONS < b1) *(reinterpret_cast<uint4*>(xs) + base + tid + e * P_NCONS) = xv[e];
+        }
     }
     if (!UNIFORM) {
         for (int j = tid; j < K; j += P_NCONS) sm.gidx[j] = (uint16_t)(((long long)j * op.Mb) % op.Kb);
@@ -617,7 +739,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         } else {
             // Shared tile: every contributor stores its sums as (value, tag) words and moves on; the sums are
             // gathered after the unit loop, so that no CTA waits for another while it still owes partial sums.
-            unsigned long long* slot = p.xchg + (size_t)(c + tile) * P_TI;
+            unsigned long long* slot = xchg_o + (size_t)(c + tile) * P_TI;
             st_relaxed_v2(slot + 2 * tid, pack_tagged(tot[0], tag), pack_tagged(tot[1], tag));
             if (n_shared == 0) sh_tile0 = tile;
             else sh_tile1 = tile;
@@ -643,8 +765,8 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             const int i0 = base + tid, i1 = i0 + P_NCONS;
             const bool h0 = i0 < total, h1 = i1 < total;
             const int c0 = i0 / cnt, c1 = i1 / cnt;
-            const unsigned long long* s0p = p.xchg + (size_t)(cf + c0 + tile_s) * P_TI + 2 * (pb + i0 - c0 * cnt);
-            const unsigned long long* s1p = p.xchg + (size_t)(cf + c1 + tile_s) * P_TI + 2 * (pb + i1 - c1 * cnt);
+            const unsigned long long* s0p = xchg_o + (size_t)(cf + c0 + tile_s) * P_TI + 2 * (pb + i0 - c0 * cnt);
+            const unsigned long long* s1p = xchg_o + (size_t)(cf + c1 + tile_s) * P_TI + 2 * (pb + i1 - c1 * cnt);
             unsigned long long a0 = 0, b0 = 0, a1 = 0, b1 = 0;
             const long long t_begin = clock64();
             for (;;) {
@@ -676,7 +798,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         named_barrier(1, P_NCONS);   // stage is reused by the next shared tile
     }
     trace_event(p, o, 6);
-    publish(p, o);   // this CTA's outputs of the operator are written
+    if (op.flags & PASS_PUBLISH) publish(p, o);   // this CTA's outputs of the operator are written
     trace_event(p, o, 7);
     if (op.epilogue == QW3_EPI_ARGMAX && c == 0 && warp == 0) {
         // whole-vocabulary winner (lowest index among equal maxima): CTA 0 waits for every CTA and reduces the
@@ -742,6 +864,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
     const float scale = 1.0f / sqrtf(128.0f);
     float* st = sm.red;
     constexpr int NG = P_NCONS / 16;   // 32 half-warps
+    unsigned long long* const xchg_o = p.xchg + (size_t)(o & 1) * P_PSLOTS * P_TI;
     for (int item = c; item < heads * S; item += G) {
         const int head = item / S, split = item - head * S;
         const int p0 = split * chunk, p1 = min(len, p0 + chunk);
@@ -819,7 +942,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
             // tagged words, which split 0 polls: no flag, fence or second round trip
             const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
             if (split != 0) {
-                unsigned long long* mine = p.xchg + (size_t)item * P_TI;
+                unsigned long long* mine = xchg_o + (size_t)item * P_TI;
                 if (tid < 128) st_relaxed_u64(mine + tid, pack_tagged(O, tag));
                 if (tid == 0) {   // M and L are the same in all threads below 128
                     st_relaxed_u64(mine + 128, pack_tagged(M, tag));
@@ -835,7 +958,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 }
                 if (tid < 130) {
                     for (int sp = 1; sp < S; ++sp) {
-                        const unsigned long long* src = p.xchg + (size_t)(item + sp) * P_TI + tid;
+                        const unsigned long long* src = xchg_o + (size_t)(item + sp) * P_TI + tid;
                         unsigned long long w;
                         const long long t_begin = clock64();
                         for (;;) {
@@ -854,27 +977,56 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 if (tid < 128) att_merge_states(st, S, tid, M, L, O);
             }
         }
-        if (finalise && tid < 128) op.y[head * 128 + tid] = __float2half_rn(O / L);
+        if (finalise && tid < 128) {   // four full warps: even lanes store the pair (plain and tagged)
+            const __half v = __float2half_rn(O / L);
+            const uint32_t mine = __half_as_ushort(v), next = __shfl_down_sync(0xffffffffu, mine, 1);
+            if ((tid & 1) == 0) {
+                const uint32_t pair = mine | (next << 16);
+                const int i = head * 128 + tid;
+                *reinterpret_cast<uint32_t*>(op.y + i) = pair;
+                if (op.yt != nullptr) {
+                    const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
+                    st_relaxed_u64(op.yt + (i >> 1), ((unsigned long long)tag << 32) | pair);
+                }
+            }
+        }
         named_barrier(1, P_NCONS);   // st is reused by the next item
     }
-    publish(p, o);
+    if (op.flags & PASS_PUBLISH) publish(p, o);
 }
 
 // Embedding gather straight from the packed [hidden][vocab] matrix (Inference.cu:1310-1315).
-__device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBody& op, const int o, const int pos) {
+__device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBody& op, const int o, const PassSmem& sm,
+                                            const int pos) {
     const int tid = threadIdx.x, c = blockIdx.x;
-    const int idx = c * P_NCONS + tid;
+    const int i = 2 * (c * P_NCONS + tid);   // this thread's pair of hidden elements
     const bool skip = p.d_skip != nullptr && __ldcg(p.d_skip) != 0;
-    if (idx < p.hidden && !skip) {
-        long long tok = p.decode ? __ldcg(p.d_token) : __ldcg(p.d_prompt + pos);
-        if (tok < 0 || tok >= p.vocab) tok = 0;
-        const long long pc = (p.vocab + 1) / 2;
-        const uint32_t byte = op.packed[(long long)idx * pc + (tok >> 1)];
-        const uint32_t q = (tok & 1) ? (byte >> 4) : (byte & 15u);
-        const long long g = (tok / 128) % op.n_alloc;
-        op.y[idx] = dequant_one(q, op.zp[g], op.scale[g]);
+    if (i < p.hidden) {
+        uint32_t pair;
+        if (skip) {
+            pair = __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));   // keep the hidden state of the pass before
+        } else {
+            long long tok = p.decode ? __ldcg(p.d_token) : __ldcg(p.d_prompt + pos);
+            if (tok < 0 || tok >= p.vocab) tok = 0;
+            const long long pc = (p.vocab + 1) / 2;
+            const long long g = (tok / 128) % op.n_alloc;
+            const __half z = op.zp[g], sc = op.scale[g];
+            uint32_t h[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t byte = op.packed[(long long)(i + e) * pc + (tok >> 1)];
+                const uint32_t q = (tok & 1) ? (byte >> 4) : (byte & 15u);
+                h[e] = __half_as_ushort(dequant_one(q, z, sc));
+            }
+            pair = h[0] | (h[1] << 16);
+            *reinterpret_cast<uint32_t*>(op.y + i) = pair;
+        }
+        if (op.yt != nullptr) {
+            const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
+            st_relaxed_u64(op.yt + (i >> 1), ((unsigned long long)tag << 32) | pair);
+        }
     }
-    publish(p, o);
+    if (op.flags & PASS_PUBLISH) publish(p, o);
 }
 
 __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassParams p) {
@@ -893,7 +1045,7 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
     sm.s_argi = reinterpret_cast<int*>(misc + 832);                  // 64
     sm.s_dead = reinterpret_cast<int*>(misc + 900);
     sm.s_epoch = reinterpret_cast<int*>(misc + 904);
-    sm.s_op = reinterpret_cast<uint32_t*>(misc + 1024);              // 2 x 128 bytes
+    sm.s_op = reinterpret_cast<uint32_t*>(misc + 1024);              // 2 x 192 bytes
 
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) {
@@ -934,11 +1086,11 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
                 else gemv_phase<false, false>(p, op, o, sm, uc_base, pos, pf);
             }
         } else if (op.kind == PASS_ATTN) {
-            wait_for_previous(p, sm, o);
+            if (op.flags & PASS_WAIT_PREV) wait_for_previous(p, sm, o);
             attn_phase(p, op, o, sm, pos);
         } else {
-            wait_for_previous(p, sm, o);
-            embed_phase(p, op, o, pos);
+            if (op.flags & PASS_WAIT_PREV) wait_for_previous(p, sm, o);
+            embed_phase(p, op, o, sm, pos);
         }
     }
     if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
@@ -1013,9 +1165,21 @@ void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const vo
     b.y = static_cast<__half*>(hidden_out);
 }
 
+// How an operator is tied to its neighbours inside one launch: `xt` (written by operator `src`) replaces the
+// plain input, `yt` receives a tagged copy of the output, `rt` (written by operator `rsrc`) holds the value a
+// RESIDUAL epilogue adds to.
+void pass_link(PassOp* op, int flags, int src, const void* xt, void* yt, const void* rt, int rsrc) {
+    op->b.flags = flags;
+    op->b.src = src;
+    op->b.rsrc = rsrc;
+    op->b.xt = static_cast<const unsigned long long*>(xt);
+    op->b.yt = static_cast<unsigned long long*>(yt);
+    op->b.rt = static_cast<const unsigned long long*>(rt);
+}
+
 size_t pass_op_bytes() { return sizeof(PassOp); }
 // Exchange buffer of tagged partial sums: one 1024-word slot per (CTA, tile) pair c + tile.
-size_t pass_xchg_bytes() { return (size_t)P_PSLOTS * P_TI * sizeof(unsigned long long); }
+size_t pass_xchg_bytes() { return 2 * (size_t)P_PSLOTS * P_TI * sizeof(unsigned long long); }
 
 struct PassLaunch {
     PassParams p;

@@ -46,6 +46,7 @@ void pass_fill_attn(PassOp* op, const void* q, void* kc, void* vc, void* ctx, in
 void pass_fill_embed(PassOp* op, const void* packed, const void* scale, const void* zp, long long n_alloc, void* hidden_out,
                      int hidden);
 size_t pass_xchg_bytes();
+void pass_link(PassOp* op, int flags, int src, const void* xt, void* yt, const void* rt, int rsrc);
 int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d_xchg, const int* d_epoch, const int* d_pos, const int* d_token, const int* d_skip,
                 const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
                 long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
@@ -97,6 +98,7 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     int* d_done = nullptr;    // persistent pass: per-operator arrival counters + the launch epoch word behind them
     int* d_epoch = nullptr;
     unsigned long long* d_xchg = nullptr;   // tagged partial sums exchanged between CTAs
+    unsigned long long *hidden_t = nullptr, *ctx_t = nullptr, *mlp_t = nullptr;   // tagged activations, one word per pair
     unsigned long long* d_trace = nullptr;   // per-operator entry times of the last pass (debug)
     unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
     bool persistent = false;
@@ -316,17 +318,45 @@ static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, 
     base += (256 - (reinterpret_cast<uintptr_t>(base) & 255)) & 255;   // descriptors hold 64-byte aligned tensor maps
     int k = 0;
     auto at = [&](int i) { return reinterpret_cast<PassOp*>(base + (size_t)i * ob); };
-    if (first) pass_fill_embed(at(k++), s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, s.hidden, c.hidden);
-    for (LayerDev& L : s.layers) {
-        pass_fill_gemv(at(k++), w4_desc(L.wqkv.desc), s.hidden, L.gamma, c.eps, QW3_EPI_ROPE_KV, s.q, L.kc, L.vc);
-        pass_fill_attn(at(k++), s.q, L.kc, L.vc, s.ctx, c.heads);
-        pass_fill_gemv(at(k++), w4_desc(L.wo.desc), s.ctx, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
-        pass_fill_gemv(at(k++), w4_desc(L.w1.desc), s.hidden, L.gamma, c.eps, QW3_EPI_GELU, s.mlp, nullptr, nullptr);
-        pass_fill_gemv(at(k++), w4_desc(L.w2.desc), s.mlp, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
+    // Inside a launch activations go from operator to operator as tagged words (hidden_t, ctx_t, mlp_t); only the
+    // attention reads plain memory of the operator before it (q and the new cache rows) and so waits on its
+    // arrival counter, and the final arg-max waits on the unembedding's.
+    constexpr int WAIT = 1, PUBLISH = 2;   // PassOpFlags
+    bool hidden_tagged = false;            // hidden_t holds the residual stream (written in this launch)
+    int hidden_src = -1;                   // operator that wrote it last
+    if (first) {
+        pass_fill_embed(at(k), s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, s.hidden, c.hidden);
+        pass_link(at(k), 0, -1, nullptr, s.hidden_t, nullptr, -1);
+        hidden_src = k;
+        ++k;
+        hidden_tagged = true;
     }
-    if (decode && last)
-        pass_fill_gemv(at(k++), w4_desc(s.unemb.desc), s.hidden, s.layers.back().gamma, c.eps, QW3_EPI_ARGMAX, s.logits16,
+    for (LayerDev& L : s.layers) {
+        pass_fill_gemv(at(k), w4_desc(L.wqkv.desc), s.hidden, L.gamma, c.eps, QW3_EPI_ROPE_KV, s.q, L.kc, L.vc);
+        pass_link(at(k), PUBLISH, k - 1, hidden_tagged ? s.hidden_t : nullptr, nullptr, nullptr, -1);
+        ++k;
+        pass_fill_attn(at(k), s.q, L.kc, L.vc, s.ctx, c.heads);
+        pass_link(at(k), WAIT, k - 1, nullptr, s.ctx_t, nullptr, -1);
+        ++k;
+        pass_fill_gemv(at(k), w4_desc(L.wo.desc), s.ctx, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
+        pass_link(at(k), 0, k - 1, s.ctx_t, s.hidden_t, hidden_tagged ? s.hidden_t : nullptr, hidden_src);
+        hidden_src = k;
+        ++k;
+        hidden_tagged = true;
+        pass_fill_gemv(at(k), w4_desc(L.w1.desc), s.hidden, L.gamma, c.eps, QW3_EPI_GELU, s.mlp, nullptr, nullptr);
+        pass_link(at(k), 0, k - 1, s.hidden_t, s.mlp_t, nullptr, -1);
+        ++k;
+        pass_fill_gemv(at(k), w4_desc(L.w2.desc), s.mlp, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
+        pass_link(at(k), 0, k - 1, s.mlp_t, s.hidden_t, s.hidden_t, hidden_src);
+        hidden_src = k;
+        ++k;
+    }
+    if (decode && last) {
+        pass_fill_gemv(at(k), w4_desc(s.unemb.desc), s.hidden, s.layers.back().gamma, c.eps, QW3_EPI_ARGMAX, s.logits16,
                        nullptr, nullptr);
+        pass_link(at(k), PUBLISH, k - 1, hidden_tagged ? s.hidden_t : nullptr, nullptr, nullptr, -1);
+        ++k;
+    }
     QW3_TRY(dev_alloc(e, s.device, d_ops, (size_t)n * ob));
     QW3_CUDA(cudaMemcpy(*d_ops, base, (size_t)n * ob, cudaMemcpyHostToDevice));
     *n_ops = n;
@@ -538,6 +568,15 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
             if (!ok) continue;   // shapes outside the persistent kernel's limits: per-operator launches
             QW3_CUDA(cudaSetDevice(s.device));
             QW3_TRY(pass_init_device());
+            {   // tagged activations: 8 bytes per pair of halves
+                const size_t hb = (size_t)c.hidden * 4, ib = (size_t)c.inter * 4;
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.hidden_t), hb));
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.ctx_t), hb));
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.mlp_t), ib));
+                QW3_CUDA(cudaMemset(s.hidden_t, 0, hb));
+                QW3_CUDA(cudaMemset(s.ctx_t, 0, hb));
+                QW3_CUDA(cudaMemset(s.mlp_t, 0, ib));
+            }
             QW3_TRY(build_pass_program(e, si, false, &s.ops_prompt, &s.n_ops_prompt));
             QW3_TRY(build_pass_program(e, si, true, &s.ops_decode, &s.n_ops_decode));
             {
