@@ -42,6 +42,7 @@ constexpr int P_MAX_GROUPS = 256;
 constexpr int P_RED_BYTES = 32768;       // cross-warp reduction (8 slots x 4 KB) / 32 attention states (16.9 KB)
 constexpr int P_OPW = 48;                // 32-bit words of a descriptor after its tensor map
 constexpr int P_DONE = 256;              // largest number of tiles / heads of an operator
+constexpr int P_MAX_OPS = 256;           // operators of one pass (their unit ranges are cached in shared memory)
 constexpr int P_TAG_OPS = 1024;          // tags: launch epoch * P_TAG_OPS + operator index
 constexpr int P_PSLOTS = WS_MAX_CTAS + P_DONE;   // partial-sum slots (CTA + tile) of an operator
 
@@ -50,7 +51,8 @@ constexpr size_t P_OFF_XS = P_OFF_RED + P_RED_BYTES;
 constexpr size_t P_OFF_GIDX = P_OFF_XS + (size_t)P_MAXK * 2;
 constexpr size_t P_OFF_GTAB = P_OFF_GIDX + (size_t)P_MAXK_NU * 2;
 constexpr size_t P_OFF_MISC = P_OFF_GTAB + (size_t)P_MAX_GROUPS * 16;
-constexpr size_t P_SMEM_BYTES = P_OFF_MISC + 2048;
+constexpr size_t P_OFF_RNG = P_OFF_MISC + 2048;                 // per-operator unit range of this CTA
+constexpr size_t P_SMEM_BYTES = P_OFF_RNG + (size_t)P_MAX_OPS * 16;
 
 enum PassOpKind { PASS_EMBED = 0, PASS_GEMV = 1, PASS_ATTN = 2 };
 
@@ -217,6 +219,7 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
 }
 
 struct PassSmem {
+    const int4* s_rng;   // [n_ops] {first unit, units, units per tile, kind} of this CTA, filled at kernel start
     int* s_epoch;   // value this launch writes into its flags
     uint8_t* ring;
     float* red;
@@ -333,13 +336,15 @@ __device__ __forceinline__ void prefetch_next(Prefetch& pf, const PassParams& p,
         pf.n = 0;
         do {
             ++pf.op;
-        } while (pf.op < p.n_ops && p.ops[pf.op].b.kind != PASS_GEMV);
+        } while (pf.op < p.n_ops && sm.s_rng[pf.op].w != PASS_GEMV);
         if (pf.op >= p.n_ops) {
             pf.end = true;
             return;
         }
-        pf.upt = p.ops[pf.op].b.upt;
-        cta_range(p.ops[pf.op].b.U, pf.upt, p.ops[pf.op].b.n_tiles, blockIdx.x, pf.ub, pf.n);
+        const int4 rg = sm.s_rng[pf.op];
+        pf.ub = rg.x;
+        pf.n = rg.y;
+        pf.upt = rg.z;
         pf.next_u = pf.ub;
         pf.tile = pf.ub / pf.upt;
         pf.r = pf.ub - pf.tile * pf.upt;
@@ -373,8 +378,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
     const int c = blockIdx.x;
     const long long U = op.U;
     const int upt = op.upt, K = op.K;
-    int u_begin, n_units;
-    cta_range(U, upt, op.n_tiles, c, u_begin, n_units);
+    const int u_begin = sm.s_rng[o].x, n_units = sm.s_rng[o].y;
     const int t0 = u_begin / upt, r0 = u_begin - t0 * upt;
     __half* xs = sm.xs;
 
@@ -1048,6 +1052,16 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
     sm.s_op = reinterpret_cast<uint32_t*>(misc + 1024);              // 2 x 192 bytes
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    {   // this CTA's share of every operator, computed once (the prefetch cursors walk this table)
+        int4* rng = reinterpret_cast<int4*>(smem + P_OFF_RNG);
+        for (int o = tid; o < p.n_ops; o += P_NTHREADS) {
+            const PassOpBody& b = p.ops[o].b;
+            int ub = 0, n = 0;
+            if (b.kind == PASS_GEMV) cta_range(b.U, b.upt, b.n_tiles, blockIdx.x, ub, n);
+            rng[o] = make_int4(ub, n, b.upt, b.kind);
+        }
+        sm.s_rng = rng;
+    }
     if (tid == 0) {
         for (int s = 0; s < P_RING; ++s) mbar_init(sm.full0 + 8 * s, 1);
         *sm.s_dead = 0;
@@ -1191,7 +1205,7 @@ int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d
                 const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
                 long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
                 unsigned long long* trace2, const Workspace* ws, cudaStream_t st) {
-    QW3_REQUIRE(n_ops <= P_TAG_OPS, "pass_launch: too many operators in one pass");
+    QW3_REQUIRE(n_ops <= P_MAX_OPS, "pass_launch: too many operators in one pass");
     PassParams p;
     std::memset(&p, 0, sizeof(p));
     p.ops = static_cast<const PassOp*>(d_ops);
