@@ -326,6 +326,7 @@ struct Prefetch {
     int upt;
     int next_u, tile, r;   // last unit issued in `op` and its (tile, row unit)
     bool end;
+    uint64_t policy;       // L2 eviction policy of the weight stream
 };
 
 __device__ __forceinline__ void prefetch_next(Prefetch& pf, const PassParams& p, const PassSmem& sm) {
@@ -364,7 +365,8 @@ __device__ __forceinline__ void prefetch_next(Prefetch& pf, const PassParams& p,
         // the slot was read by this warp with ordinary loads: order them before the bulk write
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_expect_tx(bar, P_UNIT_BYTES);
-        tma_load_2d(smem_u32(sm.ring + slot * P_UNIT_BYTES), &p.ops[pf.op].tmap, tile * (P_TI / 8), r * P_UNIT_ROWS, bar);
+        tma_load_2d_hint(smem_u32(sm.ring + slot * P_UNIT_BYTES), &p.ops[pf.op].tmap, tile * (P_TI / 8), r * P_UNIT_ROWS, bar,
+                         pf.policy);
     }
 }
 
@@ -1072,7 +1074,7 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
 
     // prime the ring: the first two units of this warp (weights do not depend on activations)
     Prefetch pf;
-    pf.op = -1; pf.uc = warp - P_NCW; pf.base = 0; pf.n = 0; pf.ub = 0; pf.upt = 1; pf.next_u = 0; pf.tile = 0; pf.r = 0; pf.end = false;
+    pf.op = -1; pf.uc = warp - P_NCW; pf.base = 0; pf.n = 0; pf.ub = 0; pf.upt = 1; pf.next_u = 0; pf.tile = 0; pf.r = 0; pf.end = false; pf.policy = l2_policy_evict_first();
     prefetch_next(pf, p, sm);
     prefetch_next(pf, p, sm);
 
