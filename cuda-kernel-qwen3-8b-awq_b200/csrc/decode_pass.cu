@@ -474,7 +474,10 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
                     o1 = h_add(h_mul(h0, sn), h_mul(h1, cs));
                 }
                 __half* dst = sec == 0 ? op.y + idx : (sec == 1 ? op.kc : op.vc) + ((size_t)head * p.max_pos + pos) * 128 + d;
-                *reinterpret_cast<__half2*>(dst) = __halves2half2(o0, o1);
+                const __half2 v = __halves2half2(o0, o1);
+                *reinterpret_cast<__half2*>(dst) = v;
+                if (op.yt != nullptr)   // q, k, v of this token as tagged words for the attention of this launch
+                    st_relaxed_u64(op.yt + (i >> 1), ((unsigned long long)tag << 32) | *reinterpret_cast<const uint32_t*>(&v));
             }
         } else {  // QW3_EPI_ARGMAX: winner of this CTA's outputs of the tile -> slot c + tile_e
             float bv = -INFINITY;
@@ -842,6 +845,26 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
     uc_base += n_units;
 }
 
+// Eight halves that the operator before wrote as four tagged words: polled until all four carry its tag.
+__device__ __forceinline__ uint4 load8_tagged(const PassParams& p, const PassSmem& sm, const unsigned long long* src,
+                                              const uint32_t tag, const int code) {
+    unsigned long long w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+    const long long t_begin = clock64();
+    for (;;) {
+        ld_relaxed_v2(src, w0, w1);
+        ld_relaxed_v2(src + 2, w2, w3);
+        if (((uint32_t)(w0 >> 32) == tag && (uint32_t)(w1 >> 32) == tag && (uint32_t)(w2 >> 32) == tag && (uint32_t)(w3 >> 32) == tag) ||
+            *sm.s_dead != 0)
+            break;
+        if (clock64() - t_begin > (1ll << 31)) {
+            atomicCAS(p.ws.err, 0, code);
+            *sm.s_dead = 1;
+            break;
+        }
+    }
+    return make_uint4((uint32_t)w0, (uint32_t)w1, (uint32_t)w2, (uint32_t)w3);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Decode attention of one layer (attentionKernel, Inference.cu:182-266, intended math): work items
 // (head, split of the KV length) are dealt round-robin to the CTAs; 32 half-warps of a CTA keep an
@@ -871,12 +894,14 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
     float* st = sm.red;
     constexpr int NG = P_NCONS / 16;   // 32 half-warps
     unsigned long long* const xchg_o = p.xchg + (size_t)(o & 1) * P_PSLOTS * P_TI;
+    const uint32_t xtag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.src;
     for (int item = c; item < heads * S; item += G) {
         const int head = item / S, split = item - head * S;
         const int p0 = split * chunk, p1 = min(len, p0 + chunk);
         float qf[8];
         {
-            const uint4 qv = __ldcg(reinterpret_cast<const uint4*>(op.x + head * 128 + sl * 8));
+            const uint4 qv = op.xt != nullptr ? load8_tagged(p, sm, op.xt + head * 64 + sl * 4, xtag, 0x70000 | o)
+                                              : __ldcg(reinterpret_cast<const uint4*>(op.x + head * 128 + sl * 8));
             const __half2* h = reinterpret_cast<const __half2*>(&qv);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -899,8 +924,15 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 kv[u] = make_uint4(0u, 0u, 0u, 0u);
                 vv[u] = make_uint4(0u, 0u, 0u, 0u);
                 if (kp < p1) {
-                    kv[u] = __ldcg(reinterpret_cast<const uint4*>(kh + (size_t)kp * 128));
-                    vv[u] = __ldcg(reinterpret_cast<const uint4*>(vh + (size_t)kp * 128));
+                    if (kp == pos && op.xt != nullptr) {
+                        // this token's own row: the projection before wrote it to the cache for later tokens and as
+                        // tagged words (behind q: k at hidden/2 words, v at hidden words) for this launch
+                        kv[u] = load8_tagged(p, sm, op.xt + (p.hidden >> 1) + head * 64 + sl * 4, xtag, 0x70000 | o);
+                        vv[u] = load8_tagged(p, sm, op.xt + p.hidden + head * 64 + sl * 4, xtag, 0x70000 | o);
+                    } else {
+                        kv[u] = __ldcg(reinterpret_cast<const uint4*>(kh + (size_t)kp * 128));
+                        vv[u] = __ldcg(reinterpret_cast<const uint4*>(vh + (size_t)kp * 128));
+                    }
                 }
             }
 #pragma unroll

@@ -98,7 +98,7 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     int* d_done = nullptr;    // persistent pass: per-operator arrival counters + the launch epoch word behind them
     int* d_epoch = nullptr;
     unsigned long long* d_xchg = nullptr;   // tagged partial sums exchanged between CTAs
-    unsigned long long *hidden_t = nullptr, *ctx_t = nullptr, *mlp_t = nullptr;   // tagged activations, one word per pair
+    unsigned long long *hidden_t = nullptr, *ctx_t = nullptr, *mlp_t = nullptr, *qkv_t = nullptr;   // tagged activations, one word per pair
     unsigned long long* d_trace = nullptr;   // per-operator entry times of the last pass (debug)
     unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
     bool persistent = false;
@@ -318,10 +318,9 @@ static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, 
     base += (256 - (reinterpret_cast<uintptr_t>(base) & 255)) & 255;   // descriptors hold 64-byte aligned tensor maps
     int k = 0;
     auto at = [&](int i) { return reinterpret_cast<PassOp*>(base + (size_t)i * ob); };
-    // Inside a launch activations go from operator to operator as tagged words (hidden_t, ctx_t, mlp_t); only the
-    // attention reads plain memory of the operator before it (q and the new cache rows) and so waits on its
-    // arrival counter, and the final arg-max waits on the unembedding's.
-    constexpr int WAIT = 1, PUBLISH = 2;   // PassOpFlags
+    // Inside a launch activations go from operator to operator as tagged words (hidden_t, qkv_t, ctx_t, mlp_t); only
+    // the final arg-max waits on an arrival counter (the unembedding's).
+    constexpr int PUBLISH = 2;   // PassOpFlags
     bool hidden_tagged = false;            // hidden_t holds the residual stream (written in this launch)
     int hidden_src = -1;                   // operator that wrote it last
     if (first) {
@@ -333,10 +332,10 @@ static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, 
     }
     for (LayerDev& L : s.layers) {
         pass_fill_gemv(at(k), w4_desc(L.wqkv.desc), s.hidden, L.gamma, c.eps, QW3_EPI_ROPE_KV, s.q, L.kc, L.vc);
-        pass_link(at(k), PUBLISH, k - 1, hidden_tagged ? s.hidden_t : nullptr, nullptr, nullptr, -1);
+        pass_link(at(k), 0, k - 1, hidden_tagged ? s.hidden_t : nullptr, s.qkv_t, nullptr, -1);
         ++k;
         pass_fill_attn(at(k), s.q, L.kc, L.vc, s.ctx, c.heads);
-        pass_link(at(k), WAIT, k - 1, nullptr, s.ctx_t, nullptr, -1);
+        pass_link(at(k), 0, k - 1, s.qkv_t, s.ctx_t, nullptr, -1);
         ++k;
         pass_fill_gemv(at(k), w4_desc(L.wo.desc), s.ctx, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
         pass_link(at(k), 0, k - 1, s.ctx_t, s.hidden_t, hidden_tagged ? s.hidden_t : nullptr, hidden_src);
@@ -576,6 +575,8 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
                 QW3_CUDA(cudaMemset(s.hidden_t, 0, hb));
                 QW3_CUDA(cudaMemset(s.ctx_t, 0, hb));
                 QW3_CUDA(cudaMemset(s.mlp_t, 0, ib));
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.qkv_t), 3 * hb));
+                QW3_CUDA(cudaMemset(s.qkv_t, 0, 3 * hb));
             }
             QW3_TRY(build_pass_program(e, si, false, &s.ops_prompt, &s.n_ops_prompt));
             QW3_TRY(build_pass_program(e, si, true, &s.ops_decode, &s.n_ops_decode));
