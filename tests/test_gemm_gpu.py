@@ -67,12 +67,13 @@ def test_gemm_sweep_rows_equal_gemv(ops, orc, cuda, M, K, R):
     y32, y16 = orc.gemm_w4a16(p, s, z, M, K, X[rows])
     # the tensor cores add the fp32 products of a K=16 step with their own internal alignment, so a few
     # per cent of the fp16 results land on the other side of a rounding boundary (never more than one ulp)
-    _check(got[rows], y32, y16, f"{M}x{K} rows {R}", differ=0.05)
+    _check(got[rows], y32, y16, f"{M}x{K} rows {R}", differ=0.05 if K <= 4096 else 0.08)
     y = torch.zeros(M, dtype=torch.float16, device=cuda)
     for r in rows:
         ops.gemv_w4a16(w, ws, ops.gemv_args(_to_dev(X[r], cuda), y=y))
         yv = y.cpu().numpy()
         d = _ulp_diff(got[r], yv)
         near = np.abs(got[r].astype(np.float32) - yv.astype(np.float32)) <= 1e-4 * np.abs(yv.astype(np.float32)).mean()
-        assert ((d <= 1) | near).all() and (d > 0).mean() < 0.05
+        # one-ulp differences only; their share grows with the number of accumulation steps (K)
+        assert ((d <= 1) | near).all() and (d > 0).mean() < (0.05 if K <= 4096 else 0.08)
     ws.check()
