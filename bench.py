@@ -34,7 +34,7 @@ METRIC = "batch-1 decode tokens/s (Qwen3-8B W4A16)"
 LAST_REF_GEMV_US = None
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_pass_kernel over its algorithmic bytes, from the ncu
 # capture summarised in profiles/ (a 6-layer pass; traffic grows with the bytes streamed).
-NCU_TRAFFIC_RATIO = 508.5 / 507.5
+NCU_TRAFFIC_RATIO = (509.27 + 4.81) / 507.6
 PROMPT_LEN = 128
 SEED = 0
 # Algorithmic bytes of one decoded token: packed weights of 36 layers + unembed, scale/zero-point
@@ -208,6 +208,52 @@ def roofline_gemv(pkg, torch, M, K, n_mats, reps):
     return us, n, us_pdl
 
 
+def pass_only(pkg, orc, args):
+    """Token passes of a model cut to --pass-layers layers (full-size matrices, small vocabulary unless asked
+    otherwise): the small case for profilers.  With QW3_TRACE=1 the engine records global-timer stamps inside
+    decode_pass_kernel; they are summarised per operator (CTA 0 entering each operator) and per phase (all
+    CTAs, one layer in the middle)."""
+    import ctypes as C
+    import numpy as np
+    L, V = args.pass_layers, args.pass_vocab
+    cfg = dict(hidden=4096, inter=12288, heads=32, head_dim=128, layers=L, vocab=V, max_pos=args.prompt_len + args.steps + args.warmup + 8,
+               rope_base=10000.0)
+    wdir = args.weights or os.path.join(tempfile.gettempdir(), f"qw3_pass_weights_{L}_{V}")
+    if not os.path.exists(os.path.join(wdir, "unembed_zp.bin")):
+        orc.write_weight_dir(orc.default_config(**cfg), SEED, wdir)
+    prompt = [int(t) for t in orc.gen_tokens(SEED, orc.TOKENS, args.prompt_len, V)]
+    inf = pkg.QWen3AWQInfer(wdir, **cfg)
+    inf.generateResponse(prompt, args.warmup)
+    inf.decode_more(args.steps)
+    out = {"kernel": "decode_pass_kernel", "layers": L, "vocab": V, "context": args.prompt_len + args.warmup,
+           "ms_per_token": inf.last_timing()[1] / args.steps}
+    if os.environ.get("QW3_TRACE"):
+        n_ops = 1 + 5 * L + 1
+        buf = (C.c_uint64 * (n_ops + 8))()
+        n = C.c_int32()
+        pkg.cabi.check(pkg.cabi.lib().qw3_debug_trace(inf._h, 0, buf, n_ops + 8, C.byref(n)), "qw3_debug_trace")
+        d = np.diff(np.array(buf[:n.value], dtype=np.float64)) / 1e3
+        lay = d[1:1 + 5 * L].reshape(L, 5)
+        out["op_us"] = {"embed": float(d[0]), "unembed_argmax": float(d[1 + 5 * L]), "layer": float(lay.sum(axis=1).mean()),
+                        **{k: float(v) for k, v in zip(["wqkv", "attention", "wo", "w1", "w2"], lay.mean(axis=0))}}
+        G = 148
+        buf2 = (C.c_uint64 * (256 * n_ops * 8))()
+        pkg.cabi.check(pkg.cabi.lib().qw3_debug_trace(inf._h, 0, buf2, -(256 * n_ops * 8), C.byref(n)), "qw3_debug_trace")
+        t = np.ctypeslib.as_array(buf2).reshape(256, n_ops, 8)[:G].astype(np.float64)
+        t[t == 0] = np.nan
+        names = ["enter", "input wait", "prologue", "units", "flush", "gather", "epilogue", "end"]
+        li = L // 2
+        phases = {}
+        for k, op in enumerate(["wqkv", "attention", "wo", "w1", "w2"]):
+            e = t[:, 1 + 5 * li + k, :]
+            e = e - np.nanmin(e[:, 0])
+            if op != "attention":   # median over CTAs of the time each phase ends, from the first CTA entering
+                phases[op] = {nm: float(np.nanmedian(e[:, j]) / 1e3) for j, nm in enumerate(names) if np.isfinite(e[:, j]).any()}
+        out["phase_end_us_median_over_ctas"] = phases
+    inf.close()
+    return out
+
+
 def gemm_sweep(pkg, torch, shapes, rows_list, reps=10, ref_cublas=True):
     """Batched-row sweep of the tcgen05 W4A16 contraction: one CUDA graph of `reps` launches per
     configuration, CUDA events on the launching stream.  Rows <= 64 are HBM-bound, above that the
@@ -286,6 +332,11 @@ def main():
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)
     ap.add_argument("--roofline-shape", default="12288x4096")
+    ap.add_argument("--only-pass", action="store_true",
+                    help="run token passes of a model with --pass-layers layers (small case for profilers); with QW3_TRACE=1 in "
+                         "the environment also prints the per-operator and per-phase times of the pass kernel")
+    ap.add_argument("--pass-layers", type=int, default=6)
+    ap.add_argument("--pass-vocab", type=int, default=2048)
     ap.add_argument("--only-gemm", action="store_true", help="batched-row sweep of the tensor-core W4A16 contraction")
     ap.add_argument("--gemm-shapes", default="12288x4096,4096x4096,4096x12288,151936x4096")
     ap.add_argument("--gemm-rows", default="16,64,256,2048")
@@ -311,6 +362,9 @@ def main():
         us, n, us_pdl = roofline_gemv(pkg, torch, M, K, args.roofline_mats, args.roofline_reps)
         print(json.dumps({"kernel": "gemv_w4a16_kernel", "shape": [M, K], "avg_launch_us": us, "avg_launch_us_pdl": us_pdl,
                           "launches": n, "GBps": gemv_bytes(M, K) / us / 1e3, "ref_dequant_then_cublas_us": LAST_REF_GEMV_US}))
+        return
+    if args.only_pass:
+        print(json.dumps(pass_only(pkg, load_oracle(), args)))
         return
     if args.only_gemm:
         shapes = [tuple(int(v) for v in t.split("x")) for t in args.gemm_shapes.split(",")]
@@ -403,7 +457,7 @@ def main():
                              "unit": "GB/s", "frac": decode_gbs / peaks["hbm_gbs"],
                              "traffic": int(token_bytes(ctx_mid) * NCU_TRAFFIC_RATIO), "bytes_per_launch": token_bytes(ctx_mid),
                              "avg_launch_us": decode_ms * 1e3 / args.steps,
-                             "traffic_note": "dram read+write of an ncu capture of a 6-layer pass (508.5 MB for 507.5 MB "
+                             "traffic_note": "dram read+write of an ncu capture of a 6-layer pass (514.1 MB for 507.6 MB "
                                              "algorithmic), scaled by bytes to the 36-layer launch",
                              "note": "at batch 1 the stages of N GPUs run one after another: one GPU's bandwidth is in use at a time"},
                 "gemv_roofline": gemv_roof,
