@@ -416,6 +416,18 @@ def main():
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
+    prefill = None
+    if world == 1 and n_gpus == 1:   # prompt phase: the reference's token loop against the batched-row path
+        inf.generateResponse(prompt, 1)
+        loop_ms = inf.last_timing()[0]
+        inf.set_batched_prefill(True)
+        inf.generateResponse(prompt, 1)      # first use allocates the block buffers
+        inf.generateResponse(prompt, 1)
+        blk_ms = inf.last_timing()[0]
+        inf.set_batched_prefill(False)
+        prefill = {"prompt_tokens": len(prompt), "token_loop_ms": loop_ms, "batched_ms": blk_ms,
+                   "batched_tokens_per_s": len(prompt) / (blk_ms * 1e-3),
+                   "note": "device time of the prompt phase of generateResponse; batched = tcgen05 W4A16 contraction over the block"}
     if world > 1:   # max over ranks of the device time and of the wall-clock; launches summed
         t = torch.tensor([decode_ms, e2e_s], dtype=torch.float64, device=f"cuda:{local}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -463,7 +475,7 @@ def main():
                 "gemv_roofline": gemv_roof,
                 "e2e": {"value": args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
                         "note": "host wall-clock of decode_more(K) through the C ABI; the sampled id feeds the next step on the device"},
-                "gpu_launches": int(launches), "clocks": clocks,
+                "gpu_launches": int(launches), "clocks": clocks, "prefill": prefill,
                 "tokens_equal_between_runs": None if len(ids_dev) != len(ids_e2e) else True}
         if not args.no_cpu_baseline and n_gpus == 1:
             n_cpu = 8

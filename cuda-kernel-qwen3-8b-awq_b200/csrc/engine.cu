@@ -25,6 +25,15 @@ int attn_decode_launch(const void* q, const void* kc, const void* vc, int heads,
 int embed_gather_launch(const void* packed, const void* scale, const void* zp, long long n_alloc, long long hidden,
                         long long vocab, const int* d_token, const int* d_index, const int* d_skip, int token, void* out,
                         bool pdl, cudaStream_t st);
+int embed_rows_launch(const void* packed, const void* scale, const void* zp, long long n_alloc, int hidden, long long vocab,
+                      const int* d_tokens, int rows, void* out, cudaStream_t st);
+int rmsnorm_rows_launch(const void* x, const void* gamma, int n, float eps, int rows, void* out, cudaStream_t st);
+int rope_kv_rows_launch(void* qkv, void* kc, void* vc, const void* cos_t, const void* sin_t, int hidden, long long max_pos,
+                        int pos0, int rows, cudaStream_t st);
+int attn_prefill_launch(const void* qkv, const void* kc, const void* vc, int heads, int hidden, long long max_pos, int pos0,
+                        int rows, void* ctx, cudaStream_t st);
+int add_rows_launch(void* h, const void* y, long long n, cudaStream_t st);
+int gelu_rows_launch(void* x, long long n, cudaStream_t st);
 int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, int* d_epoch, bool pdl,
                      cudaStream_t st);
 const W4Desc* w4_desc(qw3_w4_t w);
@@ -102,6 +111,8 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     unsigned long long* d_trace = nullptr;   // per-operator entry times of the last pass (debug)
     unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
     bool persistent = false;
+    // batched prompt phase: activations of a block of PF_BLOCK prompt rows (allocated at the first use)
+    void *pf_h = nullptr, *pf_n = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_mlp = nullptr, *pf_y = nullptr;
 };
 
 }  // namespace qw3
@@ -125,6 +136,7 @@ struct qw3_engine {
     bool next_is_prev = false;
     int msg_out = 0, msg_in = 0;        // hidden-state messages sent to the next stage / taken from the previous one
     int tok_out = 0, tok_in = 0;        // token messages (last stage -> first stage)
+    bool batched_prefill = false;       // prompt in blocks of rows through the tensor-core contraction (qw3_set_batched_prefill)
     int seq_len = 0;                    // token passes through the layers so far (next position)
     int sampled = 0;                    // ids sampled since the last prompt
 };
@@ -394,6 +406,69 @@ static int handoff(qw3_engine* e, int from, int to, bool hidden, bool token) {
     QW3_CUDA(cudaEventRecord(b.taken, b.stream));
     QW3_CUDA(cudaSetDevice(a.device));
     QW3_CUDA(cudaStreamWaitEvent(a.stream, b.taken, 0));
+    return QW3_OK;
+}
+
+// ---- batched prompt phase ---------------------------------------------------------------------------
+// A block of `rows` prompt tokens at positions pos0.. goes through every stage together: the projections are
+// the tensor-core contraction, the rest the row kernels of prefill.cu.  Same per-element arithmetic as the
+// token-at-a-time loop (Inference.cu:1304-1343); the contractions sum in a different fp32 order.
+constexpr int PF_BLOCK = 256;
+
+static int prefill_alloc(qw3_engine* e, Stage& s) {
+    if (s.pf_h) return QW3_OK;
+    const Qw3Config& c = e->cfg;
+    const size_t H = (size_t)c.hidden * 2 * PF_BLOCK, I = (size_t)c.inter * 2 * PF_BLOCK;
+    QW3_TRY(dev_alloc(e, s.device, &s.pf_h, H));
+    QW3_TRY(dev_alloc(e, s.device, &s.pf_n, H));
+    QW3_TRY(dev_alloc(e, s.device, &s.pf_qkv, 3 * H));
+    QW3_TRY(dev_alloc(e, s.device, &s.pf_ctx, H));
+    QW3_TRY(dev_alloc(e, s.device, &s.pf_mlp, I));
+    QW3_TRY(dev_alloc(e, s.device, &s.pf_y, H));
+    return QW3_OK;
+}
+
+static int prefill_block(qw3_engine* e, int t0, int rows) {
+    const Qw3Config& c = e->cfg;
+    const int N = c.n_stages, H = c.hidden;
+    for (int si = 0; si < N; ++si) {
+        Stage& s = e->st[si];
+        QW3_TRY(prefill_alloc(e, s));
+        QW3_CUDA(cudaSetDevice(s.device));
+        if (si > 0) {   // the block's hidden rows from the stage before, ordered by events as the one-row hand-off
+            Stage& a = e->st[si - 1];
+            QW3_CUDA(cudaStreamWaitEvent(s.stream, a.done, 0));
+            QW3_CUDA(cudaMemcpyPeerAsync(s.pf_h, s.device, a.pf_h, a.device, (size_t)rows * H * 2, s.stream));
+            QW3_CUDA(cudaEventRecord(s.taken, s.stream));
+            QW3_CUDA(cudaSetDevice(a.device));
+            QW3_CUDA(cudaStreamWaitEvent(a.stream, s.taken, 0));
+            QW3_CUDA(cudaSetDevice(s.device));
+        } else {
+            QW3_TRY(embed_rows_launch(s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, H, c.vocab, s.d_prompt + t0, rows,
+                                      s.pf_h, s.stream));
+            e->launches += 1;
+        }
+        for (LayerDev& L : s.layers) {
+            QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
+            QW3_TRY(qw3_gemm_w4a16(L.wqkv.desc, s.pf_n, rows, s.pf_qkv, s.ws, s.stream));
+            QW3_TRY(rope_kv_rows_launch(s.pf_qkv, L.kc, L.vc, s.cos_t, s.sin_t, H, c.max_pos, t0, rows, s.stream));
+            QW3_TRY(attn_prefill_launch(s.pf_qkv, L.kc, L.vc, c.heads, H, c.max_pos, t0, rows, s.pf_ctx, s.stream));
+            QW3_TRY(qw3_gemm_w4a16(L.wo.desc, s.pf_ctx, rows, s.pf_y, s.ws, s.stream));
+            QW3_TRY(add_rows_launch(s.pf_h, s.pf_y, (long long)rows * H, s.stream));
+            QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
+            QW3_TRY(qw3_gemm_w4a16(L.w1.desc, s.pf_n, rows, s.pf_mlp, s.ws, s.stream));
+            QW3_TRY(gelu_rows_launch(s.pf_mlp, (long long)rows * c.inter, s.stream));
+            QW3_TRY(qw3_gemm_w4a16(L.w2.desc, s.pf_mlp, rows, s.pf_y, s.ws, s.stream));
+            QW3_TRY(add_rows_launch(s.pf_h, s.pf_y, (long long)rows * H, s.stream));
+            e->launches += 11;
+        }
+        // what the token loop leaves behind: the last row's hidden state and the position counter
+        QW3_CUDA(cudaMemcpyAsync(s.hidden, static_cast<char*>(s.pf_h) + (size_t)(rows - 1) * H * 2, (size_t)H * 2,
+                                 cudaMemcpyDeviceToDevice, s.stream));
+        const int next_pos[4] = {t0 + rows, 0, 0, 0};
+        QW3_CUDA(cudaMemcpyAsync(s.d_pos, next_pos, 4, cudaMemcpyHostToDevice, s.stream));
+        QW3_CUDA(cudaEventRecord(s.done, s.stream));
+    }
     return QW3_OK;
 }
 
@@ -799,7 +874,11 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaMemcpyAsync(s0.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s0.stream));
     QW3_CUDA(cudaEventRecord(e->ev0, s0.stream));
-    for (int t = 0; t < n_prompt; ++t) QW3_TRY(run_pass(e, false, true));            // Inference.cu:1304-1343
+    if (e->batched_prefill) {
+        for (int t0 = 0; t0 < n_prompt; t0 += PF_BLOCK) QW3_TRY(prefill_block(e, t0, n_prompt - t0 < PF_BLOCK ? n_prompt - t0 : PF_BLOCK));
+    } else {
+        for (int t = 0; t < n_prompt; ++t) QW3_TRY(run_pass(e, false, true));        // Inference.cu:1304-1343
+    }
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaStreamWaitEvent(s0.stream, sl.done, 0));
     QW3_CUDA(cudaEventRecord(e->ev1, s0.stream));
@@ -842,6 +921,16 @@ int qw3_last_logits(qw3_handle e, float* out_vocab) {
     QW3_CUDA(cudaSetDevice(sl.device));
     QW3_CUDA(cudaStreamSynchronize(sl.stream));
     QW3_CUDA(cudaMemcpy(out_vocab, sl.logits32, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost));
+    return QW3_OK;
+}
+
+int qw3_set_batched_prefill(qw3_handle e, int on) {
+    QW3_REQUIRE(e, "qw3_set_batched_prefill: null handle");
+    if (on && e->cfg.world > 1) {
+        set_last_error("qw3_set_batched_prefill: one process per GPU runs the prompt token by token");
+        return QW3_ERR_STATE;
+    }
+    e->batched_prefill = on != 0;
     return QW3_OK;
 }
 

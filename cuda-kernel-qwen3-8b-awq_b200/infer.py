@@ -36,6 +36,11 @@ class QWen3AWQInfer:
         cabi.check(self._lib.qw3_generate(self._h, prompt, n, max_new_tokens, out, C.byref(n_out)), "qw3_generate")
         return [int(out[i]) for i in range(n_out.value)]
 
+    def set_batched_prefill(self, on):
+        """Prompt in blocks of rows through the tensor-core contraction (True) or token by token as the
+        reference (False, the default)."""
+        cabi.check(self._lib.qw3_set_batched_prefill(self._h, 1 if on else 0), "qw3_set_batched_prefill")
+
     def decode_more(self, max_new_tokens):
         """Continue the last generateResponse call for max_new_tokens more ids (same KV state)."""
         out = (C.c_int32 * max(max_new_tokens, 1))()

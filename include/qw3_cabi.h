@@ -209,6 +209,14 @@ int qw3_generate(qw3_handle h, const int32_t* prompt, int32_t n_prompt, int32_t 
  * caller stream a long generation in pieces and lets a benchmark time decode steps alone. */
 int qw3_decode_more(qw3_handle h, int32_t max_new, int32_t* out_ids, int32_t* n_out);
 
+/* Prompt phase in blocks of up to 256 rows (on = 1) instead of token by token (on = 0, the default and the
+ * reference's flow, Inference.cu:1304-1343): the four projections of a layer become the tensor-core
+ * contraction of qw3_gemm_w4a16 over the block, with row versions of RMSNorm, RoPE + KV append, causal
+ * attention, residual add and GeLU around them.  Per-element arithmetic is unchanged; the contractions sum
+ * in a different fp32 order, so cache rows and the hidden state can differ from the token loop in the last
+ * fp16 bit.  Not available with one process per GPU (world > 1). */
+int qw3_set_batched_prefill(qw3_handle h, int on);
+
 /* fp32 logits of the last decode step (keep_logits = 1), vocab floats to host memory. */
 int qw3_last_logits(qw3_handle h, float* out_vocab);
 /* Device time of the last call's prompt loop and decode loop (CUDA events, milliseconds). */

@@ -50,6 +50,24 @@ def test_small_model_tokens_match_oracle(pkg, orc, cuda, small_dir, persistent, 
     inf.close()
 
 
+def test_small_model_batched_prefill(pkg, orc, cuda, small_dir):
+    """Prompt in one block through the tensor-core contraction: same ids as the oracle's token loop, logits
+    within the stated tolerance of it and of the token-at-a-time engine path."""
+    prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
+    ids, logits, margins = _oracle_generate(orc, SMALL, 0, small_dir, prompt, 10)
+    inf = pkg.QWen3AWQInfer(small_dir, keep_logits=1, **SMALL)
+    loop_ids = inf.generateResponse(prompt, 10)
+    loop_logits = inf.last_logits()
+    inf.set_batched_prefill(True)
+    got = inf.generateResponse(prompt, 10)
+    assert got == [int(t) for t in ids] == loop_ids, f"margins {margins}"
+    assert _logits_close(inf.last_logits(), logits)
+    assert _logits_close(inf.last_logits(), loop_logits.astype(np.float16))
+    inf.set_batched_prefill(False)
+    assert inf.generateResponse(prompt, 10) == loop_ids                    # switching back restores the token loop
+    inf.close()
+
+
 def test_small_model_sample_first(pkg, orc, cuda, small_dir):
     prompt = orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])
     ids, _, _ = _oracle_generate(orc, SMALL, 0, small_dir, prompt, 10, sample_first=1)
@@ -110,11 +128,19 @@ def test_full_model_tokens_match_golden(pkg, orc, cuda, tmp_path):
     inf = pkg.QWen3AWQInfer(d, keep_logits=1, **g["config"])
     got = inf.generateResponse(prompt, g["max_new"])
     logits = inf.last_logits()
+    # the same run with the prompt as one block of 128 rows through the tensor-core contraction
+    inf.set_batched_prefill(True)
+    got_b = inf.generateResponse(prompt, g["max_new"])
+    logits_b = inf.last_logits()
+    prompt_ms_b = inf.last_timing()[0]
     inf.close()
     assert got == g["ids"], f"oracle top-1/top-2 margins per step: {g['margins']}"
     top = np.array(g["last_logits_top8_idx"])
     want = np.array(g["last_logits_top8"], np.float32)
     assert (np.abs(logits[top] - want) <= 2e-2 * np.abs(want)).all()
+    assert got_b == g["ids"], f"batched prompt phase; margins {g['margins']}"
+    assert (np.abs(logits_b[top] - want) <= 2e-2 * np.abs(want)).all()
+    assert prompt_ms_b > 0
 
 
 def test_errors_are_status_codes(pkg, orc, cuda, small_dir, tmp_path):
