@@ -174,12 +174,12 @@ __device__ __forceinline__ bool slice_pair(int cf, int cl, int c, int t, int& pp
 // contribute to tile `tile_q`.
 __device__ __forceinline__ void cta_range(long long U, int upt, int n_tiles, int c, int& ub, int& n) {
     const int Gf = gridDim.x;
-    if (n_tiles < Gf) {
-        const int t = (int)(((long long)(c + 1) * n_tiles - 1) / Gf);
-        const int cb = (int)((long long)t * Gf / n_tiles), cb1 = (int)((long long)(t + 1) * Gf / n_tiles);
+    if (n_tiles < Gf) {   // 32-bit arithmetic: tiles <= 256, CTAs <= 256, units per tile <= 1536
+        const int t = ((c + 1) * n_tiles - 1) / Gf;
+        const int cb = t * Gf / n_tiles, cb1 = (t + 1) * Gf / n_tiles;
         const int cnt = min(cb1 - cb, upt), idx = c - cb;
         if (idx < cnt) {
-            const int lo = (int)((long long)idx * upt / cnt), hi = (int)((long long)(idx + 1) * upt / cnt);
+            const int lo = idx * upt / cnt, hi = (idx + 1) * upt / cnt;
             ub = t * upt + lo;
             n = hi - lo;
         } else {
@@ -201,7 +201,7 @@ __device__ __forceinline__ void cta_range(long long U, int upt, int n_tiles, int
 __device__ __forceinline__ void tile_contributors(long long U, int upt, int n_tiles, int tile, int& cf, int& cl) {
     const int Gf = gridDim.x;
     if (n_tiles < Gf) {
-        const int cb = (int)((long long)tile * Gf / n_tiles), cb1 = (int)((long long)(tile + 1) * Gf / n_tiles);
+        const int cb = tile * Gf / n_tiles, cb1 = (tile + 1) * Gf / n_tiles;
         cf = cb;
         cl = cb + min(cb1 - cb, upt) - 1;
     } else {
