@@ -247,7 +247,9 @@ def pass_only(pkg, orc, args):
         for k, op in enumerate(["wqkv", "attention", "wo", "w1", "w2"]):
             e = t[:, 1 + 5 * li + k, :]
             e = e - np.nanmin(e[:, 0])
-            if op != "attention":   # median over CTAs of the time each phase ends, from the first CTA entering
+            if op == "attention":   # its events: q polled, rows done, CTA merge, splits merged, ctx stored
+                e = e[::4]          # the CTAs that merge a head (split 0 of 4)
+            if True:   # median over CTAs of the time each phase ends, from the first CTA entering
                 phases[op] = {nm: float(np.nanmedian(e[:, j]) / 1e3) for j, nm in enumerate(names) if np.isfinite(e[:, j]).any()}
         out["phase_end_us_median_over_ctas"] = phases
     inf.close()

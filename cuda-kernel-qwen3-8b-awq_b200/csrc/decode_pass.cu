@@ -898,6 +898,25 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
     for (int item = c; item < heads * S; item += G) {
         const int head = item / S, split = item - head * S;
         const int p0 = split * chunk, p1 = min(len, p0 + chunk);
+        const __half* kh = op.kc + (size_t)head * p.max_pos * 128 + sl * 8;
+        const __half* vh = op.vc + (size_t)head * p.max_pos * 128 + sl * 8;
+        constexpr int UN = 2;
+        // Cache rows of earlier tokens do not depend on this token: the first batch is requested before q is
+        // polled, and every later batch while the one before is being used.
+        uint4 nk[UN], nv[UN];
+        auto request_rows = [&](const int kb) {
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int kp = kb + grp + u * NG;
+                nk[u] = make_uint4(0u, 0u, 0u, 0u);
+                nv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (kp < p1 && !(kp == pos && op.xt != nullptr)) {
+                    nk[u] = __ldcg(reinterpret_cast<const uint4*>(kh + (size_t)kp * 128));
+                    nv[u] = __ldcg(reinterpret_cast<const uint4*>(vh + (size_t)kp * 128));
+                }
+            }
+        };
+        request_rows(p0);
         float qf[8];
         {
             const uint4 qv = op.xt != nullptr ? load8_tagged(p, sm, op.xt + head * 64 + sl * 4, xtag, 0x70000 | o)
@@ -910,31 +929,25 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 qf[2 * e + 1] = f.y;
             }
         }
-        const __half* kh = op.kc + (size_t)head * p.max_pos * 128 + sl * 8;
-        const __half* vh = op.vc + (size_t)head * p.max_pos * 128 + sl * 8;
+        trace_event(p, o, 2);
         float m = -INFINITY, l = 0.0f, ov[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) ov[e] = 0.0f;
-        constexpr int UN = 2;
         for (int kb = p0; kb < p1; kb += NG * UN) {   // trip count uniform across the CTA
             uint4 kv[UN], vv[UN];
 #pragma unroll
             for (int u = 0; u < UN; ++u) {
                 const int kp = kb + grp + u * NG;
-                kv[u] = make_uint4(0u, 0u, 0u, 0u);
-                vv[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (kp < p1) {
-                    if (kp == pos && op.xt != nullptr) {
-                        // this token's own row: the projection before wrote it to the cache for later tokens and as
-                        // tagged words (behind q: k at hidden/2 words, v at hidden words) for this launch
-                        kv[u] = load8_tagged(p, sm, op.xt + (p.hidden >> 1) + head * 64 + sl * 4, xtag, 0x70000 | o);
-                        vv[u] = load8_tagged(p, sm, op.xt + p.hidden + head * 64 + sl * 4, xtag, 0x70000 | o);
-                    } else {
-                        kv[u] = __ldcg(reinterpret_cast<const uint4*>(kh + (size_t)kp * 128));
-                        vv[u] = __ldcg(reinterpret_cast<const uint4*>(vh + (size_t)kp * 128));
-                    }
+                kv[u] = nk[u];
+                vv[u] = nv[u];
+                if (kp < p1 && kp == pos && op.xt != nullptr) {
+                    // this token's own row: the projection before wrote it to the cache for later tokens and as
+                    // tagged words (behind q: k at hidden/2 words, v at hidden words) for this launch
+                    kv[u] = load8_tagged(p, sm, op.xt + (p.hidden >> 1) + head * 64 + sl * 4, xtag, 0x70000 | o);
+                    vv[u] = load8_tagged(p, sm, op.xt + p.hidden + head * 64 + sl * 4, xtag, 0x70000 | o);
                 }
             }
+            if (kb + NG * UN < p1) request_rows(kb + NG * UN);
 #pragma unroll
             for (int u = 0; u < UN; ++u) {
                 const int kp = kb + grp + u * NG;
@@ -965,6 +978,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 }
             }
         }
+trace_event(p, o, 3);
 #pragma unroll
         for (int e = 0; e < 8; ++e) st[grp * WS_ATT_STRIDE + sl * 8 + e] = ov[e];
         if (sl == 0) {
@@ -972,8 +986,32 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
             st[grp * WS_ATT_STRIDE + 129] = l;
         }
         named_barrier(1, P_NCONS);
+        // merge of the 32 half-warp states, same arithmetic and order as att_merge_states, but the weight
+        // exp(m_g - M) of a state is computed once (lane g of warp 0) instead of once per output element
+        float* wts = st + NG * WS_ATT_STRIDE;   // [NG] weights, then the maximum
+        static_assert(NG == 32, "one lane per half-warp state");
+        if (tid < 32) {
+            const float mg = st[tid * WS_ATT_STRIDE + 128];
+            float mx = mg;
+#pragma unroll
+            for (int msk = 16; msk > 0; msk >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, msk));
+            wts[tid] = (mg == -INFINITY) ? 0.0f : expf(mg - mx);
+            if (tid == 0) wts[NG] = mx;
+        }
+        named_barrier(1, P_NCONS);
         float M = 0.f, L = 1.f, O = 0.f;
-        if (tid < 128) att_merge_states(st, NG, tid, M, L, O);
+        if (tid < 128) {
+            M = wts[NG];
+            L = 0.0f;
+            O = 0.0f;
+#pragma unroll 8
+            for (int g = 0; g < NG; ++g) {
+                const float w = wts[g];
+                L += st[g * WS_ATT_STRIDE + 129] * w;
+                O += st[g * WS_ATT_STRIDE + tid] * w;
+            }
+        }
+        trace_event(p, o, 4);
         bool finalise = true;
         if (S > 1) {
             // split 0 of the head finalises; the other splits hand over their state (128 outputs, max, sum) as
@@ -1015,6 +1053,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 if (tid < 128) att_merge_states(st, S, tid, M, L, O);
             }
         }
+        trace_event(p, o, 5);
         if (finalise && tid < 128) {   // four full warps: even lanes store the pair (plain and tagged)
             const __half v = __float2half_rn(O / L);
             const uint32_t mine = __half_as_ushort(v), next = __shfl_down_sync(0xffffffffu, mine, 1);
@@ -1028,6 +1067,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 }
             }
         }
+        trace_event(p, o, 6);
         named_barrier(1, P_NCONS);   // st is reused by the next item
     }
     if (op.flags & PASS_PUBLISH) publish(p, o);
