@@ -547,9 +547,9 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         for (int m = 16; m > 0; m >>= 1) s += shfl_xor_double(s, m);
         if (lane == 0) sm.dsum[warp] = s;
         named_barrier(1, P_NCONS);
-        double tot = 0.0;
+        double tot = sm.dsum[lane & (P_NCW - 1)];   // 16 partial sums: butterfly over the low four lane bits
 #pragma unroll
-        for (int w = 0; w < P_NCW; ++w) tot += sm.dsum[w];
+        for (int m = 8; m > 0; m >>= 1) tot += shfl_xor_double(tot, m);
         const float mean_sq = __fdiv_rn((float)tot, (float)K);                         // Inference.cu:136
         const float denom = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, op.eps)));    // Inference.cu:137
         const __half nscale = __float2half_rn(denom);                                  // Inference.cu:138
