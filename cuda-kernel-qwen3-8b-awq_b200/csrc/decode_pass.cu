@@ -259,8 +259,8 @@ __device__ __forceinline__ void publish(const PassParams& p, int o) {
 // Up to three 16-byte chunks (8 halves each) of an operator's input vector for this thread: chunk indices
 // first, first + 512, first + 1024 below `limit`.  Plain input: ordinary L2 loads.  Tagged input: every
 // chunk is four (two halves, tag) words; all loads are in flight together and are repeated until every word
-// carries the producer's tag (bounded).  A cheap one-word poll per warp comes first, so that CTAs that are
-// early do not flood the L2 with full-vector polls while the producers still work.
+// carries the producer's tag (bounded).  (A one-word sentinel poll before the full fetch was measured: it
+// costs one more L2 round trip per operator than it saves in polling traffic.)
 __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm, const PassOpBody& op, const int o,
                                          const uint32_t xtag, const int first, const int limit, uint4 (&xv)[3]) {
 #pragma unroll
@@ -274,16 +274,6 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
         return;
     }
     const long long t_begin = clock64();
-    if ((threadIdx.x & 31) == 0 && first < limit) {
-        while ((uint32_t)(ld_relaxed_u64(op.xt + 4 * (size_t)first) >> 32) != xtag && *sm.s_dead == 0) {
-            if (clock64() - t_begin > (1ll << 31)) {
-                atomicCAS(p.ws.err, 0, 0x20000 | o);   // the input of operator o never arrived
-                *sm.s_dead = 1;
-                break;
-            }
-            __nanosleep(40);
-        }
-    }
     __syncwarp();
     unsigned long long w[3][4] = {{0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}};
     for (;;) {
