@@ -39,7 +39,7 @@ constexpr int P_RING = 32;               // units in flight per SM (128 KB): two
 constexpr int P_MAXK = 12288;            // largest in_dim (activation vector kept in shared memory)
 constexpr int P_MAXK_NU = 4096;          // largest in_dim of an operator with j-dependent groups
 constexpr int P_MAX_GROUPS = 256;
-constexpr int P_RED_BYTES = 32768;       // cross-warp reduction (8 slots x 4 KB) / 32 attention states (16.9 KB)
+constexpr int P_RED_BYTES = 65536;       // cross-warp reduction (16 slots x 4 KB) / 32 attention states (16.9 KB)
 constexpr int P_OPW = 48;                // 32-bit words of a descriptor after its tensor map
 constexpr int P_DONE = 256;              // largest number of tiles / heads of an operator
 constexpr int P_MAX_OPS = 256;           // operators of one pass (their unit ranges are cached in shared memory)
@@ -48,8 +48,9 @@ constexpr int P_PSLOTS = WS_MAX_CTAS + P_DONE;   // partial-sum slots (CTA + til
 
 constexpr size_t P_OFF_RED = (size_t)P_RING * P_UNIT_BYTES;
 constexpr size_t P_OFF_XS = P_OFF_RED + P_RED_BYTES;
-constexpr size_t P_OFF_GIDX = P_OFF_XS + (size_t)P_MAXK * 2;
-constexpr size_t P_OFF_GTAB = P_OFF_GIDX + (size_t)P_MAXK_NU * 2;
+constexpr size_t P_OFF_GIDX = P_OFF_XS + (size_t)P_MAXK_NU * 2;   // inside xs: operators that use it have K <= P_MAXK_NU
+constexpr size_t P_OFF_GTAB = P_OFF_XS + (size_t)P_MAXK * 2;
+static_assert(2 * P_MAXK_NU <= P_MAXK, "the per-row group indices must fit behind the input vector");
 constexpr size_t P_OFF_MISC = P_OFF_GTAB + (size_t)P_MAX_GROUPS * 16;
 constexpr size_t P_OFF_RNG = P_OFF_MISC + 2048;                 // per-operator unit range of this CTA
 constexpr size_t P_SMEM_BYTES = P_OFF_RNG + (size_t)P_MAX_OPS * 16;
@@ -683,29 +684,15 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
 
         trace_event(p, o, 3);
         // ---- flush the tile: cross-warp reduction in a fixed order ------------------------------
-        // red[slot][lane][32 floats], 16-byte chunks rotated by the lane index (conflict-free 128-bit
-        // accesses).  Warps 0-7 store, warps 8-15 add on top, then every thread sums the 8 slots.
+        // red[warp][lane][32 floats], 16-byte chunks rotated by the lane index (conflict-free 128-bit
+        // accesses).  Every warp stores its sums; after one barrier every thread adds the 16 slots of its pair.
         {
-            float4* mine = reinterpret_cast<float4*>(sm.red) + (warp & 7) * (P_TI / 4) + lane * 8;
-            float4 v[8];
+            float4* mine = reinterpret_cast<float4*>(sm.red) + warp * (P_TI / 4) + lane * 8;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {   // outputs 4*ch .. 4*ch+3 of this lane's 32
                 const int wd = ch >> 1, d0 = ch & 1;   // nibbles 4*d0 + {0,1,2,3} = (h0,d0) (h0,d0+2) (h1,d0) (h1,d0+2)
-                v[ch] = make_float4(acc[wd][0][d0], acc[wd][0][d0 + 2], acc[wd][1][d0], acc[wd][1][d0 + 2]);
+                mine[(ch + lane) & 7] = make_float4(acc[wd][0][d0], acc[wd][0][d0 + 2], acc[wd][1][d0], acc[wd][1][d0 + 2]);
             }
-            if (warp >= 8) named_barrier(2, P_NCONS);          // wait for the stores of warps 0-7
-            if (warp >= 8) {
-                float4 w[8];
-#pragma unroll
-                for (int ch = 0; ch < 8; ++ch) w[ch] = mine[(ch + lane) & 7];
-#pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    v[ch].x += w[ch].x; v[ch].y += w[ch].y; v[ch].z += w[ch].z; v[ch].w += w[ch].w;
-                }
-            }
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) mine[(ch + lane) & 7] = v[ch];
-            if (warp < 8) named_barrier(2, P_NCONS);
 #pragma unroll
             for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -721,7 +708,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             tot[0] = 0.0f;
             tot[1] = 0.0f;
 #pragma unroll
-            for (int sl = 0; sl < 8; ++sl) {
+            for (int sl = 0; sl < P_NCW; ++sl) {
                 const float2 t2 = *reinterpret_cast<const float2*>(sm.red + sl * P_TI + fidx);
                 tot[0] += t2.x;
                 tot[1] += t2.y;
