@@ -714,7 +714,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
                 tot[1] += t2.y;
             }
         }
-        named_barrier(1, P_NCONS);
+        if (k + seg < n_units) named_barrier(1, P_NCONS);   // another tile follows: its flush reuses the slots
         trace_event(p, o, 4);
 
         // ---- cross-CTA fix-up --------------------------------------------------------------------
@@ -746,7 +746,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         const int n = cl - cf + 1, pb = pp - tid;
         const int cnt = (P_TI / 2) * (c - cf + 1) / n - pb, total = n * cnt;   // (contributor, pair) words to fetch
         // all threads fetch: word idx = contributor * cnt + pair, so that every load is in flight at once
-        float2* stage = reinterpret_cast<float2*>(sm.red);
+        float2* stage = reinterpret_cast<float2*>(sm.xs);   // the input vector is no longer needed (unit loop is over)
         for (int base = 0; base < total; base += 2 * P_NCONS) {
             const int i0 = base + tid, i1 = i0 + P_NCONS;
             const bool h0 = i0 < total, h1 = i1 < total;
@@ -783,6 +783,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         epilogue(tile_s, pp, s0, s1, active);
         named_barrier(1, P_NCONS);   // stage is reused by the next shared tile
     }
+    if (n_shared == 0) named_barrier(1, P_NCONS);   // every operator ends with a CTA barrier (see the operator loop)
     trace_event(p, o, 6);
     if (op.flags & PASS_PUBLISH) publish(p, o);   // this CTA's outputs of the operator are written
     trace_event(p, o, 7);
@@ -1047,6 +1048,7 @@ trace_event(p, o, 3);
         trace_event(p, o, 6);
         named_barrier(1, P_NCONS);   // st is reused by the next item
     }
+    if (c >= heads * S) named_barrier(1, P_NCONS);   // CTAs without an item: every operator ends with a CTA barrier
     if (op.flags & PASS_PUBLISH) publish(p, o);
 }
 
@@ -1081,6 +1083,7 @@ __device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBod
             st_relaxed_u64(op.yt + (i >> 1), ((unsigned long long)tag << 32) | pair);
         }
     }
+    named_barrier(1, P_NCONS);   // every operator ends with a CTA barrier
     if (op.flags & PASS_PUBLISH) publish(p, o);
 }
 
@@ -1131,9 +1134,11 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
     const int pos = __ldcg(p.d_pos);
     if (tid < P_OPW) sm.s_op[tid] = reinterpret_cast<const uint32_t*>(&p.ops[0].b)[tid];
     int uc_base = 0;
+    named_barrier(1, P_NCONS);   // descriptor of operator 0
     for (int o = 0; o < p.n_ops; ++o) {
+        // Every operator ends with a CTA barrier after its last use of shared memory: the descriptor of this
+        // operator (copied during the one before) is visible, and the buffer of the one before is free.
         trace_event(p, o, 0);
-        named_barrier(1, P_NCONS);   // the descriptor of this operator (copied during the previous one) is visible
         if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
