@@ -83,7 +83,7 @@ def _check_against_oracle(got, y32, y16, what):
     tol = RTOL * np.abs(y32) + RTOL * np.abs(y32).mean()
     assert (err <= tol).all(), f"{what}: max err {err.max()} vs oracle"
     # fp16 results: equal, or one ulp apart where the fp32 sum sits on a rounding boundary; outputs
-    # that cancel to almost nothing are judged on absolute error (an ulp there is far below the
+    # that cancel to almost nothing are compared on absolute error (an ulp there is far below the
     # fp32 summation noise of the terms that cancelled).
     ulps = _ulp_diff(got, y16)
     tiny = np.abs(got.astype(np.float32) - y16.astype(np.float32)) <= 1e-4 * np.abs(y32).mean()
@@ -160,7 +160,7 @@ def test_gemv_epilogues(ops, orc, cuda):
     ops.gemv_w4a16(w, ws, ops.gemv_args(xd, epilogue=ops.cabi.EPI_GELU, y=y, gamma=gd))
     got = y.cpu().numpy()
     # a one-ulp difference of the GEMV result may move the GeLU output by a few ulps where GeLU is
-    # steep relative to its value (negative tail); judge those on absolute error
+    # steep relative to its value (negative tail); compare those on absolute error
     d = _ulp_diff(got, want)
     near = np.abs(got.astype(np.float32) - want.astype(np.float32)) <= 1e-3 * np.abs(want.astype(np.float32)).mean()
     assert ((d <= 2) | near).all() and (d > 0).mean() < 0.02
