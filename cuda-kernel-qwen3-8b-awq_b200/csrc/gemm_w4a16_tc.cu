@@ -4,14 +4,14 @@
 // feeds prompts token by token through cublasGemmEx at n = 1 (Inference.cu:1304-1343, 1052-1065);
 // this is the same product for `rows` tokens at once.
 //
-// One CTA computes a tile of 128 outputs x N rows of X (N = 16..256).  Six warps:
+// One CTA computes a tile of 128 outputs x N rows of X (N = 16..256).  Eighteen warps:
 //   warp 0      TMA producer: per 64-deep K block one box of packed nibbles [64 rows][64 B] and one
 //               box of activations [N][64] (128-byte swizzle, K-major operand B)
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
-//   warps 2..5  unpack the nibbles to fp16 with the reference's two roundings and write operand A
+//   warps 2..17 unpack the nibbles (four groups of four warps take the K blocks in turn) to fp16 with the reference's two roundings and write operand A
 //               to shared memory in the MN-major 128-byte-swizzled canonical layout (outputs are
 //               contiguous in the packed stream, so MN-major needs no transposition); afterwards the
-//               same four warps read the accumulators back (tcgen05.ld) and store Y as fp16.
+//               same warps read the accumulators back (tcgen05.ld) and store Y as fp16.
 // Within every group of 8 outputs the rows of A are stored in the order the lop3 unpack yields them
 // (0,4,1,5,2,6,3,7); the epilogue undoes that permutation when it computes the output index.
 // All mbarrier waits are bounded; a wait that gives up sets the workspace error word.
@@ -29,9 +29,15 @@ constexpr int GM_TILE_M = 128;                 // outputs per CTA
 constexpr int GM_BK = 64;                      // K per pipeline stage
 constexpr int GM_PACKED_BYTES = GM_BK * GM_TILE_M / 2;   // 4096
 constexpr int GM_A_BYTES = GM_TILE_M * GM_BK * 2;        // 16384
-constexpr int GM_LD_STAGES = 4;
-constexpr int GM_A_STAGES = 3;
-constexpr int GM_THREADS = 192;
+constexpr int GM_MAX_STAGES = 24;              // mbarrier slots per ring
+constexpr int GM_A_STAGES = 6;                 // unpacked operand-A ring (16 KB each): released by the MMAs' commit
+                                               // (the activation ring, released by the same commit, and the packed-nibble
+                                               // ring, released by the unpack warps, are template parameters: a 64-row box
+                                               // of 64-byte pieces takes ~3 us to arrive, so the nibble ring is made as
+                                               // deep as shared memory allows)
+constexpr int GM_UNPACK_WARPS = 16;           // unpack / epilogue warps: four groups of four, taking K blocks in turn
+                                              // (an unpack warp is latency-bound on its own chain: more groups, more K blocks in flight)
+constexpr int GM_THREADS = 64 + 32 * GM_UNPACK_WARPS + 32;   // + the activation producer warp
 
 struct GemmParams {
     const __half* scale;
@@ -40,8 +46,13 @@ struct GemmParams {
     int uniform, exact;
     int rows;          // rows of X / Y
     int n_tile;        // UMMA N: 16..256, multiple of 16
-    int tmem_cols;     // power of two >= max(32, n_tile)
+    int tmem_cols;     // power of two >= n_acc * acc_stride
+    int n_acc;         // accumulators in tensor memory (1, 2 or 4): the MMAs of a K block go to different ones, so
+                       // that they do not wait for each other (an MMA into the same accumulator is ~240 cycles
+                       // behind the one before, whatever N); the epilogue adds them in a fixed order
+    int acc_stride;    // columns between accumulators
     __half* y;         // [rows][M]
+    float* part;       // split-K: fp32 partial products [splits][rows][M] (null: one split, y is written directly)
     int* err;
     int a_lbo, a_sbo, a_kstep;   // operand A descriptor: byte offsets between 64-output blocks, between 8-deep K blocks, per K=16 step
 };
@@ -91,31 +102,41 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+template <int GM_X_STAGES, int GM_W_STAGES>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int x_bytes = p.n_tile * 128;                                   // [n_tile][64] fp16
+    static_assert(GM_X_STAGES <= GM_MAX_STAGES && GM_W_STAGES <= GM_MAX_STAGES && GM_A_STAGES >= GM_UNPACK_WARPS / 4, "ring depths");
     uint8_t* a_st = smem;                                                 // GM_A_STAGES x 16 KB (1024-aligned)
-    uint8_t* x_st = smem + GM_A_STAGES * GM_A_BYTES;                      // GM_LD_STAGES x x_bytes (multiple of 1024)
-    uint8_t* w_st = x_st + GM_LD_STAGES * x_bytes;                        // GM_LD_STAGES x 4 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(w_st + GM_LD_STAGES * GM_PACKED_BYTES);
-    const uint32_t ld_full = smem_u32(bars), ld_empty = smem_u32(bars + GM_LD_STAGES);
-    const uint32_t a_full = smem_u32(bars + 2 * GM_LD_STAGES), a_empty = smem_u32(bars + 2 * GM_LD_STAGES + GM_A_STAGES);
-    const uint32_t acc_full = smem_u32(bars + 2 * GM_LD_STAGES + 2 * GM_A_STAGES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GM_LD_STAGES + 2 * GM_A_STAGES + 1);
-    int* s_dead = reinterpret_cast<int*>(tmem_slot + 1);
+    uint8_t* x_st = smem + GM_A_STAGES * GM_A_BYTES;                      // GM_X_STAGES x x_bytes (multiple of 1024)
+    uint8_t* w_st = x_st + GM_X_STAGES * x_bytes;                         // GM_W_STAGES x 4 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_st + GM_W_STAGES * GM_PACKED_BYTES);
+    const uint32_t w_full = smem_u32(bars), w_empty = smem_u32(bars + GM_MAX_STAGES);
+    const uint32_t a_full = smem_u32(bars + 2 * GM_MAX_STAGES), a_empty = smem_u32(bars + 3 * GM_MAX_STAGES);
+    const uint32_t x_full = smem_u32(bars + 4 * GM_MAX_STAGES), x_empty = smem_u32(bars + 5 * GM_MAX_STAGES);
+    const uint32_t acc_full = smem_u32(bars + 6 * GM_MAX_STAGES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 * GM_MAX_STAGES + 1);
+    int* s_dead = reinterpret_cast<int*>(tmem_slot + 1);   // bars: (6 * 24 + 2) * 8 bytes < 1280
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile_m = blockIdx.x, tile_n = blockIdx.y;
-    const int n_kb = p.K / GM_BK;
+    // split-K: grid.z CTAs share the K blocks of a tile; each handles [kb_lo, kb_lo + n_kb)
+    const int n_kb_all = p.K / GM_BK;
+    const int kb_lo = (int)((long long)blockIdx.z * n_kb_all / gridDim.z);
+    const int n_kb = (int)((long long)(blockIdx.z + 1) * n_kb_all / gridDim.z) - kb_lo;
 
     if (tid == 0) {
-        for (int s = 0; s < GM_LD_STAGES; ++s) {
-            mbar_init(ld_full + 8 * s, 1);
-            mbar_init(ld_empty + 8 * s, 5);     // 4 unpack warps + 1 commit of the MMAs that read X
+        for (int s = 0; s < GM_W_STAGES; ++s) {
+            mbar_init(w_full + 8 * s, 1);
+            mbar_init(w_empty + 8 * s, 4);      // the 4 unpack warps of the group that owns the K block
+        }
+        for (int s = 0; s < GM_X_STAGES; ++s) {
+            mbar_init(x_full + 8 * s, 1);
+            mbar_init(x_empty + 8 * s, 1);      // commit of the MMAs that read X
         }
         for (int s = 0; s < GM_A_STAGES; ++s) {
-            mbar_init(a_full + 8 * s, 4);       // 4 unpack warps
+            mbar_init(a_full + 8 * s, 4);       // the 4 unpack warps of the group that owns the K block
             mbar_init(a_empty + 8 * s, 1);      // commit of the MMAs that read A
         }
         mbar_init(acc_full, 1);
@@ -135,28 +156,54 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         // ---------------- TMA producer ----------------------------------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_w);
+            // packed nibbles: freed by the unpack warps (the activations have their own producer warp: one lane
+            // issues a bulk tensor copy every ~200 ns at best, and a K block needs one of each)
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; ++kb) {
+                const int s = kb % GM_W_STAGES;
+                if (kb >= GM_W_STAGES) ok = mbar_wait(w_empty + 8 * s, ((kb / GM_W_STAGES) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(w_full + 8 * s, (uint32_t)GM_PACKED_BYTES);
+                tma_load_2d(smem_u32(w_st + s * GM_PACKED_BYTES), &tmap_w, tile_m * (GM_TILE_M / 2), (kb_lo + kb) * GM_BK, w_full + 8 * s);
+            }
+            if (!ok) {
+                atomicCAS(p.err, 0, 0x30001);
+                *s_dead = 1;
+            }
+        }
+    } else if (warp == GM_THREADS / 32 - 1) {
+        // ---------------- TMA producer of the activations ------------------------------------------
+        if (lane == 0) {
             tma_prefetch_desc(&tmap_x);
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % GM_LD_STAGES;
-                if (kb >= GM_LD_STAGES && !mbar_wait(ld_empty + 8 * s, ((kb / GM_LD_STAGES) - 1) & 1)) {
-                    atomicCAS(p.err, 0, 0x30001);
-                    *s_dead = 1;
-                    break;
-                }
-                mbar_expect_tx(ld_full + 8 * s, (uint32_t)(GM_PACKED_BYTES + x_bytes));
-                tma_load_2d(smem_u32(w_st + s * GM_PACKED_BYTES), &tmap_w, tile_m * (GM_TILE_M / 2), kb * GM_BK, ld_full + 8 * s);
-                tma_load_2d(smem_u32(x_st + s * x_bytes), &tmap_x, kb * GM_BK, tile_n * p.n_tile, ld_full + 8 * s);
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; ++kb) {
+                const int s = kb % GM_X_STAGES;
+                if (kb >= GM_X_STAGES) ok = mbar_wait(x_empty + 8 * s, ((kb / GM_X_STAGES) - 1) & 1);   // freed by the MMAs' commit
+                if (!ok) break;
+                mbar_expect_tx(x_full + 8 * s, (uint32_t)x_bytes);
+                tma_load_2d(smem_u32(x_st + s * x_bytes), &tmap_x, (kb_lo + kb) * GM_BK, tile_n * p.n_tile, x_full + 8 * s);
+            }
+            if (!ok) {
+                atomicCAS(p.err, 0, 0x30005);
+                *s_dead = 1;
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer -------------------------------------------------------------
         // instruction descriptor: D = f32, A = B = f16, A MN-major (bit 15), B K-major, N >> 3, M >> 4
         const uint32_t idesc = (1u << 4) | (1u << 15) | ((uint32_t)(p.n_tile >> 3) << 17) | ((uint32_t)(GM_TILE_M >> 4) << 24);
+        // One lane issues everything, so its instruction chain per K block sets the rate for small row tiles:
+        // ring indices and phases are running counters, and the descriptors are a constant high word plus a
+        // low word advanced by additions.
+        const uint64_t adesc0 = make_smem_desc(smem_u32(a_st), p.a_lbo, p.a_sbo);
+        const uint64_t bdesc0 = make_smem_desc(smem_u32(x_st), 16, 1024);
+        const uint32_t a_step = (uint32_t)(p.a_kstep >> 4), a_stage = (uint32_t)(GM_A_BYTES >> 4), x_stage = (uint32_t)(x_bytes >> 4);
+        int s = 0, t = 0;
+        uint32_t s_phase = 0, t_phase = 0;
         for (int kb = 0; kb < n_kb; ++kb) {
-            const int s = kb % GM_LD_STAGES, t = kb % GM_A_STAGES;
             bool ok = true;
             if (*s_dead == 0) {
-                ok = mbar_wait(ld_full + 8 * s, (kb / GM_LD_STAGES) & 1) && mbar_wait(a_full + 8 * t, (kb / GM_A_STAGES) & 1);
+                ok = mbar_wait(x_full + 8 * s, s_phase) && mbar_wait(a_full + 8 * t, t_phase);
                 if (!ok && lane == 0) {
                     atomicCAS(p.err, 0, 0x30002);
                     *s_dead = 1;
@@ -166,24 +213,28 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             if (*s_dead != 0) break;
             tc_fence_after();
             if (elect_one()) {
-                const uint32_t a_addr = smem_u32(a_st + t * GM_A_BYTES), b_addr = smem_u32(x_st + s * x_bytes);
+                // A (MN-major): 64-output blocks 8 KB apart (LBO), 8-deep K blocks 1 KB apart (SBO); K=16 = 2 blocks
+                // B (K-major): 8-row groups 1 KB apart (SBO); K=16 = 32 bytes inside the swizzled row
+                const uint64_t adesc = adesc0 + (uint64_t)((uint32_t)t * a_stage);
+                const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)s * x_stage);
 #pragma unroll
                 for (int ks = 0; ks < GM_BK / 16; ++ks) {
-                    // A (MN-major): 64-output blocks 8 KB apart (LBO), 8-deep K blocks 1 KB apart (SBO); K=16 = 2 blocks
-                    const uint64_t adesc = make_smem_desc(a_addr + ks * p.a_kstep, p.a_lbo, p.a_sbo);
-                    // B (K-major): 8-row groups 1 KB apart (SBO); K=16 = 32 bytes inside the swizzled row
-                    const uint64_t bdesc = make_smem_desc(b_addr + ks * 32, 16, 1024);
-                    umma_f16(tmem_base, adesc, bdesc, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    const int acc = ks & (p.n_acc - 1);
+                    umma_f16(tmem_base + (uint32_t)(acc * p.acc_stride), adesc + (uint64_t)(ks * a_step), bdesc + (uint64_t)(ks * 2), idesc,
+                             (kb > 0 || ks >= p.n_acc) ? 1u : 0u);
                 }
                 umma_commit(a_empty + 8 * t);    // A stage free once these MMAs have read it
-                umma_commit(ld_empty + 8 * s);   // X stage likewise
+                umma_commit(x_empty + 8 * s);    // X stage likewise
                 if (kb == n_kb - 1) umma_commit(acc_full);
             }
             __syncwarp();
+            if (++s == GM_X_STAGES) { s = 0; s_phase ^= 1u; }
+            if (++t == GM_A_STAGES) { t = 0; t_phase ^= 1u; }
         }
     } else {
-        // ---------------- unpack warps (2..5), then epilogue ------------------------------------
-        const int ut = tid - 64;                  // 0..127
+        // ---------------- unpack warps (2..17), then epilogue -----------------------------------
+        const int grp = (warp - 2) >> 2;          // group g unpacks the K blocks g, g + 4, ...
+        const int ut = (tid - 64) & 127;          // 0..127 inside the group
         const int c4 = ut & 3, krow = ut >> 2;    // 16-byte chunk (32 outputs) of a row; row 0..31 (+32)
         const int ib = tile_m;                    // the tile is exactly one block of 128 outputs
         const int ibk = ib % p.Kb;
@@ -193,9 +244,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             ku = p.exact ? make_const<true>(p.zp[g], p.scale[g]) : make_const<false>(p.zp[g], p.scale[g]);
         }
         bool dead = false;
-        for (int kb = 0; kb < n_kb && !dead; ++kb) {
-            const int s = kb % GM_LD_STAGES, t = kb % GM_A_STAGES;
-            if (!mbar_wait(ld_full + 8 * s, (kb / GM_LD_STAGES) & 1) ||
+        for (int kb = grp; kb < n_kb && !dead; kb += GM_UNPACK_WARPS / 4) {
+            const int s = kb % GM_W_STAGES, t = kb % GM_A_STAGES;
+            if (!mbar_wait(w_full + 8 * s, (kb / GM_W_STAGES) & 1) ||
                 (kb >= GM_A_STAGES && !mbar_wait(a_empty + 8 * t, ((kb / GM_A_STAGES) - 1) & 1))) {
                 if (lane == 0) atomicCAS(p.err, 0, 0x30003);
                 *s_dead = 1;
@@ -210,7 +261,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 const uint4 raw = *reinterpret_cast<const uint4*>(wsrc + k * 64 + c4 * 16);
                 DqConst kc = ku;
                 if (!p.uniform) {
-                    const long long j = (long long)kb * GM_BK + k;
+                    const long long j = (long long)(kb_lo + kb) * GM_BK + k;
                     int g = ibk + (int)((j * p.Mb) % p.Kb);
                     g -= g >= p.Kb ? p.Kb : 0;
                     g %= p.n_alloc;
@@ -237,7 +288,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(a_full + 8 * t);
-                mbar_arrive(ld_empty + 8 * s);
+                mbar_arrive(w_empty + 8 * s);
             }
         }
         // ---------------- epilogue: accumulators -> fp16 Y ----------------------------------------
@@ -253,13 +304,25 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             const int pos = m & 7;                            // position inside the 8-group, in unpack order
             const int nib = (pos >> 1) + ((pos & 1) << 2);    // 0,4,1,5,2,6,3,7
             const int i = tile_m * GM_TILE_M + (m & ~7) + nib;
-            for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+            // the warps of a lane quarter take the 16-column groups in turn
+            for (int c0 = 16 * ((warp - 2) >> 2); c0 < p.n_tile; c0 += 16 * (GM_UNPACK_WARPS / 4)) {
                 uint32_t v[16];
                 tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+                float f[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
+                for (int acc = 1; acc < p.n_acc; ++acc) {   // fixed order: accumulator 0 + 1 + 2 + 3
+                    tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(acc * p.acc_stride + c0), v);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) f[e] += __uint_as_float(v[e]);
+                }
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const int r = tile_n * p.n_tile + c0 + e;
-                    if (r < p.rows) p.y[(size_t)r * p.M + i] = __float2half_rn(__uint_as_float(v[e]));
+                    if (r < p.rows) {
+                        if (p.part != nullptr) p.part[((size_t)blockIdx.z * p.rows + r) * p.M + i] = f[e];
+                        else p.y[(size_t)r * p.M + i] = __float2half_rn(f[e]);
+                    }
                 }
             }
         }
@@ -270,6 +333,19 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
     }
+}
+
+// Split-K: sums the fp32 partial products of the splits in split order and rounds once to fp16.
+__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ part, int splits, long long n, __half* __restrict__ y) {
+    const long long i = 2 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
+    if (i >= n) return;
+    float2 acc = *reinterpret_cast<const float2*>(part + i);
+    for (int z = 1; z < splits; ++z) {
+        const float2 v = *reinterpret_cast<const float2*>(part + (size_t)z * n + i);
+        acc.x += v.x;
+        acc.y += v.y;
+    }
+    *reinterpret_cast<__half2*>(y + i) = __floats2half2_rn(acc.x, acc.y);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -320,7 +396,9 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     p.uniform = d->uniform; p.exact = d->zp_integral;
     p.rows = (int)rows;
     p.n_tile = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-    p.tmem_cols = p.n_tile < 32 ? 32 : p.n_tile;
+    p.n_acc = p.n_tile <= 64 ? 4 : p.n_tile <= 128 ? 2 : 1;
+    p.acc_stride = p.n_tile < 32 ? 32 : p.n_tile;
+    p.tmem_cols = p.n_acc * p.acc_stride;   // 128, 128, 256, 256, 256 columns: powers of two
     p.y = static_cast<__half*>(d_y);
     p.err = ws_struct(ws)->err;
     p.a_lbo = 8192; p.a_sbo = 1024; p.a_kstep = 2048;
@@ -333,16 +411,46 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     rc = encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d_x, (uint64_t)d->K, (uint64_t)rows, (uint64_t)d->K * 2, GM_BK,
                    (uint32_t)p.n_tile, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != QW3_OK) return rc;
-    const size_t smem = (size_t)GM_A_STAGES * GM_A_BYTES + (size_t)GM_LD_STAGES * (p.n_tile * 128 + GM_PACKED_BYTES) + 256;
+    // shared memory: 6 operand-A stages of 16 KB plus the two TMA rings, as deep as fits.  An activation stage is
+    // only released when the MMAs that read it have completed (load + wait + MMA + commit ~ 1.6 us), so the depth of
+    // that ring sets the K blocks per microsecond when the row tile is small.
+    const int x_stages = p.n_tile <= 32 ? 16 : p.n_tile <= 64 ? 8 : p.n_tile <= 128 ? 4 : 3;
+    const int w_stages = p.n_tile <= 128 ? 16 : 8;
+    const size_t smem = (size_t)GM_A_STAGES * GM_A_BYTES + (size_t)w_stages * GM_PACKED_BYTES + (size_t)x_stages * p.n_tile * 128 + 1280;
     static std::once_flag attr_once[16];
     int dev = 0;
     QW3_CUDA(cudaGetDevice(&dev));
     if (dev < 16)
         std::call_once(attr_once[dev], [] {
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<3, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         });
-    dim3 grid((unsigned)(d->M / GM_TILE_M), (unsigned)((rows + p.n_tile - 1) / p.n_tile));
-    gemm_w4a16_tc_kernel<<<grid, GM_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmap_w, tmap_x, p);
+    // Few rows and few output tiles leave most SMs without a CTA: split K over grid.z (fp32 partial products in the
+    // workspace, summed in split order by a second kernel) until ~one CTA per SM, while the partials fit.
+    const long long ctas = (d->M / GM_TILE_M) * ((rows + p.n_tile - 1) / p.n_tile);
+    const long long part_cap = (long long)(WS_MAX_CTAS + WS_MAX_TILES) * WS_TILE;   // floats in the workspace
+    int splits = 1;
+    while (splits < 8 && ctas * (splits * 2) <= ws_struct(ws)->sm_count && (p.K / GM_BK) / (splits * 2) >= 8 &&
+           (long long)(splits * 2) * rows * d->M <= part_cap)
+        splits *= 2;
+    p.part = splits > 1 ? ws_struct(ws)->partials : nullptr;
+    dim3 grid((unsigned)(d->M / GM_TILE_M), (unsigned)((rows + p.n_tile - 1) / p.n_tile), (unsigned)splits);
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (x_stages == 16)
+        gemm_w4a16_tc_kernel<16, 16><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+    else if (x_stages == 8)
+        gemm_w4a16_tc_kernel<8, 16><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+    else if (x_stages == 4)
+        gemm_w4a16_tc_kernel<4, 16><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+    else
+        gemm_w4a16_tc_kernel<3, 8><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
     QW3_CUDA(cudaGetLastError());
+    if (splits > 1) {
+        const long long n = rows * d->M;
+        gemm_splitk_reduce_kernel<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(p.part, splits, n, p.y);
+        QW3_CUDA(cudaGetLastError());
+    }
     return QW3_OK;
 }
