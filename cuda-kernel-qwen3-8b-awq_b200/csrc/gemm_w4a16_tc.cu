@@ -5,11 +5,12 @@
 // this is the same product for `rows` tokens at once.
 //
 // One CTA computes a tile of 128 outputs x N rows of X (N = 16..256).  Eighteen warps:
-//   warp 0      TMA producer: per 64-deep K block one box of packed nibbles [64 rows][64 B] and one
-//               box of activations [N][64] (128-byte swizzle, K-major operand B)
+//   warp 0      TMA producer: per 64-deep K block one box of activations [N][64] (128-byte swizzle, K-major
+//               operand B)
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
-//   warps 2..17 unpack the nibbles (four groups of four warps take the K blocks in turn) to fp16 with the reference's two roundings and write operand A
-//               to shared memory in the MN-major 128-byte-swizzled canonical layout (outputs are
+//   warps 2..17 read the packed nibbles of the tile straight from global memory (16 bytes per thread and row, one
+//               K block ahead; four groups of four warps take the K blocks in turn), unpack them to fp16 with
+//               the reference's two roundings and write operand A to shared memory in the MN-major 128-byte-swizzled canonical layout (outputs are
 //               contiguous in the packed stream, so MN-major needs no transposition); afterwards the
 //               same warps read the accumulators back (tcgen05.ld) and store Y as fp16.
 // Within every group of 8 outputs the rows of A are stored in the order the lop3 unpack yields them
@@ -27,7 +28,6 @@ const W4Desc* w4_desc(qw3_w4_t w);
 
 constexpr int GM_TILE_M = 128;                 // outputs per CTA
 constexpr int GM_BK = 64;                      // K per pipeline stage
-constexpr int GM_PACKED_BYTES = GM_BK * GM_TILE_M / 2;   // 4096
 constexpr int GM_A_BYTES = GM_TILE_M * GM_BK * 2;        // 16384
 constexpr int GM_MAX_STAGES = 24;              // mbarrier slots per ring
 constexpr int GM_A_STAGES = 6;                 // unpacked operand-A ring (16 KB each): released by the MMAs' commit
@@ -37,9 +37,10 @@ constexpr int GM_A_STAGES = 6;                 // unpacked operand-A ring (16 KB
                                                // deep as shared memory allows)
 constexpr int GM_UNPACK_WARPS = 16;           // unpack / epilogue warps: four groups of four, taking K blocks in turn
                                               // (an unpack warp is latency-bound on its own chain: more groups, more K blocks in flight)
-constexpr int GM_THREADS = 64 + 32 * GM_UNPACK_WARPS + 32;   // + the activation producer warp
+constexpr int GM_THREADS = 64 + 32 * GM_UNPACK_WARPS;
 
 struct GemmParams {
+    const uint8_t* packed;   // [K][M/2] bytes; the unpack warps read their 16-byte pieces straight from global memory
     const __half* scale;
     const __half* zp;
     int n_alloc, M, K, Mb, Kb;
@@ -102,17 +103,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int GM_X_STAGES, int GM_W_STAGES>
+template <int GM_X_STAGES>
 __global__ void __launch_bounds__(GM_THREADS, 1)
-gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int x_bytes = p.n_tile * 128;                                   // [n_tile][64] fp16
-    static_assert(GM_X_STAGES <= GM_MAX_STAGES && GM_W_STAGES <= GM_MAX_STAGES && GM_A_STAGES >= GM_UNPACK_WARPS / 4, "ring depths");
+    static_assert(GM_X_STAGES <= GM_MAX_STAGES && GM_A_STAGES >= GM_UNPACK_WARPS / 4, "ring depths");
     uint8_t* a_st = smem;                                                 // GM_A_STAGES x 16 KB (1024-aligned)
     uint8_t* x_st = smem + GM_A_STAGES * GM_A_BYTES;                      // GM_X_STAGES x x_bytes (multiple of 1024)
-    uint8_t* w_st = x_st + GM_X_STAGES * x_bytes;                         // GM_W_STAGES x 4 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(w_st + GM_W_STAGES * GM_PACKED_BYTES);
-    const uint32_t w_full = smem_u32(bars), w_empty = smem_u32(bars + GM_MAX_STAGES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_st + GM_X_STAGES * x_bytes);
     const uint32_t a_full = smem_u32(bars + 2 * GM_MAX_STAGES), a_empty = smem_u32(bars + 3 * GM_MAX_STAGES);
     const uint32_t x_full = smem_u32(bars + 4 * GM_MAX_STAGES), x_empty = smem_u32(bars + 5 * GM_MAX_STAGES);
     const uint32_t acc_full = smem_u32(bars + 6 * GM_MAX_STAGES);
@@ -127,10 +126,6 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const int n_kb = (int)((long long)(blockIdx.z + 1) * n_kb_all / gridDim.z) - kb_lo;
 
     if (tid == 0) {
-        for (int s = 0; s < GM_W_STAGES; ++s) {
-            mbar_init(w_full + 8 * s, 1);
-            mbar_init(w_empty + 8 * s, 4);      // the 4 unpack warps of the group that owns the K block
-        }
         for (int s = 0; s < GM_X_STAGES; ++s) {
             mbar_init(x_full + 8 * s, 1);
             mbar_init(x_empty + 8 * s, 1);      // commit of the MMAs that read X
@@ -153,26 +148,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------------------------------------------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap_w);
-            // packed nibbles: freed by the unpack warps (the activations have their own producer warp: one lane
-            // issues a bulk tensor copy every ~200 ns at best, and a K block needs one of each)
-            bool ok = true;
-            for (int kb = 0; kb < n_kb && ok; ++kb) {
-                const int s = kb % GM_W_STAGES;
-                if (kb >= GM_W_STAGES) ok = mbar_wait(w_empty + 8 * s, ((kb / GM_W_STAGES) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(w_full + 8 * s, (uint32_t)GM_PACKED_BYTES);
-                tma_load_2d(smem_u32(w_st + s * GM_PACKED_BYTES), &tmap_w, tile_m * (GM_TILE_M / 2), (kb_lo + kb) * GM_BK, w_full + 8 * s);
-            }
-            if (!ok) {
-                atomicCAS(p.err, 0, 0x30001);
-                *s_dead = 1;
-            }
-        }
-    } else if (warp == GM_THREADS / 32 - 1) {
         // ---------------- TMA producer of the activations ------------------------------------------
+        // (the packed nibbles do not go through TMA: a 128-output tile is 64 bytes wide, and a box of 64 such rows
+        // cost the copy engine more per K block than everything else in the CTA)
         if (lane == 0) {
             tma_prefetch_desc(&tmap_x);
             bool ok = true;
@@ -184,7 +162,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 tma_load_2d(smem_u32(x_st + s * x_bytes), &tmap_x, (kb_lo + kb) * GM_BK, tile_n * p.n_tile, x_full + 8 * s);
             }
             if (!ok) {
-                atomicCAS(p.err, 0, 0x30005);
+                atomicCAS(p.err, 0, 0x30001);
                 *s_dead = 1;
             }
         }
@@ -244,21 +222,33 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             ku = p.exact ? make_const<true>(p.zp[g], p.scale[g]) : make_const<false>(p.zp[g], p.scale[g]);
         }
         bool dead = false;
+        // this thread's two 16-byte pieces of a K block (rows krow and krow + 32), requested one own block ahead
+        const size_t pitch = (size_t)p.M / 2;
+        const uint8_t* gsrc = p.packed + (size_t)tile_m * (GM_TILE_M / 2) + c4 * 16;
+        auto request = [&](const int kb, uint4 (&dst)[2]) {
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                const size_t row = (size_t)(kb_lo + kb) * GM_BK + krow + pass * 32;
+                dst[pass] = kb < n_kb ? __ldg(reinterpret_cast<const uint4*>(gsrc + row * pitch)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        uint4 nxt[2];
+        request(grp, nxt);
         for (int kb = grp; kb < n_kb && !dead; kb += GM_UNPACK_WARPS / 4) {
-            const int s = kb % GM_W_STAGES, t = kb % GM_A_STAGES;
-            if (!mbar_wait(w_full + 8 * s, (kb / GM_W_STAGES) & 1) ||
-                (kb >= GM_A_STAGES && !mbar_wait(a_empty + 8 * t, ((kb / GM_A_STAGES) - 1) & 1))) {
+            const int t = kb % GM_A_STAGES;
+            const uint4 cur[2] = {nxt[0], nxt[1]};
+            request(kb + GM_UNPACK_WARPS / 4, nxt);
+            if (kb >= GM_A_STAGES && !mbar_wait(a_empty + 8 * t, ((kb / GM_A_STAGES) - 1) & 1)) {
                 if (lane == 0) atomicCAS(p.err, 0, 0x30003);
                 *s_dead = 1;
                 dead = true;
                 break;
             }
-            const uint8_t* wsrc = w_st + s * GM_PACKED_BYTES;
             uint8_t* adst = a_st + t * GM_A_BYTES + (c4 >> 1) * 8192;
 #pragma unroll
             for (int pass = 0; pass < 2; ++pass) {
                 const int k = krow + pass * 32;
-                const uint4 raw = *reinterpret_cast<const uint4*>(wsrc + k * 64 + c4 * 16);
+                const uint4 raw = cur[pass];
                 DqConst kc = ku;
                 if (!p.uniform) {
                     const long long j = (long long)(kb_lo + kb) * GM_BK + k;
@@ -286,10 +276,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             // generic-proxy writes of A must be visible to the tensor core (async proxy) before the arrive
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(a_full + 8 * t);
-                mbar_arrive(w_empty + 8 * s);
-            }
+            if (lane == 0) mbar_arrive(a_full + 8 * t);
         }
         // ---------------- epilogue: accumulators -> fp16 Y ----------------------------------------
         if (!dead && *s_dead == 0 && !mbar_wait(acc_full, 0)) {
@@ -391,6 +378,7 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     QW3_REQUIRE((reinterpret_cast<uintptr_t>(d_x) & 15) == 0, "qw3_gemm_w4a16: X must be 16-byte aligned");
     const W4Desc* d = w4_desc(w);
     GemmParams p = {};
+    p.packed = d->packed;
     p.scale = d->scale; p.zp = d->zp; p.n_alloc = (int)d->n_alloc;
     p.M = (int)d->M; p.K = (int)d->K; p.Mb = p.M / 128; p.Kb = p.K / 128;
     p.uniform = d->uniform; p.exact = d->zp_integral;
@@ -404,28 +392,24 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     p.a_lbo = 8192; p.a_sbo = 1024; p.a_kstep = 2048;
     if (const char* e = std::getenv("QW3_GEMM_A_LBO")) p.a_lbo = std::atoi(e);
     if (const char* e = std::getenv("QW3_GEMM_A_SBO")) p.a_sbo = std::atoi(e);
-    CUtensorMap tmap_w, tmap_x;
-    int rc = encode_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->packed, (uint64_t)d->M / 2, (uint64_t)d->K, (uint64_t)d->M / 2,
-                       GM_TILE_M / 2, GM_BK, CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != QW3_OK) return rc;
+    CUtensorMap tmap_x;
+    int rc;
     rc = encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d_x, (uint64_t)d->K, (uint64_t)rows, (uint64_t)d->K * 2, GM_BK,
                    (uint32_t)p.n_tile, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != QW3_OK) return rc;
-    // shared memory: 6 operand-A stages of 16 KB plus the two TMA rings, as deep as fits.  An activation stage is
-    // only released when the MMAs that read it have completed (load + wait + MMA + commit ~ 1.6 us), so the depth of
-    // that ring sets the K blocks per microsecond when the row tile is small.
+    // shared memory: 6 operand-A stages of 16 KB plus the activation ring.  An activation stage is only released when
+    // the MMAs that read it have completed, so that ring is made deep for small row tiles.
     const int x_stages = p.n_tile <= 32 ? 16 : p.n_tile <= 64 ? 8 : p.n_tile <= 128 ? 4 : 3;
-    const int w_stages = p.n_tile <= 128 ? 16 : 8;
-    const size_t smem = (size_t)GM_A_STAGES * GM_A_BYTES + (size_t)w_stages * GM_PACKED_BYTES + (size_t)x_stages * p.n_tile * 128 + 1280;
+    const size_t smem = (size_t)GM_A_STAGES * GM_A_BYTES + (size_t)x_stages * p.n_tile * 128 + 1280;
     static std::once_flag attr_once[16];
     int dev = 0;
     QW3_CUDA(cudaGetDevice(&dev));
     if (dev < 16)
         std::call_once(attr_once[dev], [] {
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<3, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         });
     // Few rows and few output tiles leave most SMs without a CTA: split K over grid.z (fp32 partial products in the
     // workspace, summed in split order by a second kernel) until ~one CTA per SM, while the partials fit.
@@ -439,13 +423,13 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     dim3 grid((unsigned)(d->M / GM_TILE_M), (unsigned)((rows + p.n_tile - 1) / p.n_tile), (unsigned)splits);
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (x_stages == 16)
-        gemm_w4a16_tc_kernel<16, 16><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+        gemm_w4a16_tc_kernel<16><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
     else if (x_stages == 8)
-        gemm_w4a16_tc_kernel<8, 16><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+        gemm_w4a16_tc_kernel<8><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
     else if (x_stages == 4)
-        gemm_w4a16_tc_kernel<4, 16><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+        gemm_w4a16_tc_kernel<4><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
     else
-        gemm_w4a16_tc_kernel<3, 8><<<grid, GM_THREADS, smem, st>>>(tmap_w, tmap_x, p);
+        gemm_w4a16_tc_kernel<3><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
     QW3_CUDA(cudaGetLastError());
     if (splits > 1) {
         const long long n = rows * d->M;
