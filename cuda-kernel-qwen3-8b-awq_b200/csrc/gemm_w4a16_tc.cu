@@ -222,7 +222,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
             ku = p.exact ? make_const<true>(p.zp[g], p.scale[g]) : make_const<false>(p.zp[g], p.scale[g]);
         }
         bool dead = false;
-        // this thread's two 16-byte pieces of a K block (rows krow and krow + 32), requested one own block ahead
+        // this thread's two 16-byte pieces of a K block (rows krow and krow + 32), requested two own blocks ahead
         const size_t pitch = (size_t)p.M / 2;
         const uint8_t* gsrc = p.packed + (size_t)tile_m * (GM_TILE_M / 2) + c4 * 16;
         auto request = [&](const int kb, uint4 (&dst)[2]) {
@@ -232,12 +232,15 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
                 dst[pass] = kb < n_kb ? __ldg(reinterpret_cast<const uint4*>(gsrc + row * pitch)) : make_uint4(0u, 0u, 0u, 0u);
             }
         };
-        uint4 nxt[2];
+        uint4 nxt[2], nxt2[2];   // two own K blocks in flight
         request(grp, nxt);
+        request(grp + GM_UNPACK_WARPS / 4, nxt2);
         for (int kb = grp; kb < n_kb && !dead; kb += GM_UNPACK_WARPS / 4) {
             const int t = kb % GM_A_STAGES;
             const uint4 cur[2] = {nxt[0], nxt[1]};
-            request(kb + GM_UNPACK_WARPS / 4, nxt);
+            nxt[0] = nxt2[0];
+            nxt[1] = nxt2[1];
+            request(kb + 2 * (GM_UNPACK_WARPS / 4), nxt2);
             if (kb >= GM_A_STAGES && !mbar_wait(a_empty + 8 * t, ((kb / GM_A_STAGES) - 1) & 1)) {
                 if (lane == 0) atomicCAS(p.err, 0, 0x30003);
                 *s_dead = 1;
