@@ -14,13 +14,17 @@
 //     never depend on activations.  The ring is therefore full again by the time the warps have
 //     crossed an operator boundary, and no empty-slot barrier exists;
 //   * the warps take units round-robin (no stage-wide lock-step), unpack and accumulate exactly
-//     as the stand-alone GEMV does, and finish a tile with the same deterministic fix-up
-//     (partials in CTA order, last arriver runs the epilogue);
-//   * operators are chained by arrival counters in global memory: the CTA that finalises a tile
-//     (or an attention head) publishes it with a fence + atomic, consumers of the next operator
-//     wait with a bounded acquire-poll.  All CTAs are co-resident (cooperative launch), so the
-//     waits cannot deadlock; every wait gives up after about a second and reports an error.
-// Activations written inside the kernel are read with ld.global.cg (L1 is not coherent across SMs).
+//     as the stand-alone GEMV does, and reduce across warps once per tile in a fixed order;
+//   * everything that crosses CTAs inside the launch travels as tagged 64-bit words -- (payload, tag) in
+//     one aligned store, tag = launch epoch * 1024 + operator index -- which the reader polls: seeing the
+//     tag means having the value, so there is no flag, fence or second round trip, and nothing is cleared
+//     between launches.  Partial sums of a tile shared by several CTAs: every contributor stores its sums
+//     and later gathers, for its own share of the tile's outputs, the words of all contributors in CTA
+//     order (deterministic) and runs the epilogue there.  Activations: the epilogue stores (two halves,
+//     tag) per output pair, the next operator's prologue polls them.  The only arrival counter left
+//     precedes the final arg-max.  All CTAs are co-resident (cooperative launch), so the polls cannot
+//     deadlock; every poll gives up after about a second and reports a located error word.
+// Plain activations written inside the kernel (for readers after the launch) are never read back in it.
 #include <cstdlib>
 #include <cstring>
 
@@ -125,19 +129,8 @@ __device__ __forceinline__ void trace_event(const PassParams& p, int o, int ev) 
     }
 }
 
-__device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
-    int old;   // release: the CTA's earlier writes (ordered before by the CTA barrier) are published; acquire: the
-               // writes published by the other arrivals are visible to this CTA after its next barrier
-    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-    return old;
-}
 __device__ __forceinline__ void red_add_release(int* p, int v) {
     asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Publishing is a plain release store (no read-modify-write round trip): after the CTA barrier it
-// orders every write of the CTA before the flag.
-__device__ __forceinline__ void st_release(int* p, int v) {
-    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Partial sums cross CTAs as (value, tag) words: the tag names the launch and the operator, value and tag
@@ -956,7 +949,7 @@ __device__ __forceinline__ void attn_phase(const PassParams& p, const PassOpBody
                 }
             }
         }
-trace_event(p, o, 3);
+        trace_event(p, o, 3);
 #pragma unroll
         for (int e = 0; e < 8; ++e) st[grp * WS_ATT_STRIDE + sl * 8 + e] = ov[e];
         if (sl == 0) {
@@ -1250,10 +1243,6 @@ void pass_link(PassOp* op, int flags, int src, const void* xt, void* yt, const v
 size_t pass_op_bytes() { return sizeof(PassOp); }
 // Exchange buffer of tagged partial sums: one 1024-word slot per (CTA, tile) pair c + tile.
 size_t pass_xchg_bytes() { return 2 * (size_t)P_PSLOTS * P_TI * sizeof(unsigned long long); }
-
-struct PassLaunch {
-    PassParams p;
-};
 
 // Enqueues one pass: clears the arrival counters, then one cooperative launch.  The caller increments
 // *d_epoch on the same stream afterwards.
