@@ -88,6 +88,20 @@ __device__ __forceinline__ __half h_mul(__half a, __half b) {
         : "h"(*reinterpret_cast<unsigned short*>(&a)), "h"(*reinterpret_cast<unsigned short*>(&b)));
     return r;
 }
+__device__ __forceinline__ __half h_fma(__half a, __half b, __half c) {
+    __half r;
+    asm("fma.rn.f16 %0, %1, %2, %3;" : "=h"(*reinterpret_cast<unsigned short*>(&r))
+        : "h"(*reinterpret_cast<unsigned short*>(&a)), "h"(*reinterpret_cast<unsigned short*>(&b)),
+          "h"(*reinterpret_cast<unsigned short*>(&c)));
+    return r;
+}
+// Interleaved-pair rotation of applyRotaryKernel (Inference.cu:172-173) as the reference's build executes it: the
+// intrinsics emit mul.f16 / sub.f16 / add.f16 without a rounding modifier and the compiler contracts the first
+// product of each line into the add; the second product keeps its own rounding.  Bit-equal to the compiled kernel.
+__device__ __forceinline__ void rope_pair(__half x0, __half x1, __half cs, __half sn, __half& o0, __half& o1) {
+    o0 = h_fma(x0, cs, __hneg(h_mul(x1, sn)));
+    o1 = h_fma(x0, sn, h_mul(x1, cs));
+}
 __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));

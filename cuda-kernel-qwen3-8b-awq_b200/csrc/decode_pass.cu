@@ -454,8 +454,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
                 if (sec < 2) {
                     const __half cs = tile_e == t0 ? __ushort_as_half((unsigned short)pre_a) : p.cos_t[(size_t)pos * 64 + (d >> 1)];
                     const __half sn = tile_e == t0 ? __ushort_as_half((unsigned short)pre_b) : p.sin_t[(size_t)pos * 64 + (d >> 1)];
-                    o0 = h_sub(h_mul(h0, cs), h_mul(h1, sn));
-                    o1 = h_add(h_mul(h0, sn), h_mul(h1, cs));
+                    rope_pair(h0, h1, cs, sn, o0, o1);
                 }
                 __half* dst = sec == 0 ? op.y + idx : (sec == 1 ? op.kc : op.vc) + ((size_t)head * p.max_pos + pos) * 128 + d;
                 const __half2 v = __halves2half2(o0, o1);

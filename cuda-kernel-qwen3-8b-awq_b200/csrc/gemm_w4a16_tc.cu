@@ -30,11 +30,9 @@ constexpr int GM_TILE_M = 128;                 // outputs per CTA
 constexpr int GM_BK = 64;                      // K per pipeline stage
 constexpr int GM_A_BYTES = GM_TILE_M * GM_BK * 2;        // 16384
 constexpr int GM_MAX_STAGES = 24;              // mbarrier slots per ring
-constexpr int GM_A_STAGES = 6;                 // unpacked operand-A ring (16 KB each): released by the MMAs' commit
-                                               // (the activation ring, released by the same commit, and the packed-nibble
-                                               // ring, released by the unpack warps, are template parameters: a 64-row box
-                                               // of 64-byte pieces takes ~3 us to arrive, so the nibble ring is made as
-                                               // deep as shared memory allows)
+// Operand A (16 KB per K block, unpacked) and the activations share one ring depth and ONE release barrier per
+// stage: a tcgen05.commit costs the issuing lane ~150 ns, so a K block gets a single commit.  The depth is a template
+// parameter (6, or 4 with 256-row tiles).
 constexpr int GM_UNPACK_WARPS = 16;           // unpack / epilogue warps: four groups of four, taking K blocks in turn
                                               // (an unpack warp is latency-bound on its own chain: more groups, more K blocks in flight)
 constexpr int GM_THREADS = 64 + 32 * GM_UNPACK_WARPS;
@@ -103,17 +101,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int GM_X_STAGES>
+template <int GM_STAGES>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int x_bytes = p.n_tile * 128;                                   // [n_tile][64] fp16
-    static_assert(GM_X_STAGES <= GM_MAX_STAGES && GM_A_STAGES >= GM_UNPACK_WARPS / 4, "ring depths");
+    static_assert(GM_STAGES <= GM_MAX_STAGES && GM_STAGES >= GM_UNPACK_WARPS / 4, "ring depth");
+    constexpr int GM_A_STAGES = GM_STAGES, GM_X_STAGES = GM_STAGES;
     uint8_t* a_st = smem;                                                 // GM_A_STAGES x 16 KB (1024-aligned)
     uint8_t* x_st = smem + GM_A_STAGES * GM_A_BYTES;                      // GM_X_STAGES x x_bytes (multiple of 1024)
     uint64_t* bars = reinterpret_cast<uint64_t*>(x_st + GM_X_STAGES * x_bytes);
     const uint32_t a_full = smem_u32(bars + 2 * GM_MAX_STAGES), a_empty = smem_u32(bars + 3 * GM_MAX_STAGES);
-    const uint32_t x_full = smem_u32(bars + 4 * GM_MAX_STAGES), x_empty = smem_u32(bars + 5 * GM_MAX_STAGES);
+    const uint32_t x_full = smem_u32(bars + 4 * GM_MAX_STAGES), x_empty = a_empty;   // one release barrier per stage
     const uint32_t acc_full = smem_u32(bars + 6 * GM_MAX_STAGES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 * GM_MAX_STAGES + 1);
     int* s_dead = reinterpret_cast<int*>(tmem_slot + 1);   // bars: (6 * 24 + 2) * 8 bytes < 1280
@@ -128,11 +127,10 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
     if (tid == 0) {
         for (int s = 0; s < GM_X_STAGES; ++s) {
             mbar_init(x_full + 8 * s, 1);
-            mbar_init(x_empty + 8 * s, 1);      // commit of the MMAs that read X
         }
         for (int s = 0; s < GM_A_STAGES; ++s) {
             mbar_init(a_full + 8 * s, 4);       // the 4 unpack warps of the group that owns the K block
-            mbar_init(a_empty + 8 * s, 1);      // commit of the MMAs that read A
+            mbar_init(a_empty + 8 * s, 1);      // commit of the MMAs that read A and X of the stage
         }
         mbar_init(acc_full, 1);
         *s_dead = 0;
@@ -201,8 +199,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
                     umma_f16(tmem_base + (uint32_t)(acc * p.acc_stride), adesc + (uint64_t)(ks * a_step), bdesc + (uint64_t)(ks * 2), idesc,
                              (kb > 0 || ks >= p.n_acc) ? 1u : 0u);
                 }
-                umma_commit(a_empty + 8 * t);    // A stage free once these MMAs have read it
-                umma_commit(x_empty + 8 * s);    // X stage likewise
+                umma_commit(a_empty + 8 * t);    // A and X of the stage are free once these MMAs have read them
                 if (kb == n_kb - 1) umma_commit(acc_full);
             }
             __syncwarp();
@@ -400,19 +397,16 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     rc = encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d_x, (uint64_t)d->K, (uint64_t)rows, (uint64_t)d->K * 2, GM_BK,
                    (uint32_t)p.n_tile, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != QW3_OK) return rc;
-    // shared memory: 6 operand-A stages of 16 KB plus the activation ring.  An activation stage is only released when
-    // the MMAs that read it have completed, so that ring is made deep for small row tiles.
-    const int x_stages = p.n_tile <= 32 ? 16 : p.n_tile <= 64 ? 8 : p.n_tile <= 128 ? 4 : 3;
-    const size_t smem = (size_t)GM_A_STAGES * GM_A_BYTES + (size_t)x_stages * p.n_tile * 128 + 1280;
+    // shared memory per stage: 16 KB of operand A + n_tile x 128 bytes of activations; 6 stages (4 with 256-row tiles)
+    const int stages = p.n_tile <= 128 ? 6 : 4;
+    const size_t smem = (size_t)stages * (GM_A_BYTES + p.n_tile * 128) + 1280;
     static std::once_flag attr_once[16];
     int dev = 0;
     QW3_CUDA(cudaGetDevice(&dev));
     if (dev < 16)
         std::call_once(attr_once[dev], [] {
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             cudaFuncSetAttribute(gemm_w4a16_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            cudaFuncSetAttribute(gemm_w4a16_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         });
     // Few rows and few output tiles leave most SMs without a CTA: split K over grid.z (fp32 partial products in the
     // workspace, summed in split order by a second kernel) until ~one CTA per SM, while the partials fit.
@@ -425,14 +419,10 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     p.part = splits > 1 ? ws_struct(ws)->partials : nullptr;
     dim3 grid((unsigned)(d->M / GM_TILE_M), (unsigned)((rows + p.n_tile - 1) / p.n_tile), (unsigned)splits);
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x_stages == 16)
-        gemm_w4a16_tc_kernel<16><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
-    else if (x_stages == 8)
-        gemm_w4a16_tc_kernel<8><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
-    else if (x_stages == 4)
-        gemm_w4a16_tc_kernel<4><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
+    if (stages == 6)
+        gemm_w4a16_tc_kernel<6><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
     else
-        gemm_w4a16_tc_kernel<3><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
+        gemm_w4a16_tc_kernel<4><<<grid, GM_THREADS, smem, st>>>(tmap_x, p);
     QW3_CUDA(cudaGetLastError());
     if (splits > 1) {
         const long long n = rows * d->M;

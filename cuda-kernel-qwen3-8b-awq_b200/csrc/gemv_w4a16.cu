@@ -262,8 +262,7 @@ gemv_w4a16_kernel(const __grid_constant__ CUtensorMap tmap, const GemvParams p) 
                 __half o0 = h0, o1 = h1;
                 if (sec < 2) {                                            // Inference.cu:166-176
                     const __half cs = p.cos_t[(size_t)pos * 64 + (d >> 1)], sn = p.sin_t[(size_t)pos * 64 + (d >> 1)];
-                    o0 = h_sub(h_mul(h0, cs), h_mul(h1, sn));
-                    o1 = h_add(h_mul(h0, sn), h_mul(h1, cs));
+                    rope_pair(h0, h1, cs, sn, o0, o1);
                 }
                 __half* dst = sec == 0 ? p.y + idx
                                        : (sec == 1 ? p.kc : p.vc) + ((size_t)head * p.max_pos + pos) * 128 + d;

@@ -78,8 +78,7 @@ __global__ void rope_kv_kernel(const __half* __restrict__ qkv, __half* __restric
     if (sec < 2) {
         const __half cs = cos_t[(size_t)pos * 64 + (d >> 1)], sn = sin_t[(size_t)pos * 64 + (d >> 1)];
         const __half x0 = o0, x1 = o1;
-        o0 = h_sub(h_mul(x0, cs), h_mul(x1, sn));
-        o1 = h_add(h_mul(x0, sn), h_mul(x1, cs));
+        rope_pair(x0, x1, cs, sn, o0, o1);
     }
     __half* dst = sec == 0 ? q_out + idx : (sec == 1 ? kc : vc) + ((size_t)head * max_pos + pos) * 128 + d;
     *reinterpret_cast<__half2*>(dst) = __halves2half2(o0, o1);

@@ -102,9 +102,13 @@ def rope(qk, heads, head_dim, cos_t, sin_t, pos):
     v = qk.reshape(heads, head_dim // 2, 2).astype(np.float16)
     c = cos_t[pos][None, :].astype(np.float16)
     s = sin_t[pos][None, :].astype(np.float16)
-    x0, x1 = v[:, :, 0], v[:, :, 1]
-    t0 = (x0 * c) - (x1 * s)
-    t1 = (x0 * s) + (x1 * c)
+    x0, x1 = v[:, :, 0].astype(np.float64), v[:, :, 1].astype(np.float64)
+    c, s = c.astype(np.float64), s.astype(np.float64)
+    r16 = lambda a: a.astype(np.float16).astype(np.float64)
+    # as the reference's build executes Inference.cu:172-173: the first product of each line is contracted into
+    # the add (fma, exact in float64 here), the second product is rounded to fp16 first
+    t0 = (x0 * c - r16(x1 * s)).astype(np.float16)
+    t1 = (x0 * s + r16(x1 * c)).astype(np.float16)
     return np.stack([t0, t1], axis=-1).reshape(-1)
 
 

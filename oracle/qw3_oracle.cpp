@@ -39,6 +39,21 @@ inline float rh(float f) { return h2f(f2h(f)); }  // round an fp32 value to the 
 inline float hadd_(float a, float b) { return rh(a + b); }
 inline float hsub_(float a, float b) { return rh(a - b); }
 inline float hmul_(float a, float b) { return rh(a * b); }
+// fma.rn.f16: a * b + c with ONE rounding.  The product of two fp16 values and its sum with a third are exact in
+// double; the double is taken to float with round-to-odd so that the final float -> half rounding is the correct
+// rounding of the exact value.
+inline float hfma_(float a, float b, float c) {
+    const double e = (double)a * (double)b + (double)c;
+    float f = (float)e;
+    if ((double)f != e) {
+        if (std::fabs((double)f) > std::fabs(e)) f = std::nextafterf(f, 0.0f);
+        uint32_t u;
+        std::memcpy(&u, &f, 4);
+        u |= 1u;
+        std::memcpy(&f, &u, 4);
+    }
+    return rh(f);
+}
 
 constexpr uint64_t GOLD = 0x9E3779B97F4A7C15ull;
 inline uint64_t mix64(uint64_t x) {
@@ -245,8 +260,11 @@ void orc_rope(uint16_t* qk, int heads, int head_dim, const uint16_t* cos_t, cons
         for (int p = 0; p < half; ++p) {
             float x0 = h2f(qk[h * head_dim + 2 * p]), x1 = h2f(qk[h * head_dim + 2 * p + 1]);
             float c = h2f(cos_t[(int64_t)pos * half + p]), s = h2f(sin_t[(int64_t)pos * half + p]);
-            float t0 = hsub_(hmul_(x0, c), hmul_(x1, s));  // Inference.cu:172
-            float t1 = hadd_(hmul_(x0, s), hmul_(x1, c));  // Inference.cu:173
+            // Inference.cu:172-173 as the reference's build executes them: __hmul / __hsub / __hadd emit mul.f16 /
+            // sub.f16 / add.f16 without a rounding modifier, and the compiler contracts the first product of each
+            // line into the add (one fma), keeping the second product rounded (checked against the compiled kernel)
+            float t0 = hfma_(x0, c, -hmul_(x1, s));
+            float t1 = hfma_(x0, s, hmul_(x1, c));
             qk[h * head_dim + 2 * p] = f2h(t0);
             qk[h * head_dim + 2 * p + 1] = f2h(t1);
         }
