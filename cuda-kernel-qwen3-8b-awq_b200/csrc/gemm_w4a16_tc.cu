@@ -4,10 +4,11 @@
 // feeds prompts token by token through cublasGemmEx at n = 1 (Inference.cu:1304-1343, 1052-1065);
 // this is the same product for `rows` tokens at once.
 //
-// One CTA computes a tile of 128 outputs x N rows of X (N = 16..256).  Eighteen warps:
+// One CTA computes a tile of 128 outputs x N rows of X (N = 16..256).  Nineteen warps:
 //   warp 0      TMA producer: per 64-deep K block one box of activations [N][64] (128-byte swizzle, K-major
 //               operand B)
-//   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
+//   warp 1, 18  MMA issuers (one lane each; even / odd K blocks into separate accumulators in tensor memory, which
+//               warp 1 allocates), tcgen05.commit frees the stages
 //   warps 2..17 read the packed nibbles of the tile straight from global memory (16 bytes per thread and row, one
 //               K block ahead; four groups of four warps take the K blocks in turn), unpack them to fp16 with
 //               the reference's two roundings and write operand A to shared memory in the MN-major 128-byte-swizzled canonical layout (outputs are
@@ -35,7 +36,8 @@ constexpr int GM_MAX_STAGES = 24;              // mbarrier slots per ring
 // parameter (6, or 4 with 256-row tiles).
 constexpr int GM_UNPACK_WARPS = 16;           // unpack / epilogue warps: four groups of four, taking K blocks in turn
                                               // (an unpack warp is latency-bound on its own chain: more groups, more K blocks in flight)
-constexpr int GM_THREADS = 64 + 32 * GM_UNPACK_WARPS;
+constexpr int GM_ISSUER_B = 2 + GM_UNPACK_WARPS;   // warp index of the second MMA issuer
+constexpr int GM_THREADS = 32 * (GM_ISSUER_B + 1);
 
 struct GemmParams {
     const uint8_t* packed;   // [K][M/2] bytes; the unpack warps read their 16-byte pieces straight from global memory
@@ -46,7 +48,7 @@ struct GemmParams {
     int rows;          // rows of X / Y
     int n_tile;        // UMMA N: 16..256, multiple of 16
     int tmem_cols;     // power of two >= n_acc * acc_stride
-    int n_acc;         // accumulators in tensor memory (1, 2 or 4): the MMAs of a K block go to different ones, so
+    int n_acc;         // accumulators in tensor memory (2 or 4, half per MMA issuer): the MMAs of a K block go to different ones, so
                        // that they do not wait for each other (an MMA into the same accumulator is ~240 cycles
                        // behind the one before, whatever N); the epilogue adds them in a fixed order
     int acc_stride;    // columns between accumulators
@@ -132,7 +134,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
             mbar_init(a_full + 8 * s, 4);       // the 4 unpack warps of the group that owns the K block
             mbar_init(a_empty + 8 * s, 1);      // commit of the MMAs that read A and X of the stage
         }
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, 2);             // the last commit of each of the two MMA issuers
         *s_dead = 0;
         mbar_fence_init();
     }
@@ -164,48 +166,49 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
                 *s_dead = 1;
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer -------------------------------------------------------------
-        // instruction descriptor: D = f32, A = B = f16, A MN-major (bit 15), B K-major, N >> 3, M >> 4
-        const uint32_t idesc = (1u << 4) | (1u << 15) | ((uint32_t)(p.n_tile >> 3) << 17) | ((uint32_t)(GM_TILE_M >> 4) << 24);
-        // One lane issues everything, so its instruction chain per K block sets the rate for small row tiles:
-        // ring indices and phases are running counters, and the descriptors are a constant high word plus a
-        // low word advanced by additions.
-        const uint64_t adesc0 = make_smem_desc(smem_u32(a_st), p.a_lbo, p.a_sbo);
-        const uint64_t bdesc0 = make_smem_desc(smem_u32(x_st), 16, 1024);
-        const uint32_t a_step = (uint32_t)(p.a_kstep >> 4), a_stage = (uint32_t)(GM_A_BYTES >> 4), x_stage = (uint32_t)(x_bytes >> 4);
-        int s = 0, t = 0;
-        uint32_t s_phase = 0, t_phase = 0;
-        for (int kb = 0; kb < n_kb; ++kb) {
-            bool ok = true;
-            if (*s_dead == 0) {
-                ok = mbar_wait(x_full + 8 * s, s_phase) && mbar_wait(a_full + 8 * t, t_phase);
-                if (!ok && lane == 0) {
+    } else if (warp == 1 || warp == GM_ISSUER_B) {
+        // ---------------- MMA issuers ------------------------------------------------------------
+        // The instruction chain of an issuing lane (two barrier waits, four MMAs, one commit: ~900 cycles) is what a
+        // K block costs a CTA when the row tile is small, so TWO warps issue: warp 1 takes the even K blocks, the
+        // last warp the odd ones, each into its own accumulators (summed by the epilogue).  One lane per warp runs
+        // the loop; ring indices and phases are running counters, descriptors a constant plus additions.
+        if (lane == 0) {
+            const int who = warp == 1 ? 0 : 1;
+            // instruction descriptor: D = f32, A = B = f16, A MN-major (bit 15), B K-major, N >> 3, M >> 4
+            const uint32_t idesc = (1u << 4) | (1u << 15) | ((uint32_t)(p.n_tile >> 3) << 17) | ((uint32_t)(GM_TILE_M >> 4) << 24);
+            const uint64_t adesc0 = make_smem_desc(smem_u32(a_st), p.a_lbo, p.a_sbo);
+            const uint64_t bdesc0 = make_smem_desc(smem_u32(x_st), 16, 1024);
+            const uint32_t a_step = (uint32_t)(p.a_kstep >> 4), a_stage = (uint32_t)(GM_A_BYTES >> 4), x_stage = (uint32_t)(x_bytes >> 4);
+            const int half_acc = p.n_acc >> 1;                        // accumulators of this issuer
+            const uint32_t my_tmem = tmem_base + (uint32_t)(who * half_acc * p.acc_stride);
+            int s = who;                                              // stage of K block `who` (GM_STAGES >= 2)
+            uint32_t phase = 0;
+            bool first = true;
+            for (int kb = who; kb < n_kb; kb += 2) {
+                if (*s_dead != 0) break;
+                if (!(mbar_wait(x_full + 8 * s, phase) && mbar_wait(a_full + 8 * s, phase))) {
                     atomicCAS(p.err, 0, 0x30002);
                     *s_dead = 1;
+                    break;
                 }
-            }
-            __syncwarp();
-            if (*s_dead != 0) break;
-            tc_fence_after();
-            if (elect_one()) {
                 // A (MN-major): 64-output blocks 8 KB apart (LBO), 8-deep K blocks 1 KB apart (SBO); K=16 = 2 blocks
                 // B (K-major): 8-row groups 1 KB apart (SBO); K=16 = 32 bytes inside the swizzled row
-                const uint64_t adesc = adesc0 + (uint64_t)((uint32_t)t * a_stage);
+                const uint64_t adesc = adesc0 + (uint64_t)((uint32_t)s * a_stage);
                 const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)s * x_stage);
 #pragma unroll
                 for (int ks = 0; ks < GM_BK / 16; ++ks) {
-                    const int acc = ks & (p.n_acc - 1);
-                    umma_f16(tmem_base + (uint32_t)(acc * p.acc_stride), adesc + (uint64_t)(ks * a_step), bdesc + (uint64_t)(ks * 2), idesc,
-                             (kb > 0 || ks >= p.n_acc) ? 1u : 0u);
+                    const int acc = ks & (half_acc - 1);
+                    umma_f16(my_tmem + (uint32_t)(acc * p.acc_stride), adesc + (uint64_t)(ks * a_step), bdesc + (uint64_t)(ks * 2), idesc,
+                             (!first || ks >= half_acc) ? 1u : 0u);
                 }
-                umma_commit(a_empty + 8 * t);    // A and X of the stage are free once these MMAs have read them
-                if (kb == n_kb - 1) umma_commit(acc_full);
+                first = false;
+                umma_commit(a_empty + 8 * s);    // A and X of the stage are free once these MMAs have read them
+                if (kb + 2 >= n_kb) umma_commit(acc_full);   // this issuer's last K block
+                s += 2;
+                if (s >= GM_STAGES) { s -= GM_STAGES; phase ^= 1u; }
             }
-            __syncwarp();
-            if (++s == GM_X_STAGES) { s = 0; s_phase ^= 1u; }
-            if (++t == GM_A_STAGES) { t = 0; t_phase ^= 1u; }
         }
+        __syncwarp();
     } else {
         // ---------------- unpack warps (2..17), then epilogue -----------------------------------
         const int grp = (warp - 2) >> 2;          // group g unpacks the K blocks g, g + 4, ...
@@ -384,9 +387,9 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     p.uniform = d->uniform; p.exact = d->zp_integral;
     p.rows = (int)rows;
     p.n_tile = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-    p.n_acc = p.n_tile <= 64 ? 4 : p.n_tile <= 128 ? 2 : 1;
+    p.n_acc = p.n_tile <= 64 ? 4 : 2;       // half of them per MMA issuer
     p.acc_stride = p.n_tile < 32 ? 32 : p.n_tile;
-    p.tmem_cols = p.n_acc * p.acc_stride;   // 128, 128, 256, 256, 256 columns: powers of two
+    p.tmem_cols = p.n_acc * p.acc_stride;   // 128, 128, 256, 256, 512 columns: powers of two
     p.y = static_cast<__half*>(d_y);
     p.err = ws_struct(ws)->err;
     p.a_lbo = 8192; p.a_sbo = 1024; p.a_kstep = 2048;
