@@ -207,6 +207,16 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
                 s += 2;
                 if (s >= GM_STAGES) { s -= GM_STAGES; phase ^= 1u; }
             }
+            // Drain: the release arrivals of this issuer's last K blocks are waited for by nobody else (no later block
+            // reuses those stages).  They must have landed before the CTA exits, or they would hit the barriers of
+            // the next CTA that gets this shared memory.
+            for (int kb = who; kb < n_kb; kb += 2) {
+                if (kb + GM_STAGES < n_kb || *s_dead != 0) continue;
+                if (!mbar_wait(a_empty + 8 * (kb % GM_STAGES), (uint32_t)(kb / GM_STAGES) & 1u)) {
+                    atomicCAS(p.err, 0, 0x30006);
+                    *s_dead = 1;
+                }
+            }
         }
         __syncwarp();
     } else {
