@@ -86,6 +86,8 @@ def test_stage_split_does_not_change_tokens(pkg, orc, cuda, small_dir, n_stages,
     inf = pkg.QWen3AWQInfer(small_dir, n_stages=n_stages, device=[0] * n_stages, keep_logits=1, persistent=persistent, **SMALL)
     got = inf.generateResponse(prompt, 10)
     assert got == GOLDEN["small_model"]["ids"]
+    inf.set_batched_prefill(True)       # the block of prompt rows is handed from stage to stage as well
+    assert inf.generateResponse(prompt, 10) == GOLDEN["small_model"]["ids"]
     inf.close()
 
 
