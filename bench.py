@@ -494,6 +494,12 @@ def main():
             cpu_tps, _ = cpu_decode_tokens_per_s(orc, wdir, n_cpu, args.prompt_len)
             line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
                                     "sample": f"{n_cpu} decode-token passes of the same model on the host, KV rows pre-filled to context {args.prompt_len}"}
+            all_threads = orc.num_threads()
+            orc.set_num_threads(1)
+            cpu1_tps, _ = cpu_decode_tokens_per_s(orc, wdir, 1, args.prompt_len)
+            orc.set_num_threads(all_threads)
+            line["cpu_baseline_1thread"] = {"value": cpu1_tps, "unit": "tokens/s", "cores": 1, "kind": "port",
+                                            "sample": "1 decode-token pass of the same model on one host thread (after a warm-up pass)"}
         result = line
     barrier()
     if rank == 0:

@@ -74,6 +74,7 @@ def lib():
         "orc_model_f16": (vp, [vp, i32, i32]),
         "orc_model_kv": (vp, [vp, i32, i32]),
         "orc_num_threads": (i32, []),
+        "orc_set_num_threads": (None, [i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -259,3 +260,7 @@ def write_weight_dir(cfg, seed, path):
 
 def num_threads():
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n):
+    lib().orc_set_num_threads(int(n))

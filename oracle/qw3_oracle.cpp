@@ -598,5 +598,12 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 
 }  // extern "C"

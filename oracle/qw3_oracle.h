@@ -144,6 +144,7 @@ const uint16_t* orc_model_f16(OrcModel* m, int layer, int kind);
 uint16_t*       orc_model_kv(OrcModel* m, int layer, int which /*0=K,1=V*/);
 
 int orc_num_threads(void);
+void orc_set_num_threads(int n);   /* host threads of the parallel loops (timing the baseline at 1 thread) */
 
 #ifdef __cplusplus
 }
