@@ -32,8 +32,7 @@ int rope_kv_rows_launch(void* qkv, void* kc, void* vc, const void* cos_t, const 
                         int pos0, int rows, cudaStream_t st);
 int attn_prefill_launch(const void* qkv, const void* kc, const void* vc, int heads, int hidden, long long max_pos, int pos0,
                         int rows, void* ctx, cudaStream_t st);
-int add_rows_launch(void* h, const void* y, long long n, cudaStream_t st);
-int gelu_rows_launch(void* x, long long n, cudaStream_t st);
+int gemm_launch(qw3_w4_t w, const void* d_x, int64_t rows, void* d_y, qw3_ws_t ws, void* stream, int epilogue);
 int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids, int* d_skip, int* d_epoch, bool pdl,
                      cudaStream_t st);
 const W4Desc* w4_desc(qw3_w4_t w);
@@ -112,7 +111,7 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
     bool persistent = false;
     // batched prompt phase: activations of a block of PF_BLOCK prompt rows (allocated at the first use)
-    void *pf_h = nullptr, *pf_n = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_mlp = nullptr, *pf_y = nullptr;
+    void *pf_h = nullptr, *pf_n = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_mlp = nullptr;
 };
 
 }  // namespace qw3
@@ -424,7 +423,6 @@ static int prefill_alloc(qw3_engine* e, Stage& s) {
     QW3_TRY(dev_alloc(e, s.device, &s.pf_qkv, 3 * H));
     QW3_TRY(dev_alloc(e, s.device, &s.pf_ctx, H));
     QW3_TRY(dev_alloc(e, s.device, &s.pf_mlp, I));
-    QW3_TRY(dev_alloc(e, s.device, &s.pf_y, H));
     return QW3_OK;
 }
 
@@ -453,14 +451,11 @@ static int prefill_block(qw3_engine* e, int t0, int rows) {
             QW3_TRY(qw3_gemm_w4a16(L.wqkv.desc, s.pf_n, rows, s.pf_qkv, s.ws, s.stream));
             QW3_TRY(rope_kv_rows_launch(s.pf_qkv, L.kc, L.vc, s.cos_t, s.sin_t, H, c.max_pos, t0, rows, s.stream));
             QW3_TRY(attn_prefill_launch(s.pf_qkv, L.kc, L.vc, c.heads, H, c.max_pos, t0, rows, s.pf_ctx, s.stream));
-            QW3_TRY(qw3_gemm_w4a16(L.wo.desc, s.pf_ctx, rows, s.pf_y, s.ws, s.stream));
-            QW3_TRY(add_rows_launch(s.pf_h, s.pf_y, (long long)rows * H, s.stream));
+            QW3_TRY(gemm_launch(L.wo.desc, s.pf_ctx, rows, s.pf_h, s.ws, s.stream, QW3_EPI_RESIDUAL));
             QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
-            QW3_TRY(qw3_gemm_w4a16(L.w1.desc, s.pf_n, rows, s.pf_mlp, s.ws, s.stream));
-            QW3_TRY(gelu_rows_launch(s.pf_mlp, (long long)rows * c.inter, s.stream));
-            QW3_TRY(qw3_gemm_w4a16(L.w2.desc, s.pf_mlp, rows, s.pf_y, s.ws, s.stream));
-            QW3_TRY(add_rows_launch(s.pf_h, s.pf_y, (long long)rows * H, s.stream));
-            e->launches += 11;
+            QW3_TRY(gemm_launch(L.w1.desc, s.pf_n, rows, s.pf_mlp, s.ws, s.stream, QW3_EPI_GELU));
+            QW3_TRY(gemm_launch(L.w2.desc, s.pf_mlp, rows, s.pf_h, s.ws, s.stream, QW3_EPI_RESIDUAL));
+            e->launches += 7;
         }
         // what the token loop leaves behind: the last row's hidden state and the position counter
         QW3_CUDA(cudaMemcpyAsync(s.hidden, static_cast<char*>(s.pf_h) + (size_t)(rows - 1) * H * 2, (size_t)H * 2,

@@ -53,6 +53,8 @@ struct GemmParams {
                        // behind the one before, whatever N); the epilogue adds them in a fixed order
     int acc_stride;    // columns between accumulators
     __half* y;         // [rows][M]
+    int epilogue;      // QW3_EPI_STORE, QW3_EPI_RESIDUAL (y = hadd(y, result), Inference.cu:1145-1156) or QW3_EPI_GELU
+                       // (Inference.cu:271-279): what the batched prompt phase needs after wo / w2 and after w1
     float* part;       // split-K: fp32 partial products [splits][rows][M] (null: one split, y is written directly)
     int* err;
     int a_lbo, a_sbo, a_kstep;   // operand A descriptor: byte offsets between 64-output blocks, between 8-deep K blocks, per K=16 step
@@ -101,6 +103,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// One output element: fp32 sum -> fp16, then the epilogue in fp16 as the decode path does it.
+__device__ __forceinline__ __half gemm_epilogue(float v, int epilogue, __half old) {
+    const __half h = __float2half_rn(v);
+    if (epilogue == QW3_EPI_RESIDUAL) return h_add(old, h);
+    if (epilogue == QW3_EPI_GELU) return gelu_h(h);
+    return h;
 }
 
 template <int GM_STAGES>
@@ -321,7 +331,10 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
                     const int r = tile_n * p.n_tile + c0 + e;
                     if (r < p.rows) {
                         if (p.part != nullptr) p.part[((size_t)blockIdx.z * p.rows + r) * p.M + i] = f[e];
-                        else p.y[(size_t)r * p.M + i] = __float2half_rn(f[e]);
+                        else {
+                            __half* dst = p.y + (size_t)r * p.M + i;
+                            *dst = gemm_epilogue(f[e], p.epilogue, p.epilogue == QW3_EPI_RESIDUAL ? *dst : __half());
+                        }
                     }
                 }
             }
@@ -336,7 +349,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParam
 }
 
 // Split-K: sums the fp32 partial products of the splits in split order and rounds once to fp16.
-__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ part, int splits, long long n, __half* __restrict__ y) {
+__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ part, int splits, long long n, int epilogue, __half* y) {
     const long long i = 2 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
     if (i >= n) return;
     float2 acc = *reinterpret_cast<const float2*>(part + i);
@@ -345,7 +358,9 @@ __global__ void gemm_splitk_reduce_kernel(const float* __restrict__ part, int sp
         acc.x += v.x;
         acc.y += v.y;
     }
-    *reinterpret_cast<__half2*>(y + i) = __floats2half2_rn(acc.x, acc.y);
+    const __half2 old = epilogue == QW3_EPI_RESIDUAL ? *reinterpret_cast<const __half2*>(y + i) : __half2();
+    *reinterpret_cast<__half2*>(y + i) =
+        __halves2half2(gemm_epilogue(acc.x, epilogue, __low2half(old)), gemm_epilogue(acc.y, epilogue, __high2half(old)));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -385,8 +400,18 @@ static int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base,
 
 using namespace qw3;
 
+namespace qw3 {
+int gemm_launch(qw3_w4_t w, const void* d_x, int64_t rows, void* d_y, qw3_ws_t ws, void* stream, int epilogue);
+}
+
 extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d_y, qw3_ws_t ws, void* stream) {
+    return qw3::gemm_launch(w, d_x, rows, d_y, ws, stream, QW3_EPI_STORE);
+}
+
+// The contraction with an optional epilogue (the engine's batched prompt phase fuses the residual add and the GeLU).
+int qw3::gemm_launch(qw3_w4_t w, const void* d_x, int64_t rows, void* d_y, qw3_ws_t ws, void* stream, int epilogue) {
     QW3_REQUIRE(w && d_x && d_y && ws, "qw3_gemm_w4a16: null argument");
+    QW3_REQUIRE(epilogue == QW3_EPI_STORE || epilogue == QW3_EPI_RESIDUAL || epilogue == QW3_EPI_GELU, "qw3_gemm_w4a16: epilogue");
     QW3_REQUIRE(rows >= 1 && rows <= (1 << 20), "qw3_gemm_w4a16: rows out of range");
     QW3_REQUIRE((reinterpret_cast<uintptr_t>(d_x) & 15) == 0, "qw3_gemm_w4a16: X must be 16-byte aligned");
     const W4Desc* d = w4_desc(w);
@@ -401,6 +426,7 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     p.acc_stride = p.n_tile < 32 ? 32 : p.n_tile;
     p.tmem_cols = p.n_acc * p.acc_stride;   // 128, 128, 256, 256, 512 columns: powers of two
     p.y = static_cast<__half*>(d_y);
+    p.epilogue = epilogue;
     p.err = ws_struct(ws)->err;
     p.a_lbo = 8192; p.a_sbo = 1024; p.a_kstep = 2048;
     if (const char* e = std::getenv("QW3_GEMM_A_LBO")) p.a_lbo = std::atoi(e);
@@ -439,7 +465,7 @@ extern "C" int qw3_gemm_w4a16(qw3_w4_t w, const void* d_x, int64_t rows, void* d
     QW3_CUDA(cudaGetLastError());
     if (splits > 1) {
         const long long n = rows * d->M;
-        gemm_splitk_reduce_kernel<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(p.part, splits, n, p.y);
+        gemm_splitk_reduce_kernel<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(p.part, splits, n, p.epilogue, p.y);
         QW3_CUDA(cudaGetLastError());
     }
     return QW3_OK;

@@ -163,19 +163,8 @@ attn_prefill_kernel(const __half* __restrict__ qkv, const __half* __restrict__ k
     ctx[(size_t)r * hidden + head * 128 + tid] = __float2half_rn(O / L);
 }
 
-// ---- addKernel (Inference.cu:1145-1156) and geluKernel (Inference.cu:271-279) over R rows ------------
-__global__ void add_rows_kernel(__half* __restrict__ h, const __half* __restrict__ y, long long n) {
-    const long long i = 2 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
-    if (i >= n) return;
-    const __half2 a = *reinterpret_cast<const __half2*>(h + i), b = *reinterpret_cast<const __half2*>(y + i);
-    *reinterpret_cast<__half2*>(h + i) = __halves2half2(h_add(__low2half(a), __low2half(b)), h_add(__high2half(a), __high2half(b)));
-}
-__global__ void gelu_rows_kernel(__half* __restrict__ x, long long n) {
-    const long long i = 2 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
-    if (i >= n) return;
-    const __half2 a = *reinterpret_cast<const __half2*>(x + i);
-    *reinterpret_cast<__half2*>(x + i) = __halves2half2(gelu_h(__low2half(a)), gelu_h(__high2half(a)));
-}
+// The residual add (Inference.cu:1145-1156) and the GeLU (Inference.cu:271-279) of the block run in the epilogue of the
+// tensor-core contraction that produces their operand.
 
 // ---- launchers used by the engine (all dimensions even; hidden a multiple of 128) --------------------
 int embed_rows_launch(const void* packed, const void* scale, const void* zp, long long n_alloc, int hidden, long long vocab,
@@ -205,16 +194,6 @@ int attn_prefill_launch(const void* qkv, const void* kc, const void* vc, int hea
     attn_prefill_kernel<<<dim3(heads, rows), PF_THREADS, 0, st>>>(static_cast<const __half*>(qkv), static_cast<const __half*>(kc),
                                                                   static_cast<const __half*>(vc), hidden, max_pos, pos0,
                                                                   static_cast<__half*>(ctx));
-    QW3_CUDA(cudaGetLastError());
-    return QW3_OK;
-}
-int add_rows_launch(void* h, const void* y, long long n, cudaStream_t st) {
-    add_rows_kernel<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<__half*>(h), static_cast<const __half*>(y), n);
-    QW3_CUDA(cudaGetLastError());
-    return QW3_OK;
-}
-int gelu_rows_launch(void* x, long long n, cudaStream_t st) {
-    gelu_rows_kernel<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<__half*>(x), n);
     QW3_CUDA(cudaGetLastError());
     return QW3_OK;
 }
