@@ -550,7 +550,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
                 *(reinterpret_cast<uint4*>(xs) + ch) = ov;
             }
         }
-    } else if (n_units >= upt || K <= 4096) {
+    } else if (n_units >= upt) {
         for (int base = 0; base < n_chunks; base += 3 * P_NCONS) {
             uint4 xv[3];
             fetch_x3(p, sm, op, o, xtag, base + tid, n_chunks, xv);

@@ -35,7 +35,7 @@ def build(reference_dir="/root/reference", force=False):
                     break
                 g.write(line)
         cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
-               "-diag-suppress", "177", f'-DQW3_REF_PREFIX="{prefix}"', wrap, "-o", OUT]
+               "-diag-suppress", "177", f'-DQW3_REF_PREFIX="{prefix}"', wrap, "-o", OUT, "-lcublas"]
         subprocess.run(cmd, check=True)
     return OUT
 

@@ -8,9 +8,11 @@
  * PINNING: the reference ships no tests, no golden vectors and no CPU path, and its file does not compile as a
  * whole.  Its device kernels do: build_ref.py compiles them from the reference checkout into _ref/ and the GPU tests
  * run them beside this oracle.  Pinned that way: orc_dequant and orc_rope (bit for bit), orc_rmsnorm and orc_gelu
- * (up to the reference's fp32 summation order and the device's erff).  PARITY UNPINNED for the rest (the cuBLAS
- * contraction, the attention, whose reference kernel is broken, and the token loop): anchored by a second,
- * independent numpy restatement of the same rules and by the committed fixtures under tests/golden/.
+ * (up to the reference's fp32 summation order and the device's erff), orc_gemm_w4a16 (the reference's cublasGemmEx
+ * call, same operands and leading dimensions, on the buffer its own dequantAwqKernel wrote: never more than the last
+ * fp16 bit apart).  PARITY UNPINNED for the rest (the attention, whose reference kernel is broken and is never run,
+ * and the token loop, which does not compile): anchored by a second, independent numpy restatement of the same rules
+ * and by the committed fixtures under tests/golden/.
  *
  * Every function cites the reference lines (Inference.cu:N) whose arithmetic it follows.
  * All fp16 values cross this interface as raw uint16_t bit patterns.

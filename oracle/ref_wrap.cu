@@ -42,4 +42,22 @@ int ref_gelu(void* x, int len, void* stream) {
     return (int)cudaGetLastError();
 }
 
+// runOneLayer, Inference.cu:1049-1065 (and 1128, 1176, 1201, 1260): the contraction as the reference calls it, on the
+// fp16 buffer dequantAwqKernel wrote: cublasGemmEx(OP_N, OP_N, m = out_dim, n = 1, k = in_dim, A = d_dq with lda = m,
+// B = x with ldb = k, C = y with ldc = m), fp16 alpha / beta, tensor-op algorithm.  The compute type the reference
+// names, CUBLAS_COMPUTE_16F_FAST_16F, is not an enumerator of this cuBLAS; compute32 == 0 uses CUBLAS_COMPUTE_16F (what
+// its fp16 alpha / beta imply), compute32 != 0 CUBLAS_COMPUTE_32F with float alpha / beta (the oracle's arithmetic).
+int ref_gemv_cublas(const void* dq, const void* x, void* y, int m, int k, int compute32, void* stream) {
+    static cublasHandle_t handle = nullptr;
+    if (handle == nullptr && cublasCreate(&handle) != CUBLAS_STATUS_SUCCESS) return -1;
+    if (cublasSetStream(handle, static_cast<cudaStream_t>(stream)) != CUBLAS_STATUS_SUCCESS) return -2;
+    const half alpha_h = __float2half(1.0f), beta_h = __float2half(0.0f);
+    const float alpha_f = 1.0f, beta_f = 0.0f;
+    const cublasStatus_t st = cublasGemmEx(
+        handle, CUBLAS_OP_N, CUBLAS_OP_N, m, 1, k, compute32 ? static_cast<const void*>(&alpha_f) : &alpha_h, dq, CUDA_R_16F, m,
+        x, CUDA_R_16F, k, compute32 ? static_cast<const void*>(&beta_f) : &beta_h, y, CUDA_R_16F, m,
+        compute32 ? CUBLAS_COMPUTE_32F : CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+    return (int)st;
+}
+
 }  // extern "C"

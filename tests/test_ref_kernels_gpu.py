@@ -1,10 +1,11 @@
 """The reference's OWN device kernels, run unmodified on the GPU, against the CPU oracle and the product kernels.
 
 oracle/build_ref.py compiles the kernel-only prefix of the reference's Inference.cu (the rest of that file does
-not compile with this toolkit) behind four C entry points into oracle/_ref/libref_kernels.so; the library is
+not compile with this toolkit) behind five C entry points into oracle/_ref/libref_kernels.so; the library is
 built where the reference checkout is present and travels with the repository.  These tests pin the oracle:
 dequantAwqKernel and applyRotaryKernel must agree with it (and with the product kernels) bit for bit, geluKernel
-up to the last bit of erff, rmsNormKernel up to its own fp32 summation order.  Without the library the tests skip."""
+up to the last bit of erff, rmsNormKernel up to its own fp32 summation order, and the reference's cublasGemmEx call
+on the reference's dequantised buffer within the last fp16 bit.  Without the library the tests skip."""
 import ctypes as C
 import os
 
@@ -12,7 +13,7 @@ import numpy as np
 import pytest
 import torch
 
-from test_gemv_gpu import _to_dev, _ulp_diff
+from test_gemv_gpu import _run_gemv, _to_dev, _ulp_diff
 
 pytestmark = pytest.mark.gpu
 
@@ -29,6 +30,7 @@ def ref():
     L.ref_rmsnorm.argtypes = [vp, vp, vp, C.c_int, C.c_float, vp]
     L.ref_rotary.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]
     L.ref_gelu.argtypes = [vp, C.c_int, vp]
+    L.ref_gemv_cublas.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]
     return L
 
 
@@ -123,3 +125,34 @@ def test_reference_rmsnorm_kernel_against_oracle_and_product(ref, ops, orc, cuda
         assert _ulp_diff(got_ref, want).max() <= 2                           # a last-bit scale moves outputs by <= 2 ulp
         agree += int(np.array_equal(_bits(got_ref), _bits(want)))
     assert agree >= 6, f"reference rmsNormKernel bit-equal to the oracle on only {agree} of 8 inputs"
+
+
+@pytest.mark.parametrize("M,K", [(4096, 4096), (12288, 4096), (1536, 512)])
+def test_reference_contraction_dequant_then_cublas(ref, ops, orc, cuda, M, K):
+    """The reference's contraction, run as the reference runs it: dequantAwqKernel into an fp16 buffer, then
+    cublasGemmEx(OP_N, OP_N, m = out_dim, n = 1, k = in_dim, lda = out_dim) on it (Inference.cu:1049-1065).  This pins
+    the oracle's reading of the buffer (column-major, element (i, j) at i + j * out_dim) and its fp32 sum; the
+    fp16-accumulating compute type is looser by its own rounding and is only bounded."""
+    p, s, z = orc.gen_linear(0, M, K)
+    x = orc.gen_normal_f16(0, orc.ACT, K)
+    y32, y16 = orc.gemm_w4a16(p, s, z, M, K, x)
+    dp, ds, dz, dx = _to_dev(p, cuda), _to_dev(s, cuda), _to_dev(z, cuda), _to_dev(x, cuda)
+    dq = torch.empty((M, K), dtype=torch.float16, device=cuda)
+    assert ref.ref_dequant(_ptr(dp), _ptr(ds), _ptr(dz), _ptr(dq), M, K, None) == 0
+    y = torch.empty(M, dtype=torch.float16, device=cuda)
+    assert ref.ref_gemv_cublas(_ptr(dq), _ptr(dx), _ptr(y), M, K, 1, None) == 0
+    torch.cuda.synchronize()
+    got_ref32 = y.cpu().numpy()
+    # the library sums in fp32 in its own (tensor-core) order: never more than the last fp16 bit from the oracle's
+    # correctly rounded sum, and that on a few percent of the outputs (measured: 1.6 %)
+    for name, other in (("oracle", y16), ("product", _run_gemv(ops, cuda, p, s, z, M, K, x))):
+        ulps = _ulp_diff(got_ref32, other)
+        tiny = np.abs(got_ref32.astype(np.float32) - other.astype(np.float32)) <= 1e-4 * np.abs(y32).mean()
+        assert ((ulps <= 1) | tiny).all(), f"{name}: {int(ulps[~tiny].max())} ulp from cuBLAS on the reference's buffer"
+        assert (ulps > 0).mean() < 0.05, f"{name}: {(ulps > 0).mean():.4f} of outputs differ from cuBLAS"
+    # fp16 accumulation (what the reference's fp16 alpha / beta ask for): same layout, its own rounding noise
+    assert ref.ref_gemv_cublas(_ptr(dq), _ptr(dx), _ptr(y), M, K, 0, None) == 0
+    torch.cuda.synchronize()
+    err16 = np.abs(y.cpu().numpy().astype(np.float32) - y32)
+    rms = float(np.sqrt((y32 ** 2).mean()))
+    assert err16.max() <= 0.25 * rms, (float(err16.max()), rms)
