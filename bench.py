@@ -208,6 +208,43 @@ def roofline_gemv(pkg, torch, M, K, n_mats, reps):
     return us, n, us_pdl
 
 
+def reference_method_token_us(torch, n_layers_cycled=6, reps=6):
+    """The reference's decode method, contractions only: cuBLAS at n = 1 on fp16 copies of wqkv, wo, w1, w2 of every
+    layer and of unembed (Inference.cu:1052-1273; 13.3 GB of fp16 per token instead of 3.3 GB packed).  Random fp16
+    matrices of those shapes, several distinct layers cycled so that nothing stays in L2.  No norms, attention, copies
+    or host waits: a lower bound on the time per token of the dequantise-then-cuBLAS design on this GPU."""
+    dev = torch.device("cuda:0")
+    shapes = [(4096, 12288), (4096, 4096), (4096, 12288), (12288, 4096)]          # [K][M] as the library reads them
+    layers = [[torch.randn(k, m, device=dev, dtype=torch.float16) for k, m in shapes] for _ in range(n_layers_cycled)]
+    unemb = torch.randn(4096, 151936, device=dev, dtype=torch.float16)
+    xs = {4096: torch.randn(1, 4096, device=dev, dtype=torch.float16), 12288: torch.randn(1, 12288, device=dev, dtype=torch.float16)}
+
+    def one_round():
+        for mats in layers:
+            for w in mats:
+                torch.matmul(xs[w.shape[0]], w)
+        torch.matmul(xs[4096], unemb)
+
+    one_round()
+    torch.cuda.synchronize()
+    e_l = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_layers = t_unemb = 0.0
+    for _ in range(reps):
+        e_l[0].record()
+        for mats in layers:
+            for w in mats:
+                torch.matmul(xs[w.shape[0]], w)
+        e_l[1].record()
+        torch.matmul(xs[4096], unemb)
+        e_l[2].record()
+        torch.cuda.synchronize()
+        t_layers += e_l[0].elapsed_time(e_l[1])
+        t_unemb += e_l[1].elapsed_time(e_l[2])
+    per_layer_us = t_layers * 1e3 / (reps * n_layers_cycled)
+    unemb_us = t_unemb * 1e3 / reps
+    return 36 * per_layer_us + unemb_us, per_layer_us, unemb_us
+
+
 def pass_only(pkg, orc, args):
     """Token passes of a model cut to --pass-layers layers (full-size matrices, small vocabulary unless asked
     otherwise): the small case for profilers.  With QW3_TRACE=1 the engine records global-timer stamps inside
@@ -465,6 +502,11 @@ def main():
                      "avg_launch_us": us, "avg_launch_us_with_pdl": us_pdl, "launches_timed": n_launch,
                      "bytes_per_launch": gemv_bytes(M, K), "l2": "36 distinct matrices cycled (906 MB > 126 MB L2)",
                      "ref_dequant_then_cublas_us": LAST_REF_GEMV_US}
+        ref_us, ref_layer_us, ref_unemb_us = reference_method_token_us(torch)
+        ref_method = {"what": "the reference's design on this GPU, contractions only: cuBLAS at n=1 on fp16 copies of the five "
+                              "matrices per layer and of unembed (13.3 GB per token); no norms, attention, copies or host waits",
+                      "us_per_token": ref_us, "us_per_layer": ref_layer_us, "unembed_us": ref_unemb_us,
+                      "tokens_per_s_upper_bound": 1e6 / ref_us}
         decode_gbs = token_bytes(ctx_mid) * tps / 1e9
         line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": decode_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -484,7 +526,7 @@ def main():
                              "traffic_note": "dram read+write of an ncu capture of a 6-layer pass (514.4 MB for 507.6 MB "
                                              "algorithmic), scaled by bytes to the 36-layer launch",
                              "note": "at batch 1 the stages of N GPUs run one after another: one GPU's bandwidth is in use at a time"},
-                "gemv_roofline": gemv_roof,
+                "gemv_roofline": gemv_roof, "reference_method_gpu": ref_method,
                 "e2e": {"value": args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
                         "note": "host wall-clock of decode_more(K) through the C ABI; the sampled id feeds the next step on the device"},
                 "gpu_launches": int(launches), "clocks": clocks, "prefill": prefill,

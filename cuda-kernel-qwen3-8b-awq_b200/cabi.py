@@ -24,6 +24,7 @@ EXPORTS = [
     "qw3_rope_kv_append", "qw3_attn_decode", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
     "qw3_create", "qw3_destroy", "qw3_generate", "qw3_decode_more", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
     "qw3_set_batched_prefill",
+    "qw3_set_chained_decode",
     "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect", "qw3_stage_layers",
 ]
 
@@ -100,6 +101,7 @@ def lib():
         "qw3_decode_more": [vp, i32, vp, C.POINTER(i32)],
         "qw3_last_logits": [vp, vp],
         "qw3_set_batched_prefill": [vp, i32],
+        "qw3_set_chained_decode": [vp, i32],
         "qw3_last_timing": [vp, C.POINTER(f32), C.POINTER(f32)],
         "qw3_last_launches": [vp, C.POINTER(i64)],
         "qw3_kv_upload": [vp, i32, i32, vp, i64],

@@ -48,6 +48,7 @@ constexpr int P_OPW = 48;                // 32-bit words of a descriptor after i
 constexpr int P_DONE = 256;              // largest number of tiles / heads of an operator
 constexpr int P_MAX_OPS = 256;           // operators of one pass (their unit ranges are cached in shared memory)
 constexpr int P_TAG_OPS = 1024;          // tags: launch epoch * P_TAG_OPS + operator index
+constexpr int P_SRC_PEER = P_TAG_OPS - 1; // `src` / `rsrc` of words the stage before this one stores from another GPU
 constexpr int P_PSLOTS = WS_MAX_CTAS + P_DONE;   // partial-sum slots (CTA + tile) of an operator
 
 constexpr size_t P_OFF_RED = (size_t)P_RING * P_UNIT_BYTES;
@@ -64,6 +65,8 @@ enum PassOpKind { PASS_EMBED = 0, PASS_GEMV = 1, PASS_ATTN = 2 };
 enum PassOpFlags {
     PASS_WAIT_PREV = 1,   // inputs are plain memory written by the operator before: wait for its arrival counter
     PASS_PUBLISH = 2,     // the operator after (or the final arg-max) waits on this operator's arrival counter
+    PASS_PEER_OUT = 4,    // yt is the next stage's inbox in another GPU's memory: system-scope stores, peer tag
+    PASS_TOKEN_PEER = 8,  // embedding of a decode pass: the id arrives as a tagged word the last stage stores
 };
 
 struct PassOpBody {          // 192 bytes, copied to shared memory per operator
@@ -115,6 +118,11 @@ struct PassParams {
     int heads, hidden;
     long long max_pos, vocab;
     int* d_token_out;
+    // One process per GPU, stages chained inside the kernels (no hand-off launches between passes): words that cross
+    // GPUs carry a tag made of the generation counter and the token position, which every stage knows.
+    const int* d_gen;                         // generation counter of this sequence (null: 0)
+    const unsigned long long* tok_in;         // first stage: (sampled id, peer tag) stored by the last stage
+    unsigned long long* const* tok_out_slot;  // last stage: device word holding the first stage's tok_in address (or null)
     float* logits_f32;
     unsigned long long* trace2;  // optional [grid][n_ops][8]: per-CTA event times inside each operator (debug)
     unsigned long long* trace;   // optional [n_ops + 1]: global timer when CTA 0 enters each operator
@@ -152,6 +160,26 @@ __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
     return a;
 }
+// The same single-word hand-over between GPUs (the writer is a kernel on the stage before / after): system scope.
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long a) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+    unsigned long long a;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return a;
+}
+__device__ __forceinline__ void ld_relaxed_sys_v2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+// Tag of a word that crosses GPUs: bit 31 (no launch tag has it while the epoch is below 2^21), the generation
+// counter and the position + 1.  The words of an inbox are rewritten for every token, so the newest content always
+// belongs to this position or to an earlier one of this or the previous generation.
+__device__ __forceinline__ uint32_t peer_tag(int gen, int pos) {
+    return 0x80000000u | (((uint32_t)gen & 0x3ffu) << 21) | (((uint32_t)pos + 1u) & 0x1fffffu);
+}
+// Waits on another GPU are bounded more generously than waits inside a launch (the stages run one after another).
+constexpr long long P_PEER_WAIT_CLOCKS = 1ll << 34;
 // Output pairs of a tile shared by CTAs cf..cl are dealt evenly: CTA c finalises pairs [pb, pe) of the
 // 512; thread t of it takes pair pb + t.  Returns whether thread t has a pair.
 __device__ __forceinline__ bool slice_pair(int cf, int cl, int c, int t, int& pp) {
@@ -215,6 +243,7 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
 struct PassSmem {
     const int4* s_rng;   // [n_ops] {first unit, units, units per tile, kind} of this CTA, filled at kernel start
     int* s_epoch;   // value this launch writes into its flags
+    uint32_t* s_ptag;   // peer_tag(generation, position) of this pass
     uint8_t* ring;
     float* red;
     __half* xs;
@@ -268,6 +297,8 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
         return;
     }
     const long long t_begin = clock64();
+    const bool peer = op.src == P_SRC_PEER;   // written by the stage before, on another GPU
+    const long long t_limit = peer ? P_PEER_WAIT_CLOCKS : (1ll << 31);
     __syncwarp();
     unsigned long long w[3][4] = {{0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}};
     for (;;) {
@@ -276,8 +307,13 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
         for (int e = 0; e < 3; ++e) {
             const int ch = first + e * P_NCONS;
             if (ch < limit) {
-                ld_relaxed_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
-                ld_relaxed_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
+                if (peer) {
+                    ld_relaxed_sys_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
+                    ld_relaxed_sys_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
+                } else {
+                    ld_relaxed_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
+                    ld_relaxed_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
+                }
             }
         }
 #pragma unroll
@@ -288,8 +324,8 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
             }
         }
         if (ok || *sm.s_dead != 0) break;
-        if (clock64() - t_begin > (1ll << 31)) {
-            atomicCAS(p.ws.err, 0, 0x20000 | o);
+        if (clock64() - t_begin > t_limit) {
+            atomicCAS(p.ws.err, 0, (peer ? 0x90000 : 0x20000) | o);
             *sm.s_dead = 1;
             break;
         }
@@ -380,9 +416,11 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
     }
     if (op.flags & PASS_WAIT_PREV) wait_for_previous(p, sm, o);
     else trace_event(p, o, 1);
-    const uint32_t xtag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.src;
-    // what the epilogue of the first tile will need (written two or more operators ago)
+    const uint32_t xtag = op.src == P_SRC_PEER ? *sm.s_ptag : (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.src;
     const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
+    const bool peer_out = (op.flags & PASS_PEER_OUT) != 0;          // the tagged output goes to the next stage's GPU
+    const uint32_t ytag = peer_out ? *sm.s_ptag : tag;
+    // what the epilogue of the first tile will need (written two or more operators ago)
     uint32_t pre_a = 0u, pre_b = 0u;   // RESIDUAL: y[i], y[i+1];  ROPE_KV: cos, sin of this thread's pair
     if (n_units > 0) {
         int cf, cl, pp = tid;
@@ -392,7 +430,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         if (active && i < op.M) {
             if (op.epilogue == QW3_EPI_RESIDUAL) {
                 if (op.rt != nullptr) {   // value and tag; the tag is checked when the value is used
-                    const unsigned long long w = ld_relaxed_u64(op.rt + (i >> 1));
+                    const unsigned long long w = op.rsrc == P_SRC_PEER ? ld_relaxed_sys_u64(op.rt + (i >> 1)) : ld_relaxed_u64(op.rt + (i >> 1));
                     pre_a = (uint32_t)w;
                     pre_b = (uint32_t)(w >> 32);
                 } else {
@@ -415,8 +453,11 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         auto store_pair = [&](const __half a, const __half b) {
             const __half2 v = __halves2half2(a, b);
             *reinterpret_cast<__half2*>(op.y + i) = v;
-            if (op.yt != nullptr)
-                st_relaxed_u64(op.yt + (i >> 1), ((unsigned long long)tag << 32) | *reinterpret_cast<const uint32_t*>(&v));
+            if (op.yt != nullptr) {
+                const unsigned long long w = ((unsigned long long)ytag << 32) | *reinterpret_cast<const uint32_t*>(&v);
+                if (peer_out) st_relaxed_sys_u64(op.yt + (i >> 1), w);
+                else st_relaxed_u64(op.yt + (i >> 1), w);
+            }
         };
         if (op.epilogue == QW3_EPI_STORE) {
             if (valid) store_pair(h0, h1);
@@ -426,16 +467,18 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
                 if (op.rt != nullptr) {
                     // the word must carry the tag of the operator that wrote the residual stream last: a CTA that
                     // had no part in the operators in between may be here before that word is written
-                    const uint32_t rtag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.rsrc;
-                    unsigned long long w = tile_e == t0 ? (((unsigned long long)pre_b << 32) | pre_a) : ld_relaxed_u64(op.rt + (i >> 1));
+                    const bool rpeer = op.rsrc == P_SRC_PEER;
+                    const uint32_t rtag = rpeer ? *sm.s_ptag : (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.rsrc;
+                    unsigned long long w = tile_e == t0 ? (((unsigned long long)pre_b << 32) | pre_a)
+                                                        : (rpeer ? ld_relaxed_sys_u64(op.rt + (i >> 1)) : ld_relaxed_u64(op.rt + (i >> 1)));
                     const long long t_begin = clock64();
                     while ((uint32_t)(w >> 32) != rtag && *sm.s_dead == 0) {
-                        if (clock64() - t_begin > (1ll << 31)) {
+                        if (clock64() - t_begin > (rpeer ? P_PEER_WAIT_CLOCKS : (1ll << 31))) {
                             atomicCAS(p.ws.err, 0, 0x80000 | o);   // the residual stream was never written
                             *sm.s_dead = 1;
                             break;
                         }
-                        w = ld_relaxed_u64(op.rt + (i >> 1));
+                        w = rpeer ? ld_relaxed_sys_u64(op.rt + (i >> 1)) : ld_relaxed_u64(op.rt + (i >> 1));
                     }
                     rv = (uint32_t)w;
                 } else {
@@ -811,6 +854,13 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
         if (lane == 0 && p.d_token_out) *p.d_token_out = bi;
+        if (lane == 0 && p.tok_out_slot != nullptr) {
+            // The first stage's next pass (position pos + 1) polls this word instead of waiting for a hand-off launch.
+            unsigned long long* const dst = *p.tok_out_slot;
+            const int gen = p.d_gen != nullptr ? __ldcg(p.d_gen) : 0;
+            if (dst != nullptr && *sm.s_dead == 0)
+                st_relaxed_sys_u64(dst, ((unsigned long long)peer_tag(gen, pos + 1) << 32) | (uint32_t)bi);
+        }
     }
     uc_base += n_units;
 }
@@ -1055,7 +1105,23 @@ __device__ __forceinline__ void embed_phase(const PassParams& p, const PassOpBod
         if (skip) {
             pair = __ldcg(reinterpret_cast<const uint32_t*>(op.y + i));   // keep the hidden state of the pass before
         } else {
-            long long tok = p.decode ? __ldcg(p.d_token) : __ldcg(p.d_prompt + pos);
+            long long tok;
+            if (p.decode && (op.flags & PASS_TOKEN_PEER)) {
+                // the id sampled by the last stage's pass of the previous position, stored from its GPU
+                unsigned long long w = ld_relaxed_sys_u64(p.tok_in);
+                const long long t_begin = clock64();
+                while ((uint32_t)(w >> 32) != *sm.s_ptag && *sm.s_dead == 0) {
+                    if (clock64() - t_begin > P_PEER_WAIT_CLOCKS) {
+                        atomicCAS(p.ws.err, 0, 0xA0000 | o);   // the sampled id never arrived
+                        *sm.s_dead = 1;
+                        break;
+                    }
+                    w = ld_relaxed_sys_u64(p.tok_in);
+                }
+                tok = (long long)(int)(uint32_t)w;
+            } else {
+                tok = p.decode ? __ldcg(p.d_token) : __ldcg(p.d_prompt + pos);
+            }
             if (tok < 0 || tok >= p.vocab) tok = 0;
             const long long pc = (p.vocab + 1) / 2;
             const long long g = (tok / 128) % op.n_alloc;
@@ -1095,6 +1161,7 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
     sm.s_argi = reinterpret_cast<int*>(misc + 832);                  // 64
     sm.s_dead = reinterpret_cast<int*>(misc + 900);
     sm.s_epoch = reinterpret_cast<int*>(misc + 904);
+    sm.s_ptag = reinterpret_cast<uint32_t*>(misc + 908);
     sm.s_op = reinterpret_cast<uint32_t*>(misc + 1024);              // 2 x 192 bytes
 
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -1112,6 +1179,7 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
         for (int s = 0; s < P_RING; ++s) mbar_init(sm.full0 + 8 * s, 1);
         *sm.s_dead = 0;
         *sm.s_epoch = __ldcg(p.d_epoch) + 1;
+        *sm.s_ptag = peer_tag(p.d_gen != nullptr ? __ldcg(p.d_gen) : 0, __ldcg(p.d_pos));
         mbar_fence_init();
     }
     __syncthreads();
@@ -1248,7 +1316,8 @@ size_t pass_xchg_bytes() { return 2 * (size_t)P_PSLOTS * P_TI * sizeof(unsigned 
 int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d_xchg, const int* d_epoch, const int* d_pos, const int* d_token, const int* d_skip,
                 const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
                 long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
-                unsigned long long* trace2, const Workspace* ws, cudaStream_t st) {
+                unsigned long long* trace2, const int* d_gen, const void* tok_in, const void* tok_out_slot, const Workspace* ws,
+                cudaStream_t st) {
     QW3_REQUIRE(n_ops <= P_MAX_OPS, "pass_launch: too many operators in one pass");
     PassParams p;
     std::memset(&p, 0, sizeof(p));
@@ -1262,6 +1331,9 @@ int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d
     p.cos_t = static_cast<const __half*>(cos_t); p.sin_t = static_cast<const __half*>(sin_t);
     p.heads = heads; p.hidden = hidden; p.max_pos = max_pos; p.vocab = vocab;
     p.d_token_out = d_token_out; p.logits_f32 = logits_f32; p.trace = trace; p.trace2 = trace2;
+    p.d_gen = d_gen;
+    p.tok_in = static_cast<const unsigned long long*>(tok_in);
+    p.tok_out_slot = static_cast<unsigned long long* const*>(tok_out_slot);
     p.ws = *ws;
     int grid = ws->sm_count < WS_MAX_CTAS ? ws->sm_count : WS_MAX_CTAS;
     QW3_CUDA(cudaMemsetAsync(d_done, 0, (size_t)n_ops * sizeof(int), st));

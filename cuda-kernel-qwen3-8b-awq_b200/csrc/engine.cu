@@ -39,6 +39,8 @@ const W4Desc* w4_desc(qw3_w4_t w);
 const Workspace* ws_struct(qw3_ws_t ws);
 // stage hand-off between processes (handoff.cu)
 size_t mailbox_bytes(int hidden);
+void* mailbox_linked_inbox(void* mb, int hidden);
+void* mailbox_token_word(void* mb);
 int handoff_send(const void* hidden, void* next_mb, const void* my_mb, int msg, int hidden_n, int* err, cudaStream_t st);
 int handoff_recv(void* hidden, const void* my_mb, void* prev_mb, int msg, int hidden_n, int* err, cudaStream_t st);
 int token_send(const int* d_token, void* first_mb, int msg, cudaStream_t st);
@@ -58,7 +60,7 @@ void pass_link(PassOp* op, int flags, int src, const void* xt, void* yt, const v
 int pass_launch(const void* d_ops, int n_ops, int* d_done, unsigned long long* d_xchg, const int* d_epoch, const int* d_pos, const int* d_token, const int* d_skip,
                 const int* d_prompt, int decode, const void* cos_t, const void* sin_t, int heads, int hidden,
                 long long max_pos, long long vocab, int* d_token_out, float* logits_f32, unsigned long long* trace,
-                unsigned long long* trace2, const Workspace* ws, cudaStream_t st);
+                unsigned long long* trace2, const int* d_gen, const void* tok_in, const void* tok_out_slot, const Workspace* ws, cudaStream_t st);
 
 #define QW3_TRY(expr)                     \
     do {                                  \
@@ -103,6 +105,13 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     void* ops_prompt = nullptr;
     void* ops_decode = nullptr;
     int n_ops_prompt = 0, n_ops_decode = 0;
+    // one process per GPU: decode pass whose first / last operators poll / store the neighbours' mailboxes themselves
+    void* ops_linked = nullptr;
+    int n_ops_linked = 0;
+    cudaGraphExec_t g_linked = nullptr;
+    int launches_linked = 0;
+    int* d_gen = nullptr;                        // generation counter of the sequence (part of the cross-GPU tags)
+    unsigned long long** d_tok_out_slot = nullptr;   // last stage: holds the address of the first stage's token word
     int* d_done = nullptr;    // persistent pass: per-operator arrival counters + the launch epoch word behind them
     int* d_epoch = nullptr;
     unsigned long long* d_xchg = nullptr;   // tagged partial sums exchanged between CTAs
@@ -138,6 +147,9 @@ struct qw3_engine {
     bool batched_prefill = false;       // prompt in blocks of rows through the tensor-core contraction (qw3_set_batched_prefill)
     int seq_len = 0;                    // token passes through the layers so far (next position)
     int sampled = 0;                    // ids sampled since the last prompt
+    int gen = 0;                        // generate calls so far (one process per GPU: part of the cross-GPU tags)
+    bool linked_now = false;            // the pass being enqueued is a chained decode pass (ops_linked)
+    bool chain_decode = true;           // qw3_set_chained_decode
 };
 
 namespace qw3 {
@@ -293,9 +305,13 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
     QW3_CUDA(cudaSetDevice(s.device));
     if (layers && s.persistent) {
         // the whole pass of this stage is one cooperative launch
-        QW3_TRY(pass_launch(decode ? s.ops_decode : s.ops_prompt, decode ? s.n_ops_decode : s.n_ops_prompt, s.d_done, s.d_xchg, s.d_epoch, s.d_pos,
-                            s.d_token, first ? s.d_skip : nullptr, s.d_prompt, decode ? 1 : 0, s.cos_t, s.sin_t, c.heads,
-                            c.hidden, c.max_pos, c.vocab, s.d_token, s.logits32, s.d_trace, s.d_trace2, ws_struct(s.ws), s.stream));
+        const bool linked = decode && e->linked_now;
+        const void* ops = linked ? s.ops_linked : (decode ? s.ops_decode : s.ops_prompt);
+        const int n_ops = linked ? s.n_ops_linked : (decode ? s.n_ops_decode : s.n_ops_prompt);
+        QW3_TRY(pass_launch(ops, n_ops, s.d_done, s.d_xchg, s.d_epoch, s.d_pos, s.d_token, first ? s.d_skip : nullptr, s.d_prompt,
+                            decode ? 1 : 0, s.cos_t, s.sin_t, c.heads, c.hidden, c.max_pos, c.vocab, s.d_token, s.logits32, s.d_trace,
+                            s.d_trace2, s.d_gen, (e->mailbox && first) ? mailbox_token_word(e->mailbox) : nullptr,
+                            (decode && last) ? s.d_tok_out_slot : nullptr, ws_struct(s.ws), s.stream));
         *launches += 1;
     } else if (layers) {
         if (first) {
@@ -318,7 +334,10 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
 }
 
 // Operator list of one pass of a stage, uploaded once (runOneLayer's sequence, Inference.cu:1029-1230).
-static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, int* n_ops) {
+// `linked` (one process per GPU, decode): the first operators read the hidden state from this stage's tagged inbox,
+// which the stage before stores from its GPU, the last residual operator stores its tagged output into the next
+// stage's inbox, and the embedding takes the sampled id from the tagged token word.
+static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, int* n_ops, bool linked = false) {
     const Qw3Config& c = e->cfg;
     Stage& s = e->st[si];
     const bool first = e->st[si].gidx == 0, last = e->st[si].gidx == c.n_stages - 1;
@@ -331,35 +350,49 @@ static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, 
     auto at = [&](int i) { return reinterpret_cast<PassOp*>(base + (size_t)i * ob); };
     // Inside a launch activations go from operator to operator as tagged words (hidden_t, qkv_t, ctx_t, mlp_t); only
     // the final arg-max waits on an arrival counter (the unembedding's).
-    constexpr int PUBLISH = 2;   // PassOpFlags
+    constexpr int PUBLISH = 2, PEER_OUT = 4, TOKEN_PEER = 8, SRC_PEER = 1023;   // PassOpFlags, P_SRC_PEER
     bool hidden_tagged = false;            // hidden_t holds the residual stream (written in this launch)
     int hidden_src = -1;                   // operator that wrote it last
+    const unsigned long long* hidden_in = s.hidden_t;   // where the tagged residual stream is read from
+    if (linked && !first) {
+        hidden_in = static_cast<const unsigned long long*>(mailbox_linked_inbox(e->mailbox, c.hidden));
+        hidden_tagged = true;
+        hidden_src = SRC_PEER;
+    }
+    void* const peer_inbox = (linked && !last) ? mailbox_linked_inbox(e->next_mb, c.hidden) : nullptr;
+    const int n_layers = (int)s.layers.size();
+    int li = 0;
     if (first) {
         pass_fill_embed(at(k), s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, s.hidden, c.hidden);
-        pass_link(at(k), 0, -1, nullptr, s.hidden_t, nullptr, -1);
+        pass_link(at(k), linked ? TOKEN_PEER : 0, -1, nullptr, s.hidden_t, nullptr, -1);
         hidden_src = k;
         ++k;
         hidden_tagged = true;
     }
     for (LayerDev& L : s.layers) {
         pass_fill_gemv(at(k), w4_desc(L.wqkv.desc), s.hidden, L.gamma, c.eps, QW3_EPI_ROPE_KV, s.q, L.kc, L.vc);
-        pass_link(at(k), 0, k - 1, hidden_tagged ? s.hidden_t : nullptr, s.qkv_t, nullptr, -1);
+        pass_link(at(k), 0, hidden_src == SRC_PEER ? SRC_PEER : k - 1, hidden_tagged ? hidden_in : nullptr, s.qkv_t, nullptr, -1);
         ++k;
         pass_fill_attn(at(k), s.q, L.kc, L.vc, s.ctx, c.heads);
         pass_link(at(k), 0, k - 1, s.qkv_t, s.ctx_t, nullptr, -1);
         ++k;
         pass_fill_gemv(at(k), w4_desc(L.wo.desc), s.ctx, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
-        pass_link(at(k), 0, k - 1, s.ctx_t, s.hidden_t, hidden_tagged ? s.hidden_t : nullptr, hidden_src);
+        pass_link(at(k), 0, k - 1, s.ctx_t, s.hidden_t, hidden_tagged ? hidden_in : nullptr, hidden_src);
         hidden_src = k;
+        hidden_in = s.hidden_t;
         ++k;
         hidden_tagged = true;
         pass_fill_gemv(at(k), w4_desc(L.w1.desc), s.hidden, L.gamma, c.eps, QW3_EPI_GELU, s.mlp, nullptr, nullptr);
         pass_link(at(k), 0, k - 1, s.hidden_t, s.mlp_t, nullptr, -1);
         ++k;
         pass_fill_gemv(at(k), w4_desc(L.w2.desc), s.mlp, nullptr, c.eps, QW3_EPI_RESIDUAL, s.hidden, nullptr, nullptr);
-        pass_link(at(k), 0, k - 1, s.mlp_t, s.hidden_t, s.hidden_t, hidden_src);
+        if (peer_inbox != nullptr && li == n_layers - 1)   // the stage's result goes straight into the next stage's inbox
+            pass_link(at(k), PEER_OUT, k - 1, s.mlp_t, peer_inbox, s.hidden_t, hidden_src);
+        else
+            pass_link(at(k), 0, k - 1, s.mlp_t, s.hidden_t, s.hidden_t, hidden_src);
         hidden_src = k;
         ++k;
+        ++li;
     }
     if (decode && last) {
         pass_fill_gemv(at(k), w4_desc(s.unemb.desc), s.hidden, s.layers.back().gamma, c.eps, QW3_EPI_ARGMAX, s.logits16,
@@ -378,7 +411,7 @@ static int capture_stage_graph(qw3_engine* e, int si, bool decode, cudaGraphExec
     QW3_CUDA(cudaSetDevice(s.device));
     QW3_CUDA(cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeThreadLocal));
     *launches = 0;
-    int rc = enqueue_stage_pass(e, si, decode, true, e->cfg.use_pdl != 0, launches);
+    int rc = enqueue_stage_pass(e, si, decode, true, e->cfg.use_pdl != 0, launches);   // e->linked_now selects the chained program
     cudaGraph_t g = nullptr;
     cudaError_t ce = cudaStreamEndCapture(s.stream, &g);
     if (rc != QW3_OK) {
@@ -509,6 +542,7 @@ int qw3_destroy(qw3_handle e) {
         if (s.stream) cudaStreamSynchronize(s.stream);
         if (s.g_prompt) cudaGraphExecDestroy(s.g_prompt);
         if (s.g_decode) cudaGraphExecDestroy(s.g_decode);
+        if (s.g_linked) cudaGraphExecDestroy(s.g_linked);
         for (LayerDev& L : s.layers) {
             qw3_w4_destroy(L.wqkv.desc); qw3_w4_destroy(L.wo.desc); qw3_w4_destroy(L.w1.desc); qw3_w4_destroy(L.w2.desc);
         }
@@ -655,6 +689,9 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_done), (size_t)(n_max + 64) * sizeof(int)));
                 QW3_CUDA(cudaMemset(s.d_done, 0, (size_t)(n_max + 64) * sizeof(int)));
                 s.d_epoch = s.d_done + n_max + 32;
+                s.d_gen = s.d_done + n_max + 40;
+                QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_tok_out_slot), 16));
+                QW3_CUDA(cudaMemset(s.d_tok_out_slot, 0, 16));
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_xchg), pass_xchg_bytes()));
                 QW3_CUDA(cudaMemset(s.d_xchg, 0, pass_xchg_bytes()));
             }
@@ -709,10 +746,11 @@ int qw3_create(const char* weight_dir, const Qw3Config* cfg, qw3_handle* out) {
 static int pass_mp(qw3_engine* e, bool decode, bool layers) {
     Stage& s = e->st[0];
     QW3_CUDA(cudaSetDevice(s.device));
-    cudaGraphExec_t g = decode ? s.g_decode : s.g_prompt;
+    const bool linked = decode && layers && e->linked_now;
+    cudaGraphExec_t g = linked ? s.g_linked : (decode ? s.g_decode : s.g_prompt);
     if (layers && g) {
         QW3_CUDA(cudaGraphLaunch(g, s.stream));
-        e->launches += decode ? s.launches_decode : s.launches_prompt;
+        e->launches += linked ? s.launches_linked : (decode ? s.launches_decode : s.launches_prompt);
     } else {
         int n = 0;
         QW3_TRY(enqueue_stage_pass(e, 0, decode, layers, false, &n));
@@ -744,7 +782,18 @@ static int decode_loop_mp(qw3_engine* e, int max_new, int32_t* out_ids, int32_t*
     for (int step = 0; step < max_new; ++step) {
         const bool very_first = (e->sampled == 0);
         const bool layers = !(c.sample_first && very_first);
-        if (layers) {
+        // From the second pass through the layers on, the stages are chained inside the token-pass kernels: the last
+        // operator of a stage stores the tagged hidden state into the next GPU's inbox, the first operator of the next
+        // stage polls it, and the sampled id reaches the first stage the same way.  Every stage takes this decision
+        // from the same counters, so the stages switch at the same step.
+        const bool chained = layers && e->chain_decode && s.ops_linked != nullptr && e->sampled >= (c.sample_first ? 2 : 1);
+        if (chained) {
+            e->linked_now = true;
+            const int rc = pass_mp(e, true, true);
+            e->linked_now = false;
+            QW3_TRY(rc);
+            e->seq_len += 1;
+        } else if (layers) {
             if (very_first) {
                 // Reference flow (Inference.cu:1357): the last stage's final hidden state re-enters layer 0.
                 if (last) QW3_TRY(mp_send(e));
@@ -785,6 +834,8 @@ static int generate_mp(qw3_engine* e, const int32_t* prompt, int32_t n_prompt, i
     e->launches = 0;
     QW3_CUDA(cudaSetDevice(s.device));
     QW3_CUDA(cudaMemsetAsync(s.d_pos, 0, 16, s.stream));
+    e->gen += 1;   // every stage counts the generations alike: the cross-GPU tags of this sequence
+    if (s.d_gen) QW3_CUDA(cudaMemcpyAsync(s.d_gen, &e->gen, 4, cudaMemcpyHostToDevice, s.stream));
     if (first) QW3_CUDA(cudaMemcpyAsync(s.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s.stream));
     QW3_CUDA(cudaEventRecord(e->ev0, s.stream));
     for (int t = 0; t < n_prompt; ++t) {     // stages overlap on successive prompt tokens (two inbox slots)
@@ -1041,6 +1092,28 @@ int qw3_stage_connect(qw3_handle e, const void* next_stage_handle_64B, const voi
     } else {
         QW3_CUDA(cudaIpcOpenMemHandle(&e->prev_mb, hp, cudaIpcMemLazyEnablePeerAccess));
     }
+    // Chained decode passes: their operator list names the neighbours' mailboxes, so it is built here.
+    Stage& s = e->st[0];
+    if (s.persistent) {
+        const bool last = s.gidx == e->cfg.n_stages - 1;
+        if (last) {   // the first stage is the next one in the ring
+            unsigned long long* tw = static_cast<unsigned long long*>(mailbox_token_word(e->next_mb));
+            QW3_CUDA(cudaMemcpy(s.d_tok_out_slot, &tw, sizeof(tw), cudaMemcpyHostToDevice));
+        }
+        QW3_TRY(build_pass_program(e, 0, true, &s.ops_linked, &s.n_ops_linked, true));
+        if (e->cfg.use_graph) {
+            e->linked_now = true;
+            const int rc = capture_stage_graph(e, 0, true, &s.g_linked, &s.launches_linked);
+            e->linked_now = false;
+            QW3_TRY(rc);
+        }
+    }
+    return QW3_OK;
+}
+
+int qw3_set_chained_decode(qw3_handle e, int on) {
+    QW3_REQUIRE(e, "qw3_set_chained_decode: null handle");
+    e->chain_decode = on != 0;
     return QW3_OK;
 }
 

@@ -10,6 +10,9 @@
 //     nine seconds, then it records an error and returns), copies the inbox out and acknowledges
 //     into the sender's mailbox, which is what lets the sender reuse the two inbox slots;
 //   * the sampled token id travels the same way from the last stage to the first.
+// That protocol serves the prompt phase and the first decode step.  From the second decode step on the stages are
+// chained inside the token-pass kernels (decode_pass.cu): the mailbox also holds a tagged inbox and a tagged token
+// word which the kernels store to and poll directly, so no hand-off launch sits between two stages.
 // No collective exists on this path, so no NCCL; no multicast of any kind is used.
 #include "common.cuh"
 
@@ -20,12 +23,18 @@ struct Mailbox {
     int ack_flag;    // number of the newest message the stage after this one has taken out of ITS inbox
     int tok_flag;    // number of the newest token message
     int tok_val;
-    int pad[60];
-    // followed by __half inbox[2][hidden]
+    int pad0[12];
+    unsigned long long tok_word;   // byte 64: (sampled id, tag) stored by the last stage's token-pass kernel itself
+    int pad1[46];
+    // followed by __half inbox[2][hidden], then unsigned long long linked_inbox[hidden / 2]: the hidden state as
+    // (two halves, tag) words stored by the last operator of the previous stage's token-pass kernel and polled by
+    // the first operator of this stage's (decode steps chained inside the kernels, no hand-off launches)
 };
 static_assert(sizeof(Mailbox) == 256, "mailbox header is 256 bytes");
 
-size_t mailbox_bytes(int hidden) { return sizeof(Mailbox) + (size_t)2 * hidden * 2; }
+size_t mailbox_bytes(int hidden) { return sizeof(Mailbox) + (size_t)2 * hidden * 2 + (size_t)(hidden / 2) * 8; }
+void* mailbox_linked_inbox(void* mb, int hidden) { return static_cast<uint8_t*>(mb) + sizeof(Mailbox) + (size_t)2 * hidden * 2; }
+void* mailbox_token_word(void* mb) { return &static_cast<Mailbox*>(mb)->tok_word; }
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     int v;

@@ -41,6 +41,11 @@ class QWen3AWQInfer:
         reference (False, the default)."""
         cabi.check(self._lib.qw3_set_batched_prefill(self._h, 1 if on else 0), "qw3_set_batched_prefill")
 
+    def set_chained_decode(self, on):
+        """One process per GPU: chain the stages inside the token-pass kernels from the second decode step on (True,
+        the default) or keep the mailbox send / receive launches for every step (False).  Set every stage alike."""
+        cabi.check(self._lib.qw3_set_chained_decode(self._h, 1 if on else 0), "qw3_set_chained_decode")
+
     def decode_more(self, max_new_tokens):
         """Continue the last generateResponse call for max_new_tokens more ids (same KV state)."""
         out = (C.c_int32 * max(max_new_tokens, 1))()

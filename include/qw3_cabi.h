@@ -217,6 +217,14 @@ int qw3_decode_more(qw3_handle h, int32_t max_new, int32_t* out_ids, int32_t* n_
  * fp16 bit.  Not available with one process per GPU (world > 1). */
 int qw3_set_batched_prefill(qw3_handle h, int on);
 
+/* One process per GPU (world > 1): from the second decode step on the stages are chained inside the token-pass
+ * kernels: the last operator of a stage stores the hidden state as tagged words into the next GPU's mailbox over
+ * NVLink, the first operator of the next stage polls it, and the sampled id returns to the first stage the same
+ * way, so no hand-off launch sits between two stages (the reference: cudaMemcpyPeerAsync plus a host
+ * synchronisation per boundary, Inference.cu:1013-1023).  on = 1 is the default; on = 0 keeps the mailbox
+ * send / receive launches for every step.  Results are identical.  Every stage must be set alike. */
+int qw3_set_chained_decode(qw3_handle h, int on);
+
 /* fp32 logits of the last decode step (keep_logits = 1), vocab floats to host memory. */
 int qw3_last_logits(qw3_handle h, float* out_vocab);
 /* Device time of the last call's prompt loop and decode loop (CUDA events, milliseconds). */

@@ -1,5 +1,5 @@
 """Two stages in two processes on two GPUs: the hidden state and the sampled id cross NVLink by peer
-stores into CUDA-IPC mailboxes; the ids must equal the single-GPU run and the oracle's golden ids.
+stores into CUDA-IPC mailboxes (by hand-off launches, or by the token-pass kernels themselves); the ids must equal the single-GPU run and the oracle's golden ids.
 Needs two visible GPUs (skipped otherwise).  gloo carries the handle exchange."""
 import json
 import multiprocessing as mp
@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SMALL = dict(hidden=512, inter=1536, heads=4, head_dim=128, layers=4, vocab=2176, max_pos=64, rope_base=10000.0)
 
 
-def _rank_main(rank, world, port, wdir, prompt, q, sample_first):
+def _rank_main(rank, world, port, wdir, prompt, q, sample_first, chained):
     import sys
     sys.path.insert(0, HERE)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -31,6 +31,7 @@ def _rank_main(rank, world, port, wdir, prompt, q, sample_first):
         inf = pkg.QWen3AWQInfer(wdir, n_stages=world, world=world, rank=rank, device=list(range(world)),
                                 sample_first=sample_first, **SMALL)
         pipeline.connect_ring(inf, dist)
+        inf.set_chained_decode(bool(chained))
         dist.barrier()
         ids = inf.generateResponse(prompt, 6)
         more = inf.decode_more(4)
@@ -42,8 +43,10 @@ def _rank_main(rank, world, port, wdir, prompt, q, sample_first):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,sample_first", [(2, 0), (2, 1), (4, 0)])
-def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_first):
+# chained = 1: from the second decode step on the stages hand over inside the token-pass kernels (tagged words stored
+# into the next GPU's mailbox); chained = 0: mailbox send / receive launches for every step
+@pytest.mark.parametrize("world,sample_first,chained", [(2, 0, 1), (2, 1, 1), (4, 0, 1), (2, 0, 0)])
+def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_first, chained):
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -57,7 +60,7 @@ def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_f
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, wdir, prompt, q, sample_first)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, wdir, prompt, q, sample_first, chained)) for r in range(world)]
     for p in procs:
         p.start()
     got = sorted(q.get(timeout=300) for _ in range(world))
