@@ -41,6 +41,8 @@ const Workspace* ws_struct(qw3_ws_t ws);
 size_t mailbox_bytes(int hidden);
 void* mailbox_linked_inbox(void* mb, int hidden);
 void* mailbox_token_word(void* mb);
+int block_send(const void* rows_src, size_t bytes, void* next_mb, const void* my_mb, int msg, int hidden, int* err, cudaStream_t st);
+int block_recv(void* rows_dst, size_t bytes, void* my_mb, void* prev_mb, int msg, int hidden, int* err, cudaStream_t st);
 int handoff_send(const void* hidden, void* next_mb, const void* my_mb, int msg, int hidden_n, int* err, cudaStream_t st);
 int handoff_recv(void* hidden, const void* my_mb, void* prev_mb, int msg, int hidden_n, int* err, cudaStream_t st);
 int token_send(const int* d_token, void* first_mb, int msg, cudaStream_t st);
@@ -144,6 +146,7 @@ struct qw3_engine {
     bool next_is_prev = false;
     int msg_out = 0, msg_in = 0;        // hidden-state messages sent to the next stage / taken from the previous one
     int tok_out = 0, tok_in = 0;        // token messages (last stage -> first stage)
+    int blk_out = 0, blk_in = 0;        // blocks of prompt rows (batched prompt phase)
     bool batched_prefill = false;       // prompt in blocks of rows through the tensor-core contraction (qw3_set_batched_prefill)
     int seq_len = 0;                    // token passes through the layers so far (next position)
     int sampled = 0;                    // ids sampled since the last prompt
@@ -445,7 +448,7 @@ static int handoff(qw3_engine* e, int from, int to, bool hidden, bool token) {
 // A block of `rows` prompt tokens at positions pos0.. goes through every stage together: the projections are
 // the tensor-core contraction, the rest the row kernels of prefill.cu.  Same per-element arithmetic as the
 // token-at-a-time loop (Inference.cu:1304-1343); the contractions sum in a different fp32 order.
-constexpr int PF_BLOCK = 256;
+constexpr int PF_BLOCK = 256;   // also the rows a block inbox of the mailbox holds (handoff.cu)
 
 static int prefill_alloc(qw3_engine* e, Stage& s) {
     if (s.pf_h) return QW3_OK;
@@ -459,6 +462,35 @@ static int prefill_alloc(qw3_engine* e, Stage& s) {
     return QW3_OK;
 }
 
+// One stage's share of a block: its layers over `rows` rows in s.pf_h (the first stage gathers the embeddings first),
+// then what the token loop leaves behind: the last row's hidden state and the position counter.
+static int prefill_stage_block(qw3_engine* e, Stage& s, int t0, int rows) {
+    const Qw3Config& c = e->cfg;
+    const int H = c.hidden;
+    if (s.gidx == 0) {
+        QW3_TRY(embed_rows_launch(s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, H, c.vocab, s.d_prompt + t0, rows, s.pf_h,
+                                  s.stream));
+        e->launches += 1;
+    }
+    for (LayerDev& L : s.layers) {
+        QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
+        QW3_TRY(qw3_gemm_w4a16(L.wqkv.desc, s.pf_n, rows, s.pf_qkv, s.ws, s.stream));
+        QW3_TRY(rope_kv_rows_launch(s.pf_qkv, L.kc, L.vc, s.cos_t, s.sin_t, H, c.max_pos, t0, rows, s.stream));
+        QW3_TRY(attn_prefill_launch(s.pf_qkv, L.kc, L.vc, c.heads, H, c.max_pos, t0, rows, s.pf_ctx, s.stream));
+        QW3_TRY(gemm_launch(L.wo.desc, s.pf_ctx, rows, s.pf_h, s.ws, s.stream, QW3_EPI_RESIDUAL));
+        QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
+        QW3_TRY(gemm_launch(L.w1.desc, s.pf_n, rows, s.pf_mlp, s.ws, s.stream, QW3_EPI_GELU));
+        QW3_TRY(gemm_launch(L.w2.desc, s.pf_mlp, rows, s.pf_h, s.ws, s.stream, QW3_EPI_RESIDUAL));
+        e->launches += 7;
+    }
+    QW3_CUDA(cudaMemcpyAsync(s.hidden, static_cast<char*>(s.pf_h) + (size_t)(rows - 1) * H * 2, (size_t)H * 2,
+                             cudaMemcpyDeviceToDevice, s.stream));
+    const int next_pos[4] = {t0 + rows, 0, 0, 0};
+    QW3_CUDA(cudaMemcpyAsync(s.d_pos, next_pos, 4, cudaMemcpyHostToDevice, s.stream));
+    return QW3_OK;
+}
+
+// Single process: the block goes through the stages one after another.
 static int prefill_block(qw3_engine* e, int t0, int rows) {
     const Qw3Config& c = e->cfg;
     const int N = c.n_stages, H = c.hidden;
@@ -474,28 +506,30 @@ static int prefill_block(qw3_engine* e, int t0, int rows) {
             QW3_CUDA(cudaSetDevice(a.device));
             QW3_CUDA(cudaStreamWaitEvent(a.stream, s.taken, 0));
             QW3_CUDA(cudaSetDevice(s.device));
-        } else {
-            QW3_TRY(embed_rows_launch(s.emb.packed, s.emb.scale, s.emb.zp, s.emb.n_alloc, H, c.vocab, s.d_prompt + t0, rows,
-                                      s.pf_h, s.stream));
-            e->launches += 1;
         }
-        for (LayerDev& L : s.layers) {
-            QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
-            QW3_TRY(qw3_gemm_w4a16(L.wqkv.desc, s.pf_n, rows, s.pf_qkv, s.ws, s.stream));
-            QW3_TRY(rope_kv_rows_launch(s.pf_qkv, L.kc, L.vc, s.cos_t, s.sin_t, H, c.max_pos, t0, rows, s.stream));
-            QW3_TRY(attn_prefill_launch(s.pf_qkv, L.kc, L.vc, c.heads, H, c.max_pos, t0, rows, s.pf_ctx, s.stream));
-            QW3_TRY(gemm_launch(L.wo.desc, s.pf_ctx, rows, s.pf_h, s.ws, s.stream, QW3_EPI_RESIDUAL));
-            QW3_TRY(rmsnorm_rows_launch(s.pf_h, L.gamma, H, c.eps, rows, s.pf_n, s.stream));
-            QW3_TRY(gemm_launch(L.w1.desc, s.pf_n, rows, s.pf_mlp, s.ws, s.stream, QW3_EPI_GELU));
-            QW3_TRY(gemm_launch(L.w2.desc, s.pf_mlp, rows, s.pf_h, s.ws, s.stream, QW3_EPI_RESIDUAL));
-            e->launches += 7;
-        }
-        // what the token loop leaves behind: the last row's hidden state and the position counter
-        QW3_CUDA(cudaMemcpyAsync(s.hidden, static_cast<char*>(s.pf_h) + (size_t)(rows - 1) * H * 2, (size_t)H * 2,
-                                 cudaMemcpyDeviceToDevice, s.stream));
-        const int next_pos[4] = {t0 + rows, 0, 0, 0};
-        QW3_CUDA(cudaMemcpyAsync(s.d_pos, next_pos, 4, cudaMemcpyHostToDevice, s.stream));
+        QW3_TRY(prefill_stage_block(e, s, t0, rows));
         QW3_CUDA(cudaEventRecord(s.done, s.stream));
+    }
+    return QW3_OK;
+}
+
+// One process per GPU: this stage takes the block from the stage before through its block inbox (the stages overlap
+// on successive blocks: two inbox slots, acknowledged), runs its layers and hands the rows on.
+static int prefill_block_mp(qw3_engine* e, int t0, int rows) {
+    const Qw3Config& c = e->cfg;
+    Stage& s = e->st[0];
+    const bool first = s.gidx == 0, last = s.gidx == c.n_stages - 1;
+    const size_t bytes = (size_t)rows * c.hidden * 2;
+    QW3_TRY(prefill_alloc(e, s));
+    QW3_CUDA(cudaSetDevice(s.device));
+    if (!first) {
+        QW3_TRY(block_recv(s.pf_h, bytes, e->mailbox, e->prev_mb, ++e->blk_in, c.hidden, ws_struct(s.ws)->err, s.stream));
+        e->launches += 2;
+    }
+    QW3_TRY(prefill_stage_block(e, s, t0, rows));
+    if (!last) {
+        QW3_TRY(block_send(s.pf_h, bytes, e->next_mb, e->mailbox, ++e->blk_out, c.hidden, ws_struct(s.ws)->err, s.stream));
+        e->launches += 2;
     }
     return QW3_OK;
 }
@@ -838,10 +872,15 @@ static int generate_mp(qw3_engine* e, const int32_t* prompt, int32_t n_prompt, i
     if (s.d_gen) QW3_CUDA(cudaMemcpyAsync(s.d_gen, &e->gen, 4, cudaMemcpyHostToDevice, s.stream));
     if (first) QW3_CUDA(cudaMemcpyAsync(s.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s.stream));
     QW3_CUDA(cudaEventRecord(e->ev0, s.stream));
-    for (int t = 0; t < n_prompt; ++t) {     // stages overlap on successive prompt tokens (two inbox slots)
-        if (!first) QW3_TRY(mp_recv(e));
-        QW3_TRY(pass_mp(e, false, true));
-        if (!last) QW3_TRY(mp_send(e));
+    if (e->batched_prefill) {
+        for (int t0 = 0; t0 < n_prompt; t0 += PF_BLOCK)
+            QW3_TRY(prefill_block_mp(e, t0, n_prompt - t0 < PF_BLOCK ? n_prompt - t0 : PF_BLOCK));
+    } else {
+        for (int t = 0; t < n_prompt; ++t) {     // stages overlap on successive prompt tokens (two inbox slots)
+            if (!first) QW3_TRY(mp_recv(e));
+            QW3_TRY(pass_mp(e, false, true));
+            if (!last) QW3_TRY(mp_send(e));
+        }
     }
     QW3_CUDA(cudaEventRecord(e->ev1, s.stream));
     e->seq_len = n_prompt;
@@ -972,11 +1011,7 @@ int qw3_last_logits(qw3_handle e, float* out_vocab) {
 
 int qw3_set_batched_prefill(qw3_handle e, int on) {
     QW3_REQUIRE(e, "qw3_set_batched_prefill: null handle");
-    if (on && e->cfg.world > 1) {
-        set_last_error("qw3_set_batched_prefill: one process per GPU runs the prompt token by token");
-        return QW3_ERR_STATE;
-    }
-    e->batched_prefill = on != 0;
+    e->batched_prefill = on != 0;   // one process per GPU: every stage must be set alike
     return QW3_OK;
 }
 

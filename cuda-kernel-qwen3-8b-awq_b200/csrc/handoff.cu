@@ -23,16 +23,26 @@ struct Mailbox {
     int ack_flag;    // number of the newest message the stage after this one has taken out of ITS inbox
     int tok_flag;    // number of the newest token message
     int tok_val;
-    int pad0[12];
+    int blk_flag;    // number of the newest block of prompt rows delivered into `block_inbox`
+    int blk_ack;     // number of the newest block the stage after this one has taken out of ITS block inbox
+    int pad0[10];
     unsigned long long tok_word;   // byte 64: (sampled id, tag) stored by the last stage's token-pass kernel itself
     int pad1[46];
     // followed by __half inbox[2][hidden], then unsigned long long linked_inbox[hidden / 2]: the hidden state as
     // (two halves, tag) words stored by the last operator of the previous stage's token-pass kernel and polled by
-    // the first operator of this stage's (decode steps chained inside the kernels, no hand-off launches)
+    // the first operator of this stage's (decode steps chained inside the kernels, no hand-off launches),
+    // then __half block_inbox[2][block_rows][hidden]: blocks of prompt rows of the batched prompt phase
 };
 static_assert(sizeof(Mailbox) == 256, "mailbox header is 256 bytes");
 
-size_t mailbox_bytes(int hidden) { return sizeof(Mailbox) + (size_t)2 * hidden * 2 + (size_t)(hidden / 2) * 8; }
+constexpr int MB_BLOCK_ROWS = 256;   // largest block of prompt rows handed over at once
+size_t mailbox_bytes(int hidden) {
+    return sizeof(Mailbox) + (size_t)2 * hidden * 2 + (size_t)(hidden / 2) * 8 + (size_t)2 * MB_BLOCK_ROWS * hidden * 2;
+}
+void* mailbox_block_inbox(void* mb, int hidden, int slot) {
+    return static_cast<uint8_t*>(mb) + sizeof(Mailbox) + (size_t)2 * hidden * 2 + (size_t)(hidden / 2) * 8 +
+           (size_t)slot * MB_BLOCK_ROWS * hidden * 2;
+}
 void* mailbox_linked_inbox(void* mb, int hidden) { return static_cast<uint8_t*>(mb) + sizeof(Mailbox) + (size_t)2 * hidden * 2; }
 void* mailbox_token_word(void* mb) { return &static_cast<Mailbox*>(mb)->tok_word; }
 
@@ -101,6 +111,36 @@ __global__ void token_recv_kernel(int* __restrict__ d_token, const Mailbox* my_m
         return;
     }
     *d_token = __ldcg(&my_mb->tok_val);
+}
+
+// Blocks of prompt rows: the rows move with a copy-engine copy between the two GPUs; these two one-thread kernels
+// around it carry the protocol (wait for the flag, bounded; publish the flag after the copy before it in the stream).
+__global__ void flag_wait_kernel(const int* flag, int want, int* err, int code) {
+    if (threadIdx.x == 0 && !wait_flag(flag, want)) atomicCAS(err, 0, code);
+}
+__global__ void flag_set_kernel(int* flag, int value) {
+    if (threadIdx.x != 0) return;
+    __threadfence_system();
+    st_release_sys(flag, value);
+}
+
+// Block `msg` (1, 2, ...) of `bytes` from `rows_src` into the next stage's block inbox.
+int block_send(const void* rows_src, size_t bytes, void* next_mb, const void* my_mb, int msg, int hidden, int* err, cudaStream_t st) {
+    flag_wait_kernel<<<1, 32, 0, st>>>(&static_cast<const Mailbox*>(my_mb)->blk_ack, msg - 2, err, 0x40004);
+    QW3_CUDA(cudaGetLastError());
+    QW3_CUDA(cudaMemcpyAsync(mailbox_block_inbox(next_mb, hidden, msg & 1), rows_src, bytes, cudaMemcpyDeviceToDevice, st));
+    flag_set_kernel<<<1, 32, 0, st>>>(&static_cast<Mailbox*>(next_mb)->blk_flag, msg);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
+// Block `msg` out of this stage's block inbox into `rows_dst`, then the acknowledgement to the stage before.
+int block_recv(void* rows_dst, size_t bytes, void* my_mb, void* prev_mb, int msg, int hidden, int* err, cudaStream_t st) {
+    flag_wait_kernel<<<1, 32, 0, st>>>(&static_cast<const Mailbox*>(my_mb)->blk_flag, msg, err, 0x40005);
+    QW3_CUDA(cudaGetLastError());
+    QW3_CUDA(cudaMemcpyAsync(rows_dst, mailbox_block_inbox(my_mb, hidden, msg & 1), bytes, cudaMemcpyDeviceToDevice, st));
+    flag_set_kernel<<<1, 32, 0, st>>>(&static_cast<Mailbox*>(prev_mb)->blk_ack, msg);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
 }
 
 int handoff_send(const void* hidden, void* next_mb, const void* my_mb, int msg, int hidden_n, int* err, cudaStream_t st) {

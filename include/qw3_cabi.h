@@ -214,7 +214,9 @@ int qw3_decode_more(qw3_handle h, int32_t max_new, int32_t* out_ids, int32_t* n_
  * contraction of qw3_gemm_w4a16 over the block, with row versions of RMSNorm, RoPE + KV append, causal
  * attention, residual add and GeLU around them.  Per-element arithmetic is unchanged; the contractions sum
  * in a different fp32 order, so cache rows and the hidden state can differ from the token loop in the last
- * fp16 bit.  Not available with one process per GPU (world > 1). */
+ * fp16 bit.  With one process per GPU (world > 1) the blocks travel from stage to stage through the mailboxes'
+ * block inboxes (a peer copy between two flag kernels) and the stages overlap on successive blocks; every stage
+ * must be set alike. */
 int qw3_set_batched_prefill(qw3_handle h, int on);
 
 /* One process per GPU (world > 1): from the second decode step on the stages are chained inside the token-pass

@@ -69,3 +69,68 @@ def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_f
         assert p.exitcode == 0
     for rank, ids in got:
         assert ids == want, (rank, ids, want)
+
+
+def _rank_main_batched(rank, world, port, wdir, prompt, q, max_pos):
+    import sys
+    sys.path.insert(0, HERE)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    from conftest import load_package
+    pkg = load_package()
+    import importlib
+    pipeline = importlib.import_module("qw3awq_b200.pipeline")
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.cuda.set_device(rank)
+        cfg = dict(SMALL, max_pos=max_pos)
+        inf = pkg.QWen3AWQInfer(wdir, n_stages=world, world=world, rank=rank, device=list(range(world)), **cfg)
+        pipeline.connect_ring(inf, dist)
+        inf.set_batched_prefill(True)
+        dist.barrier()
+        ids = inf.generateResponse(prompt, 8)
+        ids2 = inf.generateResponse(prompt, 8)      # the block counters carry on into a second sequence
+        dist.barrier()
+        last = rank == world - 1
+        ids = pipeline.broadcast_ids(ids if last else [], 8, dist)
+        ids2 = pipeline.broadcast_ids(ids2 if last else [], 8, dist)
+        q.put((rank, ids, ids2))
+        inf.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_prompt", [(2, 6), (2, 600), (4, 600)])
+def test_one_process_per_gpu_batched_prompt(pkg, orc, cuda, tmp_path, world, n_prompt):
+    """Prompt in blocks of up to 256 rows handed from stage to stage through the mailboxes' block inboxes (600 rows:
+    three blocks over two acknowledged slots): same ids as the single-GPU run with the same blocks."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    wdir = str(tmp_path)
+    orc.write_weight_dir(orc.default_config(**SMALL), 0, wdir)
+    prompt = [int(t) for t in orc.gen_tokens(0, orc.TOKENS, n_prompt, SMALL["vocab"])]
+    max_pos = n_prompt + 24
+    one = pkg.QWen3AWQInfer(wdir, **dict(SMALL, max_pos=max_pos))
+    one.set_batched_prefill(True)
+    want = one.generateResponse(prompt, 8)
+    one.close()
+    if n_prompt == 6:
+        golden = json.load(open(os.path.join(HERE, "golden", "golden.json")))
+        assert want == golden["small_model"]["ids"][:8]
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main_batched, args=(r, world, port, wdir, prompt, q, max_pos)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, ids, ids2 in got:
+        assert ids == want and ids2 == want, (rank, ids, ids2, want)
