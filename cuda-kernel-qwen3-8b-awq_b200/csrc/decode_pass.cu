@@ -23,7 +23,13 @@
 //     order (deterministic) and runs the epilogue there.  Activations: the epilogue stores (two halves,
 //     tag) per output pair, the next operator's prologue polls them.  The only arrival counter left
 //     precedes the final arg-max.  All CTAs are co-resident (cooperative launch), so the polls cannot
-//     deadlock; every poll gives up after about a second and reports a located error word.
+//     deadlock; every poll gives up after about a second and reports a located error word;
+//   * with one process per GPU the same words cross NVLink (copyHiddenBetweenGPUs, Inference.cu:1013-1023, without
+//     a launch or a host wait): the last residual operator of a stage stores its tagged output with system scope
+//     into the next GPU's inbox, the first operators of the next stage poll that inbox in their own memory, and the
+//     arg-max stores (id, tag) into the first stage's token word, which its embedding polls.  Those words carry a
+//     tag made of the generation counter and the token position, which all stages share; the waits are bounded
+//     (about nine seconds) and the kernels that wait on one another run on different GPUs.
 // Plain activations written inside the kernel (for readers after the launch) are never read back in it.
 #include <cstdlib>
 #include <cstring>
