@@ -34,7 +34,7 @@ METRIC = "batch-1 decode tokens/s (Qwen3-8B W4A16)"
 LAST_REF_GEMV_US = None
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_pass_kernel over its algorithmic bytes, from the ncu
 # capture summarised in profiles/ (a 6-layer pass; traffic grows with the bytes streamed).
-NCU_TRAFFIC_RATIO = (509.30 + 5.13) / 507.6
+NCU_TRAFFIC_RATIO = (509.30 + 4.82) / 507.6
 PROMPT_LEN = 128
 SEED = 0
 # Algorithmic bytes of one decoded token: packed weights of 36 layers + unembed, scale/zero-point
@@ -536,7 +536,7 @@ def main():
                              "unit": "GB/s", "frac": decode_gbs / peaks["hbm_gbs"],
                              "traffic": int(token_bytes(ctx_mid) * NCU_TRAFFIC_RATIO), "bytes_per_launch": token_bytes(ctx_mid),
                              "avg_launch_us": decode_ms * 1e3 / args.steps,
-                             "traffic_note": "dram read+write of an ncu capture of a 6-layer pass (514.4 MB for 507.6 MB "
+                             "traffic_note": "dram read+write of an ncu capture of a 6-layer pass (514.1 MB for 507.6 MB "
                                              "algorithmic), scaled by bytes to the 36-layer launch",
                              "note": "at batch 1 the stages of N GPUs run one after another: one GPU's bandwidth is in use at a time"},
                 "gemv_roofline": gemv_roof, "reference_method_gpu": ref_method,
