@@ -285,6 +285,32 @@ __device__ __forceinline__ void publish(const PassParams& p, int o) {
     if (threadIdx.x == 0) red_add_release(&p.done[o], 1);
 }
 
+// The chunks fetch_x3 is about to take, awaited with system-scope loads: their writer is the last operator of the
+// stage before, on another GPU.  Not inlined: it runs once per pass, in the first operator of a stage.
+__device__ __noinline__ void peer_wait_x3(const PassParams& p, const PassSmem& sm, const PassOpBody& op, const int o,
+                                          const uint32_t xtag, const int first, const int limit) {
+    const long long t_begin = clock64();
+    for (;;) {
+        bool ok = true;
+        for (int e = 0; e < 3; ++e) {
+            const int ch = first + e * P_NCONS;
+            if (ch < limit) {
+                unsigned long long a, b, c, d;
+                ld_relaxed_sys_v2(op.xt + 4 * (size_t)ch, a, b);
+                ld_relaxed_sys_v2(op.xt + 4 * (size_t)ch + 2, c, d);
+                ok = ok && (uint32_t)(a >> 32) == xtag && (uint32_t)(b >> 32) == xtag && (uint32_t)(c >> 32) == xtag &&
+                     (uint32_t)(d >> 32) == xtag;
+            }
+        }
+        if (ok || *sm.s_dead != 0) return;
+        if (clock64() - t_begin > P_PEER_WAIT_CLOCKS) {
+            atomicCAS(p.ws.err, 0, 0x90000 | o);   // the stage before never delivered
+            *sm.s_dead = 1;
+            return;
+        }
+    }
+}
+
 // Up to three 16-byte chunks (8 halves each) of an operator's input vector for this thread: chunk indices
 // first, first + 512, first + 1024 below `limit`.  Plain input: ordinary L2 loads.  Tagged input: every
 // chunk is four (two halves, tag) words; all loads are in flight together and are repeated until every word
@@ -302,9 +328,11 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
         }
         return;
     }
+    // Words the stage before stores from another GPU are first awaited with system-scope loads (bounded more
+    // generously); the loop below then finds them at its first pass.  Kept out of the loop: the common case pays
+    // one predicate.
+    if (op.src == P_SRC_PEER) peer_wait_x3(p, sm, op, o, xtag, first, limit);
     const long long t_begin = clock64();
-    const bool peer = op.src == P_SRC_PEER;   // written by the stage before, on another GPU
-    const long long t_limit = peer ? P_PEER_WAIT_CLOCKS : (1ll << 31);
     __syncwarp();
     unsigned long long w[3][4] = {{0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}, {0ull, 0ull, 0ull, 0ull}};
     for (;;) {
@@ -313,13 +341,8 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
         for (int e = 0; e < 3; ++e) {
             const int ch = first + e * P_NCONS;
             if (ch < limit) {
-                if (peer) {
-                    ld_relaxed_sys_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
-                    ld_relaxed_sys_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
-                } else {
-                    ld_relaxed_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
-                    ld_relaxed_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
-                }
+                ld_relaxed_v2(op.xt + 4 * (size_t)ch, w[e][0], w[e][1]);
+                ld_relaxed_v2(op.xt + 4 * (size_t)ch + 2, w[e][2], w[e][3]);
             }
         }
 #pragma unroll
@@ -330,8 +353,8 @@ __device__ __forceinline__ void fetch_x3(const PassParams& p, const PassSmem& sm
             }
         }
         if (ok || *sm.s_dead != 0) break;
-        if (clock64() - t_begin > t_limit) {
-            atomicCAS(p.ws.err, 0, (peer ? 0x90000 : 0x20000) | o);
+        if (clock64() - t_begin > (1ll << 31)) {
+            atomicCAS(p.ws.err, 0, 0x20000 | o);
             *sm.s_dead = 1;
             break;
         }
@@ -424,8 +447,6 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
     else trace_event(p, o, 1);
     const uint32_t xtag = op.src == P_SRC_PEER ? *sm.s_ptag : (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.src;
     const uint32_t tag = (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)o;
-    const bool peer_out = (op.flags & PASS_PEER_OUT) != 0;          // the tagged output goes to the next stage's GPU
-    const uint32_t ytag = peer_out ? *sm.s_ptag : tag;
     // what the epilogue of the first tile will need (written two or more operators ago)
     uint32_t pre_a = 0u, pre_b = 0u;   // RESIDUAL: y[i], y[i+1];  ROPE_KV: cos, sin of this thread's pair
     if (n_units > 0) {
@@ -436,7 +457,7 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
         if (active && i < op.M) {
             if (op.epilogue == QW3_EPI_RESIDUAL) {
                 if (op.rt != nullptr) {   // value and tag; the tag is checked when the value is used
-                    const unsigned long long w = op.rsrc == P_SRC_PEER ? ld_relaxed_sys_u64(op.rt + (i >> 1)) : ld_relaxed_u64(op.rt + (i >> 1));
+                    const unsigned long long w = ld_relaxed_u64(op.rt + (i >> 1));
                     pre_a = (uint32_t)w;
                     pre_b = (uint32_t)(w >> 32);
                 } else {
@@ -460,6 +481,9 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
             const __half2 v = __halves2half2(a, b);
             *reinterpret_cast<__half2*>(op.y + i) = v;
             if (op.yt != nullptr) {
+                // read here, not before the unit loop: nothing of the cross-GPU case stays live across the loop
+                const bool peer_out = (op.flags & PASS_PEER_OUT) != 0;   // the tagged output goes to the next stage's GPU
+                const uint32_t ytag = peer_out ? *sm.s_ptag : tag;
                 const unsigned long long w = ((unsigned long long)ytag << 32) | *reinterpret_cast<const uint32_t*>(&v);
                 if (peer_out) st_relaxed_sys_u64(op.yt + (i >> 1), w);
                 else st_relaxed_u64(op.yt + (i >> 1), w);
@@ -473,10 +497,11 @@ __device__ __forceinline__ void gemv_phase(const PassParams& p, const PassOpBody
                 if (op.rt != nullptr) {
                     // the word must carry the tag of the operator that wrote the residual stream last: a CTA that
                     // had no part in the operators in between may be here before that word is written
+                    // (residual stream of the stage before: its words were awaited with system-scope loads by this
+                    // stage's first operator; the retry below repeats that if this CTA is ahead of it)
                     const bool rpeer = op.rsrc == P_SRC_PEER;
                     const uint32_t rtag = rpeer ? *sm.s_ptag : (uint32_t)*sm.s_epoch * (uint32_t)P_TAG_OPS + (uint32_t)op.rsrc;
-                    unsigned long long w = tile_e == t0 ? (((unsigned long long)pre_b << 32) | pre_a)
-                                                        : (rpeer ? ld_relaxed_sys_u64(op.rt + (i >> 1)) : ld_relaxed_u64(op.rt + (i >> 1)));
+                    unsigned long long w = tile_e == t0 ? (((unsigned long long)pre_b << 32) | pre_a) : ld_relaxed_u64(op.rt + (i >> 1));
                     const long long t_begin = clock64();
                     while ((uint32_t)(w >> 32) != rtag && *sm.s_dead == 0) {
                         if (clock64() - t_begin > (rpeer ? P_PEER_WAIT_CLOCKS : (1ll << 31))) {
