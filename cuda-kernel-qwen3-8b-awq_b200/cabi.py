@@ -26,6 +26,7 @@ EXPORTS = [
     "qw3_set_batched_prefill",
     "qw3_set_chained_decode",
     "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect", "qw3_stage_layers",
+    "qw3_fused_plan", "qw3_fused_repack_host", "qw3_stage_hidden",
 ]
 
 
@@ -110,6 +111,9 @@ def lib():
         "qw3_stage_export": [vp, vp],
         "qw3_stage_connect": [vp, vp, vp],
         "qw3_stage_layers": [C.POINTER(Config), i32, C.POINTER(i32), C.POINTER(i32)],
+        "qw3_stage_hidden": [vp, i32, vp],
+        "qw3_fused_plan": [C.POINTER(Config), i32, i32, i32, vp, vp],
+        "qw3_fused_repack_host": [C.POINTER(Config), i32, i32, i32, i32, vp, i64, vp, i64],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "fused_pass.h"
 
 namespace qw3 {
 
@@ -121,6 +122,7 @@ struct Stage {  // GPUContext (Inference.cu:328-351) for one pipeline stage
     unsigned long long* d_trace = nullptr;   // per-operator entry times of the last pass (debug)
     unsigned long long* d_trace2 = nullptr;  // per-CTA event times of the last pass (debug)
     bool persistent = false;
+    FusedPass* fused = nullptr;   // fused token pass (persistent = 2): paired operators, repacked weight streams
     // batched prompt phase: activations of a block of PF_BLOCK prompt rows (allocated at the first use)
     void *pf_h = nullptr, *pf_n = nullptr, *pf_qkv = nullptr, *pf_ctx = nullptr, *pf_mlp = nullptr;
 };
@@ -306,7 +308,11 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
     Stage& s = e->st[si];
     const bool first = e->st[si].gidx == 0, last = e->st[si].gidx == c.n_stages - 1;
     QW3_CUDA(cudaSetDevice(s.device));
-    if (layers && s.persistent) {
+    if (layers && s.fused) {
+        // the whole pass of this stage is one cooperative launch of the fused kernel
+        QW3_TRY(fused_launch(s.fused, decode ? 1 : 0, s.stream));
+        *launches += 1;
+    } else if (layers && s.persistent) {
         // the whole pass of this stage is one cooperative launch
         const bool linked = decode && e->linked_now;
         const void* ops = linked ? s.ops_linked : (decode ? s.ops_decode : s.ops_prompt);
@@ -328,10 +334,10 @@ static int enqueue_stage_pass(qw3_engine* e, int si, bool decode, bool layers, b
         }
         for (int li = 0; li < (int)s.layers.size(); ++li) QW3_TRY(enqueue_layer(e, s, li, pdl, launches));
     }
-    if (decode && last && !(layers && s.persistent)) QW3_TRY(enqueue_sample(e, s, pdl, launches));
+    if (decode && last && !(layers && (s.persistent || s.fused))) QW3_TRY(enqueue_sample(e, s, pdl, launches));
     QW3_TRY(step_tail_launch(layers ? s.d_pos : nullptr, (decode && last) ? s.d_step : nullptr, s.d_token,
                              (decode && last) ? s.d_out_ids : nullptr, first ? s.d_skip : nullptr,
-                             (layers && s.persistent) ? s.d_epoch : nullptr, pdl, s.stream));
+                             (layers && s.persistent && !s.fused) ? s.d_epoch : nullptr, pdl, s.stream));
     *launches += 1;
     return QW3_OK;
 }
@@ -565,7 +571,7 @@ int qw3_config_default(Qw3Config* c) {
     std::memset(c, 0, sizeof(*c));
     c->hidden = 4096; c->inter = 12288; c->heads = 32; c->head_dim = 128; c->layers = 36; c->vocab = 151936;
     c->max_pos = 40960; c->eps = 1e-6f; c->rope_base = 10000.0f; c->sample_first = 0;
-    c->n_stages = 1; c->rank = 0; c->world = 1; c->use_graph = 1; c->use_pdl = 1; c->keep_logits = 0; c->persistent = 1;
+    c->n_stages = 1; c->rank = 0; c->world = 1; c->use_graph = 1; c->use_pdl = 1; c->keep_logits = 0; c->persistent = 2;
     return QW3_OK;
 }
 
@@ -577,6 +583,7 @@ int qw3_destroy(qw3_handle e) {
         if (s.g_prompt) cudaGraphExecDestroy(s.g_prompt);
         if (s.g_decode) cudaGraphExecDestroy(s.g_decode);
         if (s.g_linked) cudaGraphExecDestroy(s.g_linked);
+        if (s.fused) fused_destroy(s.fused);
         for (LayerDev& L : s.layers) {
             qw3_w4_destroy(L.wqkv.desc); qw3_w4_destroy(L.wo.desc); qw3_w4_destroy(L.w1.desc); qw3_w4_destroy(L.w2.desc);
         }
@@ -599,6 +606,42 @@ int qw3_destroy(qw3_handle e) {
     if (e->pinned) cudaFreeHost(e->pinned);
     delete e;
     return QW3_OK;
+}
+
+// The fused token pass of one stage, when its shapes are covered (else the stage keeps the operator-list kernel).
+static int create_fused(qw3_engine* e, Stage& s) {
+    const Qw3Config& c = e->cfg;
+    const Workspace* ws = ws_struct(s.ws);
+    const int n_layers = (int)s.layers.size();
+    FusedGeom g;
+    FGemvPlan plans[F_NOPS];
+    if (!fused_plan(c.hidden, c.inter, c.heads, c.vocab, n_layers, c.max_pos, 1, 0, ws->sm_count, &g, plans)) return QW3_OK;
+    auto mat = [](const W4Dev& w) {
+        FusedMatrix m;
+        m.packed = w.packed; m.scale = w.scale; m.zp = w.zp; m.n_alloc = w.n_alloc; m.out_dim = w.out_dim; m.in_dim = w.in_dim;
+        return m;
+    };
+    std::vector<FusedLayerIn> in((size_t)n_layers);
+    for (int l = 0; l < n_layers; ++l) {
+        const LayerDev& L = s.layers[l];
+        in[l].m[F_QKV] = mat(L.wqkv); in[l].m[F_WO] = mat(L.wo); in[l].m[F_W1] = mat(L.w1); in[l].m[F_W2] = mat(L.w2);
+        in[l].gamma = L.gamma; in[l].kc = L.kc; in[l].vc = L.vc;
+    }
+    const bool first = s.gidx == 0, last = s.gidx == c.n_stages - 1;
+    const FusedMatrix emb = mat(s.emb), unemb = mat(s.unemb);
+    FusedCreate a;
+    std::memset(&a, 0, sizeof(a));
+    a.H = c.hidden; a.I = c.inter; a.heads = c.heads; a.vocab = c.vocab; a.n_layers = n_layers; a.eps = c.eps; a.max_pos = c.max_pos;
+    a.n_ranks = 1; a.rank = 0; a.sm_count = ws->sm_count; a.device = s.device;
+    a.layers = in.data();
+    a.emb = first ? &emb : nullptr;
+    a.unemb = last ? &unemb : nullptr;
+    a.gamma_final = s.layers.back().gamma;
+    a.hidden = s.hidden; a.d_pos = s.d_pos; a.d_token = s.d_token; a.d_skip = first ? s.d_skip : nullptr; a.d_prompt = s.d_prompt;
+    a.d_gen = s.d_gen; a.cos_t = s.cos_t; a.sin_t = s.sin_t; a.logits16 = s.logits16; a.logits32 = s.logits32; a.err = ws->err;
+    a.stream = s.stream;
+    QW3_CUDA(cudaSetDevice(s.device));
+    return fused_create(a, &s.fused);
 }
 
 static int create_impl(const char* weight_dir, qw3_engine* e) {
@@ -665,6 +708,7 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
         QW3_TRY(dev_alloc(e, s.device, &ints, 256));
         QW3_CUDA(cudaMemsetAsync(ints, 0, 256, s.stream));
         s.d_pos = static_cast<int*>(ints); s.d_step = s.d_pos + 1; s.d_token = s.d_pos + 2; s.d_skip = s.d_pos + 3;
+        s.d_gen = s.d_pos + 8;   // generation counter of the sequence (part of the tags of the fused pass and of the chained stages)
         QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_prompt), (size_t)c.max_pos * 4));
         QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_out_ids), (size_t)c.max_pos * 4));
         QW3_CUDA(cudaMemsetAsync(s.hidden, 0, (size_t)H * 2, s.stream));
@@ -694,9 +738,13 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
         }
         QW3_CUDA(cudaStreamSynchronize(s.stream));
     }
+    if (c.persistent >= 2) {
+        for (int si = 0; si < N; ++si) QW3_TRY(create_fused(e, e->st[si]));
+    }
     if (c.persistent) {
         for (int si = 0; si < N; ++si) {
             Stage& s = e->st[si];
+            if (s.fused) continue;
             bool ok = c.heads <= WS_ATT_MAX_HEADS;
             for (LayerDev& L : s.layers)
                 ok = ok && pass_supports(w4_desc(L.wqkv.desc)) && pass_supports(w4_desc(L.wo.desc)) &&
@@ -723,7 +771,6 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_done), (size_t)(n_max + 64) * sizeof(int)));
                 QW3_CUDA(cudaMemset(s.d_done, 0, (size_t)(n_max + 64) * sizeof(int)));
                 s.d_epoch = s.d_done + n_max + 32;
-                s.d_gen = s.d_done + n_max + 40;
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_tok_out_slot), 16));
                 QW3_CUDA(cudaMemset(s.d_tok_out_slot, 0, 16));
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_xchg), pass_xchg_bytes()));
@@ -950,11 +997,14 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
     Stage &s0 = e->st[0], &sl = e->st[N - 1];
     e->launches = 0;
     e->seq_len = 0;
-    // The object is reusable: position and step restart for every call.
+    // The object is reusable: position and step restart for every call; the generation counter goes into the tags
+    // of the words the fused pass exchanges, so that words of an earlier sequence are never taken for this one's.
+    e->gen += 1;
     for (int si = 0; si < N; ++si) {
         Stage& s = e->st[si];
         QW3_CUDA(cudaSetDevice(s.device));
         QW3_CUDA(cudaMemsetAsync(s.d_pos, 0, 16, s.stream));
+        QW3_CUDA(cudaMemcpyAsync(s.d_gen, &e->gen, 4, cudaMemcpyHostToDevice, s.stream));
     }
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaMemcpyAsync(s0.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s0.stream));
@@ -1062,6 +1112,15 @@ int qw3_layer_decode(qw3_handle e, int32_t layer, int32_t pos, void* host_hidden
     QW3_CUDA(cudaMemcpyAsync(host_hidden, s->hidden, (size_t)e->cfg.hidden * 2, cudaMemcpyDeviceToHost, s->stream));
     QW3_CUDA(cudaStreamSynchronize(s->stream));
     return qw3_ws_check(s->ws, s->stream);
+}
+
+int qw3_stage_hidden(qw3_handle e, int32_t stage, void* host_hidden) {
+    QW3_REQUIRE(e && host_hidden && stage >= 0 && stage < (int)e->st.size(), "qw3_stage_hidden: bad argument");
+    Stage& s = e->st[stage];
+    QW3_CUDA(cudaSetDevice(s.device));
+    QW3_CUDA(cudaStreamSynchronize(s.stream));
+    QW3_CUDA(cudaMemcpy(host_hidden, s.hidden, (size_t)e->cfg.hidden * 2, cudaMemcpyDeviceToHost));
+    return QW3_OK;
 }
 
 int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries) {

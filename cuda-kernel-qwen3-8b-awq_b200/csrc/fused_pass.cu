@@ -1,0 +1,1310 @@
+// Fused token pass (sm_100a): one persistent cooperative kernel per token and GPU, with the operators of a layer
+// paired so that only two grid-wide reductions per layer remain.
+//
+// The reference runs a token through a layer as 12 launches and 68 copies (runOneLayer, Inference.cu:1029-1230).  At
+// batch 1 a layer's 84 MB of packed weights take 12.8 us of HBM time, so what sets the pace is how often the whole
+// grid has to agree on a vector.  Here every head gets a group of `gs` CTAs:
+//   group of head h:  RMSNorm -> its K-slice of Wqkv for q_h, k_h, v_h -> (group exchange) -> RoPE, KV append,
+//                     attention over its share of the positions -> (group exchange) -> Wo restricted to the 128
+//                     context inputs of head h, for its share of the outputs
+//   grid:             ordered sum of the per-head partial outputs + residual (every CTA owns `rs` hidden elements),
+//                     then the new hidden state is gathered by everybody
+//   every CTA:        RMSNorm -> its n1 outputs of W1 -> GeLU -> W2 restricted to those n1 inputs, all outputs
+//   grid:             ordered sum + residual, gather
+// Everything that crosses CTAs travels as (payload, tag) in one aligned 64-bit word which the reader polls: the tag
+// names generation, position and phase, so nothing is ever cleared and a CUDA graph replays unchanged.  Sums run in a
+// fixed order: results are bitwise repeatable.  With the matrices row-split over several GPUs (one process per GPU)
+// the same words are stored into every GPU's copy of the exchange buffers over NVLink and polled locally.
+//
+// Weights: every matrix is rewritten at load time (fused_plan.h) into per-(CTA, warp) byte streams in consumption
+// order.  Each warp owns FP_SLOTS ring slots of F_UNIT bytes and refills a slot with its own next unit (1-D bulk copy,
+// L2 evict-first) as soon as it has consumed it, across operator boundaries, since weights never depend on activations.
+// Inner loop: one 16-byte shared-memory load per lane yields four k-steps; `w & 0x000f000f`, `w & 0x00f000f0` and the
+// same on `w >> 8` ARE the fp16 A fragment of mma.sync.m16n8k16: a nibble in mantissa bits 0-3 of an fp16 with zero
+// exponent is the subnormal q * 2^-24 (bits 4-7: q * 2^-20), exactly.  So the tensor core accumulates
+// sum_j q_ij x_j in fp32 and the epilogue applies  y_i = scale_i * (2^24 * D_i - zp_i * sum_j x_j):  five integer
+// instructions and one MMA per eight weights.  This is algebraically the reference's (q - zp) * scale product
+// (Inference.cu:102-104) without its two fp16 roundings per weight; the bit-exact form stays in qw3_dequant_w4, in
+// the stand-alone GEMV and in the tensor-core GEMM, and the tests hold this kernel to the logits tolerance.
+// The unembedding's groups depend on the input index; there the scale is folded into the activations per block of
+// 128 outputs (x'_j = scale_g(b,j) * x_j) and the same loop runs.
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+#include "fused_pass.h"
+
+namespace qw3 {
+
+constexpr int FP_NT = F_NW * 32;          // threads per CTA
+constexpr int FP_SLOTS = 2;               // ring slots per warp
+constexpr int FP_MAX_H = 4096;            // largest hidden size (activation vectors kept in shared memory)
+constexpr int FP_OBUF = 4608;             // floats: GEMV outputs / partial-sum staging / 32 attention states of 132
+constexpr int FP_MAX_SEG = 4 * 64 + 24;   // weight segments of one pass (4 per layer + unembedding rounds)
+constexpr int FP_MAX_N1 = 512;            // largest number of W1 outputs per CTA
+constexpr int FP_MAX_RS = 256;            // largest number of hidden elements a CTA owns
+constexpr int FP_ATT_STRIDE = 132;
+constexpr int FP_QKV = 384;               // q, k, v of one head
+
+constexpr size_t FP_OFF_OBUF = (size_t)F_NW * FP_SLOTS * F_UNIT;
+constexpr size_t FP_OFF_HV = FP_OFF_OBUF + (size_t)FP_OBUF * 4;
+constexpr size_t FP_OFF_XS = FP_OFF_HV + (size_t)FP_MAX_H * 2;
+constexpr size_t FP_OFF_SEG = FP_OFF_XS + (size_t)FP_MAX_H * 2;
+constexpr size_t FP_OFF_MISC = FP_OFF_SEG + (size_t)FP_MAX_SEG * 16;
+constexpr size_t FP_MISC_BYTES = 8192;
+constexpr size_t FP_SMEM_BYTES = FP_OFF_MISC + FP_MISC_BYTES;
+
+struct FLayerDesc {
+    const uint8_t* w[4];        // repacked Wqkv, Wo, W1, W2 of this rank
+    const __half* scale[4];
+    const __half* zp[4];
+    const __half* gamma;
+    __half* kc;
+    __half* vc;
+};
+
+struct FusedParams {
+    const FLayerDesc* layers;
+    int n_layers;
+    FusedGeom g;
+    FGemvPlan plan[F_NOPS];
+    int n_alloc[F_NOPS];          // scale / zero-point entries of each matrix kind
+    int n_rounds;                 // unembedding rounds (0: this pass does not sample)
+    float eps;
+    // embedding (first stage) and unembedding (last stage)
+    const uint8_t* emb_packed; const __half* emb_scale; const __half* emb_zp; int emb_n_alloc;
+    const uint8_t* un_w; const __half* un_scale; const __half* un_zp;
+    const __half* gamma_final;
+    __half* logits16; float* logits32;
+    int first_stage;
+    // sequence state
+    __half* hidden;               // residual stream between passes (plain)
+    const int* d_pos; const int* d_token; const int* d_skip; const int* d_prompt; const int* d_gen;
+    int decode;
+    const __half* cos_t; const __half* sin_t;
+    long long max_pos;
+    int* d_token_out;
+    // exchange buffers of tagged words; index [r] is rank r's copy (a peer mapping when r != rank)
+    unsigned long long* xq;                    // [n_act][384]                 q/k/v partial sums (group-local)
+    unsigned long long* xa;                    // [n_act][132]                 attention states (group-local)
+    unsigned long long* xo[QW3_MAX_STAGES];    // [heads * gs][H / gs]         Wo partial sums per (head, output share)
+    unsigned long long* x2[QW3_MAX_STAGES];    // [n_ranks * n_act][H]         W2 partial sums per contributor
+    unsigned long long* hid[QW3_MAX_STAGES];   // [2][H / 2]                   gathered hidden state, two buffers
+    unsigned long long* xarg[QW3_MAX_STAGES];  // [n_ranks * grid][2]          arg-max candidates
+    int* err;
+};
+
+// ---- tagged words ------------------------------------------------------------------------------------------------
+template <bool SYS>
+__device__ __forceinline__ unsigned long long ldt(const unsigned long long* p) {
+    unsigned long long a;
+    if (SYS) asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return a;
+}
+template <bool SYS>
+__device__ __forceinline__ void ldt2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    if (SYS) asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+template <bool SYS>
+__device__ __forceinline__ void stt(unsigned long long* p, unsigned long long a) {
+    if (SYS) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+    else asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+}
+template <bool SYS>
+__device__ __forceinline__ void stt2(unsigned long long* p, unsigned long long a, unsigned long long b) {
+    if (SYS) asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+    else asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ unsigned long long tagged(uint32_t payload, uint32_t tag) {
+    return ((unsigned long long)tag << 32) | payload;
+}
+__device__ __forceinline__ unsigned long long tagged_f(float v, uint32_t tag) { return tagged(__float_as_uint(v), tag); }
+__device__ __forceinline__ bool has_tag(unsigned long long w, uint32_t tag) { return (uint32_t)(w >> 32) == tag; }
+__device__ __forceinline__ float payload_f(unsigned long long w) { return __uint_as_float((uint32_t)w); }
+
+constexpr long long FP_WAIT_LOCAL = 1ll << 31;   // about a second
+constexpr long long FP_WAIT_PEER = 1ll << 33;    // words another GPU writes
+
+// ---- shared-memory views and per-pass constants ---------------------------------------------------------------------
+struct FCtx {
+    uint8_t* ring;
+    float* obuf;
+    __half* hv;
+    __half* xs;
+    int4* seg;          // {base lo, base hi, warp_bytes, 0} per weight segment of this CTA
+    __half* qkv_s;      // [384] q, k, v of this CTA's head (after RoPE)
+    __half* ctx_s;      // [128]
+    __half* g_s;        // [n1] GeLU outputs
+    __half* hmine;      // [rs] this CTA's part of the residual stream
+    __half* rope_cs;    // [128] cos | sin of this position
+    float* wsum;        // [64]
+    double* dsum;       // [16]
+    uint32_t* un_sz;    // [<= 64] scale | zp pairs of the unembedding groups in use
+    float* argv;        // [16]
+    int* argi;          // [16]
+    int* s_dead;
+    uint32_t bars;      // shared address of the ring barriers [F_NW][FP_SLOTS]
+    uint32_t zero_addr; // shared address of 32 zero bytes
+    uint32_t tagbase;
+    int pos;
+    int n_seg;
+};
+
+__device__ __forceinline__ void fail(const FusedParams& p, const FCtx& cx, int code) {
+    atomicCAS(p.err, 0, code);
+    *cx.s_dead = 1;
+}
+
+// Up to NB words polled together (all loads in flight at once) until every one carries `tag`; bounded.
+template <bool SYS, int NB, typename AddrFn>
+__device__ __forceinline__ void poll_batch(const FusedParams& p, const FCtx& cx, const int n_valid, AddrFn addr, const uint32_t tag,
+                                           const int code, unsigned long long (&w)[NB]) {
+    const long long t_begin = clock64();
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int e = 0; e < NB; ++e)
+            if (e < n_valid) {
+                w[e] = ldt<SYS>(addr(e));
+                ok = ok && has_tag(w[e], tag);
+            }
+        if (ok || *cx.s_dead != 0) break;
+        if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
+            fail(p, cx, code);
+            break;
+        }
+    }
+}
+
+// ---- weight ring -----------------------------------------------------------------------------------------------------
+struct WarpRing {
+    int uc;        // units consumed by this warp so far
+    int pc;        // units requested so far
+    int pseg, pu;  // next unit to request: segment and unit within it
+    uint64_t policy;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
+}
+
+// Requests this warp's next unit into the slot it has just freed (slot = pc mod FP_SLOTS).  After a wait has given up
+// nothing more is requested, so that no copy is in flight when the CTA exits.
+__device__ __forceinline__ void ring_request(WarpRing& r, const FCtx& cx) {
+    const int warp = threadIdx.x >> 5;
+    if (*cx.s_dead != 0) return;
+    while (r.pseg < cx.n_seg) {
+        const int4 sg = cx.seg[r.pseg];
+        if (r.pu * F_UNIT < sg.z) {
+            if ((threadIdx.x & 31) == 0) {
+                const uint8_t* base = reinterpret_cast<const uint8_t*>(((unsigned long long)(uint32_t)sg.y << 32) | (uint32_t)sg.x);
+                const int bytes = min(F_UNIT, sg.z - r.pu * F_UNIT);
+                const int slot = r.pc % FP_SLOTS;
+                const uint32_t bar = cx.bars + 8 * (warp * FP_SLOTS + slot);
+                // the slot was read with ordinary loads: order them before the bulk write
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(bar, bytes);
+                bulk_load(smem_u32(cx.ring) + (warp * FP_SLOTS + slot) * F_UNIT, base + (size_t)warp * sg.z + (size_t)r.pu * F_UNIT,
+                          bytes, bar, r.policy);
+            }
+            ++r.pu;
+            ++r.pc;
+            return;
+        }
+        ++r.pseg;
+        r.pu = 0;
+    }
+}
+
+// Shared address of the unit this warp consumes next, once it has landed (bounded wait).
+__device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FusedParams& p, const FCtx& cx) {
+    const int warp = threadIdx.x >> 5, slot = r.uc % FP_SLOTS;
+    const uint32_t bar = cx.bars + 8 * (warp * FP_SLOTS + slot);
+    if (r.uc < r.pc && !mbar_wait(bar, (r.uc / FP_SLOTS) & 1)) {
+        if ((threadIdx.x & 31) == 0) fail(p, cx, 0x10000 | (r.uc & 0xffff));   // a weight unit never arrived
+    }
+    return smem_u32(cx.ring) + (warp * FP_SLOTS + slot) * F_UNIT;
+}
+__device__ __forceinline__ void ring_release(WarpRing& r, const FCtx& cx) {
+    __syncwarp();
+    ring_request(r, cx);
+    ++r.uc;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+
+// One k-step: the word's eight nibbles as the A fragment (subnormal fp16: bits 0-3 -> q * 2^-24, bits 4-7 -> q * 2^-20).
+__device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0, uint32_t b1) {
+    const uint32_t u = w >> 8;
+    mma_16816(d, w & 0x000f000fu, w & 0x00f000f0u, u & 0x000f000fu, u & 0x00f000f0u, b0, b1);
+}
+constexpr float FP_MULT_LO = 16777216.0f;   // 2^24: rows g of a tile
+constexpr float FP_MULT_HI = 1048576.0f;    // 2^20: rows g + 8
+
+// This warp's stream of one operator: nb blocks of TB tiles, each over nq groups of four k-steps (+ a half group when
+// rem == 2).  xs_addr: shared address of the fp16 activations of the warp's k-share.  dst[(block * TB + i) * 16 + row]
+// receives sum_j q[row][j] * x[j] of tile i of the block.
+template <int TB>
+__device__ __noinline__ void gemv_core(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int nb, const int nq,
+                                       const int rem, const int warp_bytes, const uint32_t xs_addr, float* dst) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    int left = warp_bytes, ubytes = 0, uoff = 0;
+    uint32_t ubase = 0;
+    auto item = [&](const int sz) -> uint32_t {
+        if (uoff == ubytes) {
+            if (ubytes != 0) ring_release(ring, cx);
+            ubytes = min(F_UNIT, left);
+            left -= ubytes;
+            ubase = ring_wait(ring, p, cx);
+            uoff = 0;
+        }
+        const uint32_t a = ubase + uoff;
+        uoff += sz;
+        return a;
+    };
+    for (int b = 0; b < nb; ++b) {
+        float acc[TB][4];
+#pragma unroll
+        for (int i = 0; i < TB; ++i)
+#pragma unroll
+            for (int d = 0; d < 4; ++d) acc[i][d] = 0.0f;
+        for (int q = 0; q < nq; ++q) {
+            // B fragment of the group: lanes 0-3 (column 0) hold the activations, the other columns are zero
+            const uint32_t ba = g == 0 ? xs_addr + q * 128 + t * 32 : cx.zero_addr;
+            const uint4 b03 = lds128(ba), b47 = lds128(ba + 16);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) {
+                const uint4 w = lds128(item(512) + lane * 16);
+                mma_word(acc[i], w.x, b03.x, b03.y);
+                mma_word(acc[i], w.y, b03.z, b03.w);
+                mma_word(acc[i], w.z, b47.x, b47.y);
+                mma_word(acc[i], w.w, b47.z, b47.w);
+            }
+        }
+        if (rem == 2) {
+            const uint32_t ba = g == 0 ? xs_addr + nq * 128 + t * 16 : cx.zero_addr;
+            const uint4 b03 = lds128(ba);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) {
+                const uint2 w = lds64(item(256) + lane * 8);
+                mma_word(acc[i], w.x, b03.x, b03.y);
+                mma_word(acc[i], w.y, b03.z, b03.w);
+            }
+        }
+        if (t == 0) {
+#pragma unroll
+            for (int i = 0; i < TB; ++i) {
+                dst[(b * TB + i) * 16 + g] = acc[i][0] * FP_MULT_LO;
+                dst[(b * TB + i) * 16 + g + 8] = acc[i][2] * FP_MULT_HI;
+            }
+        }
+    }
+    if (ubytes != 0) ring_release(ring, cx);
+}
+
+// Runs this warp's share of an operator: warp (a, bk) of the plan; sums land in obuf[bk][tile * 16 + row].
+__device__ __forceinline__ void run_gemv(const FusedParams& p, const FCtx& cx, WarpRing& ring, const FGemvPlan& pl,
+                                         const __half* x_cta) {
+    const int warp = threadIdx.x >> 5;
+    const int a = warp / pl.wk, bk = warp % pl.wk;
+    const int ksw = 4 * pl.nq + pl.rem;
+    const uint32_t xs_addr = smem_u32(x_cta) + bk * ksw * 32;
+    float* dst = cx.obuf + bk * (pl.n_mt * 16) + a * (pl.nb * pl.tb) * 16;
+    switch (pl.tb) {
+        case 1: gemv_core<1>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
+        case 2: gemv_core<2>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
+        case 3: gemv_core<3>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
+        default: gemv_core<4>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
+    }
+}
+__device__ __forceinline__ float sum_k_shares(const FCtx& cx, const FGemvPlan& pl, int i) {
+    float s = 0.0f;
+    for (int bk = 0; bk < pl.wk; ++bk) s += cx.obuf[bk * (pl.n_mt * 16) + i];
+    return s;
+}
+
+// Scale and zero point of output `o` of a matrix whose groups do not depend on the input index:
+// group = ((o / 128) mod (in_dim / 128)) mod entries  (dequantAwqKernel's c / 128 with the wrapped index, Inference.cu:90).
+__device__ __forceinline__ void group_consts(const __half* scale, const __half* zp, long long o, int kb, int n_alloc, float& s,
+                                             float& z) {
+    const int g = (int)((o >> 7) % kb) % n_alloc;
+    s = __half2float(scale[g]);
+    z = __half2float(zp[g]);
+}
+
+__device__ __forceinline__ float block_sum_f(const FCtx& cx, float v) {   // all threads call; fixed order
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+    __syncthreads();
+    if (lane == 0) cx.wsum[warp] = v;
+    __syncthreads();
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < F_NW; ++w) s += cx.wsum[w];
+    return s;
+}
+
+// ---- gather of the hidden state + RMSNorm (rmsNormKernel, Inference.cu:111-145) --------------------------------------
+// Polls the H/2 tagged words of `hid`, normalises with `gamma` into `out` (shared memory).  x_full: sum of the
+// normalised vector; x_slice: sum over [slice * hs, (slice + 1) * hs) (hs a multiple of 128).
+template <bool SYS>
+__device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx, const unsigned long long* hid, const uint32_t tag,
+                                            const __half* gamma, __half* out, const int slice, const int hs, float& x_full,
+                                            float& x_slice) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = p.g.H, nch = H >> 2;   // chunks of two words = four halves
+    unsigned long long w[2][2] = {{0ull, 0ull}, {0ull, 0ull}};
+    uint2 gm[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int ch = tid + e * FP_NT;
+        if (ch < nch) gm[e] = __ldg(reinterpret_cast<const uint2*>(gamma) + ch);
+    }
+    const long long t_begin = clock64();
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int ch = tid + e * FP_NT;
+            if (ch < nch) {
+                ldt2<SYS>(hid + 2 * ch, w[e][0], w[e][1]);
+                ok = ok && has_tag(w[e][0], tag) && has_tag(w[e][1], tag);
+            }
+        }
+        if (ok || *cx.s_dead != 0) break;
+        if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
+            fail(p, cx, 0x20000 | (tag & 0x1ff));   // the hidden state of this phase never arrived
+            break;
+        }
+    }
+    double s = 0.0;
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {   // chunks past the end are zero
+            const uint32_t pw = (uint32_t)w[e][k];
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw));
+            s += (double)(f.x * f.x);
+            s += (double)(f.y * f.y);
+        }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) s += shfl_xor_double(s, m);
+    __syncthreads();   // dsum / wsum of the phase before are no longer read
+    if (lane == 0) cx.dsum[warp] = s;
+    __syncthreads();
+    double tot = cx.dsum[lane & (F_NW - 1)];
+#pragma unroll
+    for (int m = 8; m > 0; m >>= 1) tot += shfl_xor_double(tot, m);
+    const float mean_sq = __fdiv_rn((float)tot, (float)H);                          // Inference.cu:136
+    const float denom = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, p.eps)));     // Inference.cu:137
+    const __half nscale = __float2half_rn(denom);                                   // Inference.cu:138
+    float ps[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int ch = tid + e * FP_NT;
+        if (ch < nch) {
+            const uint32_t p0 = (uint32_t)w[e][0], p1 = (uint32_t)w[e][1];
+            const __half2 xa = *reinterpret_cast<const __half2*>(&p0), xb = *reinterpret_cast<const __half2*>(&p1);
+            const __half* gh = reinterpret_cast<const __half*>(&gm[e]);
+            __half o[4];
+            o[0] = h_mul(h_mul(__low2half(xa), nscale), gh[0]);             // Inference.cu:142-143
+            o[1] = h_mul(h_mul(__high2half(xa), nscale), gh[1]);
+            o[2] = h_mul(h_mul(__low2half(xb), nscale), gh[2]);
+            o[3] = h_mul(h_mul(__high2half(xb), nscale), gh[3]);
+            uint2 ov;
+            ov.x = pack_h2(o[0], o[1]);
+            ov.y = pack_h2(o[2], o[3]);
+            *reinterpret_cast<uint2*>(out + 4 * ch) = ov;
+            ps[e] = (__half2float(o[0]) + __half2float(o[1])) + (__half2float(o[2]) + __half2float(o[3]));
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ps[e] += __shfl_xor_sync(0xffffffffu, ps[e], m);
+        if (lane == 0) cx.wsum[e * F_NW + warp] = ps[e];
+    }
+    __syncthreads();   // `out` and the warp sums are visible
+    x_full = 0.0f;
+    x_slice = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 2 * F_NW; ++k) {
+        const float v = cx.wsum[k];
+        x_full += v;
+        const int first = 4 * ((k & (F_NW - 1)) * 32 + (k / F_NW) * FP_NT);   // first element of that warp's row of chunks
+        if (slice >= 0 && first / hs == slice) x_slice += v;
+    }
+}
+
+// This CTA's rs elements of the residual stream (hmine) as tagged words into buffer `buf` of every rank's copy.
+template <bool SYS>
+__device__ __forceinline__ void publish_hidden(const FusedParams& p, const FCtx& cx, const int buf, const uint32_t tag, const int cglob) {
+    const int tid = threadIdx.x;
+    const FusedGeom& G = p.g;
+    if (tid < (G.rs >> 1)) {
+        const uint32_t pair = pack_h2(cx.hmine[2 * tid], cx.hmine[2 * tid + 1]);
+        const size_t at = (size_t)buf * (G.H >> 1) + (size_t)((G.rs * cglob) >> 1) + tid;
+        for (int r = 0; r < G.n_ranks; ++r) stt<SYS>(p.hid[r] + at, tagged(pair, tag));
+    }
+}
+
+// ---- one decoder layer for the CTAs that run the layers (runOneLayer, Inference.cu:1029-1230) -----------------------------
+template <bool SYS>
+__device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int li) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, c = blockIdx.x;
+    const FusedGeom& G = p.g;
+    const FLayerDesc& L = p.layers[li];
+    const int H = G.H, gs = G.gs, rs = G.rs, n1 = G.n1;
+    const int h_l = c / gs, r = c % gs, hglob = G.rank * G.heads_local + h_l, cglob = G.rank * G.n_act + c;
+    const int hs = H / gs;
+    const int pos = cx.pos;
+    const uint32_t t0 = cx.tagbase + 2 + 6 * li;                 // + 0 xq, 1 xa, 2 xo, 3 hid[0], 4 x2, 5 hid[1]
+    const uint32_t tag_in = li == 0 ? cx.tagbase + 1 : t0 - 1;   // hid[1] of the embedding / of the layer before
+    const int o_first = rs * cglob;                              // this CTA's part of the residual stream
+
+    // ---- RMSNorm + this CTA's K-slice of Wqkv for its head (Inference.cu:1036-1065) -----------------------------------
+    float x_full, x_slice;
+    gather_norm<SYS>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, L.gamma, cx.xs, r, hs, x_full, x_slice);
+    float sc = 0.0f, zp = 0.0f;
+    if (tid < FP_QKV) {
+        const int tile = tid >> 4, row = tid & 15;
+        const long long o = (long long)(tile >> 3) * H + hglob * 128 + (tile & 7) * 16 + row;
+        group_consts(L.scale[F_QKV], L.zp[F_QKV], o, H >> 7, p.n_alloc[F_QKV], sc, zp);
+    }
+    run_gemv(p, cx, ring, p.plan[F_QKV], cx.xs + r * hs);
+    __syncthreads();
+    if (tid < FP_QKV) {
+        const float S = sum_k_shares(cx, p.plan[F_QKV], tid);
+        stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(sc * (S - zp * x_slice), t0));
+    }
+    // ---- attention: cache rows of earlier positions are requested before q is known -----------------------------------
+    const int len = pos + 1, chunk = (len + gs - 1) / gs;
+    const int p0 = r * chunk, p1 = min(len, p0 + chunk);
+    const int grp = tid >> 4, sl = tid & 15;
+    constexpr int NG = FP_NT / 16, UN = 2;
+    const __half* kh = L.kc + (size_t)hglob * p.max_pos * 128 + sl * 8;
+    const __half* vh = L.vc + (size_t)hglob * p.max_pos * 128 + sl * 8;
+    uint4 nk[UN], nv[UN];
+    auto request_rows = [&](const int kb) {
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int kp = kb + grp + u * NG;
+            nk[u] = make_uint4(0u, 0u, 0u, 0u);
+            nv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (kp < p1 && kp != pos) {
+                nk[u] = __ldcg(reinterpret_cast<const uint4*>(kh + (size_t)kp * 128));
+                nv[u] = __ldcg(reinterpret_cast<const uint4*>(vh + (size_t)kp * 128));
+            }
+        }
+    };
+    request_rows(p0);
+    // ---- group exchange: q, k, v of the head = ordered sum of the gs K-slices; RoPE; KV append (Inference.cu:1070-1103)
+    if (tid < FP_QKV) {
+        float v = 0.0f;
+        const unsigned long long* src = p.xq + (size_t)(h_l * gs) * FP_QKV + tid;
+        for (int r0 = 0; r0 < gs; r0 += 4) {
+            unsigned long long w[4];
+            poll_batch<false, 4>(p, cx, gs - r0, [&](int e) { return src + (size_t)(r0 + e) * FP_QKV; }, t0, 0x30000 | li, w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (r0 + e < gs) v += payload_f(w[e]);
+        }
+        const int tile = tid >> 4, row = tid & 15, sec = tile >> 3, d = (tile & 7) * 16 + row;
+        __half me = __float2half_rn(v);                                                       // Inference.cu:1062 (fp16 store)
+        const __half other = __ushort_as_half((unsigned short)__shfl_xor_sync(0xffffffffu, (unsigned)__half_as_ushort(me), 1));
+        if (sec < 2) {   // applyRotaryKernel, Inference.cu:150-177: pairs (2i, 2i+1)
+            const __half cs = cx.rope_cs[d >> 1], sn = cx.rope_cs[64 + (d >> 1)];
+            __half o0, o1;
+            rope_pair((d & 1) ? other : me, (d & 1) ? me : other, cs, sn, o0, o1);
+            me = (d & 1) ? o1 : o0;
+        }
+        cx.qkv_s[tid] = me;
+        if (r == 0 && sec > 0) (sec == 1 ? L.kc : L.vc)[((size_t)hglob * p.max_pos + pos) * 128 + d] = me;   // Inference.cu:1094-1103
+    }
+    __syncthreads();
+    // ---- attention over positions [p0, p1) (attentionKernel, Inference.cu:182-266, intended math) -----------------------
+    {
+        float qf[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qf[e] = __half2float(cx.qkv_s[sl * 8 + e]);
+        const float scale = 1.0f / sqrtf(128.0f);
+        float m = -INFINITY, l = 0.0f, ov[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ov[e] = 0.0f;
+        for (int kb = p0; kb < p1; kb += NG * UN) {   // trip count uniform across the CTA
+            uint4 kv[UN], vv[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int kp = kb + grp + u * NG;
+                kv[u] = nk[u];
+                vv[u] = nv[u];
+                if (kp < p1 && kp == pos) {   // this token's own row is not in the cache yet for the other CTAs of the group
+                    kv[u] = *reinterpret_cast<const uint4*>(cx.qkv_s + 128 + sl * 8);
+                    vv[u] = *reinterpret_cast<const uint4*>(cx.qkv_s + 256 + sl * 8);
+                }
+            }
+            if (kb + NG * UN < p1) request_rows(kb + NG * UN);
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int kp = kb + grp + u * NG;
+                const __half2* kh2 = reinterpret_cast<const __half2*>(&kv[u]);
+                float dot = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(kh2[e]);
+                    dot = fmaf(qf[2 * e], f.x, dot);
+                    dot = fmaf(qf[2 * e + 1], f.y, dot);
+                }
+#pragma unroll
+                for (int msk = 8; msk > 0; msk >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, msk);
+                if (kp < p1) {
+                    const float s = dot * scale;
+                    const float mn = fmaxf(m, s);
+                    const float corr = (m == -INFINITY) ? 0.0f : expf(m - mn);
+                    const float pr = expf(s - mn);
+                    l = l * corr + pr;
+                    const __half2* vh2 = reinterpret_cast<const __half2*>(&vv[u]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __half22float2(vh2[e]);
+                        ov[2 * e] = fmaf(pr, f.x, ov[2 * e] * corr);
+                        ov[2 * e + 1] = fmaf(pr, f.y, ov[2 * e + 1] * corr);
+                    }
+                    m = mn;
+                }
+            }
+        }
+        // merge of the 32 half-warp states of the CTA in a fixed order
+        float* st = cx.obuf;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) st[grp * FP_ATT_STRIDE + sl * 8 + e] = ov[e];
+        if (sl == 0) {
+            st[grp * FP_ATT_STRIDE + 128] = m;
+            st[grp * FP_ATT_STRIDE + 129] = l;
+        }
+        __syncthreads();
+        float* wts = st + NG * FP_ATT_STRIDE;   // [NG] weights, then the maximum
+        static_assert(NG == 32 && (NG + 1) * FP_ATT_STRIDE <= FP_OBUF, "one lane per half-warp state");
+        if (tid < 32) {
+            const float mg = st[tid * FP_ATT_STRIDE + 128];
+            float mx = mg;
+#pragma unroll
+            for (int msk = 16; msk > 0; msk >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, msk));
+            wts[tid] = (mg == -INFINITY) ? 0.0f : expf(mg - mx);
+            if (tid == 0) wts[NG] = mx;
+        }
+        __syncthreads();
+        float M = -INFINITY, Lsum = 0.0f, O = 0.0f;
+        if (tid < 128) {
+            M = wts[NG];
+#pragma unroll 8
+            for (int gq = 0; gq < NG; ++gq) {
+                const float w = wts[gq];
+                Lsum += st[gq * FP_ATT_STRIDE + 129] * w;
+                O += st[gq * FP_ATT_STRIDE + tid] * w;
+            }
+        }
+        if (gs > 1) {
+            // group exchange: every CTA of the head stores its state and merges all gs of them in CTA order
+            if (tid < 128) stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + tid, tagged_f(O, t0 + 1));
+            if (tid == 0) {
+                stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + 128, tagged_f(M, t0 + 1));
+                stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + 129, tagged_f(Lsum, t0 + 1));
+            }
+            __syncthreads();   // everybody has read st
+            if (tid < 130) {
+                const unsigned long long* src = p.xa + (size_t)(h_l * gs) * FP_ATT_STRIDE + tid;
+                for (int r0 = 0; r0 < gs; r0 += 4) {
+                    unsigned long long w[4];
+                    poll_batch<false, 4>(p, cx, gs - r0, [&](int e) { return src + (size_t)(r0 + e) * FP_ATT_STRIDE; }, t0 + 1,
+                                         0x40000 | li, w);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (r0 + e < gs) st[(r0 + e) * FP_ATT_STRIDE + tid] = payload_f(w[e]);
+                }
+            }
+            __syncthreads();
+            if (tid < 128) {
+                M = -INFINITY;
+                for (int q = 0; q < gs; ++q) M = fmaxf(M, st[q * FP_ATT_STRIDE + 128]);
+                Lsum = 0.0f;
+                O = 0.0f;
+                for (int q = 0; q < gs; ++q) {
+                    const float mq = st[q * FP_ATT_STRIDE + 128];
+                    const float w = (mq == -INFINITY) ? 0.0f : expf(mq - M);
+                    Lsum += st[q * FP_ATT_STRIDE + 129] * w;
+                    O += st[q * FP_ATT_STRIDE + tid] * w;
+                }
+            }
+        }
+        float cf = 0.0f;
+        if (tid < 128) {
+            const __half ch = __float2half_rn(O / Lsum);   // one rounding to fp16, Inference.cu:257-265
+            cx.ctx_s[tid] = ch;
+            cf = __half2float(ch);
+        }
+        const float x_o = block_sum_f(cx, cf);   // its barriers also publish ctx_s and free st
+
+        // ---- Wo restricted to the head's 128 inputs, this CTA's share of the outputs (Inference.cu:1122-1141) ----------
+        const FGemvPlan& plo = p.plan[F_WO];
+        run_gemv(p, cx, ring, plo, cx.ctx_s);
+        __syncthreads();
+        const int n_out = plo.n_mt * 16;   // = hs
+        for (int i0 = 2 * tid; i0 < n_out; i0 += 2 * FP_NT) {
+            const long long o = (long long)r * hs + i0;
+            float s2, z2;
+            group_consts(L.scale[F_WO], L.zp[F_WO], o, H >> 7, p.n_alloc[F_WO], s2, z2);
+            const float y0 = s2 * (sum_k_shares(cx, plo, i0) - z2 * x_o), y1 = s2 * (sum_k_shares(cx, plo, i0 + 1) - z2 * x_o);
+            const int ro = (int)(o / (H / G.n_ranks));   // rank that owns these two elements of the residual stream
+            stt2<SYS>(p.xo[ro] + (size_t)(hglob * gs + r) * n_out + i0, tagged_f(y0, t0 + 2), tagged_f(y1, t0 + 2));
+        }
+        __syncthreads();   // obuf is free again
+        // ---- ordered sum over the heads for this CTA's rs outputs + residual (Inference.cu:1145-1156) ----------------------
+        {
+            const int r_src = o_first / n_out, off = o_first % n_out;
+            const int nw = G.heads * rs;
+            unsigned long long w[8];
+            const unsigned long long* src = p.xo[G.rank] + (size_t)r_src * n_out + off;
+            poll_batch<SYS, 8>(p, cx, (nw - tid + FP_NT - 1) / FP_NT,
+                               [&](int e) { const int k = tid + e * FP_NT; return src + (size_t)(k / rs) * gs * n_out + (k % rs); }, t0 + 2,
+                               0x50000 | li, w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
+        }
+        __syncthreads();
+        if (tid < rs) {
+            float v = 0.0f;
+            for (int hg = 0; hg < G.heads; ++hg) v += cx.obuf[hg * rs + tid];
+            cx.hmine[tid] = h_add(cx.hmine[tid], __float2half_rn(v));   // fp16 store of the GEMV, then __hadd
+        }
+        __syncthreads();
+        publish_hidden<SYS>(p, cx, 0, t0 + 3, cglob);
+    }
+
+    // ---- RMSNorm (same gamma) + this CTA's n1 outputs of W1 + GeLU (Inference.cu:1158-1197) ----------------------------------
+    gather_norm<SYS>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, cx.xs, -1, H, x_full, x_slice);
+    if (tid < n1) group_consts(L.scale[F_W1], L.zp[F_W1], (long long)cglob * n1 + tid, H >> 7, p.n_alloc[F_W1], sc, zp);
+    run_gemv(p, cx, ring, p.plan[F_W1], cx.xs);
+    __syncthreads();
+    float gv = 0.0f;
+    if (tid < n1) {
+        const float S = sum_k_shares(cx, p.plan[F_W1], tid);
+        const __half ge = gelu_h(__float2half_rn(sc * (S - zp * x_full)));
+        cx.g_s[tid] = ge;
+        gv = __half2float(ge);
+    }
+    const float x_g = block_sum_f(cx, gv);   // its barriers also publish g_s and free obuf
+    // ---- W2 restricted to those n1 inputs, all outputs (Inference.cu:1198-1214) ------------------------------------------------
+    run_gemv(p, cx, ring, p.plan[F_W2], cx.g_s);
+    __syncthreads();
+    for (int i0 = 2 * tid; i0 < H; i0 += 2 * FP_NT) {
+        float s2, z2;
+        group_consts(L.scale[F_W2], L.zp[F_W2], i0, G.I >> 7, p.n_alloc[F_W2], s2, z2);
+        const float y0 = s2 * (cx.obuf[i0] - z2 * x_g), y1 = s2 * (cx.obuf[i0 + 1] - z2 * x_g);
+        const int ro = i0 / (H / G.n_ranks);
+        stt2<SYS>(p.x2[ro] + (size_t)cglob * H + i0, tagged_f(y0, t0 + 4), tagged_f(y1, t0 + 4));
+    }
+    __syncthreads();
+    // ---- ordered sum over all contributors for this CTA's rs outputs + residual (Inference.cu:1217-1228) ----------------------
+    const int ncontrib = G.n_ranks * G.n_act, nw = ncontrib * rs;
+    {
+        unsigned long long w[8];
+        const unsigned long long* src = p.x2[G.rank] + o_first;
+        poll_batch<SYS, 8>(p, cx, (nw - tid + FP_NT - 1) / FP_NT,
+                           [&](int e) { const int k = tid + e * FP_NT; return src + (size_t)(k / rs) * H + (k % rs); }, t0 + 4, 0x60000 | li, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
+    }
+    __syncthreads();
+    const int parts = (ncontrib % 4 == 0 && nw + 4 * rs <= FP_OBUF && 4 * rs <= FP_NT) ? 4 : 1;
+    if (tid < parts * rs) {
+        const int part = tid / rs, idx = tid % rs, per = ncontrib / parts;
+        float v = 0.0f;
+        for (int cc = part * per; cc < (part + 1) * per; ++cc) v += cx.obuf[cc * rs + idx];
+        cx.obuf[nw + part * rs + idx] = v;
+    }
+    __syncthreads();
+    if (tid < rs) {
+        float v = cx.obuf[nw + tid];
+        for (int q = 1; q < parts; ++q) v += cx.obuf[nw + q * rs + tid];
+        cx.hmine[tid] = h_add(cx.hmine[tid], __float2half_rn(v));
+    }
+    __syncthreads();
+    publish_hidden<SYS>(p, cx, 1, t0 + 5, cglob);
+    (void)lane; (void)warp;
+}
+
+// ---- final norm + unembedding + arg-max (sampleNextToken, Inference.cu:1235-1292) ---------------------------------------------
+template <bool SYS>
+__device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx, WarpRing& ring) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, c = blockIdx.x;
+    const FusedGeom& G = p.g;
+    const int H = G.H, Kb = H >> 7, Mb = G.vocab >> 7;
+    const uint32_t tag_in = p.n_layers > 0 ? cx.tagbase + 2 + 6 * (p.n_layers - 1) + 5 : cx.tagbase + 1;
+    if (c >= G.n_act) {
+        // CTAs without a part in the layers wait here for the whole pass: one thread polls, gently
+        if (tid == 0) {
+            const long long t_begin = clock64();
+            while (!has_tag(ldt<SYS>(p.hid[G.rank] + (H >> 1)), tag_in) && *cx.s_dead == 0) {
+                if (clock64() - t_begin > FP_WAIT_PEER) {
+                    fail(p, cx, 0x70000);
+                    break;
+                }
+                __nanosleep(1000);
+            }
+        }
+        __syncthreads();
+    }
+    float xf, xsl;
+    gather_norm<SYS>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, p.gamma_final, cx.hv, -1, H, xf, xsl);
+    const int n_alloc = p.n_alloc[F_UNEMB];
+    const int n_used = min(Kb, n_alloc);
+    if (tid < n_used) cx.un_sz[tid] = pack_h2(p.un_scale[tid], p.un_zp[tid]);
+    __syncthreads();
+    const FGemvPlan& pl = p.plan[F_UNEMB];
+    const int mstep = Mb % Kb;
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int round = 0; round < p.n_rounds; ++round) {
+        const long long blk = fused_unemb_block(G, c, round);
+        if (blk < 0) break;
+        // x'_j = scale[g(blk, j)] * x_j and Z = sum_j zp[g(blk, j)] * x'_j,  g(b, j) = ((b + j * Mb) mod Kb) mod entries
+        const int bmod = (int)(blk % Kb);
+        float zacc = 0.0f;
+        for (int ch = tid; ch < (H >> 3); ch += FP_NT) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(cx.hv + 8 * ch);
+            const __half* xh = reinterpret_cast<const __half*>(&xv);
+            uint4 ov;
+            __half* oh = reinterpret_cast<__half*>(&ov);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int j = 8 * ch + e;
+                const int gq = ((bmod + (j % Kb) * mstep) % Kb) % n_alloc;
+                const uint32_t sz = cx.un_sz[gq];
+                const __half xp = h_mul(__ushort_as_half((unsigned short)(sz & 0xffffu)), xh[e]);
+                oh[e] = xp;
+                zacc = fmaf(__half2float(__ushort_as_half((unsigned short)(sz >> 16))), __half2float(xp), zacc);
+            }
+            *reinterpret_cast<uint4*>(cx.xs + 8 * ch) = ov;
+        }
+        const float Z = block_sum_f(cx, zacc);   // its barriers also publish xs
+        run_gemv(p, cx, ring, pl, cx.xs);
+        __syncthreads();
+        if (tid < 128) {
+            const __half hl = __float2half_rn(sum_k_shares(cx, pl, tid) - Z);   // fp16 logits, Inference.cu:1270
+            const long long i = blk * 128 + tid;
+            if (p.logits16) p.logits16[i] = hl;
+            const float f = __half2float(hl);                                   // finalSoftmaxKernel, Inference.cu:284-292
+            if (p.logits32) p.logits32[i] = f;
+            if (f > best) {   // indices grow with the rounds: strict '>' keeps the first maximum (Inference.cu:1282-1289)
+                best = f;
+                besti = (int)i;
+            }
+        }
+        __syncthreads();   // xs and obuf are rewritten by the next round
+    }
+    // winner of this CTA, then of all CTAs of all ranks
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, m);
+        if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+    }
+    if (lane == 0) { cx.argv[warp] = best; cx.argi[warp] = besti; }
+    __syncthreads();
+    const uint32_t tag = cx.tagbase + 511;
+    if (warp == 0) {
+        best = lane < F_NW ? cx.argv[lane] : -INFINITY;
+        besti = lane < F_NW ? cx.argi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int m = 8; m > 0; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, m);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, m);
+            if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+        }
+        if (lane == 0) {
+            const size_t at = 2 * (size_t)(G.rank * G.grid + c);
+            for (int r = 0; r < G.n_ranks; ++r) stt2<SYS>(p.xarg[r] + at, tagged_f(best, tag), tagged((uint32_t)besti, tag));
+        }
+        if (c == 0) {
+            const int n = G.n_ranks * G.grid;
+            best = -INFINITY;
+            besti = 0x7fffffff;
+            for (int e = lane; e < n; e += 32) {
+                unsigned long long a = 0, b = 0;
+                const long long t_begin = clock64();
+                for (;;) {
+                    ldt2<SYS>(p.xarg[G.rank] + 2 * (size_t)e, a, b);
+                    if ((has_tag(a, tag) && has_tag(b, tag)) || *cx.s_dead != 0) break;
+                    if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
+                        fail(p, cx, 0x80000);
+                        break;
+                    }
+                }
+                const float ov = payload_f(a);
+                const int oi = (int)(uint32_t)b;
+                if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+            }
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, m);
+                const int oi = __shfl_xor_sync(0xffffffffu, besti, m);
+                if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+            }
+            if (lane == 0 && p.d_token_out) *p.d_token_out = besti;
+        }
+    }
+}
+
+template <bool SYS>
+__global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    FCtx cx;
+    cx.ring = smem;
+    cx.obuf = reinterpret_cast<float*>(smem + FP_OFF_OBUF);
+    cx.hv = reinterpret_cast<__half*>(smem + FP_OFF_HV);
+    cx.xs = reinterpret_cast<__half*>(smem + FP_OFF_XS);
+    cx.seg = reinterpret_cast<int4*>(smem + FP_OFF_SEG);
+    uint8_t* misc = smem + FP_OFF_MISC;
+    cx.qkv_s = reinterpret_cast<__half*>(misc);                  // 768
+    cx.ctx_s = reinterpret_cast<__half*>(misc + 768);            // 256
+    cx.g_s = reinterpret_cast<__half*>(misc + 1024);             // 1024
+    cx.hmine = reinterpret_cast<__half*>(misc + 2048);           // 512
+    cx.rope_cs = reinterpret_cast<__half*>(misc + 2560);         // 256
+    cx.wsum = reinterpret_cast<float*>(misc + 2816);             // 256
+    cx.dsum = reinterpret_cast<double*>(misc + 3072);            // 128
+    cx.un_sz = reinterpret_cast<uint32_t*>(misc + 3200);         // 256
+    cx.argv = reinterpret_cast<float*>(misc + 3456);             // 64
+    cx.argi = reinterpret_cast<int*>(misc + 3520);               // 64
+    cx.s_dead = reinterpret_cast<int*>(misc + 3584);             // 16
+    uint32_t* zero = reinterpret_cast<uint32_t*>(misc + 3616);   // 32 (16-byte aligned)
+    cx.zero_addr = smem_u32(zero);
+    cx.bars = smem_u32(misc + 3712);                             // F_NW * FP_SLOTS * 8
+    static_assert(3712 + F_NW * FP_SLOTS * 8 <= FP_MISC_BYTES, "misc area");
+
+    const int tid = threadIdx.x, c = blockIdx.x;
+    const FusedGeom& G = p.g;
+    const bool active = c < G.n_act;
+    const int cglob = G.rank * G.n_act + c;
+    cx.n_seg = 4 * p.n_layers + p.n_rounds;
+    // this CTA's share of every weight stream, in the order of consumption
+    for (int i = tid; i < cx.n_seg; i += FP_NT) {
+        const uint8_t* base = nullptr;
+        int wb = 0;
+        if (i < 4 * p.n_layers) {
+            const FGemvPlan& pl = p.plan[i & 3];
+            if (c < pl.n_cta) {
+                wb = pl.warp_bytes;
+                base = p.layers[i >> 2].w[i & 3] + (size_t)c * F_NW * wb;
+            }
+        } else {
+            const int round = i - 4 * p.n_layers;
+            if (fused_unemb_block(G, c, round) >= 0) {
+                wb = p.plan[F_UNEMB].warp_bytes;
+                base = p.un_w + ((size_t)round * G.grid + c) * F_NW * wb;
+            }
+        }
+        const unsigned long long b = reinterpret_cast<unsigned long long>(base);
+        cx.seg[i] = make_int4((int)(uint32_t)b, (int)(uint32_t)(b >> 32), wb, 0);
+    }
+    if (tid == 0) {
+        for (int s = 0; s < F_NW * FP_SLOTS; ++s) mbar_init(cx.bars + 8 * s, 1);
+        *cx.s_dead = 0;
+        mbar_fence_init();
+    }
+    if (tid < 8) zero[tid] = 0u;
+    cx.pos = __ldcg(p.d_pos);
+    const int gen = p.d_gen != nullptr ? __ldcg(p.d_gen) : 0;
+    cx.tagbase = (((uint32_t)gen & 0x3fu) << 26) | ((((uint32_t)cx.pos + 1u) & 0x1ffffu) << 9);
+    if (tid < 64) {   // applyRotaryKernel's table row of this position (Inference.cu:444-454)
+        cx.rope_cs[tid] = p.cos_t[(size_t)cx.pos * 64 + tid];
+        cx.rope_cs[64 + tid] = p.sin_t[(size_t)cx.pos * 64 + tid];
+    }
+    __syncthreads();
+    WarpRing ring;
+    ring.uc = 0; ring.pc = 0; ring.pseg = 0; ring.pu = 0;
+    ring.policy = l2_policy_evict_first();
+#pragma unroll
+    for (int s = 0; s < FP_SLOTS; ++s) ring_request(ring, cx);
+
+    if (active) {
+        // embedding gather (Inference.cu:1310-1315) or the hidden state the pass before left (Inference.cu:1357)
+        if (tid < G.rs) {
+            const int i = G.rs * cglob + tid;
+            const bool keep = !p.first_stage || (p.d_skip != nullptr && __ldcg(p.d_skip) != 0);
+            __half v;
+            if (keep) {
+                v = __ldcg(p.hidden + i);
+            } else {
+                long long tok = p.decode ? __ldcg(p.d_token) : __ldcg(p.d_prompt + cx.pos);
+                if (tok < 0 || tok >= G.vocab) tok = 0;
+                const long long pc = ((long long)G.vocab + 1) / 2;
+                const long long gq = (tok / 128) % p.emb_n_alloc;
+                const uint32_t byte = p.emb_packed[(long long)i * pc + (tok >> 1)];
+                v = dequant_one((tok & 1) ? (byte >> 4) : (byte & 15u), p.emb_zp[gq], p.emb_scale[gq]);
+            }
+            cx.hmine[tid] = v;
+        }
+        __syncthreads();
+        publish_hidden<SYS>(p, cx, 1, cx.tagbase + 1, cglob);
+        for (int li = 0; li < p.n_layers; ++li) layer_pass<SYS>(p, cx, ring, li);
+        if (tid < G.rs) p.hidden[G.rs * cglob + tid] = cx.hmine[tid];   // for the next pass / the next stage
+    }
+    if (p.n_rounds > 0) sample_pass<SYS>(p, cx, ring);
+}
+
+// ---- load-time repack ------------------------------------------------------------------------------------------------------
+// One 32-bit word of a stream: `stream` is the CTA (or, for the unembedding, round * grid + CTA), `warp` and `off` the
+// position inside it.  raw: the matrix as on disk, element (o, j) = nibble (f & 1) of byte f >> 1, f = o + j * out_dim
+// (the flat stream read column-major, Inference.cu:1052-1065 over Inference.cu:84-105).
+QW3_HD uint32_t fused_repack_word(const FusedGeom& g, const FGemvPlan& pl, int op, const uint8_t* raw, long long out_dim,
+                                  long long stream, int warp, int off) {
+    const int cta = op == F_UNEMB ? (int)(stream % g.grid) : (int)stream;
+    const long long blk = op == F_UNEMB ? fused_unemb_block(g, cta, (int)(stream / g.grid)) : 0;
+    if (blk < 0) return 0u;
+    const FWordPos wp = fused_word_pos(pl, warp, off);
+    const long long o0 = fused_tile_out(g, op, cta, wp.tile, blk), k0 = fused_k0(g, op, cta);
+    uint32_t word = 0u;
+    for (int n = 0; n < 8; ++n) {
+        int row, j;
+        fused_nibble_src(wp, n, row, j);
+        const long long f = (o0 + row) + (k0 + j) * out_dim;
+        const uint32_t byte = raw[f >> 1];
+        word |= ((f & 1) ? (byte >> 4) : (byte & 15u)) << (4 * n);
+    }
+    return word;
+}
+
+__global__ void fused_repack_kernel(const FusedGeom g, const FGemvPlan pl, const int op, const uint8_t* __restrict__ raw,
+                                    const long long out_dim, uint32_t* __restrict__ out, const long long n_words) {
+    const long long wi = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi >= n_words) return;
+    const long long wps = (long long)F_NW * pl.warp_bytes / 4;   // words per stream
+    const long long stream = wi / wps;
+    const int rem = (int)(wi % wps);
+    const int warp = rem / (pl.warp_bytes / 4), off = (rem % (pl.warp_bytes / 4)) * 4;
+    out[wi] = fused_repack_word(g, pl, op, raw, out_dim, stream, warp, off);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------------------
+static bool make_plan(int n_cta, int n_mt, int n_ks, FGemvPlan* pl) {
+    for (int wm = F_NW; wm >= 1; wm >>= 1) {
+        if (n_mt % wm) continue;
+        const int wk = F_NW / wm;
+        if (n_ks % wk) continue;
+        const int ksw = n_ks / wk, rem = ksw % 4, mtw = n_mt / wm;
+        if (rem != 0 && rem != 2) continue;
+        int tb = 0;
+        for (int t = 4; t >= 1; --t)
+            if (mtw % t == 0 && (rem == 0 || t % 2 == 0)) { tb = t; break; }   // 256-byte items come in pairs
+        if (tb == 0) continue;
+        if ((long long)wk * n_mt * 16 > FP_OBUF) continue;
+        pl->n_cta = n_cta; pl->n_mt = n_mt; pl->n_ks = n_ks; pl->wk = wk; pl->tb = tb; pl->nb = mtw / tb;
+        pl->nq = ksw / 4; pl->rem = rem;
+        pl->warp_bytes = pl->nb * tb * (pl->nq * 512 + rem * 128);
+        pl->n_units = (pl->warp_bytes + F_UNIT - 1) / F_UNIT;
+        return true;
+    }
+    return false;
+}
+
+// group(b, j) = ((b + j * Mb) mod Kb) mod entries does not depend on j
+static bool groups_uniform(long long M, long long K, long long n_alloc) {
+    const long long Mb = M / 128, Kb = K / 128;
+    for (long long b = 0; b < Mb; ++b)
+        for (long long j = 1; j < Kb; ++j)
+            if (((b + j * Mb) % Kb) % n_alloc != (b % Kb) % n_alloc) return false;
+    return true;
+}
+
+bool fused_plan(int H, int I, int heads, int vocab, int n_layers, long long max_pos, int n_ranks, int rank, int grid,
+                FusedGeom* geom, FGemvPlan* plans) {
+    if (H <= 0 || heads <= 0 || H != heads * 128 || H > FP_MAX_H || H % 128 || I % 128 || vocab % 128) return false;
+    if (n_ranks < 1 || n_ranks > QW3_MAX_STAGES || rank < 0 || rank >= n_ranks || heads % n_ranks) return false;
+    if (grid < 1 || max_pos > 0x1fffe || 6 * n_layers + 8 >= 511) return false;
+    FusedGeom g;
+    g.H = H; g.I = I; g.heads = heads; g.vocab = vocab; g.n_ranks = n_ranks; g.rank = rank; g.grid = grid;
+    g.heads_local = heads / n_ranks;
+    g.n_blocks = vocab / 128;
+    bool found = false;
+    for (int gs = 32; gs >= 1 && !found; gs >>= 1) {
+        const int n_act = g.heads_local * gs;
+        if (n_act > grid || H % gs || (H / gs) % 128 || gs * FP_ATT_STRIDE > FP_OBUF) continue;
+        if (H % (n_ranks * n_act) || I % (n_ranks * n_act)) continue;
+        const int rs = H / (n_ranks * n_act), n1 = I / (n_ranks * n_act);
+        if (rs < 2 || rs % 2 || rs > FP_MAX_RS || (H / gs) % rs || (H / n_ranks) % rs) continue;
+        if (n1 % 32 || n1 > FP_MAX_N1 || n1 > FP_NT) continue;
+        if ((H / gs) % 2 || (long long)heads * rs > 8 * FP_NT || (long long)n_ranks * n_act * rs > 8 * FP_NT) continue;
+        g.gs = gs; g.n_act = n_act; g.rs = rs; g.n1 = n1;
+        FGemvPlan pl[F_NOPS];
+        if (!make_plan(n_act, 24, H / 16 / gs, &pl[F_QKV])) continue;
+        if (!make_plan(n_act, H / gs / 16, 8, &pl[F_WO])) continue;
+        if (!make_plan(n_act, n1 / 16, H / 16, &pl[F_W1])) continue;
+        if (!make_plan(n_act, H / 16, n1 / 16, &pl[F_W2])) continue;
+        if (!make_plan(grid, 8, H / 16, &pl[F_UNEMB])) continue;
+        for (int k = 0; k < F_NOPS; ++k) plans[k] = pl[k];
+        found = true;
+    }
+    if (!found) return false;
+    const int n_rounds = (g.n_blocks + n_ranks * grid - 1) / (n_ranks * grid);
+    if (4 * n_layers + n_rounds > FP_MAX_SEG) return false;
+    // the layer matrices must have groups that depend on the output only (they do for the reference's shapes)
+    if (!groups_uniform(3LL * H, H, 3LL * H / 128) || !groups_uniform(H, H, H / 128) || !groups_uniform(I, H, I / 128) ||
+        !groups_uniform(H, I, H / 128))
+        return false;
+    *geom = g;
+    return true;
+}
+
+size_t fused_stream_bytes(const FusedGeom& g, const FGemvPlan& pl, int op) {
+    const long long streams = op == F_UNEMB ? (long long)((g.n_blocks + g.n_ranks * g.grid - 1) / (g.n_ranks * g.grid)) * g.grid : pl.n_cta;
+    return (size_t)streams * F_NW * pl.warp_bytes;
+}
+
+void fused_repack_host(const FusedGeom& g, const FGemvPlan& pl, int op, const uint8_t* raw, long long out_dim, uint8_t* out) {
+    const size_t bytes = fused_stream_bytes(g, pl, op);
+    const long long wps = (long long)F_NW * pl.warp_bytes / 4;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
+    for (size_t wi = 0; wi < bytes / 4; ++wi) {
+        const long long stream = (long long)(wi / wps);
+        const int rem = (int)(wi % wps);
+        o32[wi] = fused_repack_word(g, pl, op, raw, out_dim, stream, rem / (pl.warp_bytes / 4), (rem % (pl.warp_bytes / 4)) * 4);
+    }
+}
+
+struct FusedPass {
+    FusedParams prm;
+    std::vector<void*> allocs;
+    int device = 0;
+    int grid = 0;
+    bool sys = false;
+    void* xbase = nullptr;        // this rank's exchange buffers (one allocation, exported to the peers when row-split)
+    size_t xoff[4] = {0, 0, 0, 0};
+};
+
+static int fp_alloc(FusedPass* f, void** p, size_t bytes) {
+    cudaError_t r = cudaMalloc(p, bytes);
+    if (r != cudaSuccess) {
+        set_last_error("cudaMalloc(%zu bytes) for the fused pass -> %s", bytes, cudaGetErrorString(r));
+        return r == cudaErrorMemoryAllocation ? QW3_ERR_NOMEM : QW3_ERR_CUDA;
+    }
+    f->allocs.push_back(*p);
+    return QW3_OK;
+}
+
+#define FP_TRY(expr)                      \
+    do {                                  \
+        int rc__ = (expr);                \
+        if (rc__ != QW3_OK) return rc__;  \
+    } while (0)
+
+static int repack_to_device(FusedPass* f, const FusedGeom& g, const FGemvPlan& pl, int op, const FusedMatrix& m, const uint8_t** out,
+                            cudaStream_t st) {
+    const size_t bytes = fused_stream_bytes(g, pl, op);
+    void* d = nullptr;
+    FP_TRY(fp_alloc(f, &d, bytes));
+    const long long n_words = (long long)(bytes / 4);
+    const long long blocks = (n_words + 255) / 256;
+    fused_repack_kernel<<<(unsigned)blocks, 256, 0, st>>>(g, pl, op, static_cast<const uint8_t*>(m.packed), m.out_dim,
+                                                          static_cast<uint32_t*>(d), n_words);
+    QW3_CUDA(cudaGetLastError());
+    *out = static_cast<const uint8_t*>(d);
+    return QW3_OK;
+}
+
+// Sizes of the four exchange buffers that other ranks store into (xo, x2, hid, xarg), in 64-bit words.
+static void exchange_words(const FusedGeom& g, size_t (&w)[4]) {
+    w[0] = (size_t)g.heads * g.gs * (g.H / g.gs);
+    w[1] = (size_t)g.n_ranks * g.n_act * g.H;
+    w[2] = (size_t)g.H;   // two buffers of H / 2
+    w[3] = 2 * (size_t)g.n_ranks * g.grid;
+}
+
+int fused_create(const FusedCreate& a, FusedPass** out) {
+    FusedPass* f = new (std::nothrow) FusedPass();
+    if (!f) return QW3_ERR_NOMEM;
+    f->device = a.device;
+    f->grid = a.sm_count;
+    FusedParams& P = f->prm;
+    std::memset(&P, 0, sizeof(P));
+    auto bail = [&](int rc) {
+        fused_destroy(f);
+        return rc;
+    };
+    if (!fused_plan(a.H, a.I, a.heads, a.vocab, a.n_layers, a.max_pos, a.n_ranks, a.rank, a.sm_count, &P.g, P.plan)) {
+        set_last_error("the fused pass does not support this configuration");
+        return bail(QW3_ERR_ARG);
+    }
+    const FusedGeom& g = P.g;
+    cudaError_t ce = cudaFuncSetAttribute(fused_pass_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FP_SMEM_BYTES);
+    if (ce == cudaSuccess) ce = cudaFuncSetAttribute(fused_pass_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FP_SMEM_BYTES);
+    int nb = 0;
+    if (ce == cudaSuccess) ce = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fused_pass_kernel<false>, FP_NT, FP_SMEM_BYTES);
+    if (ce != cudaSuccess || nb < 1) {
+        set_last_error("fused_pass_kernel does not fit on an SM (%zu bytes of shared memory): %s", FP_SMEM_BYTES, cudaGetErrorString(ce));
+        return bail(QW3_ERR_CUDA);
+    }
+    P.n_layers = a.n_layers;
+    P.eps = a.eps;
+    P.n_rounds = a.unemb ? (g.n_blocks + g.n_ranks * g.grid - 1) / (g.n_ranks * g.grid) : 0;
+    P.first_stage = a.emb ? 1 : 0;
+    std::vector<FLayerDesc> ld((size_t)a.n_layers);
+    for (int l = 0; l < a.n_layers; ++l) {
+        const FusedLayerIn& in = a.layers[l];
+        for (int k = 0; k < 4; ++k) {
+            int rc = repack_to_device(f, g, P.plan[k], k, in.m[k], &ld[l].w[k], a.stream);
+            if (rc != QW3_OK) return bail(rc);
+            ld[l].scale[k] = static_cast<const __half*>(in.m[k].scale);
+            ld[l].zp[k] = static_cast<const __half*>(in.m[k].zp);
+            if (l == 0) P.n_alloc[k] = (int)in.m[k].n_alloc;
+        }
+        ld[l].gamma = static_cast<const __half*>(in.gamma);
+        ld[l].kc = static_cast<__half*>(in.kc);
+        ld[l].vc = static_cast<__half*>(in.vc);
+    }
+    void* d_layers = nullptr;
+    int rc = fp_alloc(f, &d_layers, sizeof(FLayerDesc) * (size_t)(a.n_layers > 0 ? a.n_layers : 1));
+    if (rc != QW3_OK) return bail(rc);
+    if (a.n_layers > 0 && cudaMemcpyAsync(d_layers, ld.data(), sizeof(FLayerDesc) * ld.size(), cudaMemcpyHostToDevice, a.stream) != cudaSuccess)
+        return bail(QW3_ERR_CUDA);
+    P.layers = static_cast<const FLayerDesc*>(d_layers);
+    if (a.emb) {
+        P.emb_packed = static_cast<const uint8_t*>(a.emb->packed);
+        P.emb_scale = static_cast<const __half*>(a.emb->scale);
+        P.emb_zp = static_cast<const __half*>(a.emb->zp);
+        P.emb_n_alloc = (int)a.emb->n_alloc;
+    }
+    if (a.unemb) {
+        rc = repack_to_device(f, g, P.plan[F_UNEMB], F_UNEMB, *a.unemb, &P.un_w, a.stream);
+        if (rc != QW3_OK) return bail(rc);
+        P.un_scale = static_cast<const __half*>(a.unemb->scale);
+        P.un_zp = static_cast<const __half*>(a.unemb->zp);
+        P.n_alloc[F_UNEMB] = (int)a.unemb->n_alloc;
+        P.gamma_final = static_cast<const __half*>(a.gamma_final);
+        P.logits16 = static_cast<__half*>(a.logits16);
+        P.logits32 = a.logits32;
+    }
+    P.hidden = static_cast<__half*>(a.hidden);
+    P.d_pos = a.d_pos; P.d_token = a.d_token; P.d_skip = a.d_skip; P.d_prompt = a.d_prompt; P.d_gen = a.d_gen;
+    P.cos_t = static_cast<const __half*>(a.cos_t); P.sin_t = static_cast<const __half*>(a.sin_t);
+    P.max_pos = a.max_pos;
+    P.d_token_out = a.d_token;
+    P.err = a.err;
+    // exchange buffers: the group-local ones, then one allocation for those other ranks store into
+    void* loc = nullptr;
+    const size_t loc_words = (size_t)g.n_act * (FP_QKV + FP_ATT_STRIDE);
+    rc = fp_alloc(f, &loc, loc_words * 8);
+    if (rc != QW3_OK) return bail(rc);
+    if (cudaMemsetAsync(loc, 0, loc_words * 8, a.stream) != cudaSuccess) return bail(QW3_ERR_CUDA);
+    P.xq = static_cast<unsigned long long*>(loc);
+    P.xa = P.xq + (size_t)g.n_act * FP_QKV;
+    size_t w[4];
+    exchange_words(g, w);
+    size_t total = 0;
+    for (int k = 0; k < 4; ++k) {
+        f->xoff[k] = total;
+        total += (w[k] + 31) & ~(size_t)31;
+    }
+    rc = fp_alloc(f, &f->xbase, total * 8);
+    if (rc != QW3_OK) return bail(rc);
+    if (cudaMemsetAsync(f->xbase, 0, total * 8, a.stream) != cudaSuccess) return bail(QW3_ERR_CUDA);
+    if (cudaStreamSynchronize(a.stream) != cudaSuccess) return bail(QW3_ERR_CUDA);
+    fused_set_peer(f, g.rank, f->xbase);
+    f->sys = g.n_ranks > 1;
+    *out = f;
+    return QW3_OK;
+}
+
+void* fused_exchange_base(FusedPass* f, size_t* bytes) {
+    size_t w[4];
+    exchange_words(f->prm.g, w);
+    if (bytes) *bytes = (f->xoff[3] + ((w[3] + 31) & ~(size_t)31)) * 8;
+    return f->xbase;
+}
+
+// Exchange buffers of rank r (its own allocation, or a peer mapping of another rank's).
+void fused_set_peer(FusedPass* f, int r, void* base) {
+    unsigned long long* b = static_cast<unsigned long long*>(base);
+    f->prm.xo[r] = b + f->xoff[0];
+    f->prm.x2[r] = b + f->xoff[1];
+    f->prm.hid[r] = b + f->xoff[2];
+    f->prm.xarg[r] = b + f->xoff[3];
+}
+
+void fused_destroy(FusedPass* f) {
+    if (!f) return;
+    for (void* p : f->allocs) cudaFree(p);
+    delete f;
+}
+
+int fused_launch(FusedPass* f, int decode, cudaStream_t st) {
+    FusedParams p = f->prm;
+    p.decode = decode;
+    if (!decode) p.n_rounds = 0;   // prompt passes compute no logits (Inference.cu:1304-1343)
+    void* args[] = {&p};
+    const void* fn = f->sys ? reinterpret_cast<const void*>(fused_pass_kernel<true>) : reinterpret_cast<const void*>(fused_pass_kernel<false>);
+    QW3_CUDA(cudaLaunchCooperativeKernel(fn, dim3(f->grid), dim3(FP_NT), args, FP_SMEM_BYTES, st));
+    return QW3_OK;
+}
+
+void fused_geometry(const FusedPass* f, FusedGeom* g, FGemvPlan* plans) {
+    *g = f->prm.g;
+    for (int k = 0; k < F_NOPS; ++k) plans[k] = f->prm.plan[k];
+}
+
+}  // namespace qw3
+
+using namespace qw3;
+
+extern "C" {
+
+int qw3_fused_plan(const Qw3Config* cfg, int32_t n_ranks, int32_t rank, int32_t grid, int32_t* geom_out, int32_t* plans_out) {
+    QW3_REQUIRE(cfg && geom_out && plans_out, "qw3_fused_plan: null pointer");
+    FusedGeom g;
+    FGemvPlan pl[F_NOPS];
+    if (!fused_plan(cfg->hidden, cfg->inter, cfg->heads, cfg->vocab, cfg->layers, cfg->max_pos, n_ranks, rank, grid, &g, pl)) {
+        set_last_error("qw3_fused_plan: the fused pass does not cover this configuration");
+        return QW3_ERR_ARG;
+    }
+    const int32_t gv[16] = {g.H, g.I, g.heads, g.vocab, g.n_ranks, g.rank, g.heads_local, g.gs, g.n_act, g.rs, g.n1, g.n_blocks, g.grid, 0, 0, 0};
+    std::memcpy(geom_out, gv, sizeof(gv));
+    for (int k = 0; k < F_NOPS; ++k) {
+        const int32_t pv[10] = {pl[k].n_cta, pl[k].n_mt, pl[k].n_ks, pl[k].wk, pl[k].tb, pl[k].nb, pl[k].nq, pl[k].rem, pl[k].warp_bytes, pl[k].n_units};
+        std::memcpy(plans_out + 10 * k, pv, sizeof(pv));
+    }
+    return QW3_OK;
+}
+
+int qw3_fused_repack_host(const Qw3Config* cfg, int32_t n_ranks, int32_t rank, int32_t grid, int32_t op, const void* raw_packed,
+                          int64_t out_dim, void* out, int64_t out_bytes) {
+    QW3_REQUIRE(cfg && raw_packed && out && op >= 0 && op < F_NOPS, "qw3_fused_repack_host: bad argument");
+    FusedGeom g;
+    FGemvPlan pl[F_NOPS];
+    if (!fused_plan(cfg->hidden, cfg->inter, cfg->heads, cfg->vocab, cfg->layers, cfg->max_pos, n_ranks, rank, grid, &g, pl)) {
+        set_last_error("qw3_fused_repack_host: the fused pass does not cover this configuration");
+        return QW3_ERR_ARG;
+    }
+    QW3_REQUIRE((int64_t)fused_stream_bytes(g, pl[op], op) == out_bytes, "qw3_fused_repack_host: the stream of this operator has %zu bytes",
+                fused_stream_bytes(g, pl[op], op));
+    fused_repack_host(g, pl[op], op, static_cast<const uint8_t*>(raw_packed), out_dim, static_cast<uint8_t*>(out));
+    return QW3_OK;
+}
+
+}  // extern "C"

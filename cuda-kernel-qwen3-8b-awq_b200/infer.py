@@ -81,6 +81,13 @@ class QWen3AWQInfer:
         cabi.check(self._lib.qw3_layer_decode(self._h, layer, pos, h.ctypes.data_as(C.c_void_p)), "qw3_layer_decode")
         return h
 
+    def stage_hidden(self, stage):
+        """Hidden state a stage of this process holds after its last pass (test hook)."""
+        import numpy as np
+        h = np.empty(self.config.hidden, np.float16)
+        cabi.check(self._lib.qw3_stage_hidden(self._h, stage, h.ctypes.data_as(C.c_void_p)), "qw3_stage_hidden")
+        return h
+
     def close(self):
         if getattr(self, "_h", None) is not None and self._h.value:
             self._lib.qw3_destroy(self._h)

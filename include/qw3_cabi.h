@@ -187,7 +187,9 @@ typedef struct Qw3Config {
     int32_t use_graph;     /* replay one captured decode step per token */
     int32_t use_pdl;       /* programmatic dependent launch between the step's kernels */
     int32_t keep_logits;   /* keep an fp32 copy of the last step's logits (test hook) */
-    int32_t persistent;    /* 1: a token pass of a stage is one persistent cooperative kernel; 0: one launch per operator */
+    int32_t persistent;    /* 2 (default): a token pass of a stage is one launch of the fused kernel (operators of a layer
+                              paired, weights repacked at load time; falls back to 1 for shapes it does not cover);
+                              1: one persistent kernel walking an operator list; 0: one launch per operator */
 } Qw3Config;
 
 typedef struct qw3_engine* qw3_handle;
@@ -240,6 +242,11 @@ int qw3_last_launches(qw3_handle h, int64_t* n);
 int qw3_kv_upload(qw3_handle h, int32_t layer, int32_t which, const void* host_f16, int64_t upto);
 int qw3_layer_decode(qw3_handle h, int32_t layer, int32_t pos, void* host_hidden_f16);
 
+/* Test hook: the hidden state (fp16 [hidden], to host memory) that stage `stage` of this process holds after its last
+ * pass, i.e. the residual stream after the stage's last layer.  With a stage split placed at the layers of interest this
+ * exposes intermediate hidden states without any extra kernel. */
+int qw3_stage_hidden(qw3_handle h, int32_t stage, void* host_hidden_f16);
+
 /* Debug: global-timer value (ns) at which CTA 0 entered each operator of the last decode pass of a
  * stage, plus the end of the pass; needs QW3_TRACE set in the environment when the handle is made. */
 int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries);
@@ -254,6 +261,18 @@ int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entr
  * elsewhere). */
 int qw3_stage_export(qw3_handle h, void* out_handle_64B);
 int qw3_stage_connect(qw3_handle h, const void* next_stage_handle_64B, const void* prev_stage_handle_64B);
+
+/* Test hooks of the fused token pass (persistent = 2), pure host arithmetic: how it cuts a configuration over `grid`
+ * CTAs and `n_ranks` GPUs -- geom_out receives 16 ints {hidden, inter, heads, vocab, n_ranks, rank, heads per rank,
+ * CTAs per head, CTAs running the layers, hidden elements owned per CTA, W1 outputs per CTA, vocabulary blocks, grid,
+ * 0, 0, 0}, plans_out 5 x 10 ints {CTAs, tiles per CTA, k-steps per CTA, warps along k, tiles per block, blocks per
+ * warp, full k-groups, remaining k-steps, bytes per warp stream, ring units per warp} for Wqkv, Wo, W1, W2 and one
+ * unembedding block -- and the load-time repack of one matrix (the reference's on-disk layout, Inference.cu:780-900, is
+ * unchanged on disk) into the per-(CTA, warp) byte streams the kernel consumes.  QW3_ERR_ARG when the fused pass
+ * does not cover the configuration (the engine then keeps the operator-list kernel). */
+int qw3_fused_plan(const Qw3Config* cfg, int32_t n_ranks, int32_t rank, int32_t grid, int32_t* geom_out, int32_t* plans_out);
+int qw3_fused_repack_host(const Qw3Config* cfg, int32_t n_ranks, int32_t rank, int32_t grid, int32_t op, const void* raw_packed,
+                          int64_t out_dim, void* out, int64_t out_bytes);
 
 /* Layers [*first, *first + *count) that stage `stage` of cfg runs (pure host arithmetic). */
 int qw3_stage_layers(const Qw3Config* cfg, int32_t stage, int32_t* first, int32_t* count);

@@ -70,6 +70,7 @@ def lib():
         "orc_model_layer": (None, [vp, i32, i64, vp]),
         "orc_model_sample": (i64, [vp, vp, vp]),
         "orc_model_generate": (i32, [vp, vp, i32, i32, vp, vp, vp]),
+        "orc_model_generate_trace": (i32, [vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp]),
         "orc_model_packed": (vp, [vp, i32, i32]),
         "orc_model_f16": (vp, [vp, i32, i32]),
         "orc_model_kv": (vp, [vp, i32, i32]),
@@ -237,6 +238,25 @@ class Model:
         if rc != 0:
             raise ValueError("oracle: invalid prompt/max_new for this configuration")
         return ids, logits, margins
+
+    def generate_trace(self, prompt, max_new, probe_layers=(), probe_pos=()):
+        """generate() with probes: returns a dict with ids, last logits, margins, per-step top-8 (idx, val) and the
+        hidden state after probe_layers at probe_pos ([n_pos][n_layers][hidden] fp16)."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        ids = np.empty(max_new, np.int32)
+        logits = np.empty(self.cfg.vocab, np.float16)
+        margins = np.empty(max_new, np.float32)
+        top_idx = np.empty((max_new, 8), np.int32)
+        top_val = np.empty((max_new, 8), np.float16)
+        pl = np.ascontiguousarray(probe_layers, np.int32)
+        pp = np.ascontiguousarray(probe_pos, np.int32)
+        ph = np.zeros((pp.size, pl.size, self.cfg.hidden), np.float16)
+        rc = lib().orc_model_generate_trace(self.h, _p(prompt), prompt.size, max_new, _p(ids), _p(logits), _p(margins),
+                                            _p(top_idx), _p(top_val), _p(pl) if pl.size else None, pl.size,
+                                            _p(pp) if pp.size else None, pp.size, _p(ph) if ph.size else None)
+        if rc != 0:
+            raise ValueError("oracle: invalid prompt/max_new for this configuration")
+        return dict(ids=ids, logits=logits, margins=margins, top_idx=top_idx, top_val=top_val, probe_hidden=ph)
 
     def _view(self, ptr, n, dtype):
         return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(n * np.dtype(dtype).itemsize,)).view(dtype)

@@ -531,8 +531,32 @@ static float top2_margin(const uint16_t* logits, int64_t n) {
     return a - b;
 }
 
-int orc_model_generate(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int32_t max_new,
-                       int32_t* out_ids, uint16_t* last_logits, float* margins) {
+// The eight largest logits of a step, first-max order (larger value first, lower index first among equals).
+static void top8(const uint16_t* logits, int64_t n, int32_t* idx, uint16_t* val) {
+    float bv[8];
+    int64_t bi[8];
+    int cnt = 0;
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = h2f(logits[i]);
+        if (cnt == 8 && !(v > bv[7])) continue;
+        int p = cnt < 8 ? cnt : 7;
+        while (p > 0 && v > bv[p - 1]) { bv[p] = bv[p - 1]; bi[p] = bi[p - 1]; --p; }
+        bv[p] = v; bi[p] = i;
+        if (cnt < 8) ++cnt;
+    }
+    for (int k = 0; k < 8; ++k) {
+        idx[k] = k < cnt ? (int32_t)bi[k] : -1;
+        val[k] = k < cnt ? logits[bi[k]] : 0;
+    }
+}
+
+// generateResponse (Inference.cu:1297-1408) with optional probes: per decode step the top-1 minus top-2 margin and
+// the eight largest logits; the hidden state after the layers named in probe_layers at the positions named in
+// probe_pos (probe_hidden is [n_probe_pos][n_probe_layers][hidden]).
+int orc_model_generate_trace(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int32_t max_new,
+                             int32_t* out_ids, uint16_t* last_logits, float* margins, int32_t* top_idx, uint16_t* top_val,
+                             const int32_t* probe_layers, int32_t n_probe_layers, const int32_t* probe_pos,
+                             int32_t n_probe_pos, uint16_t* probe_hidden) {
     const OrcConfig& c = m->cfg;
     if (n_prompt < 1 || max_new < 0 || (int64_t)n_prompt + max_new > c.max_pos) return -1;
     for (int32_t t = 0; t < n_prompt; ++t)
@@ -542,9 +566,21 @@ int orc_model_generate(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int
         orc_embed_gather(m->emb.packed.data(), m->emb.scale.data(), m->emb.zp.data(), m->emb.n_alloc,
                          c.hidden, c.vocab, c.group, tok, hidden.data());
     };
+    auto layers_at = [&](int64_t pos) {
+        int pi = -1;
+        for (int32_t k = 0; k < n_probe_pos; ++k)
+            if (probe_pos[k] == pos) pi = k;
+        for (int l = 0; l < c.layers; ++l) {
+            orc_model_layer(m, l, pos, hidden.data());
+            if (pi >= 0 && probe_hidden)
+                for (int32_t k = 0; k < n_probe_layers; ++k)
+                    if (probe_layers[k] == l)
+                        std::memcpy(probe_hidden + ((size_t)pi * n_probe_layers + k) * c.hidden, hidden.data(), (size_t)c.hidden * 2);
+        }
+    };
     for (int32_t t = 0; t < n_prompt; ++t) {                 // Inference.cu:1304-1343
         embed(prompt[t]);
-        for (int l = 0; l < c.layers; ++l) orc_model_layer(m, l, t, hidden.data());
+        layers_at(t);
     }
     int64_t pos = n_prompt;
     for (int32_t step = 0; step < max_new; ++step) {         // Inference.cu:1352-1405
@@ -556,14 +592,21 @@ int orc_model_generate(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int
             embed(out_ids[step - 1]);                        // Inference.cu:1392-1398, 1357
         }                                                    // step 0: hidden carried over, Inference.cu:1357
         if (run_layers) {
-            for (int l = 0; l < c.layers; ++l) orc_model_layer(m, l, pos, hidden.data());
+            layers_at(pos);
             ++pos;
         }
         out_ids[step] = (int32_t)orc_model_sample(m, hidden.data(), logits.data());
         if (margins) margins[step] = top2_margin(logits.data(), c.vocab);
+        if (top_idx && top_val) top8(logits.data(), c.vocab, top_idx + (size_t)step * 8, top_val + (size_t)step * 8);
     }
     if (last_logits && max_new > 0) std::memcpy(last_logits, logits.data(), (size_t)c.vocab * 2);
     return 0;
+}
+
+int orc_model_generate(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int32_t max_new,
+                       int32_t* out_ids, uint16_t* last_logits, float* margins) {
+    return orc_model_generate_trace(m, prompt, n_prompt, max_new, out_ids, last_logits, margins, nullptr, nullptr,
+                                    nullptr, 0, nullptr, 0, nullptr);
 }
 
 static OrcW4* pick(OrcModel* m, int layer, int kind) {

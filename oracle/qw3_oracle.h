@@ -140,6 +140,14 @@ int64_t orc_model_sample(OrcModel* m, const uint16_t* hidden, uint16_t* logits_f
  * the top-1 minus top-2 logit of each step. Returns 0 or -1 (sequence would exceed max_pos). */
 int orc_model_generate(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int32_t max_new,
                        int32_t* out_ids, uint16_t* last_logits_f16, float* margins);
+/* The same flow with probes for the golden fixtures: per decode step the eight largest fp16 logits (top_idx,
+ * top_val: [max_new][8], larger value first, lower index first among equals) and the hidden state after the layers
+ * probe_layers[] at the positions probe_pos[] (probe_hidden: [n_probe_pos][n_probe_layers][hidden] fp16).  Any
+ * output pointer may be NULL. */
+int orc_model_generate_trace(OrcModel* m, const int32_t* prompt, int32_t n_prompt, int32_t max_new,
+                             int32_t* out_ids, uint16_t* last_logits_f16, float* margins, int32_t* top_idx,
+                             uint16_t* top_val, const int32_t* probe_layers, int32_t n_probe_layers,
+                             const int32_t* probe_pos, int32_t n_probe_pos, uint16_t* probe_hidden);
 /* Raw access for tests (pointers into the model; do not free). */
 const uint8_t*  orc_model_packed(OrcModel* m, int layer, int kind);
 const uint16_t* orc_model_f16(OrcModel* m, int layer, int kind);

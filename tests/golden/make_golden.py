@@ -1,12 +1,15 @@
-"""Regenerates tests/golden/golden.json from the CPU oracle (oracle/qw3_oracle.cpp).
+"""Regenerates tests/golden/golden.json and tests/golden/golden_hidden.npz from the CPU oracle (oracle/qw3_oracle.cpp).
 
-    python tests/golden/make_golden.py [--full]
+    python tests/golden/make_golden.py [--full] [--c4]
 
 The reference ships no golden vectors (it has no tests and does not build), so these fixtures pin
-the oracle and the seeded generator against silent change, and let the GPU tests check the
-full-size configurations without re-running minutes of CPU work.  --full also runs the 36-layer
-configuration (prompt 128 + 20 tokens; a few minutes on 8 cores); without it the entry already in
-golden.json is kept.
+the oracle and the seeded generator against silent change, and let the GPU tests and the benchmark check the
+full-size configurations without re-running minutes of CPU work.  Every model case holds, per decode step, the
+sampled id, the top-1 minus top-2 margin and the eight largest logits (index and value), and the hidden state
+after the first, a middle and the last layer at two positions (golden_hidden.npz), so that a stale cache row, a
+position slip or a wrong hand-off shows up even where the greedy ids would not change.
+--full runs the 36-layer configuration with a prompt of 128 ids (a few minutes on 8 cores); --c4 the same model with
+a prompt of 512 ids and 128 new ids (several more minutes).  Without the flags the entries already in the files are kept.
 """
 import hashlib
 import json
@@ -20,35 +23,52 @@ sys.path.insert(0, os.path.join(HERE, "..", "..", "oracle"))
 import orc  # noqa: E402
 
 OUT = os.path.join(HERE, "golden.json")
+OUT_H = os.path.join(HERE, "golden_hidden.npz")
 
 SMALL = dict(hidden=512, inter=1536, heads=4, head_dim=128, layers=4, vocab=2176, max_pos=64, rope_base=10000.0)
-FULL = dict(max_pos=256)   # reference constants otherwise; KV rows kept = 256 >= 128 + 20
+# Seed of the small model: chosen (by scanning seeds 0..39) so that the reference flow and the sample_first flow
+# produce different ids, several distinct ids each, with top-2 margins of at least 0.25 at every step.
+SMALL_SEED = 38
+FULL = dict(max_pos=256)     # reference constants otherwise; KV rows kept = 256 >= 128 + 72
+FULL_C4 = dict(max_pos=640)  # prompt 512 + 128 new ids
 
 
 def sha(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
-def model_case(cfg_kw, seed, n_prompt, max_new, sample_first=0):
+def model_case(cfg_kw, seed, n_prompt, max_new, sample_first=0, probe_step=None):
     cfg = orc.default_config(sample_first=sample_first, **cfg_kw)
     m = orc.Model(cfg)
     m.init_random(seed)
     prompt = orc.gen_tokens(seed, orc.TOKENS, n_prompt, cfg.vocab)
-    ids, logits, margins = m.generate(prompt, max_new)
+    layers = sorted({0, (cfg.layers - 1) // 2, cfg.layers - 1})
+    # positions probed: the last prompt token, and the pass of decode step `probe_step` (the reference flow runs step s
+    # at position n_prompt + s; with sample_first step 0 runs no layers and step s runs at n_prompt + s - 1)
+    if probe_step is None:
+        probe_step = max_new - 1
+    pos = [n_prompt - 1, n_prompt + probe_step - (1 if sample_first else 0)]
+    t = m.generate_trace(prompt, max_new, layers, pos)
+    logits = t["logits"]
     top = np.argsort(-logits.astype(np.float32), kind="stable")[:8]
     case = dict(config=cfg_kw, seed=seed, n_prompt=n_prompt, max_new=max_new, sample_first=sample_first,
-                prompt_head=[int(t) for t in prompt[:8]], ids=[int(t) for t in ids],
-                min_margin=float(margins.min()), margins=[float(x) for x in margins],
-                last_logits_sha256=sha(logits), last_logits_top8_idx=[int(t) for t in top],
-                last_logits_top8=[float(logits[t]) for t in top])
+                prompt_head=[int(v) for v in prompt[:8]], ids=[int(v) for v in t["ids"]],
+                min_margin=float(t["margins"].min()), margins=[float(x) for x in t["margins"]],
+                steps_top8_idx=[[int(v) for v in r] for r in t["top_idx"]],
+                steps_top8=[[float(v) for v in r] for r in t["top_val"]],
+                probe_layers=layers, probe_pos=pos, probe_step=probe_step,
+                last_logits_sha256=sha(logits), last_logits_top8_idx=[int(v) for v in top],
+                last_logits_top8=[float(logits[v]) for v in top])
     m.close()
-    return case
+    return case, t["probe_hidden"]
 
 
 def main():
     full = "--full" in sys.argv
+    c4 = "--c4" in sys.argv
     old = json.load(open(OUT)) if os.path.exists(OUT) else {}
-    g = {}
+    old_h = dict(np.load(OUT_H)) if os.path.exists(OUT_H) else {}
+    g, gh = {}, {}
     # generator pins
     g["generator"] = dict(
         codes_seed0_tag0=orc.gen_codes(0, 0, 32).tobytes().hex(),
@@ -65,14 +85,18 @@ def main():
     y32, y16 = orc.gemm_w4a16(p, s, z, M, K, x)
     g["single_linear"] = dict(M=M, K=K, seed=0, packed_sha256=sha(p), dequant_sha256=sha(dq), y_f16_sha256=sha(y16),
                               y_f16_head=y16[:8].tobytes().hex(), y_f32_head=[float(v) for v in y32[:8]])
-    g["small_model"] = model_case(SMALL, 0, 6, 10)
-    g["small_model_sample_first"] = model_case(SMALL, 0, 6, 10, sample_first=1)
-    if full:
-        g["full_model"] = model_case(FULL, 0, 128, 20)
-    elif "full_model" in old:
-        g["full_model"] = old["full_model"]
+    g["small_model"], gh["small_model"] = model_case(SMALL, SMALL_SEED, 6, 10)
+    g["small_model_sample_first"], gh["small_model_sample_first"] = model_case(SMALL, SMALL_SEED, 6, 10, sample_first=1)
+    assert g["small_model"]["ids"] != g["small_model_sample_first"]["ids"], "pick a seed where the two flows differ"
+    for name, want, make in (("full_model", full, lambda: model_case(FULL, 0, 128, 72, probe_step=19)),
+                             ("full_model_c4", c4, lambda: model_case(FULL_C4, 0, 512, 128, probe_step=19))):
+        if want:
+            g[name], gh[name] = make()
+        elif name in old and name in old_h:
+            g[name], gh[name] = old[name], old_h[name]
     json.dump(g, open(OUT, "w"), indent=1)
-    print("wrote", OUT, "full" if full else "(full-size entry kept)")
+    np.savez_compressed(OUT_H, **gh)
+    print("wrote", OUT, OUT_H, "cases:", sorted(g))
 
 
 if __name__ == "__main__":

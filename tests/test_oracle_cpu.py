@@ -158,17 +158,26 @@ SMALL = dict(hidden=512, inter=1536, heads=4, head_dim=128, layers=4, vocab=2176
 
 def test_small_model_golden_and_weight_dir_round_trip(orc, tmp_path):
     g = GOLDEN["small_model"]
+    seed = g["seed"]
     cfg = orc.default_config(**SMALL)
-    prompt = orc.gen_tokens(0, orc.TOKENS, g["n_prompt"], cfg.vocab)
+    prompt = orc.gen_tokens(seed, orc.TOKENS, g["n_prompt"], cfg.vocab)
     m = orc.Model(cfg)
-    m.init_random(0)
+    m.init_random(seed)
     ids, logits, margins = m.generate(prompt, g["max_new"])
     assert [int(t) for t in ids] == g["ids"]
+    # the probing form of the same flow: same ids, its per-step top-8 and hidden probes are what golden.json holds
+    t = m.generate_trace(prompt, g["max_new"], g["probe_layers"], g["probe_pos"])
+    assert [int(v) for v in t["ids"]] == g["ids"]
+    assert [[int(v) for v in r] for r in t["top_idx"]] == g["steps_top8_idx"]
+    assert np.array_equal(t["top_val"].astype(np.float32), np.array(g["steps_top8"], np.float32))
+    assert (t["top_idx"][:, 0] == t["ids"]).all() and (np.diff(t["top_val"].astype(np.float32), axis=1) <= 0).all()
+    hid = np.load(os.path.join(HERE, "golden", "golden_hidden.npz"))["small_model"]
+    assert np.array_equal(t["probe_hidden"].view(np.uint16), hid.view(np.uint16))
     import hashlib
     assert hashlib.sha256(logits.tobytes()).hexdigest() == g["last_logits_sha256"]
     # the weight directory holds exactly the reference's file set and sizes, and loads back
     d = str(tmp_path)
-    orc.write_weight_dir(cfg, 0, d)
+    orc.write_weight_dir(cfg, seed, d)
     names = sorted(os.listdir(d))
     assert len(names) == 13 * cfg.layers + 6
     H, I, V = cfg.hidden, cfg.inter, cfg.vocab
@@ -196,3 +205,4 @@ def test_reference_flow_versus_sample_first(orc):
     a, b = GOLDEN["small_model"], GOLDEN["small_model_sample_first"]
     assert len(a["ids"]) == len(b["ids"]) == 10
     assert a["last_logits_sha256"] != b["last_logits_sha256"]
+    assert a["ids"] != b["ids"]   # the seed was chosen so that the two flows are told apart by their ids as well

@@ -52,9 +52,10 @@ def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_f
         pytest.skip(f"needs {world} GPUs")
     golden = json.load(open(os.path.join(HERE, "golden", "golden.json")))
     want = golden["small_model_sample_first" if sample_first else "small_model"]["ids"]
+    seed = golden["small_model"]["seed"]
     wdir = str(tmp_path)
-    orc.write_weight_dir(orc.default_config(**SMALL), 0, wdir)
-    prompt = [int(t) for t in orc.gen_tokens(0, orc.TOKENS, 6, SMALL["vocab"])]
+    orc.write_weight_dir(orc.default_config(**SMALL), seed, wdir)
+    prompt = [int(t) for t in orc.gen_tokens(seed, orc.TOKENS, 6, SMALL["vocab"])]
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -109,9 +110,10 @@ def test_one_process_per_gpu_batched_prompt(pkg, orc, cuda, tmp_path, world, n_p
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    seed = json.load(open(os.path.join(HERE, "golden", "golden.json")))["small_model"]["seed"]
     wdir = str(tmp_path)
-    orc.write_weight_dir(orc.default_config(**SMALL), 0, wdir)
-    prompt = [int(t) for t in orc.gen_tokens(0, orc.TOKENS, n_prompt, SMALL["vocab"])]
+    orc.write_weight_dir(orc.default_config(**SMALL), seed, wdir)
+    prompt = [int(t) for t in orc.gen_tokens(seed, orc.TOKENS, n_prompt, SMALL["vocab"])]
     max_pos = n_prompt + 24
     one = pkg.QWen3AWQInfer(wdir, **dict(SMALL, max_pos=max_pos))
     one.set_batched_prefill(True)
