@@ -2,19 +2,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-A step is one decoded token: one pass of the 36 layers + unembed + arg-max at batch 1.  Workload
-at every N: the full 36-layer model with seeded random weights (written as the reference's .bin
-set and loaded through the constructor), prompt of 128 seeded ids, then W warm-up and K timed
-decode steps.  For N > 1 the layers are split over N GPUs as a pipeline (strong scaling: the work
-is the same model).  Prints ONE JSON line.
+A step is one decoded token: one pass of the 36 layers + unembed + arg-max at batch 1.  Workload: the full
+36-layer model with seeded random weights (written as the reference's .bin set and loaded through the
+constructor); at N = 1 a prompt of 128 seeded ids, at N > 1 a prompt of 512 ids (the multi-GPU configuration of
+the baseline), then W warm-up and K timed decode steps.  For N > 1 the same model is spread over N GPUs (strong
+scaling), as a layer pipeline (--parallel pp, the reference's contract) or with every matrix row-split over the
+GPUs (--parallel tp).  Prints ONE JSON line.
 
-`value` is device-timed (CUDA events around the decode loop, weights and KV resident in HBM);
-`e2e` is the host wall-clock of the public API call that produces the same K ids into host memory.
-`roofline` describes the dominant kernel of the timed region (decode_pass_kernel, one launch per
-token: algorithmic bytes of a token / CUDA-event time of a step); `gemv_roofline` times the stand-alone
-fused dequant-GEMV operator on the 12288x4096 matrices, cycling 36 distinct matrices (906 MB > L2).
-`cpu_baseline` / `--impl reference` time the CPU oracle port of the same math on the host cores
-(the reference has no CPU path and does not build).
+Every id the run produces (warm-up, timed and end-to-end steps) is compared with the golden ids the CPU oracle
+produced for the same seed and prompt (tests/golden/golden.json): `ids_match_golden`; a mismatch makes the run fail.
+
+`value` is device-timed: the timed region (K decode steps, CUDA events inside the engine around this rank's decode
+loop, weights and KV resident in HBM) is repeated, the median of the repeats counts, all are listed.
+`e2e` is the host wall-clock of the public API call that produces K more ids into host memory; `e2e_generate` the
+wall-clock of generateResponse(prompt, K) with the prompt ids in host memory, prompt phase included.
+`roofline` describes the dominant kernel of the timed region (one launch per token: algorithmic bytes of a token /
+CUDA-event time of a step); `gemv_roofline` times the stand-alone fused dequant-GEMV operator on the 12288x4096
+matrices, cycling 36 distinct matrices (906 MB > L2).  `cpu_baseline` / `--impl reference` time the CPU oracle port
+of the same math on the host cores (the reference has no CPU path and does not build).
 """
 import argparse
 import json
@@ -35,8 +40,12 @@ LAST_REF_GEMV_US = None
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_pass_kernel over its algorithmic bytes, from the ncu
 # capture summarised in profiles/ (a 6-layer pass; traffic grows with the bytes streamed).
 NCU_TRAFFIC_RATIO = (509.30 + 4.82) / 507.6
-PROMPT_LEN = 128
+NCU_TRAFFIC_NOTE = ("dram read+write of an ncu capture of a 6-layer pass (514.1 MB for 507.6 MB algorithmic), scaled by bytes to the "
+                    "36-layer launch")
+PROMPT_LEN = 128          # one GPU: prompt 128 + 20 new ids is the baseline's single-GPU configuration
+PROMPT_LEN_MULTI = 512    # several GPUs: prompt 512 + 128 new ids
 SEED = 0
+REPEATS = 7               # timed regions of K steps each; the median counts
 # Algorithmic bytes of one decoded token: packed weights of 36 layers + unembed, scale/zero-point
 # entries read, KV rows read (589,824 bytes per position of context).
 LAYER_PACKED = 25165824 + 8388608 + 25165824 + 25165824
@@ -123,18 +132,38 @@ def cpu_decode_tokens_per_s(orc, weight_dir, n_tokens, context):
     return n_tokens / sum(times[1:]), np.mean(times[1:]) * 1e3
 
 
+def workload_string(args):
+    return ("full 36-layer Qwen3-8B-shape W4A16 model (hidden 4096, 32 heads, inter 12288, vocab 151936), "
+            f"prompt {args.prompt_len} ids, batch-1 greedy decode steps from context {args.prompt_len + args.warmup} on, "
+            "seeded random weights")
+
+
+def golden_ids(prompt_len):
+    """Ids the CPU oracle produced for seed 0 and this prompt length (None when there is no such fixture)."""
+    path = os.path.join(ROOT, "tests", "golden", "golden.json")
+    if not os.path.exists(path):
+        return None, None
+    g = json.load(open(path))
+    for name in ("full_model", "full_model_c4"):
+        if name in g and g[name]["n_prompt"] == prompt_len and g[name]["seed"] == SEED and not g[name]["sample_first"]:
+            return name, g[name]["ids"]
+    return None, None
+
+
 def run_reference(args, rank):
     """The reference arm: the reference has no CPU implementation and does not compile, so the CPU
     oracle port of its math stands in, with every host thread it can use."""
     if rank != 0:
         return
     orc = load_oracle()
+    # every host core, whatever OMP_NUM_THREADS the launcher exported (torch.distributed.run sets it to 1)
+    orc.set_num_threads(os.cpu_count() or 1)
     tps, ms = cpu_decode_tokens_per_s(orc, None, args.steps, args.prompt_len + args.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "w4a16 (fp16 products, double accumulation)", "data": "synthetic",
-            "config": {"workload": "full 36-layer Qwen3-8B-shape W4A16 model, batch-1 decode steps at context >= 128, seeded random weights",
-                       "note": "CPU oracle port; the reference itself has no CPU path and does not build"},
+            "config": {"workload": workload_string(args),
+                       "note": "CPU oracle port on the host cores; the reference itself has no CPU path and does not build"},
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
                              "sample": f"{args.steps} decode-token passes, KV rows pre-filled to context {args.prompt_len + args.warmup}"},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -208,22 +237,67 @@ def roofline_gemv(pkg, torch, M, K, n_mats, reps):
     return us, n, us_pdl
 
 
-def reference_method_token_us(torch, n_layers_cycled=6, reps=6):
-    """The reference's decode method, contractions only: cuBLAS at n = 1 on fp16 copies of wqkv, wo, w1, w2 of every
-    layer and of unembed (Inference.cu:1052-1273; 13.3 GB of fp16 per token instead of 3.3 GB packed).  Random fp16
-    matrices of those shapes, several distinct layers cycled so that nothing stays in L2.  No norms, attention, copies
-    or host waits: a lower bound on the time per token of the dequantise-then-cuBLAS design on this GPU."""
+def reference_method_token_us(torch, orc, weight_dir, n_layers_cycled=6, reps=6):
+    """The reference's decode method on this GPU, contractions only (Inference.cu:1052-1273): its own dequantAwqKernel
+    expands the packed matrices of several layers and of unembed to fp16 once (Inference.cu:908-1008), then its own
+    cublasGemmEx call (m = out_dim, n = 1, k = in_dim on that buffer) runs per matrix, layers cycled so that nothing
+    stays in L2 (13.3 GB of fp16 per token instead of 3.3 GB packed).  Both come from oracle/_ref (the reference's
+    kernels compiled from its checkout); where that library is absent, torch.matmul on random fp16 matrices of the same
+    shapes stands in and the result says so.  No norms, attention, copies or host waits: a lower bound on the time per
+    token of the dequantise-then-cuBLAS design."""
+    import ctypes as C
+    import numpy as np
     dev = torch.device("cuda:0")
-    shapes = [(4096, 12288), (4096, 4096), (4096, 12288), (12288, 4096)]          # [K][M] as the library reads them
-    layers = [[torch.randn(k, m, device=dev, dtype=torch.float16) for k, m in shapes] for _ in range(n_layers_cycled)]
-    unemb = torch.randn(4096, 151936, device=dev, dtype=torch.float16)
-    xs = {4096: torch.randn(1, 4096, device=dev, dtype=torch.float16), 12288: torch.randn(1, 12288, device=dev, dtype=torch.float16)}
+    shapes = [("wqkv", "bqkv", 12288, 4096), ("wo", "wo", 4096, 4096), ("w1", "w1", 12288, 4096), ("w2", "w2", 4096, 12288)]
+    ref_so = os.path.join(ROOT, "oracle", "_ref", "libref_kernels.so")
+    ref = None
+    if os.path.exists(ref_so) and weight_dir is not None:
+        ref = C.CDLL(ref_so)
+        vp = C.c_void_p
+        ref.ref_dequant.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int, vp]
+        ref.ref_gemv_cublas.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]
+
+    def load(name, count, dtype):
+        return torch.from_numpy(np.fromfile(os.path.join(weight_dir, name), dtype=dtype, count=count)).to(dev)
+
+    def expand(stem, sz_stem, M, K, wrap):
+        """fp16 buffer [M*K] as the reference's dequantAwqKernel writes it (rows = out_dim, cols = in_dim)."""
+        packed = load(stem + ".bin", M * K // 2, np.uint8)
+        n = M // 128
+        sc, zp = load(sz_stem + "_scale.bin", n, np.float16), load(sz_stem + "_zp.bin", n, np.float16)
+        if wrap and K // 128 > n:   # the reference indexes past its arrays here: wrap-extended copies, as the engine reads them
+            idx = torch.arange(K // 128, device=dev) % n
+            sc, zp = sc[idx].contiguous(), zp[idx].contiguous()
+        out = torch.empty(M * K, dtype=torch.float16, device=dev)
+        rc = ref.ref_dequant(packed.data_ptr(), sc.data_ptr(), zp.data_ptr(), out.data_ptr(), M, K, None)
+        assert rc == 0, rc
+        return out
+
+    if ref is not None:
+        layers = [[(expand(f"layer_{l}_{st}", f"layer_{l}_{sz}", M, K, True), M, K) for st, sz, M, K in shapes] for l in range(n_layers_cycled)]
+        unemb = (expand("unembed", "unembed", 151936, 4096, False), 151936, 4096)
+        how = "oracle/_ref: the reference's dequantAwqKernel once, then its cublasGemmEx call (CUBLAS_COMPUTE_16F) per matrix"
+    else:
+        layers = [[(torch.randn(M * K, device=dev, dtype=torch.float16), M, K) for _, _, M, K in shapes] for _ in range(n_layers_cycled)]
+        unemb = (torch.randn(151936 * 4096, device=dev, dtype=torch.float16), 151936, 4096)
+        how = "torch.matmul (cuBLAS) on random fp16 matrices of the reference's shapes (oracle/_ref not built)"
+    xs = {4096: torch.randn(4096, device=dev, dtype=torch.float16), 12288: torch.randn(12288, device=dev, dtype=torch.float16)}
+    ys = {4096: torch.empty(4096, device=dev, dtype=torch.float16), 12288: torch.empty(12288, device=dev, dtype=torch.float16),
+          151936: torch.empty(151936, device=dev, dtype=torch.float16)}
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def gemv(w, M, K):
+        if ref is not None:
+            rc = ref.ref_gemv_cublas(w.data_ptr(), xs[K].data_ptr(), ys[M].data_ptr(), M, K, 0, stream)
+            assert rc == 0, rc
+        else:
+            torch.matmul(xs[K].view(1, K), w.view(K, M))
 
     def one_round():
         for mats in layers:
-            for w in mats:
-                torch.matmul(xs[w.shape[0]], w)
-        torch.matmul(xs[4096], unemb)
+            for w, M, K in mats:
+                gemv(w, M, K)
+        gemv(*unemb)
 
     one_round()
     torch.cuda.synchronize()
@@ -232,17 +306,17 @@ def reference_method_token_us(torch, n_layers_cycled=6, reps=6):
     for _ in range(reps):
         e_l[0].record()
         for mats in layers:
-            for w in mats:
-                torch.matmul(xs[w.shape[0]], w)
+            for w, M, K in mats:
+                gemv(w, M, K)
         e_l[1].record()
-        torch.matmul(xs[4096], unemb)
+        gemv(*unemb)
         e_l[2].record()
         torch.cuda.synchronize()
         t_layers += e_l[0].elapsed_time(e_l[1])
         t_unemb += e_l[1].elapsed_time(e_l[2])
     per_layer_us = t_layers * 1e3 / (reps * n_layers_cycled)
     unemb_us = t_unemb * 1e3 / reps
-    return 36 * per_layer_us + unemb_us, per_layer_us, unemb_us
+    return 36 * per_layer_us + unemb_us, per_layer_us, unemb_us, how
 
 
 def pass_only(pkg, orc, args):
@@ -366,7 +440,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--weights", default=None, help="existing weight directory (default: generate into a temp dir)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length (128 is the benchmark configuration)")
+    ap.add_argument("--prompt-len", type=int, default=None,
+                    help="prompt length (default: 128 on one GPU, 512 on several: the baseline's two configurations)")
+    ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of --steps decode steps each (the median counts)")
+    ap.add_argument("--parallel", default="pp", choices=["pp", "tp"],
+                    help="several GPUs: layer pipeline (the reference's contract) or row-split of every matrix")
     ap.add_argument("--only-roofline", action="store_true", help="run only the dominant-kernel timing (small case for profilers)")
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)
@@ -381,6 +459,8 @@ def main():
     ap.add_argument("--gemm-rows", default="16,64,256,2048")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.prompt_len is None:
+        args.prompt_len = PROMPT_LEN if args.gpus == 1 else PROMPT_LEN_MULTI
     # Only the result line may reach stdout: libraries (NCCL's version banner, for one) print there too, so
     # file descriptor 1 is pointed at stderr for the run and the saved descriptor is used for the JSON lines.
     sys.stdout.flush()
@@ -433,7 +513,8 @@ def main():
     n_gpus = args.gpus
     if world > 1 and world != n_gpus:
         raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch one rank per GPU")
-    # weights: rank 0 writes the reference's .bin set once; every rank loads its own stage from it
+    tp = args.parallel == "tp" and n_gpus > 1
+    # weights: rank 0 writes the reference's .bin set once; every rank loads its own part from it
     wdir = args.weights or os.path.join(tempfile.gettempdir(), f"qw3_bench_weights_{os.environ.get('MASTER_PORT', 'single')}_{os.getppid() if world > 1 else os.getpid()}")
     made = False
     if rank == 0 and not os.path.exists(os.path.join(wdir, "unembed_zp.bin")):
@@ -441,120 +522,161 @@ def main():
         made = args.weights is None
     barrier()
     prompt = [int(t) for t in orc.gen_tokens(SEED, orc.TOKENS, args.prompt_len, 151936)]
-    max_pos = args.prompt_len + args.warmup + 2 * args.steps + 8
-    if world > 1:
+    K, W, R = args.steps, args.warmup, args.repeats
+    max_pos = args.prompt_len + W + (R + 2) * K + 8
+    if world > 1 and tp:
+        # one process per GPU, every matrix row-split over the GPUs; partial sums cross NVLink inside the pass kernel
+        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, world=world, rank=rank, tensor_parallel=1, device=[local] * 8)
+        pipeline.connect_all(inf, dist)
+    elif world > 1:
         # one process per GPU: this rank owns stage `rank`; hidden state and token id move by peer stores
         inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=world, world=world, rank=rank, device=list(range(world)))
         pipeline.connect_ring(inf, dist)
     else:
         inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)))
     barrier()
-    inf.generateResponse(prompt, args.warmup)              # prompt pass + W warm-up decode steps
+    ids_all = inf.generateResponse(prompt, W)              # prompt pass + W warm-up decode steps
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     barrier()
-    # device-timed: K decode steps, CUDA events inside the engine around this rank's decode loop
-    ids_dev = inf.decode_more(args.steps)
-    _, decode_ms = inf.last_timing()
-    launches = inf.last_launches()
-    barrier()
-    # end to end: the same K steps through the public API, host wall-clock, ids to host memory
+    # device-timed: R regions of K decode steps, CUDA events inside the engine around this rank's decode loop
+    region_ms, launches = [], 0
+    for _ in range(R):
+        ids_all += inf.decode_more(K)
+        region_ms.append(inf.last_timing()[1])
+        launches = inf.last_launches()
+        barrier()
+    # end to end: K more steps through the public API, host wall-clock, ids to host memory
     t0 = time.perf_counter()
-    ids_e2e = inf.decode_more(args.steps)
+    ids_all += inf.decode_more(K)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
-    prefill = None
-    if world == 1 and n_gpus == 1:   # prompt phase: the reference's token loop against the batched-row path
-        inf.generateResponse(prompt, 1)
-        loop_ms = inf.last_timing()[0]
+    if rank == 0:
+        clocks = sampler.stop()
+    # end to end including the prompt: generateResponse(prompt, K) from host ids to host ids (prompt in blocks of rows
+    # through the tensor-core contraction, as a serving caller would run it), and the reference's token loop beside it
+    gen = {}
+    try:
         inf.set_batched_prefill(True)
-        inf.generateResponse(prompt, 1)      # first use allocates the block buffers
-        inf.generateResponse(prompt, 1)
-        blk_ms = inf.last_timing()[0]
+        inf.generateResponse(prompt, 1)                    # first use allocates the block buffers
+        barrier()
+        t0 = time.perf_counter()
+        ids_gen = inf.generateResponse(prompt, K)
+        torch.cuda.synchronize()
+        gen["batched_s"] = time.perf_counter() - t0
+        gen["batched_prompt_ms"] = inf.last_timing()[0]
         inf.set_batched_prefill(False)
-        prefill = {"prompt_tokens": len(prompt), "token_loop_ms": loop_ms, "batched_ms": blk_ms,
-                   "batched_tokens_per_s": len(prompt) / (blk_ms * 1e-3),
-                   "note": "device time of the prompt phase of generateResponse; batched = tcgen05 W4A16 contraction over the block"}
-    if world > 1:   # prompt phase with one process per GPU: token loop through the mailboxes against blocks of rows
-        loop_ms = blk_ms = 0.0
-        ok = 1.0
-        try:   # an extra beside the timed region: a failure here must not cost the decode numbers above
-            inf.generateResponse(prompt, 1)
-            loop_ms = inf.last_timing()[0]
-            inf.set_batched_prefill(True)
-            inf.generateResponse(prompt, 1)
-            inf.generateResponse(prompt, 1)
-            blk_ms = inf.last_timing()[0]
-            inf.set_batched_prefill(False)
-        except Exception as exc:   # every device wait is bounded, so the other ranks come out as well
-            sys.stderr.write(f"rank {rank}: prompt-phase comparison failed: {exc}\n")
-            ok = 0.0
-        pt = torch.tensor([loop_ms, blk_ms, -ok], dtype=torch.float64, device=f"cuda:{local}")
-        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
-        if float(pt[2]) == -1.0:
-            prefill = {"prompt_tokens": len(prompt), "token_loop_ms": float(pt[0]), "batched_ms": float(pt[1]),
-                       "batched_tokens_per_s": len(prompt) / (float(pt[1]) * 1e-3),
-                       "note": "device time of the prompt phase, max over ranks; batched = blocks of rows handed from stage to stage"}
+        barrier()
+        if not tp:
+            t0 = time.perf_counter()
+            ids_loop = inf.generateResponse(prompt, K)
+            torch.cuda.synchronize()
+            gen["loop_s"] = time.perf_counter() - t0
+            gen["loop_prompt_ms"] = inf.last_timing()[0]
         else:
-            prefill = {"error": "the prompt-phase comparison failed on a rank (see stderr)"}
-    if world > 1:   # max over ranks of the device time and of the wall-clock; launches summed
-        t = torch.tensor([decode_ms, e2e_s], dtype=torch.float64, device=f"cuda:{local}")
+            ids_loop = ids_gen
+        gen["ids_gen"], gen["ids_loop"] = ids_gen, ids_loop
+    except Exception as exc:   # every device wait is bounded, so the other ranks come out as well
+        sys.stderr.write(f"rank {rank}: generate timing failed: {exc}\n")
+        gen = {"error": str(exc)}
+    barrier()
+    if world > 1:   # max over ranks of every time; launches summed; ids from the rank that samples
+        t = torch.tensor(region_ms + [e2e_s, gen.get("batched_s", -1.0), gen.get("loop_s", -1.0), gen.get("batched_prompt_ms", -1.0),
+                                      gen.get("loop_prompt_ms", -1.0), 1.0 if "error" in gen else 0.0], dtype=torch.float64, device=f"cuda:{local}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        decode_ms, e2e_s = float(t[0]), float(t[1])
+        region_ms = [float(v) for v in t[:R]]
+        e2e_s = float(t[R])
+        if float(t[R + 5]) > 0:
+            gen = {"error": gen.get("error", "failed on another rank")}
+        else:
+            gen.update(batched_s=float(t[R + 1]), loop_s=float(t[R + 2]), batched_prompt_ms=float(t[R + 3]), loop_prompt_ms=float(t[R + 4]))
         ln = torch.tensor([launches], dtype=torch.int64, device=f"cuda:{local}")
         dist.all_reduce(ln, op=dist.ReduceOp.SUM)
         launches = int(ln[0])
-        ids_dev = pipeline.broadcast_ids(ids_dev, args.steps, dist)
-        ids_e2e = pipeline.broadcast_ids(ids_e2e, args.steps, dist)
+        n_ids = W + (R + 1) * K
+        ids_all = pipeline.broadcast_ids(ids_all, n_ids, dist)
+        if "error" not in gen:
+            gen["ids_gen"] = pipeline.broadcast_ids(gen["ids_gen"], K, dist)
+            gen["ids_loop"] = pipeline.broadcast_ids(gen["ids_loop"], K, dist)
     inf.close()
     result = None
+    rc = 0
     if rank == 0:
-        clocks = sampler.stop()
-        ctx_mid = args.prompt_len + args.warmup + args.steps // 2
-        tps = args.steps / (decode_ms * 1e-3)
+        decode_ms = statistics.median(region_ms)
+        ctx_mid = args.prompt_len + W + (R // 2) * K + K // 2
+        tps = K / (decode_ms * 1e-3)
         peaks, peak_kind = measured_peaks()
+        # parity of everything this run generated against the oracle's golden ids
+        gname, gold = golden_ids(args.prompt_len)
+        check = {"golden": gname, "ids_checked": 0, "ids_match_golden": None, "first_mismatch": None}
+        if gold is not None:
+            seqs = [("decode", ids_all)]
+            if "error" not in gen:
+                seqs += [("generate_batched_prompt", gen["ids_gen"]), ("generate_token_loop", gen["ids_loop"])]
+            ok = True
+            for name, ids in seqs:
+                n = min(len(ids), len(gold))
+                check["ids_checked"] += n
+                for i in range(n):
+                    if ids[i] != gold[i]:
+                        ok = False
+                        check["first_mismatch"] = check["first_mismatch"] or {"sequence": name, "step": i, "got": ids[i], "want": gold[i]}
+                        break
+            check["ids_match_golden"] = ok
+            if not ok:
+                rc = 3   # a run whose ids differ from the oracle's is not a measurement
         # the stand-alone GEMV operator (what a caller of qw3_gemv_w4a16 gets), reported beside the pass kernel
-        M, K = 12288, 4096
-        us, n_launch, us_pdl = roofline_gemv(pkg, torch, M, K, args.roofline_mats, args.roofline_reps)
-        achieved = gemv_bytes(M, K) / (us * 1e-6) / 1e9
+        M, Kd = 12288, 4096
+        us, n_launch, us_pdl = roofline_gemv(pkg, torch, M, Kd, args.roofline_mats, args.roofline_reps)
+        achieved = gemv_bytes(M, Kd) / (us * 1e-6) / 1e9
         gemv_roof = {"bound": "hbm", "kernel": "gemv_w4a16_kernel (12288x4096, STORE epilogue)", "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "avg_launch_us": us, "avg_launch_us_with_pdl": us_pdl, "launches_timed": n_launch,
-                     "bytes_per_launch": gemv_bytes(M, K), "l2": "36 distinct matrices cycled (906 MB > 126 MB L2)",
+                     "bytes_per_launch": gemv_bytes(M, Kd), "l2": "36 distinct matrices cycled (906 MB > 126 MB L2)",
                      "ref_dequant_then_cublas_us": LAST_REF_GEMV_US}
-        ref_us, ref_layer_us, ref_unemb_us = reference_method_token_us(torch)
-        ref_method = {"what": "the reference's design on this GPU, contractions only: cuBLAS at n=1 on fp16 copies of the five "
-                              "matrices per layer and of unembed (13.3 GB per token); no norms, attention, copies or host waits",
-                      "us_per_token": ref_us, "us_per_layer": ref_layer_us, "unembed_us": ref_unemb_us,
+        ref_us, ref_layer_us, ref_unemb_us, ref_how = reference_method_token_us(torch, orc, wdir)
+        ref_method = {"what": "the reference's design on this GPU, contractions only: fp16 copies of the matrices of every layer and "
+                              "of unembed, one cuBLAS call at n = 1 each (13.3 GB per token); no norms, attention, copies or host waits",
+                      "how": ref_how, "us_per_token": ref_us, "us_per_layer": ref_layer_us, "unembed_us": ref_unemb_us,
                       "tokens_per_s_upper_bound": 1e6 / ref_us}
         decode_gbs = token_bytes(ctx_mid) * tps / 1e9
-        line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": decode_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        par = "pp1" if n_gpus == 1 else (f"tp{n_gpus} (one process per GPU, matrices row-split, partial sums over NVLink)" if tp
+                                         else f"pp{n_gpus}" + (" (one process per GPU, P2P hand-off)" if world > 1 else ""))
+        e2e_gen = None
+        if "error" not in gen:
+            e2e_gen = {"value": K / gen["batched_s"], "unit": "tokens/s", "h2d_bytes_per_call": 4 * len(prompt), "d2h_bytes_per_call": 4 * K,
+                       "wall_s": gen["batched_s"], "prompt_phase_ms": gen["batched_prompt_ms"],
+                       "note": f"host wall-clock of generateResponse(prompt of {len(prompt)} ids in host memory, {K} new ids back in host memory); "
+                               "prompt in blocks of rows through the tensor-core contraction",
+                       "token_loop": None if tp else {"value": K / gen["loop_s"], "wall_s": gen["loop_s"], "prompt_phase_ms": gen["loop_prompt_ms"],
+                                                      "note": "the same call with the reference's token-at-a-time prompt loop (the default flow)"}}
+        line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": n_gpus, "steps": K, "warmup": W,
+                "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "w4a16 (int4 weights, fp16 activations, fp32 accumulation)", "data": "synthetic",
-                "config": {"workload": "full 36-layer Qwen3-8B-shape W4A16 model (hidden 4096, 32 heads, inter 12288, vocab 151936), "
-                                       f"prompt {args.prompt_len} ids, batch-1 greedy decode steps at context {args.prompt_len + args.warmup}.."
-                                       f"{args.prompt_len + args.warmup + 2 * args.steps}, seeded random weights",
-                           "parallelism": f"pp{n_gpus}" + (" (one process per GPU, P2P hand-off)" if world > 1 else ""),
+                "config": {"workload": workload_string(args), "parallelism": par,
                            "l2": "3.3 GB of weights streamed per step (inputs larger than L2)"},
-                # dominant kernel of the timed region: decode_pass_kernel, one launch per token per stage.  Its launch
+                "timed_regions": {"repeats": R, "steps_each": K, "ms": region_ms, "median_ms": decode_ms,
+                                  "spread": (max(region_ms) - min(region_ms)) / decode_ms},
+                **check,
+                # dominant kernel of the timed region: the token-pass kernel, one launch per token per GPU.  Its launch
                 # duration is the CUDA-event time of a step (which also holds the 1-thread step_tail launch).
-                "roofline": {"bound": "hbm", "kernel": "decode_pass_kernel (36 layers + unembed + arg-max, one launch per token)",
+                "roofline": {"bound": "hbm", "kernel": "fused_pass_kernel (36 layers + unembed + arg-max, one launch per token)",
                              "achieved": decode_gbs, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind + " (burst copy)",
                              "unit": "GB/s", "frac": decode_gbs / peaks["hbm_gbs"],
                              "traffic": int(token_bytes(ctx_mid) * NCU_TRAFFIC_RATIO), "bytes_per_launch": token_bytes(ctx_mid),
-                             "avg_launch_us": decode_ms * 1e3 / args.steps,
-                             "traffic_note": "dram read+write of an ncu capture of a 6-layer pass (514.1 MB for 507.6 MB "
-                                             "algorithmic), scaled by bytes to the 36-layer launch",
-                             "note": "at batch 1 the stages of N GPUs run one after another: one GPU's bandwidth is in use at a time"},
+                             "avg_launch_us": decode_ms * 1e3 / K,
+                             "traffic_note": NCU_TRAFFIC_NOTE,
+                             "note": "N GPUs: value counts the whole job, achieved is the bytes of one token over the step time"},
                 "gemv_roofline": gemv_roof, "reference_method_gpu": ref_method,
-                "e2e": {"value": args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
+                "e2e": {"value": K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
                         "note": "host wall-clock of decode_more(K) through the C ABI; the sampled id feeds the next step on the device"},
-                "gpu_launches": int(launches), "clocks": clocks, "prefill": prefill,
-                "tokens_equal_between_runs": None if len(ids_dev) != len(ids_e2e) else True}
+                "e2e_generate": e2e_gen,
+                "gpu_launches": int(launches), "clocks": clocks}
         if not args.no_cpu_baseline and n_gpus == 1:
             n_cpu = 8
+            orc.set_num_threads(os.cpu_count() or 1)
             cpu_tps, _ = cpu_decode_tokens_per_s(orc, wdir, n_cpu, args.prompt_len)
             line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
                                     "sample": f"{n_cpu} decode-token passes of the same model on the host, KV rows pre-filled to context {args.prompt_len}"}
@@ -572,7 +694,12 @@ def main():
             shutil.rmtree(wdir, ignore_errors=True)
         print(json.dumps(result))
     if world > 1:
+        code = torch.tensor([rc], dtype=torch.int32, device=f"cuda:{local}")
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        rc = int(code[0])
         dist.destroy_process_group()
+    if rc:
+        raise SystemExit(rc)
 
 
 if __name__ == "__main__":

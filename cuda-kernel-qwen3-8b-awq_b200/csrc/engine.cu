@@ -1126,6 +1126,21 @@ int qw3_stage_hidden(qw3_handle e, int32_t stage, void* host_hidden) {
 int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries) {
     QW3_REQUIRE(e && out && n_entries && stage >= 0 && stage < (int)e->st.size(), "qw3_debug_trace: bad argument");
     Stage& s = e->st[stage];
+    if (s.fused) {   // fused pass, tracing build: the raw stamps [grid][n_layers][16]; *n_entries = values copied
+        size_t bytes = 0;
+        const void* tr = fused_trace(s.fused, &bytes);
+        if (!tr) {
+            set_last_error("qw3_debug_trace: the library was not built with -DQW3_TRACE");
+            return QW3_ERR_STATE;
+        }
+        QW3_CUDA(cudaSetDevice(s.device));
+        QW3_CUDA(cudaStreamSynchronize(s.stream));
+        const size_t want = (size_t)(max_entries < 0 ? -max_entries : max_entries) * 8;
+        const size_t m = want < bytes ? want : bytes;
+        QW3_CUDA(cudaMemcpy(out, tr, m, cudaMemcpyDeviceToHost));
+        *n_entries = (int32_t)(m / 8);
+        return QW3_OK;
+    }
     if (!s.d_trace) {
         set_last_error("qw3_debug_trace: create the handle with QW3_TRACE set in the environment and persistent = 1");
         return QW3_ERR_STATE;

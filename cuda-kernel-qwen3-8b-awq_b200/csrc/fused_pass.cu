@@ -38,20 +38,25 @@
 namespace qw3 {
 
 constexpr int FP_NT = F_NW * 32;          // threads per CTA
-constexpr int FP_SLOTS = 2;               // ring slots per warp
+#ifndef QW3_FP_SLOTS
+#define QW3_FP_SLOTS 2
+#endif
+constexpr int FP_SLOTS = QW3_FP_SLOTS;    // ring units in flight
 constexpr int FP_MAX_H = 4096;            // largest hidden size (activation vectors kept in shared memory)
 constexpr int FP_OBUF = 4608;             // floats: GEMV outputs / partial-sum staging / 32 attention states of 132
 constexpr int FP_MAX_SEG = 4 * 64 + 24;   // weight segments of one pass (4 per layer + unembedding rounds)
 constexpr int FP_MAX_N1 = 512;            // largest number of W1 outputs per CTA
 constexpr int FP_MAX_RS = 256;            // largest number of hidden elements a CTA owns
 constexpr int FP_ATT_STRIDE = 132;
+constexpr int FP_MAX_GROUPS = 128;        // largest number of scale / zero-point entries of a layer matrix
 constexpr int FP_QKV = 384;               // q, k, v of one head
 
-constexpr size_t FP_OFF_OBUF = (size_t)F_NW * FP_SLOTS * F_UNIT;
+constexpr size_t FP_OFF_OBUF = (size_t)FP_SLOTS * F_NW * F_UNIT;
 constexpr size_t FP_OFF_HV = FP_OFF_OBUF + (size_t)FP_OBUF * 4;
 constexpr size_t FP_OFF_XS = FP_OFF_HV + (size_t)FP_MAX_H * 2;
 constexpr size_t FP_OFF_SEG = FP_OFF_XS + (size_t)FP_MAX_H * 2;
-constexpr size_t FP_OFF_MISC = FP_OFF_SEG + (size_t)FP_MAX_SEG * 16;
+constexpr size_t FP_OFF_LSZ = FP_OFF_SEG + (size_t)FP_MAX_SEG * 16;          // [2][4][FP_MAX_GROUPS] (scale, zero point) as floats
+constexpr size_t FP_OFF_MISC = FP_OFF_LSZ + (size_t)2 * 4 * FP_MAX_GROUPS * 8;
 constexpr size_t FP_MISC_BYTES = 8192;
 constexpr size_t FP_SMEM_BYTES = FP_OFF_MISC + FP_MISC_BYTES;
 
@@ -64,8 +69,15 @@ struct FLayerDesc {
     __half* vc;
 };
 
+// Descriptor plus the scale / zero-point entries of the four matrices, one flat block per layer (built on the device
+// at load time), so that a pass fetches it with single-level loads.
+struct FLayerConst {
+    FLayerDesc d;
+    uint32_t sz[4][FP_MAX_GROUPS];   // (scale, zero point) as two halves
+};
+
 struct FusedParams {
-    const FLayerDesc* layers;
+    const FLayerConst* layers;
     int n_layers;
     FusedGeom g;
     FGemvPlan plan[F_NOPS];
@@ -93,7 +105,21 @@ struct FusedParams {
     unsigned long long* hid[QW3_MAX_STAGES];   // [2][H / 2]                   gathered hidden state, two buffers
     unsigned long long* xarg[QW3_MAX_STAGES];  // [n_ranks * grid][2]          arg-max candidates
     int* err;
+    unsigned long long* trace;    // tracing builds (-DQW3_TRACE): [grid][n_layers][16] global-timer stamps of thread 0
 };
+
+#ifdef QW3_TRACE
+#define FP_STAMP(li, k)                                                                              \
+    do {                                                                                             \
+        if (threadIdx.x == 0 && p.trace != nullptr) {                                                \
+            unsigned long long t__;                                                                  \
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t__));                                   \
+            p.trace[((size_t)blockIdx.x * p.n_layers + (li)) * 16 + (k)] = t__;                       \
+        }                                                                                            \
+    } while (0)
+#else
+#define FP_STAMP(li, k) do { } while (0)
+#endif
 
 // ---- tagged words ------------------------------------------------------------------------------------------------
 template <bool SYS>
@@ -135,6 +161,8 @@ struct FCtx {
     __half* hv;
     __half* xs;
     int4* seg;          // {base lo, base hi, warp_bytes, 0} per weight segment of this CTA
+    float2* lsz;        // [2][4][FP_MAX_GROUPS] (scale, zero point) of the layer's four matrices, two layers (current / next)
+    FLayerDesc* ldesc;  // [2] descriptor of the current / next layer
     __half* qkv_s;      // [384] q, k, v of this CTA's head (after RoPE)
     __half* ctx_s;      // [128]
     __half* g_s;        // [n1] GeLU outputs
@@ -146,7 +174,9 @@ struct FCtx {
     float* argv;        // [16]
     int* argi;          // [16]
     int* s_dead;
-    uint32_t bars;      // shared address of the ring barriers [F_NW][FP_SLOTS]
+    int* ring_cnt;      // [FP_SLOTS] warps that have consumed their piece of the unit in the slot
+    int* ring_issued;   // units requested so far (only the issuing thread of the moment writes it)
+    uint32_t bars;      // shared address of the ring barriers [FP_SLOTS]
     uint32_t zero_addr; // shared address of 32 zero bytes
     uint32_t tagbase;
     int pos;
@@ -180,10 +210,15 @@ __device__ __forceinline__ void poll_batch(const FusedParams& p, const FCtx& cx,
 }
 
 // ---- weight ring -----------------------------------------------------------------------------------------------------
+// The CTA's weight stream is a sequence of units; a unit holds one piece of up to F_UNIT bytes for each of the 16
+// warps, contiguous in global memory ([warp][piece]), and is fetched by ONE bulk copy (32 KB): bulk copies cost a
+// fixed ~140 ns each on this part whatever their size, so one copy per warp and piece would cap an SM at ~15 GB/s.
+// FP_SLOTS units are in flight.  Every warp consumes its piece of a unit, then counts itself off on the slot; the
+// last warp to do so issues the copy of the unit FP_SLOTS places ahead into that slot.  All warps walk the same unit
+// sequence, so each keeps the cursor in its own registers and no shared producer state exists.
 struct WarpRing {
     int uc;        // units consumed by this warp so far
-    int pc;        // units requested so far
-    int pseg, pu;  // next unit to request: segment and unit within it
+    int pseg, pu;  // unit FP_SLOTS places ahead of uc: segment and unit within it (pseg == n_seg: past the end)
     uint64_t policy;
 };
 
@@ -193,127 +228,197 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
 }
 
-// Requests this warp's next unit into the slot it has just freed (slot = pc mod FP_SLOTS).  After a wait has given up
-// nothing more is requested, so that no copy is in flight when the CTA exits.
-__device__ __forceinline__ void ring_request(WarpRing& r, const FCtx& cx) {
-    const int warp = threadIdx.x >> 5;
-    if (*cx.s_dead != 0) return;
+// Moves the cursor to the next unit this CTA has (segments it takes no part in have no bytes).  Returns false past the end.
+__device__ __forceinline__ bool ring_cursor_valid(WarpRing& r, const FCtx& cx) {
     while (r.pseg < cx.n_seg) {
-        const int4 sg = cx.seg[r.pseg];
-        if (r.pu * F_UNIT < sg.z) {
-            if ((threadIdx.x & 31) == 0) {
-                const uint8_t* base = reinterpret_cast<const uint8_t*>(((unsigned long long)(uint32_t)sg.y << 32) | (uint32_t)sg.x);
-                const int bytes = min(F_UNIT, sg.z - r.pu * F_UNIT);
-                const int slot = r.pc % FP_SLOTS;
-                const uint32_t bar = cx.bars + 8 * (warp * FP_SLOTS + slot);
-                // the slot was read with ordinary loads: order them before the bulk write
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_expect_tx(bar, bytes);
-                bulk_load(smem_u32(cx.ring) + (warp * FP_SLOTS + slot) * F_UNIT, base + (size_t)warp * sg.z + (size_t)r.pu * F_UNIT,
-                          bytes, bar, r.policy);
-            }
-            ++r.pu;
-            ++r.pc;
-            return;
-        }
+        if (r.pu * F_UNIT < cx.seg[r.pseg].z) return true;
         ++r.pseg;
         r.pu = 0;
     }
+    return false;
+}
+// Issues the bulk copy of the unit under the cursor into `slot` (one thread calls this) and advances nothing.
+__device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, const int slot) {
+    const int4 sg = cx.seg[r.pseg];
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(((unsigned long long)(uint32_t)sg.y << 32) | (uint32_t)sg.x);
+    const int piece = min(F_UNIT, sg.z - r.pu * F_UNIT);
+    const uint32_t bar = cx.bars + 8 * slot;
+    // The slot was read with ordinary loads whose values have all been consumed (every warp counted itself off after
+    // its last MMA on the piece), so the bulk write cannot overtake them; no proxy fence is needed for this
+    // read-then-overwrite order, and one here would wait for the copies still in flight into the other slots.
+#ifdef QW3_FP_FENCE
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
+    *cx.ring_issued += 1;
+    mbar_expect_tx(bar, F_NW * piece);
+    bulk_load(smem_u32(cx.ring) + slot * (F_NW * F_UNIT), base + (size_t)r.pu * (F_NW * F_UNIT), F_NW * piece, bar, r.policy);
 }
 
-// Shared address of the unit this warp consumes next, once it has landed (bounded wait).
-__device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FusedParams& p, const FCtx& cx) {
+// Shared address of this warp's piece (of `piece` bytes) of the unit it consumes next, once the unit has landed.
+__device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FusedParams& p, const FCtx& cx, const int piece) {
     const int warp = threadIdx.x >> 5, slot = r.uc % FP_SLOTS;
-    const uint32_t bar = cx.bars + 8 * (warp * FP_SLOTS + slot);
-    if (r.uc < r.pc && !mbar_wait(bar, (r.uc / FP_SLOTS) & 1)) {
-        if ((threadIdx.x & 31) == 0) fail(p, cx, 0x10000 | (r.uc & 0xffff));   // a weight unit never arrived
+    uint32_t addr = smem_u32(cx.ring) + slot * (F_NW * F_UNIT) + warp * piece;
+#if !defined(QW3_FP_NOLOAD) && !defined(QW3_FP_NOWAIT)
+    // One lane polls the barrier (barrier operations of a CTA are served one at a time: 512 threads polling cost more
+    // than the piece's arithmetic); the warp barrier hands the observation, and the memory order it implies, to the others.
+#ifndef QW3_FP_ALLWAIT
+    if ((threadIdx.x & 31) == 0)
+#endif
+    {
+        if (*cx.s_dead == 0 && !mbar_wait(cx.bars + 8 * slot, (r.uc / FP_SLOTS) & 1)) {
+            if ((threadIdx.x & 31) == 0) fail(p, cx, 0x10000 | (r.uc & 0xffff));   // a weight unit never arrived
+        }
     }
-    return smem_u32(cx.ring) + (warp * FP_SLOTS + slot) * F_UNIT;
+    __syncwarp();
+#endif
+    asm volatile("" : "+r"(addr));   // loads from the unit use this value: none is scheduled before the wait
+    return addr;
 }
+// This warp is done with its piece of unit uc: the last of the 16 warps refills the slot.  After a wait has given up
+// nothing more is requested.
 __device__ __forceinline__ void ring_release(WarpRing& r, const FCtx& cx) {
     __syncwarp();
-    ring_request(r, cx);
+    const int slot = r.uc % FP_SLOTS;
+    const bool more = ring_cursor_valid(r, cx);
+#ifndef QW3_FP_NOLOAD
+    if ((threadIdx.x & 31) == 0) {
+        uint32_t old;
+        asm volatile("atom.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(cx.ring_cnt + slot)) : "memory");
+        if (old == F_NW - 1) {
+            cx.ring_cnt[slot] = 0;
+            if (more && *cx.s_dead == 0) ring_issue(r, cx, slot);
+        }
+    }
+#endif
+    if (more) ++r.pu;
     ++r.uc;
 }
 
+// Shared-memory loads of the weight stream and of the B fragments.  Not volatile: the compiler may schedule them
+// among the MMAs; the address they use is made to depend on the barrier wait (ring_wait), so none moves above it.
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
     uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
-
-// One k-step: the word's eight nibbles as the A fragment (subnormal fp16: bits 0-3 -> q * 2^-24, bits 4-7 -> q * 2^-20).
-__device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0, uint32_t b1) {
-    const uint32_t u = w >> 8;
-    mma_16816(d, w & 0x000f000fu, w & 0x00f000f0u, u & 0x000f000fu, u & 0x00f000f0u, b0, b1);
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-constexpr float FP_MULT_LO = 16777216.0f;   // 2^24: rows g of a tile
-constexpr float FP_MULT_HI = 1048576.0f;    // 2^20: rows g + 8
+
+#ifdef QW3_FP_A_OFFSET
+// Variant kept for comparison: normal fp16 A values 1024 + q (bits 0-3) and 64 + q (bits 4-7); the epilogues then
+// subtract offset * sum(x) together with the zero point.
+constexpr uint32_t FP_OR_LO = 0x64006400u, FP_OR_HI = 0x54005400u;
+constexpr float FP_MULT_LO = 1.0f, FP_MULT_HI = 1.0f, FP_OFF_LO = 1024.0f, FP_OFF_HI = 64.0f;
+#else
+// The word's nibbles as subnormal fp16: bits 0-3 -> q * 2^-24 (rows g of a tile), bits 4-7 -> q * 2^-20 (rows g + 8).
+constexpr uint32_t FP_OR_LO = 0u, FP_OR_HI = 0u;
+constexpr float FP_MULT_LO = 16777216.0f, FP_MULT_HI = 1048576.0f, FP_OFF_LO = 0.0f, FP_OFF_HI = 0.0f;
+#endif
+// Offset the A values of output row `row16` (0..15 within its tile) carry (0 with subnormal A values).
+__device__ __forceinline__ float a_offset(int row16) { return (row16 & 8) ? FP_OFF_HI : FP_OFF_LO; }
+
+// One k-step: the word's eight nibbles as the A fragment.
+__device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0, uint32_t b1) {
+#ifdef QW3_FP_NOCOMPUTE
+    d[0] += __uint_as_float(w & b0 & b1);   // timing experiment: the weights only stream through (results are meaningless)
+    return;
+#endif
+    const uint32_t u = w >> 8;
+    mma_f16(d, lop3_and_or(w, 0x000f000fu, FP_OR_LO), lop3_and_or(w, 0x00f000f0u, FP_OR_HI), lop3_and_or(u, 0x000f000fu, FP_OR_LO),
+            lop3_and_or(u, 0x00f000f0u, FP_OR_HI), b0, b1);
+}
 
 // This warp's stream of one operator: nb blocks of TB tiles, each over nq groups of four k-steps (+ a half group when
 // rem == 2).  xs_addr: shared address of the fp16 activations of the warp's k-share.  dst[(block * TB + i) * 16 + row]
-// receives sum_j q[row][j] * x[j] of tile i of the block.
+// receives sum_j q[row][j] * x[j] of tile i of the block.  Every tile has two accumulators (even / odd k-steps), and
+// the k-steps of a group are issued tile after tile, so 2 * TB independent MMA chains are in flight.
 template <int TB>
-__device__ __noinline__ void gemv_core(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int nb, const int nq,
+__device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int nb, const int nq,
                                        const int rem, const int warp_bytes, const uint32_t xs_addr, float* dst) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     int left = warp_bytes, ubytes = 0, uoff = 0;
     uint32_t ubase = 0;
+#ifdef QW3_TRACE_UNITS
+    long long pr_rel = 0, pr_wait = 0, pr_units = 0;
+    const long long pr_t0 = clock64();
+#define FP_PROF(acc, stmt) do { const long long c0__ = clock64(); stmt; acc += clock64() - c0__; } while (0)
+#else
+#define FP_PROF(acc, stmt) stmt
+#endif
     auto item = [&](const int sz) -> uint32_t {
         if (uoff == ubytes) {
-            if (ubytes != 0) ring_release(ring, cx);
+            if (ubytes != 0) FP_PROF(pr_rel, ring_release(ring, cx));
             ubytes = min(F_UNIT, left);
             left -= ubytes;
-            ubase = ring_wait(ring, p, cx);
+            FP_PROF(pr_wait, ubase = ring_wait(ring, p, cx, ubytes));
             uoff = 0;
+#ifdef QW3_TRACE_UNITS
+            ++pr_units;
+#endif
         }
         const uint32_t a = ubase + uoff;
         uoff += sz;
         return a;
     };
+    constexpr int NA = TB <= 2 ? 2 : 1;   // accumulators per tile: at least three independent chains in flight
     for (int b = 0; b < nb; ++b) {
-        float acc[TB][4];
+        float acc[TB][NA][4];
 #pragma unroll
         for (int i = 0; i < TB; ++i)
 #pragma unroll
-            for (int d = 0; d < 4; ++d) acc[i][d] = 0.0f;
+            for (int h = 0; h < NA; ++h)
+#pragma unroll
+                for (int d = 0; d < 4; ++d) acc[i][h][d] = 0.0f;
         for (int q = 0; q < nq; ++q) {
             // B fragment of the group: lanes 0-3 (column 0) hold the activations, the other columns are zero
             const uint32_t ba = g == 0 ? xs_addr + q * 128 + t * 32 : cx.zero_addr;
             const uint4 b03 = lds128(ba), b47 = lds128(ba + 16);
+            uint4 w[TB];
 #pragma unroll
-            for (int i = 0; i < TB; ++i) {
-                const uint4 w = lds128(item(512) + lane * 16);
-                mma_word(acc[i], w.x, b03.x, b03.y);
-                mma_word(acc[i], w.y, b03.z, b03.w);
-                mma_word(acc[i], w.z, b47.x, b47.y);
-                mma_word(acc[i], w.w, b47.z, b47.w);
-            }
+            for (int i = 0; i < TB; ++i) w[i] = lds128(item(512) + lane * 16);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].z, b47.x, b47.y);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].w, b47.z, b47.w);
         }
         if (rem == 2) {
             const uint32_t ba = g == 0 ? xs_addr + nq * 128 + t * 16 : cx.zero_addr;
             const uint4 b03 = lds128(ba);
+            uint2 w[TB];
 #pragma unroll
-            for (int i = 0; i < TB; ++i) {
-                const uint2 w = lds64(item(256) + lane * 8);
-                mma_word(acc[i], w.x, b03.x, b03.y);
-                mma_word(acc[i], w.y, b03.z, b03.w);
-            }
+            for (int i = 0; i < TB; ++i) w[i] = lds64(item(256) + lane * 8);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
+#pragma unroll
+            for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
         }
         if (t == 0) {
 #pragma unroll
             for (int i = 0; i < TB; ++i) {
-                dst[(b * TB + i) * 16 + g] = acc[i][0] * FP_MULT_LO;
-                dst[(b * TB + i) * 16 + g + 8] = acc[i][2] * FP_MULT_HI;
+                dst[(b * TB + i) * 16 + g] = (NA == 2 ? acc[i][0][0] + acc[i][NA - 1][0] : acc[i][0][0]) * FP_MULT_LO;
+                dst[(b * TB + i) * 16 + g + 8] = (NA == 2 ? acc[i][0][2] + acc[i][NA - 1][2] : acc[i][0][2]) * FP_MULT_HI;
             }
         }
     }
-    if (ubytes != 0) ring_release(ring, cx);
+    if (ubytes != 0) FP_PROF(pr_rel, ring_release(ring, cx));
+#ifdef QW3_TRACE_UNITS
+    if (lane == 0 && p.trace != nullptr && blockIdx.x < 2) {   // per-warp cycle counts of CTAs 0 and 1, summed over the pass
+        unsigned long long* pf = p.trace + (size_t)gridDim.x * p.n_layers * 16 + ((size_t)blockIdx.x * F_NW + (threadIdx.x >> 5)) * 4;
+        pf[0] += pr_rel; pf[1] += pr_wait; pf[2] += clock64() - pr_t0; pf[3] += pr_units;
+    }
+#endif
 }
 
 // Runs this warp's share of an operator: warp (a, bk) of the plan; sums land in obuf[bk][tile * 16 + row].
@@ -339,11 +444,34 @@ __device__ __forceinline__ float sum_k_shares(const FCtx& cx, const FGemvPlan& p
 
 // Scale and zero point of output `o` of a matrix whose groups do not depend on the input index:
 // group = ((o / 128) mod (in_dim / 128)) mod entries  (dequantAwqKernel's c / 128 with the wrapped index, Inference.cu:90).
-__device__ __forceinline__ void group_consts(const __half* scale, const __half* zp, long long o, int kb, int n_alloc, float& s,
-                                             float& z) {
+__device__ __forceinline__ void group_consts(const float2* table, long long o, int kb, int n_alloc, float& s, float& z) {
     const int g = (int)((o >> 7) % kb) % n_alloc;
-    s = __half2float(scale[g]);
-    z = __half2float(zp[g]);
+    const float2 v = table[g];
+    s = v.x;
+    z = v.y;
+}
+
+// Scale / zero-point tables and descriptor of a layer: requested from global memory a whole layer before they are
+// needed (the values sit in registers meanwhile), so that no epilogue waits for a global load.
+struct LayerPrefetch {
+    uint32_t sz;                 // threads 0 .. 4 * FP_MAX_GROUPS - 1: (scale, zp) bits of entry tid % FP_MAX_GROUPS of matrix tid / FP_MAX_GROUPS
+    unsigned long long word;     // threads 0 .. sizeof(FLayerDesc) / 8 - 1: one word of the descriptor
+};
+__device__ __forceinline__ void layer_request(const FusedParams& p, int li, LayerPrefetch& lp) {
+    const int tid = threadIdx.x;
+    lp.sz = 0u;
+    lp.word = 0ull;
+    if (li >= p.n_layers) return;
+    const FLayerConst& L = p.layers[li];
+    static_assert(4 * FP_MAX_GROUPS == FP_NT && sizeof(FLayerDesc) % 8 == 0 && sizeof(FLayerDesc) / 8 <= FP_NT, "one entry per thread");
+    lp.sz = __ldg(&L.sz[0][0] + tid);
+    if (tid < (int)(sizeof(FLayerDesc) / 8)) lp.word = __ldg(reinterpret_cast<const unsigned long long*>(&L.d) + tid);
+}
+__device__ __forceinline__ void layer_commit(const FCtx& cx, int buf, const LayerPrefetch& lp) {
+    const int tid = threadIdx.x;
+    cx.lsz[buf * 4 * FP_MAX_GROUPS + tid] = make_float2(__half2float(__ushort_as_half((unsigned short)(lp.sz & 0xffffu))),
+                                                        __half2float(__ushort_as_half((unsigned short)(lp.sz >> 16))));
+    if (tid < (int)(sizeof(FLayerDesc) / 8)) reinterpret_cast<unsigned long long*>(cx.ldesc + buf)[tid] = lp.word;
 }
 
 __device__ __forceinline__ float block_sum_f(const FCtx& cx, float v) {   // all threads call; fixed order
@@ -468,7 +596,10 @@ template <bool SYS>
 __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int li) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, c = blockIdx.x;
     const FusedGeom& G = p.g;
-    const FLayerDesc& L = p.layers[li];
+    const FLayerDesc& L = cx.ldesc[li & 1];
+    const float2* const lsz = cx.lsz + (li & 1) * 4 * FP_MAX_GROUPS;
+    LayerPrefetch lp;
+    layer_request(p, li + 1, lp);   // committed at the end of this layer
     const int H = G.H, gs = G.gs, rs = G.rs, n1 = G.n1;
     const int h_l = c / gs, r = c % gs, hglob = G.rank * G.heads_local + h_l, cglob = G.rank * G.n_act + c;
     const int hs = H / gs;
@@ -479,18 +610,21 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
 
     // ---- RMSNorm + this CTA's K-slice of Wqkv for its head (Inference.cu:1036-1065) -----------------------------------
     float x_full, x_slice;
+    FP_STAMP(li, 0);
     gather_norm<SYS>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, L.gamma, cx.xs, r, hs, x_full, x_slice);
+    FP_STAMP(li, 1);
     float sc = 0.0f, zp = 0.0f;
     if (tid < FP_QKV) {
         const int tile = tid >> 4, row = tid & 15;
         const long long o = (long long)(tile >> 3) * H + hglob * 128 + (tile & 7) * 16 + row;
-        group_consts(L.scale[F_QKV], L.zp[F_QKV], o, H >> 7, p.n_alloc[F_QKV], sc, zp);
+        group_consts(lsz + F_QKV * FP_MAX_GROUPS, o, H >> 7, p.n_alloc[F_QKV], sc, zp);
     }
     run_gemv(p, cx, ring, p.plan[F_QKV], cx.xs + r * hs);
     __syncthreads();
+    FP_STAMP(li, 2);
     if (tid < FP_QKV) {
         const float S = sum_k_shares(cx, p.plan[F_QKV], tid);
-        stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(sc * (S - zp * x_slice), t0));
+        stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(sc * (S - (zp + a_offset(tid & 15)) * x_slice), t0));
     }
     // ---- attention: cache rows of earlier positions are requested before q is known -----------------------------------
     const int len = pos + 1, chunk = (len + gs - 1) / gs;
@@ -537,6 +671,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         if (r == 0 && sec > 0) (sec == 1 ? L.kc : L.vc)[((size_t)hglob * p.max_pos + pos) * 128 + d] = me;   // Inference.cu:1094-1103
     }
     __syncthreads();
+    FP_STAMP(li, 3);
     // ---- attention over positions [p0, p1) (attentionKernel, Inference.cu:182-266, intended math) -----------------------
     {
         float qf[8];
@@ -619,6 +754,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
                 O += st[gq * FP_ATT_STRIDE + tid] * w;
             }
         }
+        FP_STAMP(li, 4);
         if (gs > 1) {
             // group exchange: every CTA of the head stores its state and merges all gs of them in CTA order
             if (tid < 128) stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + tid, tagged_f(O, t0 + 1));
@@ -659,17 +795,20 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
             cf = __half2float(ch);
         }
         const float x_o = block_sum_f(cx, cf);   // its barriers also publish ctx_s and free st
+        FP_STAMP(li, 5);
 
         // ---- Wo restricted to the head's 128 inputs, this CTA's share of the outputs (Inference.cu:1122-1141) ----------
         const FGemvPlan& plo = p.plan[F_WO];
         run_gemv(p, cx, ring, plo, cx.ctx_s);
         __syncthreads();
+        FP_STAMP(li, 6);
         const int n_out = plo.n_mt * 16;   // = hs
         for (int i0 = 2 * tid; i0 < n_out; i0 += 2 * FP_NT) {
             const long long o = (long long)r * hs + i0;
             float s2, z2;
-            group_consts(L.scale[F_WO], L.zp[F_WO], o, H >> 7, p.n_alloc[F_WO], s2, z2);
-            const float y0 = s2 * (sum_k_shares(cx, plo, i0) - z2 * x_o), y1 = s2 * (sum_k_shares(cx, plo, i0 + 1) - z2 * x_o);
+            group_consts(lsz + F_WO * FP_MAX_GROUPS, o, H >> 7, p.n_alloc[F_WO], s2, z2);
+            const float zo = z2 + a_offset(i0 & 15);   // i0 and i0 + 1 are rows of one half of a tile
+            const float y0 = s2 * (sum_k_shares(cx, plo, i0) - zo * x_o), y1 = s2 * (sum_k_shares(cx, plo, i0 + 1) - zo * x_o);
             const int ro = (int)(o / (H / G.n_ranks));   // rank that owns these two elements of the residual stream
             stt2<SYS>(p.xo[ro] + (size_t)(hglob * gs + r) * n_out + i0, tagged_f(y0, t0 + 2), tagged_f(y1, t0 + 2));
         }
@@ -688,6 +827,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
                 if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
         }
         __syncthreads();
+        FP_STAMP(li, 7);
         if (tid < rs) {
             float v = 0.0f;
             for (int hg = 0; hg < G.heads; ++hg) v += cx.obuf[hg * rs + tid];
@@ -695,32 +835,38 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         }
         __syncthreads();
         publish_hidden<SYS>(p, cx, 0, t0 + 3, cglob);
+        FP_STAMP(li, 8);
     }
 
     // ---- RMSNorm (same gamma) + this CTA's n1 outputs of W1 + GeLU (Inference.cu:1158-1197) ----------------------------------
     gather_norm<SYS>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, cx.xs, -1, H, x_full, x_slice);
-    if (tid < n1) group_consts(L.scale[F_W1], L.zp[F_W1], (long long)cglob * n1 + tid, H >> 7, p.n_alloc[F_W1], sc, zp);
+    FP_STAMP(li, 9);
+    if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cglob * n1 + tid, H >> 7, p.n_alloc[F_W1], sc, zp);
     run_gemv(p, cx, ring, p.plan[F_W1], cx.xs);
     __syncthreads();
     float gv = 0.0f;
     if (tid < n1) {
         const float S = sum_k_shares(cx, p.plan[F_W1], tid);
-        const __half ge = gelu_h(__float2half_rn(sc * (S - zp * x_full)));
+        const __half ge = gelu_h(__float2half_rn(sc * (S - (zp + a_offset(tid & 15)) * x_full)));
         cx.g_s[tid] = ge;
         gv = __half2float(ge);
     }
     const float x_g = block_sum_f(cx, gv);   // its barriers also publish g_s and free obuf
+    FP_STAMP(li, 10);
     // ---- W2 restricted to those n1 inputs, all outputs (Inference.cu:1198-1214) ------------------------------------------------
     run_gemv(p, cx, ring, p.plan[F_W2], cx.g_s);
     __syncthreads();
+    FP_STAMP(li, 11);
     for (int i0 = 2 * tid; i0 < H; i0 += 2 * FP_NT) {
         float s2, z2;
-        group_consts(L.scale[F_W2], L.zp[F_W2], i0, G.I >> 7, p.n_alloc[F_W2], s2, z2);
-        const float y0 = s2 * (cx.obuf[i0] - z2 * x_g), y1 = s2 * (cx.obuf[i0 + 1] - z2 * x_g);
+        group_consts(lsz + F_W2 * FP_MAX_GROUPS, i0, G.I >> 7, p.n_alloc[F_W2], s2, z2);
+        const float zo = z2 + a_offset(i0 & 15);
+        const float y0 = s2 * (cx.obuf[i0] - zo * x_g), y1 = s2 * (cx.obuf[i0 + 1] - zo * x_g);
         const int ro = i0 / (H / G.n_ranks);
         stt2<SYS>(p.x2[ro] + (size_t)cglob * H + i0, tagged_f(y0, t0 + 4), tagged_f(y1, t0 + 4));
     }
     __syncthreads();
+    FP_STAMP(li, 14);
     // ---- ordered sum over all contributors for this CTA's rs outputs + residual (Inference.cu:1217-1228) ----------------------
     const int ncontrib = G.n_ranks * G.n_act, nw = ncontrib * rs;
     {
@@ -733,6 +879,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
             if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
     }
     __syncthreads();
+    FP_STAMP(li, 12);
     const int parts = (ncontrib % 4 == 0 && nw + 4 * rs <= FP_OBUF && 4 * rs <= FP_NT) ? 4 : 1;
     if (tid < parts * rs) {
         const int part = tid / rs, idx = tid % rs, per = ncontrib / parts;
@@ -748,8 +895,51 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     }
     __syncthreads();
     publish_hidden<SYS>(p, cx, 1, t0 + 5, cglob);
+    layer_commit(cx, (li + 1) & 1, lp);
+    __syncthreads();
+    FP_STAMP(li, 13);
     (void)lane; (void)warp;
 }
+
+#ifdef QW3_FP_L2PF
+// CTAs without a part in the layers pull the weight streams into L2 half a layer ahead of their consumers, so that the
+// consumers' ring loads are L2 hits: the first half of a layer (Wqkv, Wo) once the layer before has published its
+// attention output, the second half (W1, W2) once the layer itself has started.
+template <bool SYS>
+__device__ __forceinline__ void l2_prefetch_pass(const FusedParams& p, const FCtx& cx) {
+    const int tid = threadIdx.x;
+    const FusedGeom& G = p.g;
+    const int n_idle = G.grid - G.n_act, ic = blockIdx.x - G.n_act;
+    constexpr int CH = 4096;
+    for (int li = 0; li < p.n_layers; ++li) {
+        for (int half = 0; half < 2; ++half) {
+            // half 0 of layer li waits for hid[0] of layer li - 1 (phase 3), half 1 for the hidden state layer li starts from
+            uint32_t tag = 0u;
+            const unsigned long long* word = nullptr;
+            if (half == 0 && li > 0) { tag = cx.tagbase + 2 + 6 * (li - 1) + 3; word = p.hid[G.rank]; }
+            if (half == 1) { tag = li == 0 ? cx.tagbase + 1 : cx.tagbase + 2 + 6 * (li - 1) + 5; word = p.hid[G.rank] + (G.H >> 1); }
+            if (word != nullptr) {
+                if (tid == 0) {
+                    const long long t_begin = clock64();
+                    while (!has_tag(ldt<SYS>(word), tag) && *cx.s_dead == 0) {
+                        if (clock64() - t_begin > FP_WAIT_PEER) { fail(p, cx, 0x90000 | li); break; }
+                        __nanosleep(200);
+                    }
+                }
+                __syncthreads();
+            }
+            for (int k = 2 * half; k < 2 * half + 2; ++k) {
+                const uint8_t* base = p.layers[li].d.w[k];
+                const long long bytes = (long long)p.plan[k].n_cta * F_NW * p.plan[k].warp_bytes;
+                for (long long off = ((long long)ic * FP_NT + tid) * CH; off < bytes; off += (long long)n_idle * FP_NT * CH) {
+                    const unsigned sz = (unsigned)min((long long)CH, bytes - off);
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
+                }
+            }
+        }
+    }
+}
+#endif
 
 // ---- final norm + unembedding + arg-max (sampleNextToken, Inference.cu:1235-1292) ---------------------------------------------
 template <bool SYS>
@@ -787,7 +977,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
         if (blk < 0) break;
         // x'_j = scale[g(blk, j)] * x_j and Z = sum_j zp[g(blk, j)] * x'_j,  g(b, j) = ((b + j * Mb) mod Kb) mod entries
         const int bmod = (int)(blk % Kb);
-        float zacc = 0.0f;
+        float zacc = 0.0f, xacc = 0.0f;
         for (int ch = tid; ch < (H >> 3); ch += FP_NT) {
             const uint4 xv = *reinterpret_cast<const uint4*>(cx.hv + 8 * ch);
             const __half* xh = reinterpret_cast<const __half*>(&xv);
@@ -801,10 +991,16 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
                 const __half xp = h_mul(__ushort_as_half((unsigned short)(sz & 0xffffu)), xh[e]);
                 oh[e] = xp;
                 zacc = fmaf(__half2float(__ushort_as_half((unsigned short)(sz >> 16))), __half2float(xp), zacc);
+                xacc += __half2float(xp);
             }
             *reinterpret_cast<uint4*>(cx.xs + 8 * ch) = ov;
         }
-        const float Z = block_sum_f(cx, zacc);   // its barriers also publish xs
+        float Z = block_sum_f(cx, zacc);   // its barriers also publish xs
+#ifdef QW3_FP_A_OFFSET
+        Z += a_offset(tid & 15) * block_sum_f(cx, xacc);
+#else
+        (void)xacc;
+#endif
         run_gemv(p, cx, ring, pl, cx.xs);
         __syncthreads();
         if (tid < 128) {
@@ -882,6 +1078,7 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
     cx.hv = reinterpret_cast<__half*>(smem + FP_OFF_HV);
     cx.xs = reinterpret_cast<__half*>(smem + FP_OFF_XS);
     cx.seg = reinterpret_cast<int4*>(smem + FP_OFF_SEG);
+    cx.lsz = reinterpret_cast<float2*>(smem + FP_OFF_LSZ);
     uint8_t* misc = smem + FP_OFF_MISC;
     cx.qkv_s = reinterpret_cast<__half*>(misc);                  // 768
     cx.ctx_s = reinterpret_cast<__half*>(misc + 768);            // 256
@@ -896,8 +1093,11 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
     cx.s_dead = reinterpret_cast<int*>(misc + 3584);             // 16
     uint32_t* zero = reinterpret_cast<uint32_t*>(misc + 3616);   // 32 (16-byte aligned)
     cx.zero_addr = smem_u32(zero);
-    cx.bars = smem_u32(misc + 3712);                             // F_NW * FP_SLOTS * 8
-    static_assert(3712 + F_NW * FP_SLOTS * 8 <= FP_MISC_BYTES, "misc area");
+    cx.bars = smem_u32(misc + 3712);                             // FP_SLOTS * 8
+    cx.ring_cnt = reinterpret_cast<int*>(misc + 3840);           // FP_SLOTS * 4
+    cx.ring_issued = reinterpret_cast<int*>(misc + 3968);
+    cx.ldesc = reinterpret_cast<FLayerDesc*>(misc + 4096);       // 2 descriptors
+    static_assert(FP_SLOTS <= 16 && 4096 + 2 * sizeof(FLayerDesc) <= FP_MISC_BYTES, "misc area");
 
     const int tid = threadIdx.x, c = blockIdx.x;
     const FusedGeom& G = p.g;
@@ -912,7 +1112,7 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
             const FGemvPlan& pl = p.plan[i & 3];
             if (c < pl.n_cta) {
                 wb = pl.warp_bytes;
-                base = p.layers[i >> 2].w[i & 3] + (size_t)c * F_NW * wb;
+                base = p.layers[i >> 2].d.w[i & 3] + (size_t)c * F_NW * wb;
             }
         } else {
             const int round = i - 4 * p.n_layers;
@@ -925,8 +1125,12 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         cx.seg[i] = make_int4((int)(uint32_t)b, (int)(uint32_t)(b >> 32), wb, 0);
     }
     if (tid == 0) {
-        for (int s = 0; s < F_NW * FP_SLOTS; ++s) mbar_init(cx.bars + 8 * s, 1);
+        for (int s = 0; s < FP_SLOTS; ++s) {
+            mbar_init(cx.bars + 8 * s, 1);
+            cx.ring_cnt[s] = 0;
+        }
         *cx.s_dead = 0;
+        *cx.ring_issued = 0;
         mbar_fence_init();
     }
     if (tid < 8) zero[tid] = 0u;
@@ -938,13 +1142,28 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         cx.rope_cs[64 + tid] = p.sin_t[(size_t)cx.pos * 64 + tid];
     }
     __syncthreads();
+#ifdef QW3_FP_FILL
+    for (int i = tid; i < (int)(FP_OFF_OBUF / 4); i += FP_NT) reinterpret_cast<uint32_t*>(smem)[i] = (uint32_t)i * 2654435761u + 12345u * blockIdx.x;
+    __syncthreads();
+#endif
     WarpRing ring;
-    ring.uc = 0; ring.pc = 0; ring.pseg = 0; ring.pu = 0;
+    ring.uc = 0; ring.pseg = 0; ring.pu = 0;
     ring.policy = l2_policy_evict_first();
-#pragma unroll
-    for (int s = 0; s < FP_SLOTS; ++s) ring_request(ring, cx);
+    for (int s = 0; s < FP_SLOTS; ++s) {   // prime the ring: thread 0 issues, every warp moves its cursor along
+        if (ring_cursor_valid(ring, cx)) {
+#ifndef QW3_FP_NOLOAD
+            if (tid == 0) ring_issue(ring, cx, s);
+#endif
+            ++ring.pu;
+        }
+    }
 
     if (active) {
+        {
+            LayerPrefetch lp0;
+            layer_request(p, 0, lp0);
+            layer_commit(cx, 0, lp0);   // visible after the barrier below
+        }
         // embedding gather (Inference.cu:1310-1315) or the hidden state the pass before left (Inference.cu:1357)
         if (tid < G.rs) {
             const int i = G.rs * cglob + tid;
@@ -967,7 +1186,20 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         for (int li = 0; li < p.n_layers; ++li) layer_pass<SYS>(p, cx, ring, li);
         if (tid < G.rs) p.hidden[G.rs * cglob + tid] = cx.hmine[tid];   // for the next pass / the next stage
     }
+#ifdef QW3_FP_L2PF
+    if (!active) l2_prefetch_pass<SYS>(p, cx);
+#endif
     if (p.n_rounds > 0) sample_pass<SYS>(p, cx, ring);
+    // After a wait has given up, units may have been requested that nobody consumed: their copies must have landed
+    // before the CTA gives up its shared memory (bounded; a normal pass has none outstanding).
+    __syncthreads();
+    if (tid == 0 && *cx.s_dead != 0) {
+        const int issued = *cx.ring_issued;
+        for (int u = ring.uc; u < issued; ++u) {
+            const long long t_begin = clock64();
+            while (!mbar_try_wait(cx.bars + 8 * (u % FP_SLOTS), (u / FP_SLOTS) & 1) && clock64() - t_begin < (1ll << 24)) {}
+        }
+    }
 }
 
 // ---- load-time repack ------------------------------------------------------------------------------------------------------
@@ -992,15 +1224,25 @@ QW3_HD uint32_t fused_repack_word(const FusedGeom& g, const FGemvPlan& pl, int o
     return word;
 }
 
+// Word `wi` of the repacked buffer: streams follow one another; inside a stream the units follow one another, a unit
+// being [warp][piece] (fused_stream_locate, fused_plan.h).
 __global__ void fused_repack_kernel(const FusedGeom g, const FGemvPlan pl, const int op, const uint8_t* __restrict__ raw,
                                     const long long out_dim, uint32_t* __restrict__ out, const long long n_words) {
     const long long wi = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (wi >= n_words) return;
     const long long wps = (long long)F_NW * pl.warp_bytes / 4;   // words per stream
     const long long stream = wi / wps;
-    const int rem = (int)(wi % wps);
-    const int warp = rem / (pl.warp_bytes / 4), off = (rem % (pl.warp_bytes / 4)) * 4;
+    int warp, off;
+    fused_stream_locate(pl, (int)(wi % wps) * 4, warp, off);
     out[wi] = fused_repack_word(g, pl, op, raw, out_dim, stream, warp, off);
+}
+
+// Fills the per-layer constant blocks from the descriptors (one block of FP_NT threads per layer).
+__global__ void fused_consts_kernel(FLayerConst* lc, const int4 n_alloc) {
+    FLayerConst& L = lc[blockIdx.x];
+    const int tid = threadIdx.x, k = tid / FP_MAX_GROUPS, gq = tid % FP_MAX_GROUPS;
+    const int na = k == 0 ? n_alloc.x : k == 1 ? n_alloc.y : k == 2 ? n_alloc.z : n_alloc.w;
+    L.sz[k][gq] = gq < na ? pack_h2(L.d.scale[k][gq], L.d.zp[k][gq]) : 0u;
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------------------------
@@ -1039,6 +1281,7 @@ bool fused_plan(int H, int I, int heads, int vocab, int n_layers, long long max_
     if (H <= 0 || heads <= 0 || H != heads * 128 || H > FP_MAX_H || H % 128 || I % 128 || vocab % 128) return false;
     if (n_ranks < 1 || n_ranks > QW3_MAX_STAGES || rank < 0 || rank >= n_ranks || heads % n_ranks) return false;
     if (grid < 1 || max_pos > 0x1fffe || 6 * n_layers + 8 >= 511) return false;
+    if (3 * H / 128 > FP_MAX_GROUPS || I / 128 > FP_MAX_GROUPS) return false;
     FusedGeom g;
     g.H = H; g.I = I; g.heads = heads; g.vocab = vocab; g.n_ranks = n_ranks; g.rank = rank; g.grid = grid;
     g.heads_local = heads / n_ranks;
@@ -1084,8 +1327,9 @@ void fused_repack_host(const FusedGeom& g, const FGemvPlan& pl, int op, const ui
     uint32_t* o32 = reinterpret_cast<uint32_t*>(out);
     for (size_t wi = 0; wi < bytes / 4; ++wi) {
         const long long stream = (long long)(wi / wps);
-        const int rem = (int)(wi % wps);
-        o32[wi] = fused_repack_word(g, pl, op, raw, out_dim, stream, rem / (pl.warp_bytes / 4), (rem % (pl.warp_bytes / 4)) * 4);
+        int warp, off;
+        fused_stream_locate(pl, (int)(wi % wps) * 4, warp, off);
+        o32[wi] = fused_repack_word(g, pl, op, raw, out_dim, stream, warp, off);
     }
 }
 
@@ -1165,26 +1409,37 @@ int fused_create(const FusedCreate& a, FusedPass** out) {
     P.eps = a.eps;
     P.n_rounds = a.unemb ? (g.n_blocks + g.n_ranks * g.grid - 1) / (g.n_ranks * g.grid) : 0;
     P.first_stage = a.emb ? 1 : 0;
-    std::vector<FLayerDesc> ld((size_t)a.n_layers);
+    std::vector<FLayerConst> ld((size_t)a.n_layers);
     for (int l = 0; l < a.n_layers; ++l) {
         const FusedLayerIn& in = a.layers[l];
+        std::memset(&ld[l], 0, sizeof(FLayerConst));
         for (int k = 0; k < 4; ++k) {
-            int rc = repack_to_device(f, g, P.plan[k], k, in.m[k], &ld[l].w[k], a.stream);
+            int rc = repack_to_device(f, g, P.plan[k], k, in.m[k], &ld[l].d.w[k], a.stream);
             if (rc != QW3_OK) return bail(rc);
-            ld[l].scale[k] = static_cast<const __half*>(in.m[k].scale);
-            ld[l].zp[k] = static_cast<const __half*>(in.m[k].zp);
+            ld[l].d.scale[k] = static_cast<const __half*>(in.m[k].scale);
+            ld[l].d.zp[k] = static_cast<const __half*>(in.m[k].zp);
             if (l == 0) P.n_alloc[k] = (int)in.m[k].n_alloc;
+            if (in.m[k].n_alloc > FP_MAX_GROUPS || in.m[k].n_alloc != P.n_alloc[k]) {
+                set_last_error("the fused pass keeps at most %d scale / zero-point entries per layer matrix", FP_MAX_GROUPS);
+                return bail(QW3_ERR_ARG);
+            }
         }
-        ld[l].gamma = static_cast<const __half*>(in.gamma);
-        ld[l].kc = static_cast<__half*>(in.kc);
-        ld[l].vc = static_cast<__half*>(in.vc);
+        ld[l].d.gamma = static_cast<const __half*>(in.gamma);
+        ld[l].d.kc = static_cast<__half*>(in.kc);
+        ld[l].d.vc = static_cast<__half*>(in.vc);
     }
     void* d_layers = nullptr;
-    int rc = fp_alloc(f, &d_layers, sizeof(FLayerDesc) * (size_t)(a.n_layers > 0 ? a.n_layers : 1));
+    int rc = fp_alloc(f, &d_layers, sizeof(FLayerConst) * (size_t)(a.n_layers > 0 ? a.n_layers : 1));
     if (rc != QW3_OK) return bail(rc);
-    if (a.n_layers > 0 && cudaMemcpyAsync(d_layers, ld.data(), sizeof(FLayerDesc) * ld.size(), cudaMemcpyHostToDevice, a.stream) != cudaSuccess)
-        return bail(QW3_ERR_CUDA);
-    P.layers = static_cast<const FLayerDesc*>(d_layers);
+    if (a.n_layers > 0) {
+        // pageable source: the copy is staged before the call returns
+        if (cudaMemcpyAsync(d_layers, ld.data(), sizeof(FLayerConst) * ld.size(), cudaMemcpyHostToDevice, a.stream) != cudaSuccess)
+            return bail(QW3_ERR_CUDA);
+        fused_consts_kernel<<<a.n_layers, FP_NT, 0, a.stream>>>(static_cast<FLayerConst*>(d_layers),
+                                                                make_int4(P.n_alloc[0], P.n_alloc[1], P.n_alloc[2], P.n_alloc[3]));
+        if (cudaGetLastError() != cudaSuccess) return bail(QW3_ERR_CUDA);
+    }
+    P.layers = static_cast<const FLayerConst*>(d_layers);
     if (a.emb) {
         P.emb_packed = static_cast<const uint8_t*>(a.emb->packed);
         P.emb_scale = static_cast<const __half*>(a.emb->scale);
@@ -1227,6 +1482,16 @@ int fused_create(const FusedCreate& a, FusedPass** out) {
     if (cudaMemsetAsync(f->xbase, 0, total * 8, a.stream) != cudaSuccess) return bail(QW3_ERR_CUDA);
     if (cudaStreamSynchronize(a.stream) != cudaSuccess) return bail(QW3_ERR_CUDA);
     fused_set_peer(f, g.rank, f->xbase);
+#ifdef QW3_TRACE
+    {
+        void* tr = nullptr;
+        const size_t tb = ((size_t)f->grid * (a.n_layers > 0 ? a.n_layers : 1) * 16 + 2048) * 8;   // + 1024 unit waits of CTA 0
+        rc = fp_alloc(f, &tr, tb);
+        if (rc != QW3_OK) return bail(rc);
+        cudaMemset(tr, 0, tb);
+        P.trace = static_cast<unsigned long long*>(tr);
+    }
+#endif
     f->sys = g.n_ranks > 1;
     *out = f;
     return QW3_OK;
@@ -1262,6 +1527,12 @@ int fused_launch(FusedPass* f, int decode, cudaStream_t st) {
     const void* fn = f->sys ? reinterpret_cast<const void*>(fused_pass_kernel<true>) : reinterpret_cast<const void*>(fused_pass_kernel<false>);
     QW3_CUDA(cudaLaunchCooperativeKernel(fn, dim3(f->grid), dim3(FP_NT), args, FP_SMEM_BYTES, st));
     return QW3_OK;
+}
+
+// Tracing builds: the stamps of the last pass, [grid][n_layers][16] (null otherwise).
+const void* fused_trace(const FusedPass* f, size_t* bytes) {
+    if (bytes) *bytes = ((size_t)f->grid * (f->prm.n_layers > 0 ? f->prm.n_layers : 1) * 16 + 2048) * 8;
+    return f->prm.trace;
 }
 
 void fused_geometry(const FusedPass* f, FusedGeom* g, FGemvPlan* plans) {

@@ -57,5 +57,6 @@ int fused_launch(FusedPass* f, int decode, cudaStream_t st);
 void* fused_exchange_base(FusedPass* f, size_t* bytes);
 void fused_set_peer(FusedPass* f, int rank, void* base);
 void fused_geometry(const FusedPass* f, FusedGeom* g, FGemvPlan* plans);
+const void* fused_trace(const FusedPass* f, size_t* bytes);
 
 }  // namespace qw3

@@ -4,7 +4,8 @@
 // The reference keeps every matrix as the flat nibble stream dequantAwqKernel reads (Inference.cu:84-105) and lets
 // cuBLAS walk it column-major (Inference.cu:1052-1065).  The on-disk files keep that layout (Inference.cu:780-900);
 // at load time each matrix is additionally rewritten, on the device, into the order in which the fused pass consumes
-// it: one contiguous byte stream per (CTA, warp), made of 512-byte items.  An item is one m16n8k16 A-operand tile
+// it: one byte stream per (CTA, warp), made of 512-byte items; the 16 warp streams of a CTA are interleaved in pieces of
+// F_UNIT bytes ([unit][warp][piece]) so that one bulk copy fetches the next piece of every warp.  An item is one m16n8k16 A-operand tile
 // sequence: 16 outputs x 64 inputs, every lane owning one 16-byte piece = four 32-bit words = four k-steps, the eight
 // nibbles of a word sitting where one AND per register turns them into the fp16 A fragment.  (A trailing half group of
 // two k-steps makes a 256-byte item.)
@@ -27,7 +28,10 @@
 namespace qw3 {
 
 constexpr int F_NW = 16;          // warps per CTA
-constexpr int F_UNIT = 4096;      // bytes of one ring unit (one bulk copy)
+#ifndef QW3_F_UNIT
+#define QW3_F_UNIT 4096
+#endif
+constexpr int F_UNIT = QW3_F_UNIT;   // bytes of one warp's piece of a ring unit (a unit = 16 pieces = one bulk copy)
 
 enum FusedOp { F_QKV = 0, F_WO = 1, F_W1 = 2, F_W2 = 3, F_UNEMB = 4, F_NOPS = 5 };
 
@@ -89,6 +93,15 @@ QW3_HD FWordPos fused_word_pos(const FGemvPlan& pl, int warp, int byte_off) {
     r.tile = (a * pl.nb + b) * pl.tb + i;
     r.kstep = bk * (4 * pl.nq + pl.rem) + 4 * q;
     return r;
+}
+
+// Where byte `stream_off` of a CTA's interleaved stream belongs: which warp, and which byte of that warp's own stream.
+// Unit u holds bytes [u * F_UNIT, min((u + 1) * F_UNIT, warp_bytes)) of every warp's stream, warp after warp.
+QW3_HD void fused_stream_locate(const FGemvPlan& pl, int stream_off, int& warp, int& warp_off) {
+    const int u = stream_off / (F_NW * F_UNIT), in_unit = stream_off % (F_NW * F_UNIT);
+    const int rest = pl.warp_bytes - u * F_UNIT, piece = rest < F_UNIT ? rest : F_UNIT;
+    warp = in_unit / piece;
+    warp_off = u * F_UNIT + in_unit % piece;
 }
 
 // The eight nibbles of a word: nibble n (bits 4n .. 4n+3) holds W[row][j] with

@@ -70,8 +70,25 @@ def _k0(g, op, cta):
     return 0
 
 
+PIECE = 4096   # bytes of one warp's piece of a ring unit (F_UNIT of fused_plan.h)
+
+
+def _warp_streams(stream_words, p):
+    """The ring's view of a CTA's stream: unit after unit, a unit being [warp][piece]; returns the 16 per-warp streams."""
+    wb, out, at, u = p["warp_bytes"], [[] for _ in range(16)], 0, 0
+    while u * PIECE < wb:
+        piece = min(PIECE, wb - u * PIECE) // 4
+        for warp in range(16):
+            out[warp].append(stream_words[at:at + piece])
+            at += piece
+        u += 1
+    assert at == stream_words.size
+    return np.concatenate([np.concatenate(w) for w in out])
+
+
 def _consume(stream_words, p, g, op, cta, blk, x, y):
     """What the 16 warps of one CTA do with their streams (gemv_core of fused_pass.cu), in integers."""
+    stream_words = _warp_streams(stream_words, p)
     ksw = 4 * p["nq"] + p["rem"]
     x_cta = x[_k0(g, op, cta):]
     lanes = np.arange(32)
