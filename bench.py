@@ -443,8 +443,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="prompt length (default: 128 on one GPU, 512 on several: the baseline's two configurations)")
     ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of --steps decode steps each (the median counts)")
-    ap.add_argument("--parallel", default="pp", choices=["pp", "tp"],
-                    help="several GPUs: layer pipeline (the reference's contract) or row-split of every matrix")
+    ap.add_argument("--parallel", default="tp", choices=["pp", "tp"],
+                    help="several GPUs: row-split of every matrix over the GPUs (default: the only form in which a second GPU's "
+                         "bandwidth works on the same token) or the reference's layer pipeline")
     ap.add_argument("--only-roofline", action="store_true", help="run only the dominant-kernel timing (small case for profilers)")
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)

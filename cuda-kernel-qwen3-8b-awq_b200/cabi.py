@@ -26,7 +26,7 @@ EXPORTS = [
     "qw3_set_batched_prefill",
     "qw3_set_chained_decode",
     "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect", "qw3_stage_layers",
-    "qw3_fused_plan", "qw3_fused_repack_host", "qw3_stage_hidden",
+    "qw3_fused_plan", "qw3_fused_repack_host", "qw3_stage_hidden", "qw3_tp_export", "qw3_tp_connect",
 ]
 
 
@@ -49,7 +49,7 @@ class Config(C.Structure):
                 ("rope_base", C.c_float), ("sample_first", C.c_int32), ("n_stages", C.c_int32),
                 ("first_layer", C.c_int32 * (MAX_STAGES + 1)), ("device", C.c_int32 * MAX_STAGES),
                 ("rank", C.c_int32), ("world", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32),
-                ("keep_logits", C.c_int32), ("persistent", C.c_int32)]
+                ("keep_logits", C.c_int32), ("persistent", C.c_int32), ("tensor_parallel", C.c_int32)]
 
 
 def build(force=False, verbose=False):
@@ -112,6 +112,8 @@ def lib():
         "qw3_stage_connect": [vp, vp, vp],
         "qw3_stage_layers": [C.POINTER(Config), i32, C.POINTER(i32), C.POINTER(i32)],
         "qw3_stage_hidden": [vp, i32, vp],
+        "qw3_tp_export": [vp, vp],
+        "qw3_tp_connect": [vp, vp],
         "qw3_fused_plan": [C.POINTER(Config), i32, i32, i32, vp, vp],
         "qw3_fused_repack_host": [C.POINTER(Config), i32, i32, i32, i32, vp, i64, vp, i64],
     }

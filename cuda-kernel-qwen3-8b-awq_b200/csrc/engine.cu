@@ -155,6 +155,8 @@ struct qw3_engine {
     int gen = 0;                        // generate calls so far (one process per GPU: part of the cross-GPU tags)
     bool linked_now = false;            // the pass being enqueued is a chained decode pass (ops_linked)
     bool chain_decode = true;           // qw3_set_chained_decode
+    std::vector<void*> tp_peers;        // row-split over GPUs: the other ranks' exchange buffers (CUDA IPC mappings)
+    bool tp_connected = false;
 };
 
 namespace qw3 {
@@ -594,6 +596,8 @@ int qw3_destroy(qw3_handle e) {
         if (s.stream) cudaStreamDestroy(s.stream);
     }
     if (!e->st.empty()) cudaSetDevice(e->st[0].device);
+    for (void* pm : e->tp_peers)
+        if (pm) cudaIpcCloseMemHandle(pm);
     if (e->next_mb) cudaIpcCloseMemHandle(e->next_mb);
     if (e->prev_mb && !e->next_is_prev) cudaIpcCloseMemHandle(e->prev_mb);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -615,7 +619,15 @@ static int create_fused(qw3_engine* e, Stage& s) {
     const int n_layers = (int)s.layers.size();
     FusedGeom g;
     FGemvPlan plans[F_NOPS];
-    if (!fused_plan(c.hidden, c.inter, c.heads, c.vocab, n_layers, c.max_pos, 1, 0, ws->sm_count, &g, plans)) return QW3_OK;
+    const bool tp = c.tensor_parallel != 0 && c.world > 1;
+    const int n_ranks = tp ? c.world : 1, rank = tp ? c.rank : 0;
+    if (!fused_plan(c.hidden, c.inter, c.heads, c.vocab, n_layers, c.max_pos, n_ranks, rank, ws->sm_count, &g, plans)) {
+        if (tp) {
+            set_last_error("tensor_parallel: the fused pass does not cover this configuration on %d GPUs", n_ranks);
+            return QW3_ERR_ARG;
+        }
+        return QW3_OK;
+    }
     auto mat = [](const W4Dev& w) {
         FusedMatrix m;
         m.packed = w.packed; m.scale = w.scale; m.zp = w.zp; m.n_alloc = w.n_alloc; m.out_dim = w.out_dim; m.in_dim = w.in_dim;
@@ -632,7 +644,7 @@ static int create_fused(qw3_engine* e, Stage& s) {
     FusedCreate a;
     std::memset(&a, 0, sizeof(a));
     a.H = c.hidden; a.I = c.inter; a.heads = c.heads; a.vocab = c.vocab; a.n_layers = n_layers; a.eps = c.eps; a.max_pos = c.max_pos;
-    a.n_ranks = 1; a.rank = 0; a.sm_count = ws->sm_count; a.device = s.device;
+    a.n_ranks = n_ranks; a.rank = rank; a.sm_count = ws->sm_count; a.device = s.device;
     a.layers = in.data();
     a.emb = first ? &emb : nullptr;
     a.unemb = last ? &unemb : nullptr;
@@ -641,14 +653,18 @@ static int create_fused(qw3_engine* e, Stage& s) {
     a.d_gen = s.d_gen; a.cos_t = s.cos_t; a.sin_t = s.sin_t; a.logits16 = s.logits16; a.logits32 = s.logits32; a.err = ws->err;
     a.stream = s.stream;
     QW3_CUDA(cudaSetDevice(s.device));
+    // row-split: a rank computes only its blocks of the logits; the others stay NaN in the fp32 copy (test hook)
+    if (tp && s.logits32) QW3_CUDA(cudaMemset(s.logits32, 0xff, (size_t)c.vocab * 4));
     return fused_create(a, &s.fused);
 }
 
 static int create_impl(const char* weight_dir, qw3_engine* e) {
     Qw3Config& c = e->cfg;
     QW3_TRY(validate_config(c));
-    const bool mp = c.world > 1;   // one process per GPU: this handle owns stage `rank` only
+    const bool tp = c.tensor_parallel != 0 && c.world > 1;   // one process per GPU, every matrix row-split: this handle runs all layers on its share
+    const bool mp = c.world > 1 && !tp;                       // one process per GPU, layer pipeline: this handle owns stage `rank` only
     QW3_REQUIRE(!mp || c.n_stages == c.world, "qw3_create: with world > 1 the number of stages must equal world");
+    QW3_REQUIRE(!tp || (c.n_stages == 1 && c.persistent >= 2), "qw3_create: tensor_parallel needs n_stages = 1 and persistent = 2");
     int ndev = 0;
     QW3_CUDA(cudaGetDeviceCount(&ndev));
     for (int s = 0; s < c.n_stages; ++s) {
@@ -740,6 +756,10 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
     }
     if (c.persistent >= 2) {
         for (int si = 0; si < N; ++si) QW3_TRY(create_fused(e, e->st[si]));
+        if (tp && !e->st[0].fused) {
+            set_last_error("tensor_parallel needs the fused pass");
+            return QW3_ERR_ARG;
+        }
     }
     if (c.persistent) {
         for (int si = 0; si < N; ++si) {
@@ -800,7 +820,7 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
         e->pinned = nullptr;
         e->pinned_bytes = 0;
     }
-    if (c.use_graph) {
+    if (c.use_graph && !tp) {   // row-split: captured in qw3_tp_connect, once the peers' buffers are known
         for (int si = 0; si < N; ++si) {
             QW3_TRY(capture_stage_graph(e, si, false, &e->st[si].g_prompt, &e->st[si].launches_prompt));
             QW3_TRY(capture_stage_graph(e, si, true, &e->st[si].g_decode, &e->st[si].launches_decode));
@@ -992,7 +1012,12 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
             set_last_error("qw3_generate: token id %d at %d is outside [0, %d)", prompt[t], t, c.vocab);
             return QW3_ERR_RANGE;
         }
-    if (c.world > 1) return generate_mp(e, prompt, n_prompt, max_new, out_ids, n_out);
+    const bool tp = c.tensor_parallel != 0 && c.world > 1;
+    if (tp && !e->tp_connected) {
+        set_last_error("tensor_parallel: call qw3_tp_connect before generating");
+        return QW3_ERR_STATE;
+    }
+    if (c.world > 1 && !tp) return generate_mp(e, prompt, n_prompt, max_new, out_ids, n_out);
     const int N = c.n_stages;
     Stage &s0 = e->st[0], &sl = e->st[N - 1];
     e->launches = 0;
@@ -1040,7 +1065,7 @@ int qw3_decode_more(qw3_handle e, int32_t max_new, int32_t* out_ids, int32_t* n_
     e->prompt_ms = 0.f;
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaEventRecord(e->ev1, s0.stream));
-    if (e->cfg.world > 1) return decode_loop_mp(e, max_new, out_ids, n_out);
+    if (e->cfg.world > 1 && !e->cfg.tensor_parallel) return decode_loop_mp(e, max_new, out_ids, n_out);
     QW3_TRY(decode_loop(e, max_new, out_ids));
     if (n_out) *n_out = max_new;
     return QW3_OK;
@@ -1217,6 +1242,48 @@ int qw3_stage_connect(qw3_handle e, const void* next_stage_handle_64B, const voi
             QW3_TRY(rc);
         }
     }
+    return QW3_OK;
+}
+
+int qw3_tp_export(qw3_handle e, void* out_handle_64B) {
+    QW3_REQUIRE(e && out_handle_64B, "qw3_tp_export: null pointer");
+    if (!(e->cfg.tensor_parallel && e->cfg.world > 1) || !e->st[0].fused) {
+        set_last_error("qw3_tp_export: the handle was not created with tensor_parallel = 1 and world > 1");
+        return QW3_ERR_STATE;
+    }
+    cudaIpcMemHandle_t h;
+    QW3_CUDA(cudaSetDevice(e->st[0].device));
+    QW3_CUDA(cudaIpcGetMemHandle(&h, fused_exchange_base(e->st[0].fused, nullptr)));
+    std::memcpy(out_handle_64B, &h, 64);
+    return QW3_OK;
+}
+
+int qw3_tp_connect(qw3_handle e, const void* handles_world_x_64B) {
+    QW3_REQUIRE(e && handles_world_x_64B, "qw3_tp_connect: null pointer");
+    if (!(e->cfg.tensor_parallel && e->cfg.world > 1) || !e->st[0].fused || e->tp_connected) {
+        set_last_error("qw3_tp_connect: needs a handle created with tensor_parallel = 1 and world > 1 that is not connected yet");
+        return QW3_ERR_STATE;
+    }
+    QW3_CUDA(cudaSetDevice(e->st[0].device));
+    const uint8_t* hs = static_cast<const uint8_t*>(handles_world_x_64B);
+    e->tp_peers.assign((size_t)e->cfg.world, nullptr);
+    for (int r = 0; r < e->cfg.world; ++r) {
+        if (r == e->cfg.rank) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, hs + 64 * (size_t)r, 64);
+        QW3_CUDA(cudaIpcOpenMemHandle(&e->tp_peers[r], h, cudaIpcMemLazyEnablePeerAccess));
+        fused_set_peer(e->st[0].fused, r, e->tp_peers[r]);
+    }
+    // The graphs captured at creation hold the launch parameters of that moment, without the peers' buffers:
+    // capture them again now that every address is known.
+    Stage& s = e->st[0];
+    if (e->cfg.use_graph) {
+        if (s.g_prompt) { cudaGraphExecDestroy(s.g_prompt); s.g_prompt = nullptr; }
+        if (s.g_decode) { cudaGraphExecDestroy(s.g_decode); s.g_decode = nullptr; }
+        QW3_TRY(capture_stage_graph(e, 0, false, &s.g_prompt, &s.launches_prompt));
+        QW3_TRY(capture_stage_graph(e, 0, true, &s.g_decode, &s.launches_decode));
+    }
+    e->tp_connected = true;
     return QW3_OK;
 }
 

@@ -101,7 +101,7 @@ struct FusedParams {
     unsigned long long* xq;                    // [n_act][384]                 q/k/v partial sums (group-local)
     unsigned long long* xa;                    // [n_act][132]                 attention states (group-local)
     unsigned long long* xo[QW3_MAX_STAGES];    // [heads * gs][H / gs]         Wo partial sums per (head, output share)
-    unsigned long long* x2[QW3_MAX_STAGES];    // [n_ranks * n_act][H]         W2 partial sums per contributor
+    unsigned long long* x2[QW3_MAX_STAGES];    // [n_ranks * n_mlp][H]         W2 partial sums per contributor
     unsigned long long* hid[QW3_MAX_STAGES];   // [2][H / 2]                   gathered hidden state, two buffers
     unsigned long long* xarg[QW3_MAX_STAGES];  // [n_ranks * grid][2]          arg-max candidates
     int* err;
@@ -838,10 +838,12 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         FP_STAMP(li, 8);
     }
 
+    if (c < G.n_mlp) {
+    const int cmlp = G.rank * G.n_mlp + c;
     // ---- RMSNorm (same gamma) + this CTA's n1 outputs of W1 + GeLU (Inference.cu:1158-1197) ----------------------------------
     gather_norm<SYS>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, cx.xs, -1, H, x_full, x_slice);
     FP_STAMP(li, 9);
-    if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cglob * n1 + tid, H >> 7, p.n_alloc[F_W1], sc, zp);
+    if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cmlp * n1 + tid, H >> 7, p.n_alloc[F_W1], sc, zp);
     run_gemv(p, cx, ring, p.plan[F_W1], cx.xs);
     __syncthreads();
     float gv = 0.0f;
@@ -863,12 +865,13 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         const float zo = z2 + a_offset(i0 & 15);
         const float y0 = s2 * (cx.obuf[i0] - zo * x_g), y1 = s2 * (cx.obuf[i0 + 1] - zo * x_g);
         const int ro = i0 / (H / G.n_ranks);
-        stt2<SYS>(p.x2[ro] + (size_t)cglob * H + i0, tagged_f(y0, t0 + 4), tagged_f(y1, t0 + 4));
+        stt2<SYS>(p.x2[ro] + (size_t)cmlp * H + i0, tagged_f(y0, t0 + 4), tagged_f(y1, t0 + 4));
     }
     __syncthreads();
     FP_STAMP(li, 14);
+    }
     // ---- ordered sum over all contributors for this CTA's rs outputs + residual (Inference.cu:1217-1228) ----------------------
-    const int ncontrib = G.n_ranks * G.n_act, nw = ncontrib * rs;
+    const int ncontrib = G.n_ranks * G.n_mlp, nw = ncontrib * rs;
     {
         unsigned long long w[8];
         const unsigned long long* src = p.x2[G.rank] + o_first;
@@ -1185,6 +1188,20 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         publish_hidden<SYS>(p, cx, 1, cx.tagbase + 1, cglob);
         for (int li = 0; li < p.n_layers; ++li) layer_pass<SYS>(p, cx, ring, li);
         if (tid < G.rs) p.hidden[G.rs * cglob + tid] = cx.hmine[tid];   // for the next pass / the next stage
+        if (G.n_ranks > 1) {
+            // Row-split over GPUs: the plain hidden state of this GPU is completed from the words the other GPUs'
+            // CTAs of the same index published (readers after this launch expect the whole vector).
+            const int half = G.rs >> 1, n = (G.n_ranks - 1) * half;
+            const uint32_t tag = p.n_layers > 0 ? cx.tagbase + 2 + 6 * (p.n_layers - 1) + 5 : cx.tagbase + 1;
+            if (tid < n) {
+                int r = tid / half;
+                r += r >= G.rank ? 1 : 0;
+                const size_t at = (size_t)(((r * G.n_act + c) * G.rs) >> 1) + tid % half;
+                unsigned long long w[1];
+                poll_batch<SYS, 1>(p, cx, 1, [&](int) { return p.hid[G.rank] + (G.H >> 1) + at; }, tag, 0xA0000, w);
+                reinterpret_cast<uint32_t*>(p.hidden)[at] = (uint32_t)w[0];
+            }
+        }
     }
 #ifdef QW3_FP_L2PF
     if (!active) l2_prefetch_pass<SYS>(p, cx);
@@ -1290,17 +1307,25 @@ bool fused_plan(int H, int I, int heads, int vocab, int n_layers, long long max_
     for (int gs = 32; gs >= 1 && !found; gs >>= 1) {
         const int n_act = g.heads_local * gs;
         if (n_act > grid || H % gs || (H / gs) % 128 || gs * FP_ATT_STRIDE > FP_OBUF) continue;
-        if (H % (n_ranks * n_act) || I % (n_ranks * n_act)) continue;
-        const int rs = H / (n_ranks * n_act), n1 = I / (n_ranks * n_act);
+        if (H % (n_ranks * n_act)) continue;
+        const int rs = H / (n_ranks * n_act);
         if (rs < 2 || rs % 2 || rs > FP_MAX_RS || (H / gs) % rs || (H / n_ranks) % rs) continue;
-        if (n1 % 32 || n1 > FP_MAX_N1 || n1 > FP_NT) continue;
-        if ((H / gs) % 2 || (long long)heads * rs > 8 * FP_NT || (long long)n_ranks * n_act * rs > 8 * FP_NT) continue;
-        g.gs = gs; g.n_act = n_act; g.rs = rs; g.n1 = n1;
+        // W1 / W2: as many of the n_act CTAs as give every one a multiple of 32 outputs of W1 (its k-steps of W2 then
+        // come in pairs); with the matrices row-split over many GPUs fewer CTAs than n_act take part
+        int n1 = 0, n_mlp = 0;
+        for (int cand = 32; cand <= FP_MAX_N1 && cand <= FP_NT; cand += 32) {
+            if (I % (n_ranks * cand)) continue;
+            const int m = I / (n_ranks * cand);
+            if (m <= n_act && m > n_mlp) { n_mlp = m; n1 = cand; }
+        }
+        if (n_mlp == 0) continue;
+        if ((H / gs) % 2 || (long long)heads * rs > 8 * FP_NT || (long long)n_ranks * n_mlp * rs > 8 * FP_NT) continue;
+        g.gs = gs; g.n_act = n_act; g.rs = rs; g.n1 = n1; g.n_mlp = n_mlp;
         FGemvPlan pl[F_NOPS];
         if (!make_plan(n_act, 24, H / 16 / gs, &pl[F_QKV])) continue;
         if (!make_plan(n_act, H / gs / 16, 8, &pl[F_WO])) continue;
-        if (!make_plan(n_act, n1 / 16, H / 16, &pl[F_W1])) continue;
-        if (!make_plan(n_act, H / 16, n1 / 16, &pl[F_W2])) continue;
+        if (!make_plan(g.n_mlp, n1 / 16, H / 16, &pl[F_W1])) continue;
+        if (!make_plan(g.n_mlp, H / 16, n1 / 16, &pl[F_W2])) continue;
         if (!make_plan(grid, 8, H / 16, &pl[F_UNEMB])) continue;
         for (int k = 0; k < F_NOPS; ++k) plans[k] = pl[k];
         found = true;
@@ -1376,7 +1401,7 @@ static int repack_to_device(FusedPass* f, const FusedGeom& g, const FGemvPlan& p
 // Sizes of the four exchange buffers that other ranks store into (xo, x2, hid, xarg), in 64-bit words.
 static void exchange_words(const FusedGeom& g, size_t (&w)[4]) {
     w[0] = (size_t)g.heads * g.gs * (g.H / g.gs);
-    w[1] = (size_t)g.n_ranks * g.n_act * g.H;
+    w[1] = (size_t)g.n_ranks * g.n_mlp * g.H;
     w[2] = (size_t)g.H;   // two buffers of H / 2
     w[3] = 2 * (size_t)g.n_ranks * g.grid;
 }
@@ -1554,7 +1579,7 @@ int qw3_fused_plan(const Qw3Config* cfg, int32_t n_ranks, int32_t rank, int32_t 
         set_last_error("qw3_fused_plan: the fused pass does not cover this configuration");
         return QW3_ERR_ARG;
     }
-    const int32_t gv[16] = {g.H, g.I, g.heads, g.vocab, g.n_ranks, g.rank, g.heads_local, g.gs, g.n_act, g.rs, g.n1, g.n_blocks, g.grid, 0, 0, 0};
+    const int32_t gv[16] = {g.H, g.I, g.heads, g.vocab, g.n_ranks, g.rank, g.heads_local, g.gs, g.n_act, g.rs, g.n1, g.n_blocks, g.grid, g.n_mlp, 0, 0};
     std::memcpy(geom_out, gv, sizeof(gv));
     for (int k = 0; k < F_NOPS; ++k) {
         const int32_t pv[10] = {pl[k].n_cta, pl[k].n_mt, pl[k].n_ks, pl[k].wk, pl[k].tb, pl[k].nb, pl[k].nq, pl[k].rem, pl[k].warp_bytes, pl[k].n_units};

@@ -54,7 +54,8 @@ struct FusedGeom {
     int gs;                     // CTAs that share one head (split of the Wqkv inputs, of the KV length, of the Wo outputs)
     int n_act;                  // CTAs that run the layers = heads_local * gs
     int rs;                     // hidden elements a CTA reduces and owns = H / (n_ranks * n_act)
-    int n1;                     // W1 outputs per CTA = I / (n_ranks * n_act)
+    int n_mlp;                  // CTAs that run W1 / W2 (the first n_mlp of the n_act)
+    int n1;                     // W1 outputs per such CTA = I / (n_ranks * n_mlp)
     int n_blocks;               // vocab / 128
     int grid;                   // CTAs launched (all of them take part in the unembedding)
 };
@@ -126,7 +127,7 @@ QW3_HD long long fused_tile_out(const FusedGeom& g, int op, int cta, int tile, l
         case F_WO:      // the outputs are cut evenly among the gs CTAs of a head
             return (long long)(cta % g.gs) * (g.H / g.gs) + tile * 16;
         case F_W1:
-            return (long long)(g.rank * g.n_act + cta) * g.n1 + tile * 16;
+            return (long long)(g.rank * g.n_mlp + cta) * g.n1 + tile * 16;
         case F_W2:
             return (long long)tile * 16;
         default:
@@ -137,7 +138,7 @@ QW3_HD long long fused_k0(const FusedGeom& g, int op, int cta) {
     switch (op) {
         case F_QKV: return (long long)(cta % g.gs) * (g.H / g.gs);
         case F_WO:  return (long long)(g.rank * g.heads_local + cta / g.gs) * 128;
-        case F_W2:  return (long long)(g.rank * g.n_act + cta) * g.n1;
+        case F_W2:  return (long long)(g.rank * g.n_mlp + cta) * g.n1;
         default:    return 0;
     }
 }

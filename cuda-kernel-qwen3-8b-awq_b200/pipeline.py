@@ -4,7 +4,9 @@ The reference splits its 36 layers over exactly two GPUs inside one process (Inf
 376-378).  Here every rank owns one stage (rank r runs the layers qw3_stage_layers gives it, the
 embedding lives on rank 0, final norm + unembed + arg-max on the last rank).  torch.distributed is
 only the plumbing that exchanges the 64-byte CUDA IPC handles of the stages' mailboxes; the data
-path itself is peer stores over NVLink issued by the engine's own kernels, no collective.
+path itself is peer stores over NVLink issued by the engine's own kernels, no collective.  The same
+plumbing serves the row-split mode (connect_all), where every rank runs all layers on its share of
+every matrix and the partial sums cross NVLink inside the pass kernel.
 """
 import ctypes as C
 
@@ -42,6 +44,17 @@ def connect_ring(infer, dist, group=None):
     hn = (C.c_uint8 * 64).from_buffer_copy(handles[nxt])
     hp = (C.c_uint8 * 64).from_buffer_copy(handles[prv])
     cabi.check(cabi.lib().qw3_stage_connect(infer._h, hn, hp), "qw3_stage_connect")
+
+
+def connect_all(infer, dist, group=None):
+    """Row-split tensor parallelism: exchange the handles of the ranks' exchange buffers and map every peer's."""
+    world = dist.get_world_size(group)
+    buf = (C.c_uint8 * 64)()
+    cabi.check(cabi.lib().qw3_tp_export(infer._h, buf), "qw3_tp_export")
+    handles = exchange_handles(bytes(buf), dist, group)
+    flat = (C.c_uint8 * (64 * world)).from_buffer_copy(b"".join(handles))
+    cabi.check(cabi.lib().qw3_tp_connect(infer._h, flat), "qw3_tp_connect")
+    dist.barrier(group)   # nobody generates before every rank has mapped every buffer
 
 
 def broadcast_ids(ids, n, dist, group=None):

@@ -190,6 +190,8 @@ typedef struct Qw3Config {
     int32_t persistent;    /* 2 (default): a token pass of a stage is one launch of the fused kernel (operators of a layer
                               paired, weights repacked at load time; falls back to 1 for shapes it does not cover);
                               1: one persistent kernel walking an operator list; 0: one launch per operator */
+    int32_t tensor_parallel; /* with world > 1: 1 = every matrix row-split over the `world` GPUs instead of the layer pipeline (see
+                                qw3_tp_export); needs n_stages = 1, device[0] = this process's GPU, persistent = 2 */
 } Qw3Config;
 
 typedef struct qw3_engine* qw3_handle;
@@ -261,6 +263,23 @@ int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entr
  * elsewhere). */
 int qw3_stage_export(qw3_handle h, void* out_handle_64B);
 int qw3_stage_connect(qw3_handle h, const void* next_stage_handle_64B, const void* prev_stage_handle_64B);
+
+/* Row-split tensor parallelism (world > 1, tensor_parallel = 1): one process per GPU; every process loads the whole
+ * weight directory, keeps its share of every matrix in the fused pass's layout (its heads of Wqkv / Wo and of the KV
+ * cache, its outputs of W1 / inputs of W2, its blocks of the unembedding) and runs ALL layers.  The two reductions per
+ * layer cross NVLink inside the pass kernel: partial sums and the gathered hidden state are stored as tagged words into
+ * every GPU's exchange buffer (plain peer stores) and polled locally, so each GPU streams 1/world of the weights per
+ * token.  The reference has no such mode (its only multi-GPU form is the layer pipeline, Inference.cu:43-47);
+ * the pipeline stays available with tensor_parallel = 0.
+ * qw3_tp_export returns the 64-byte CUDA IPC handle of this rank's exchange buffer; the caller gathers the handles of
+ * all ranks (any transport) and passes them, rank-major (world x 64 bytes), to qw3_tp_connect.  All ranks must have
+ * connected before any of them generates, every rank then calls qw3_generate / qw3_decode_more with the same
+ * arguments (each returns the ids), and no rank may destroy its handle while another is still generating.  Prompts
+ * run token by token through the same kernel, or, with qw3_set_batched_prefill, in blocks that every rank computes in
+ * full (the prompt phase is then replicated, not split).  qw3_last_logits returns this rank's blocks of the logits
+ * only (NaN elsewhere). */
+int qw3_tp_export(qw3_handle h, void* out_handle_64B);
+int qw3_tp_connect(qw3_handle h, const void* handles_world_x_64B);
 
 /* Test hooks of the fused token pass (persistent = 2), pure host arithmetic: how it cuts a configuration over `grid`
  * CTAs and `n_ranks` GPUs -- geom_out receives 16 ints {hidden, inter, heads, vocab, n_ranks, rank, heads per rank,

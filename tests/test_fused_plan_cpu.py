@@ -18,7 +18,7 @@ def _plan(pkg, cfg_kw, n_ranks=1, rank=0, grid=148):
     geom = (C.c_int32 * 16)()
     plans = (C.c_int32 * 50)()
     cabi.check(cabi.lib().qw3_fused_plan(C.byref(cfg), n_ranks, rank, grid, geom, plans), "qw3_fused_plan")
-    names = ["H", "I", "heads", "vocab", "n_ranks", "rank", "heads_local", "gs", "n_act", "rs", "n1", "n_blocks", "grid"]
+    names = ["H", "I", "heads", "vocab", "n_ranks", "rank", "heads_local", "gs", "n_act", "rs", "n1", "n_blocks", "grid", "n_mlp"]
     g = dict(zip(names, list(geom)))
     pn = ["n_cta", "n_mt", "n_ks", "wk", "tb", "nb", "nq", "rem", "warp_bytes", "n_units"]
     return cfg, g, [dict(zip(pn, list(plans)[10 * k:10 * k + 10])) for k in range(5)]
@@ -36,9 +36,19 @@ def test_plan_of_the_full_model(pkg):
         assert p["rem"] in (0, 2) and (p["rem"] == 0 or p["tb"] % 2 == 0)
 
 
+@pytest.mark.parametrize("n_ranks", [2, 4, 8])
+def test_plan_of_the_full_model_row_split(pkg, n_ranks):
+    """Every matrix row-split over 2, 4 and 8 GPUs: all 128 CTAs of a GPU share its heads, the bytes divide by the GPUs."""
+    _, g, pl = _plan(pkg, dict(max_pos=40960), n_ranks, n_ranks - 1)
+    assert g["n_act"] == 128 and g["gs"] == 4 * n_ranks and g["rs"] == 32 // n_ranks
+    assert g["n_mlp"] * g["n1"] * n_ranks == 12288 and g["n1"] % 32 == 0
+    per_gpu = 16 * (128 * (pl[QKV]["warp_bytes"] + pl[WO]["warp_bytes"]) + g["n_mlp"] * (pl[W1]["warp_bytes"] + pl[W2]["warp_bytes"]))
+    assert per_gpu * n_ranks == 25165824 + 8388608 + 25165824 + 25165824
+
+
 def test_unsupported_shapes_are_refused(pkg):
     cabi = pkg.cabi
-    cfg = cabi.default_config(hidden=384, heads=3, inter=1536, vocab=2176, layers=2, max_pos=64)   # 3 heads: 384 / gs not a multiple of 128 for gs > 1, inter / 3 ...
+    cfg = cabi.default_config(hidden=384, heads=3, inter=1536, vocab=2176, layers=2, max_pos=64)   # an odd head count
     geom = (C.c_int32 * 16)()
     plans = (C.c_int32 * 50)()
     rc = cabi.lib().qw3_fused_plan(C.byref(cfg), 1, 0, 148, geom, plans)
@@ -54,7 +64,7 @@ def _tile_out(g, op, cta, tile, blk):
     if op == WO:
         return (cta % g["gs"]) * (g["H"] // g["gs"]) + tile * 16
     if op == W1:
-        return (g["rank"] * g["n_act"] + cta) * g["n1"] + tile * 16
+        return (g["rank"] * g["n_mlp"] + cta) * g["n1"] + tile * 16
     if op == W2:
         return tile * 16
     return blk * 128 + tile * 16
@@ -66,7 +76,7 @@ def _k0(g, op, cta):
     if op == WO:
         return (g["rank"] * g["heads_local"] + cta // g["gs"]) * 128
     if op == W2:
-        return (g["rank"] * g["n_act"] + cta) * g["n1"]
+        return (g["rank"] * g["n_mlp"] + cta) * g["n1"]
     return 0
 
 

@@ -1,6 +1,7 @@
 """Two stages in two processes on two GPUs: the hidden state and the sampled id cross NVLink by peer
 stores into CUDA-IPC mailboxes (by hand-off launches, or by the token-pass kernels themselves); the ids must equal the single-GPU run and the oracle's golden ids.
 Needs two visible GPUs (skipped otherwise).  gloo carries the handle exchange."""
+import datetime
 import json
 import multiprocessing as mp
 import os
@@ -25,7 +26,7 @@ def _rank_main(rank, world, port, wdir, prompt, q, sample_first, chained):
     import importlib
     pipeline = importlib.import_module("qw3awq_b200.pipeline")
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
     try:
         torch.cuda.set_device(rank)
         inf = pkg.QWen3AWQInfer(wdir, n_stages=world, world=world, rank=rank, device=list(range(world)),
@@ -64,10 +65,16 @@ def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_f
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, wdir, prompt, q, sample_first, chained)) for r in range(world)]
     for p in procs:
         p.start()
-    got = sorted(q.get(timeout=300) for _ in range(world))
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        got = sorted(q.get(timeout=300) for _ in range(world))
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:   # a rank that died must not leave the others waiting in a barrier with their GPUs held
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join()
     for rank, ids in got:
         assert ids == want, (rank, ids, want)
 
@@ -83,7 +90,7 @@ def _rank_main_batched(rank, world, port, wdir, prompt, q, max_pos):
     import importlib
     pipeline = importlib.import_module("qw3awq_b200.pipeline")
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
     try:
         torch.cuda.set_device(rank)
         cfg = dict(SMALL, max_pos=max_pos)
@@ -130,9 +137,15 @@ def test_one_process_per_gpu_batched_prompt(pkg, orc, cuda, tmp_path, world, n_p
     procs = [ctx.Process(target=_rank_main_batched, args=(r, world, port, wdir, prompt, q, max_pos)) for r in range(world)]
     for p in procs:
         p.start()
-    got = sorted(q.get(timeout=300) for _ in range(world))
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        got = sorted(q.get(timeout=300) for _ in range(world))
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join()
     for rank, ids, ids2 in got:
         assert ids == want and ids2 == want, (rank, ids, ids2, want)
