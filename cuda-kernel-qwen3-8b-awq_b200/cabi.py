@@ -20,12 +20,12 @@ MAX_STAGES = 8
 # Every symbol include/qw3_cabi.h declares.
 EXPORTS = [
     "qw3_strerror", "qw3_last_error", "qw3_dequant_w4", "qw3_w4_create", "qw3_w4_destroy", "qw3_ws_create",
-    "qw3_ws_destroy", "qw3_ws_set_pdl", "qw3_ws_check", "qw3_gemv_w4a16", "qw3_gemv_w4a16_noalloc", "qw3_gemm_w4a16", "qw3_rmsnorm",
+    "qw3_ws_destroy", "qw3_ws_set_pdl", "qw3_ws_check", "qw3_gemv_w4a16", "qw3_gemv_w4a16_noalloc", "qw3_gemv_w4a16_noalloc_status", "qw3_gemm_w4a16", "qw3_rmsnorm",
     "qw3_rope_kv_append", "qw3_attn_decode", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
     "qw3_create", "qw3_destroy", "qw3_generate", "qw3_decode_more", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
     "qw3_set_batched_prefill",
     "qw3_set_chained_decode",
-    "qw3_kv_upload", "qw3_layer_decode", "qw3_debug_trace", "qw3_stage_export", "qw3_stage_connect", "qw3_stage_layers",
+    "qw3_kv_upload", "qw3_layer_decode", "qw3_stage_export", "qw3_stage_connect", "qw3_stage_layers",
     "qw3_fused_plan", "qw3_fused_repack_host", "qw3_stage_hidden", "qw3_tp_export", "qw3_tp_connect",
 ]
 
@@ -89,6 +89,7 @@ def lib():
         "qw3_ws_check": [vp, vp],
         "qw3_gemv_w4a16": [vp, C.POINTER(GemvArgs), vp, vp],
         "qw3_gemv_w4a16_noalloc": [vp, vp, vp, i64, i64, i64, C.c_int, vp, vp, vp],
+        "qw3_gemv_w4a16_noalloc_status": [vp],
         "qw3_gemm_w4a16": [vp, vp, i64, vp, vp, vp],
         "qw3_rmsnorm": [vp, vp, i64, f32, vp, vp],
         "qw3_rope_kv_append": [vp, vp, vp, vp, vp, vp, i32, i32, i64, vp, i32, vp],
@@ -107,7 +108,6 @@ def lib():
         "qw3_last_launches": [vp, C.POINTER(i64)],
         "qw3_kv_upload": [vp, i32, i32, vp, i64],
         "qw3_layer_decode": [vp, i32, i32, vp],
-        "qw3_debug_trace": [vp, i32, vp, i32, C.POINTER(i32)],
         "qw3_stage_export": [vp, vp],
         "qw3_stage_connect": [vp, vp, vp],
         "qw3_stage_layers": [C.POINTER(Config), i32, C.POINTER(i32), C.POINTER(i32)],
@@ -120,6 +120,8 @@ def lib():
     for name, args in sig.items():
         fn = getattr(L, name)
         fn.restype, fn.argtypes = C.c_int, args
+    if hasattr(L, "qw3_debug_trace"):   # tracing builds only (make EXTRA=-DQW3_TRACE)
+        L.qw3_debug_trace.restype, L.qw3_debug_trace.argtypes = C.c_int, [vp, i32, vp, i32, C.POINTER(i32)]
     _lib = L
     return L
 

@@ -35,6 +35,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "pass_flags.h"
 
 namespace qw3 {
 
@@ -53,8 +54,6 @@ constexpr int P_RED_BYTES = 65536;       // cross-warp reduction (16 slots x 4 K
 constexpr int P_OPW = 48;                // 32-bit words of a descriptor after its tensor map
 constexpr int P_DONE = 256;              // largest number of tiles / heads of an operator
 constexpr int P_MAX_OPS = 256;           // operators of one pass (their unit ranges are cached in shared memory)
-constexpr int P_TAG_OPS = 1024;          // tags: launch epoch * P_TAG_OPS + operator index
-constexpr int P_SRC_PEER = P_TAG_OPS - 1; // `src` / `rsrc` of words the stage before this one stores from another GPU
 constexpr int P_PSLOTS = WS_MAX_CTAS + P_DONE;   // partial-sum slots (CTA + tile) of an operator
 
 constexpr size_t P_OFF_RED = (size_t)P_RING * P_UNIT_BYTES;
@@ -67,13 +66,6 @@ constexpr size_t P_OFF_RNG = P_OFF_MISC + 2048;                 // per-operator 
 constexpr size_t P_SMEM_BYTES = P_OFF_RNG + (size_t)P_MAX_OPS * 16;
 
 enum PassOpKind { PASS_EMBED = 0, PASS_GEMV = 1, PASS_ATTN = 2 };
-
-enum PassOpFlags {
-    PASS_WAIT_PREV = 1,   // inputs are plain memory written by the operator before: wait for its arrival counter
-    PASS_PUBLISH = 2,     // the operator after (or the final arg-max) waits on this operator's arrival counter
-    PASS_PEER_OUT = 4,    // yt is the next stage's inbox in another GPU's memory: system-scope stores, peer tag
-    PASS_TOKEN_PEER = 8,  // embedding of a decode pass: the id arrives as a tagged word the last stage stores
-};
 
 struct PassOpBody {          // 192 bytes, copied to shared memory per operator
     int32_t kind, uniform, exact, epilogue;
@@ -135,12 +127,17 @@ struct PassParams {
     Workspace ws;
 };
 
+// Tracing builds (-DQW3_TRACE) record global-timer stamps inside every operator; other builds hold none of this code.
 __device__ __forceinline__ void trace_event(const PassParams& p, int o, int ev) {
+#ifdef QW3_TRACE
     if (p.trace2 != nullptr && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
         p.trace2[((size_t)blockIdx.x * p.n_ops + o) * 8 + ev] = t;
     }
+#else
+    (void)p; (void)o; (void)ev;
+#endif
 }
 
 __device__ __forceinline__ void red_add_release(int* p, int v) {
@@ -1230,11 +1227,13 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
         // Every operator ends with a CTA barrier after its last use of shared memory: the descriptor of this
         // operator (copied during the one before) is visible, and the buffer of the one before is free.
         trace_event(p, o, 0);
+#ifdef QW3_TRACE
         if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
             p.trace[o] = t;
         }
+#endif
         const PassOpBody& op = *reinterpret_cast<const PassOpBody*>(sm.s_op + (o & 1) * P_OPW);
         if (o + 1 < p.n_ops && tid < P_OPW)   // next descriptor, visible after the barriers of this operator
             sm.s_op[((o + 1) & 1) * P_OPW + tid] = reinterpret_cast<const uint32_t*>(&p.ops[o + 1].b)[tid];
@@ -1254,11 +1253,13 @@ __global__ void __launch_bounds__(P_NTHREADS, 1) decode_pass_kernel(const PassPa
             embed_phase(p, op, o, sm, pos);
         }
     }
+#ifdef QW3_TRACE
     if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
         p.trace[p.n_ops] = t;
     }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -17,6 +17,7 @@
 
 #include "common.cuh"
 #include "fused_pass.h"
+#include "pass_flags.h"
 
 namespace qw3 {
 
@@ -361,7 +362,7 @@ static int build_pass_program(qw3_engine* e, int si, bool decode, void** d_ops, 
     auto at = [&](int i) { return reinterpret_cast<PassOp*>(base + (size_t)i * ob); };
     // Inside a launch activations go from operator to operator as tagged words (hidden_t, qkv_t, ctx_t, mlp_t); only
     // the final arg-max waits on an arrival counter (the unembedding's).
-    constexpr int PUBLISH = 2, PEER_OUT = 4, TOKEN_PEER = 8, SRC_PEER = 1023;   // PassOpFlags, P_SRC_PEER
+    constexpr int PUBLISH = PASS_PUBLISH, PEER_OUT = PASS_PEER_OUT, TOKEN_PEER = PASS_TOKEN_PEER, SRC_PEER = P_SRC_PEER;
     bool hidden_tagged = false;            // hidden_t holds the residual stream (written in this launch)
     int hidden_src = -1;                   // operator that wrote it last
     const unsigned long long* hidden_in = s.hidden_t;   // where the tagged residual stream is read from
@@ -796,13 +797,15 @@ static int create_impl(const char* weight_dir, qw3_engine* e) {
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_xchg), pass_xchg_bytes()));
                 QW3_CUDA(cudaMemset(s.d_xchg, 0, pass_xchg_bytes()));
             }
-            if (std::getenv("QW3_TRACE")) {
+#ifdef QW3_TRACE
+            {
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_trace), (size_t)(s.n_ops_decode + 1) * 8));
                 QW3_CUDA(cudaMemset(s.d_trace, 0, (size_t)(s.n_ops_decode + 1) * 8));
                 const size_t t2 = (size_t)256 * s.n_ops_decode * 8 * 8;
                 QW3_TRY(dev_alloc(e, s.device, reinterpret_cast<void**>(&s.d_trace2), t2));
                 QW3_CUDA(cudaMemset(s.d_trace2, 0, t2));
             }
+#endif
             s.persistent = true;
         }
     }
@@ -1148,6 +1151,7 @@ int qw3_stage_hidden(qw3_handle e, int32_t stage, void* host_hidden) {
     return QW3_OK;
 }
 
+#ifdef QW3_TRACE
 int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries) {
     QW3_REQUIRE(e && out && n_entries && stage >= 0 && stage < (int)e->st.size(), "qw3_debug_trace: bad argument");
     Stage& s = e->st[stage];
@@ -1167,7 +1171,7 @@ int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entr
         return QW3_OK;
     }
     if (!s.d_trace) {
-        set_last_error("qw3_debug_trace: create the handle with QW3_TRACE set in the environment and persistent = 1");
+        set_last_error("qw3_debug_trace: the stage runs neither pass kernel");
         return QW3_ERR_STATE;
     }
     QW3_CUDA(cudaSetDevice(s.device));
@@ -1184,6 +1188,7 @@ int qw3_debug_trace(qw3_handle e, int32_t stage, uint64_t* out, int32_t max_entr
     *n_entries = n;
     return QW3_OK;
 }
+#endif  // QW3_TRACE
 
 int qw3_stage_layers(const Qw3Config* cfg, int32_t stage, int32_t* first, int32_t* count) {
     QW3_REQUIRE(cfg && first && count, "qw3_stage_layers: null pointer");

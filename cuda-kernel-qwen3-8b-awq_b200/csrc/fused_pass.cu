@@ -83,6 +83,7 @@ struct FusedParams {
     FGemvPlan plan[F_NOPS];
     int n_alloc[F_NOPS];          // scale / zero-point entries of each matrix kind
     int n_rounds;                 // unembedding rounds (0: this pass does not sample)
+    int hpr_shift, rs_shift;      // log2 of H / n_ranks and of rs when those are powers of two, else -1
     float eps;
     // embedding (first stage) and unembedding (last stage)
     const uint8_t* emb_packed; const __half* emb_scale; const __half* emb_zp; int emb_n_alloc;
@@ -160,7 +161,7 @@ struct FCtx {
     float* obuf;
     __half* hv;
     __half* xs;
-    int4* seg;          // {base lo, base hi, warp_bytes, 0} per weight segment of this CTA
+    int4* seg;          // {base lo, base hi, warp_bytes, unit_bytes} per weight segment of this CTA
     float2* lsz;        // [2][4][FP_MAX_GROUPS] (scale, zero point) of the layer's four matrices, two layers (current / next)
     FLayerDesc* ldesc;  // [2] descriptor of the current / next layer
     __half* qkv_s;      // [384] q, k, v of this CTA's head (after RoPE)
@@ -188,19 +189,26 @@ __device__ __forceinline__ void fail(const FusedParams& p, const FCtx& cx, int c
     *cx.s_dead = 1;
 }
 
-// Up to NB words polled together (all loads in flight at once) until every one carries `tag`; bounded.
+// Up to NB words polled together (all loads in flight at once) until every one carries `tag`; bounded.  A word that
+// has arrived is not loaded again: re-reading the arrived ones in every round was measured to cost 2-3 us per
+// grid-wide reduction (the rounds compete in L2 with the stores they wait for).
 template <bool SYS, int NB, typename AddrFn>
 __device__ __forceinline__ void poll_batch(const FusedParams& p, const FCtx& cx, const int n_valid, AddrFn addr, const uint32_t tag,
                                            const int code, unsigned long long (&w)[NB]) {
     const long long t_begin = clock64();
+    bool have[NB];
+#pragma unroll
+    for (int e = 0; e < NB; ++e) have[e] = e >= n_valid;
     for (;;) {
         bool ok = true;
 #pragma unroll
-        for (int e = 0; e < NB; ++e)
-            if (e < n_valid) {
+        for (int e = 0; e < NB; ++e) {
+            if (!have[e]) {
                 w[e] = ldt<SYS>(addr(e));
-                ok = ok && has_tag(w[e], tag);
+                have[e] = has_tag(w[e], tag);
             }
+            ok = ok && have[e];
+        }
         if (ok || *cx.s_dead != 0) break;
         if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
             fail(p, cx, code);
@@ -231,7 +239,8 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 // Moves the cursor to the next unit this CTA has (segments it takes no part in have no bytes).  Returns false past the end.
 __device__ __forceinline__ bool ring_cursor_valid(WarpRing& r, const FCtx& cx) {
     while (r.pseg < cx.n_seg) {
-        if (r.pu * F_UNIT < cx.seg[r.pseg].z) return true;
+        const int4 sg = cx.seg[r.pseg];
+        if (r.pu * sg.w < sg.z) return true;
         ++r.pseg;
         r.pu = 0;
     }
@@ -241,7 +250,7 @@ __device__ __forceinline__ bool ring_cursor_valid(WarpRing& r, const FCtx& cx) {
 __device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, const int slot) {
     const int4 sg = cx.seg[r.pseg];
     const uint8_t* base = reinterpret_cast<const uint8_t*>(((unsigned long long)(uint32_t)sg.y << 32) | (uint32_t)sg.x);
-    const int piece = min(F_UNIT, sg.z - r.pu * F_UNIT);
+    const int piece = sg.w;
     const uint32_t bar = cx.bars + 8 * slot;
     // The slot was read with ordinary loads whose values have all been consumed (every warp counted itself off after
     // its last MMA on the piece), so the bulk write cannot overtake them; no proxy fence is needed for this
@@ -251,7 +260,7 @@ __device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, co
 #endif
     *cx.ring_issued += 1;
     mbar_expect_tx(bar, F_NW * piece);
-    bulk_load(smem_u32(cx.ring) + slot * (F_NW * F_UNIT), base + (size_t)r.pu * (F_NW * F_UNIT), F_NW * piece, bar, r.policy);
+    bulk_load(smem_u32(cx.ring) + slot * (F_NW * F_UNIT), base + (size_t)r.pu * (F_NW * piece), F_NW * piece, bar, r.policy);
 }
 
 // Shared address of this warp's piece (of `piece` bytes) of the unit it consumes next, once the unit has landed.
@@ -337,39 +346,19 @@ __device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0,
 }
 
 // This warp's stream of one operator: nb blocks of TB tiles, each over nq groups of four k-steps (+ a half group when
-// rem == 2).  xs_addr: shared address of the fp16 activations of the warp's k-share.  dst[(block * TB + i) * 16 + row]
-// receives sum_j q[row][j] * x[j] of tile i of the block.  Every tile has two accumulators (even / odd k-steps), and
-// the k-steps of a group are issued tile after tile, so 2 * TB independent MMA chains are in flight.
+// rem == 2).  The stream comes in ring units of whole groups (gu of them; a block with a half group is one unit), so
+// that one barrier wait is followed by straight-line code: every load of the unit can be issued ahead of its MMAs.
+// xs_addr: shared address of the fp16 activations of the warp's k-share.  dst[(block * TB + i) * 16 + row] receives
+// sum_j q[row][j] * x[j] of tile i of the block.  Tiles of a block are issued one after another per k-step, so TB
+// (2 * TB for narrow blocks) independent MMA chains are in flight.
 template <int TB>
-__device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int nb, const int nq,
-                                       const int rem, const int warp_bytes, const uint32_t xs_addr, float* dst) {
+__device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, WarpRing& ring, const FGemvPlan& pl,
+                                          const uint32_t xs_addr, float* dst) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    int left = warp_bytes, ubytes = 0, uoff = 0;
-    uint32_t ubase = 0;
-#ifdef QW3_TRACE_UNITS
-    long long pr_rel = 0, pr_wait = 0, pr_units = 0;
-    const long long pr_t0 = clock64();
-#define FP_PROF(acc, stmt) do { const long long c0__ = clock64(); stmt; acc += clock64() - c0__; } while (0)
-#else
-#define FP_PROF(acc, stmt) stmt
-#endif
-    auto item = [&](const int sz) -> uint32_t {
-        if (uoff == ubytes) {
-            if (ubytes != 0) FP_PROF(pr_rel, ring_release(ring, cx));
-            ubytes = min(F_UNIT, left);
-            left -= ubytes;
-            FP_PROF(pr_wait, ubase = ring_wait(ring, p, cx, ubytes));
-            uoff = 0;
-#ifdef QW3_TRACE_UNITS
-            ++pr_units;
-#endif
-        }
-        const uint32_t a = ubase + uoff;
-        uoff += sz;
-        return a;
-    };
+    const int nq = pl.nq, rem = pl.rem;
+    const int upb = rem ? 1 : nq / pl.gu, ng = rem ? nq : pl.gu;   // units per block, full groups per unit
     constexpr int NA = TB <= 2 ? 2 : 1;   // accumulators per tile: at least three independent chains in flight
-    for (int b = 0; b < nb; ++b) {
+    for (int b = 0; b < pl.nb; ++b) {
         float acc[TB][NA][4];
 #pragma unroll
         for (int i = 0; i < TB; ++i)
@@ -377,32 +366,40 @@ __device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, 
             for (int h = 0; h < NA; ++h)
 #pragma unroll
                 for (int d = 0; d < 4; ++d) acc[i][h][d] = 0.0f;
-        for (int q = 0; q < nq; ++q) {
-            // B fragment of the group: lanes 0-3 (column 0) hold the activations, the other columns are zero
-            const uint32_t ba = g == 0 ? xs_addr + q * 128 + t * 32 : cx.zero_addr;
-            const uint4 b03 = lds128(ba), b47 = lds128(ba + 16);
-            uint4 w[TB];
+        for (int uu = 0; uu < upb; ++uu) {
+            const uint32_t ubase = ring_wait(ring, p, cx, pl.unit_bytes);
+            uint32_t a = ubase + lane * 16;
+            const uint32_t xq = xs_addr + uu * ng * 128;
+            for (int gq = 0; gq < ng; ++gq) {
+                // B fragment of the group: lanes 0-3 (column 0) hold the activations, the other columns are zero
+                const uint32_t ba = g == 0 ? xq + gq * 128 + t * 32 : cx.zero_addr;
+                const uint4 b03 = lds128(ba), b47 = lds128(ba + 16);
+                uint4 w[TB];
 #pragma unroll
-            for (int i = 0; i < TB; ++i) w[i] = lds128(item(512) + lane * 16);
+                for (int i = 0; i < TB; ++i) w[i] = lds128(a + i * 512);
+                a += TB * 512;
 #pragma unroll
-            for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
+                for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
 #pragma unroll
-            for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
+                for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
 #pragma unroll
-            for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].z, b47.x, b47.y);
+                for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].z, b47.x, b47.y);
 #pragma unroll
-            for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].w, b47.z, b47.w);
-        }
-        if (rem == 2) {
-            const uint32_t ba = g == 0 ? xs_addr + nq * 128 + t * 16 : cx.zero_addr;
-            const uint4 b03 = lds128(ba);
-            uint2 w[TB];
+                for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].w, b47.z, b47.w);
+            }
+            if (rem == 2) {
+                const uint32_t ba = g == 0 ? xs_addr + nq * 128 + t * 16 : cx.zero_addr;
+                const uint4 b03 = lds128(ba);
+                const uint32_t h = ubase + nq * TB * 512 + lane * 8;
+                uint2 w[TB];
 #pragma unroll
-            for (int i = 0; i < TB; ++i) w[i] = lds64(item(256) + lane * 8);
+                for (int i = 0; i < TB; ++i) w[i] = lds64(h + i * 256);
 #pragma unroll
-            for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
+                for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
 #pragma unroll
-            for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
+                for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
+            }
+            ring_release(ring, cx);
         }
         if (t == 0) {
 #pragma unroll
@@ -412,13 +409,6 @@ __device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, 
             }
         }
     }
-    if (ubytes != 0) FP_PROF(pr_rel, ring_release(ring, cx));
-#ifdef QW3_TRACE_UNITS
-    if (lane == 0 && p.trace != nullptr && blockIdx.x < 2) {   // per-warp cycle counts of CTAs 0 and 1, summed over the pass
-        unsigned long long* pf = p.trace + (size_t)gridDim.x * p.n_layers * 16 + ((size_t)blockIdx.x * F_NW + (threadIdx.x >> 5)) * 4;
-        pf[0] += pr_rel; pf[1] += pr_wait; pf[2] += clock64() - pr_t0; pf[3] += pr_units;
-    }
-#endif
 }
 
 // Runs this warp's share of an operator: warp (a, bk) of the plan; sums land in obuf[bk][tile * 16 + row].
@@ -430,10 +420,10 @@ __device__ __forceinline__ void run_gemv(const FusedParams& p, const FCtx& cx, W
     const uint32_t xs_addr = smem_u32(x_cta) + bk * ksw * 32;
     float* dst = cx.obuf + bk * (pl.n_mt * 16) + a * (pl.nb * pl.tb) * 16;
     switch (pl.tb) {
-        case 1: gemv_core<1>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
-        case 2: gemv_core<2>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
-        case 3: gemv_core<3>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
-        default: gemv_core<4>(p, cx, ring, pl.nb, pl.nq, pl.rem, pl.warp_bytes, xs_addr, dst); break;
+        case 1: gemv_core<1>(p, cx, ring, pl, xs_addr, dst); break;
+        case 2: gemv_core<2>(p, cx, ring, pl, xs_addr, dst); break;
+        case 3: gemv_core<3>(p, cx, ring, pl, xs_addr, dst); break;
+        default: gemv_core<4>(p, cx, ring, pl, xs_addr, dst); break;
     }
 }
 __device__ __forceinline__ float sum_k_shares(const FCtx& cx, const FGemvPlan& pl, int i) {
@@ -442,11 +432,11 @@ __device__ __forceinline__ float sum_k_shares(const FCtx& cx, const FGemvPlan& p
     return s;
 }
 
-// Scale and zero point of output `o` of a matrix whose groups do not depend on the input index:
-// group = ((o / 128) mod (in_dim / 128)) mod entries  (dequantAwqKernel's c / 128 with the wrapped index, Inference.cu:90).
-__device__ __forceinline__ void group_consts(const float2* table, long long o, int kb, int n_alloc, float& s, float& z) {
-    const int g = (int)((o >> 7) % kb) % n_alloc;
-    const float2 v = table[g];
+// Scale and zero point of output `o` of a matrix whose groups do not depend on the input index.  The table holds one
+// entry per block of 128 outputs: entry b = (scale, zero point) of group ((b mod (in_dim / 128)) mod entries), i.e.
+// dequantAwqKernel's c / 128 with the wrapped index (Inference.cu:90), resolved once at load time (fused_consts_kernel).
+__device__ __forceinline__ void group_consts(const float2* table, long long o, float& s, float& z) {
+    const float2 v = table[o >> 7];
     s = v.x;
     z = v.y;
 }
@@ -504,15 +494,16 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
         if (ch < nch) gm[e] = __ldg(reinterpret_cast<const uint2*>(gamma) + ch);
     }
     const long long t_begin = clock64();
+    bool have[2] = {tid >= nch, tid + FP_NT >= nch};
     for (;;) {
         bool ok = true;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int ch = tid + e * FP_NT;
-            if (ch < nch) {
-                ldt2<SYS>(hid + 2 * ch, w[e][0], w[e][1]);
-                ok = ok && has_tag(w[e][0], tag) && has_tag(w[e][1], tag);
+            if (!have[e]) {
+                ldt2<SYS>(hid + 2 * (tid + e * FP_NT), w[e][0], w[e][1]);
+                have[e] = has_tag(w[e][0], tag) && has_tag(w[e][1], tag);
             }
+            ok = ok && have[e];
         }
         if (ok || *cx.s_dead != 0) break;
         if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
@@ -570,12 +561,13 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
     __syncthreads();   // `out` and the warp sums are visible
     x_full = 0.0f;
     x_slice = 0.0f;
+    const int lo = slice * hs, hi = lo + hs;
 #pragma unroll
     for (int k = 0; k < 2 * F_NW; ++k) {
         const float v = cx.wsum[k];
         x_full += v;
         const int first = 4 * ((k & (F_NW - 1)) * 32 + (k / F_NW) * FP_NT);   // first element of that warp's row of chunks
-        if (slice >= 0 && first / hs == slice) x_slice += v;
+        if (first >= lo && first < hi) x_slice += v;                           // (slice < 0: the range is empty)
     }
 }
 
@@ -617,7 +609,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     if (tid < FP_QKV) {
         const int tile = tid >> 4, row = tid & 15;
         const long long o = (long long)(tile >> 3) * H + hglob * 128 + (tile & 7) * 16 + row;
-        group_consts(lsz + F_QKV * FP_MAX_GROUPS, o, H >> 7, p.n_alloc[F_QKV], sc, zp);
+        group_consts(lsz + F_QKV * FP_MAX_GROUPS, o, sc, zp);
     }
     run_gemv(p, cx, ring, p.plan[F_QKV], cx.xs + r * hs);
     __syncthreads();
@@ -806,10 +798,10 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         for (int i0 = 2 * tid; i0 < n_out; i0 += 2 * FP_NT) {
             const long long o = (long long)r * hs + i0;
             float s2, z2;
-            group_consts(lsz + F_WO * FP_MAX_GROUPS, o, H >> 7, p.n_alloc[F_WO], s2, z2);
+            group_consts(lsz + F_WO * FP_MAX_GROUPS, o, s2, z2);
             const float zo = z2 + a_offset(i0 & 15);   // i0 and i0 + 1 are rows of one half of a tile
             const float y0 = s2 * (sum_k_shares(cx, plo, i0) - zo * x_o), y1 = s2 * (sum_k_shares(cx, plo, i0 + 1) - zo * x_o);
-            const int ro = (int)(o / (H / G.n_ranks));   // rank that owns these two elements of the residual stream
+            const int ro = p.hpr_shift >= 0 ? (int)(o >> p.hpr_shift) : (int)(o / (H / G.n_ranks));   // rank that owns these two elements
             stt2<SYS>(p.xo[ro] + (size_t)(hglob * gs + r) * n_out + i0, tagged_f(y0, t0 + 2), tagged_f(y1, t0 + 2));
         }
         __syncthreads();   // obuf is free again
@@ -820,7 +812,10 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
             unsigned long long w[8];
             const unsigned long long* src = p.xo[G.rank] + (size_t)r_src * n_out + off;
             poll_batch<SYS, 8>(p, cx, (nw - tid + FP_NT - 1) / FP_NT,
-                               [&](int e) { const int k = tid + e * FP_NT; return src + (size_t)(k / rs) * gs * n_out + (k % rs); }, t0 + 2,
+                               [&](int e) {
+                                   const int k = tid + e * FP_NT, hq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
+                                   return src + (size_t)hq * gs * n_out + (k - hq * rs);
+                               }, t0 + 2,
                                0x50000 | li, w);
 #pragma unroll
             for (int e = 0; e < 8; ++e)
@@ -843,7 +838,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     // ---- RMSNorm (same gamma) + this CTA's n1 outputs of W1 + GeLU (Inference.cu:1158-1197) ----------------------------------
     gather_norm<SYS>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, cx.xs, -1, H, x_full, x_slice);
     FP_STAMP(li, 9);
-    if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cmlp * n1 + tid, H >> 7, p.n_alloc[F_W1], sc, zp);
+    if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cmlp * n1 + tid, sc, zp);
     run_gemv(p, cx, ring, p.plan[F_W1], cx.xs);
     __syncthreads();
     float gv = 0.0f;
@@ -861,10 +856,10 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     FP_STAMP(li, 11);
     for (int i0 = 2 * tid; i0 < H; i0 += 2 * FP_NT) {
         float s2, z2;
-        group_consts(lsz + F_W2 * FP_MAX_GROUPS, i0, G.I >> 7, p.n_alloc[F_W2], s2, z2);
+        group_consts(lsz + F_W2 * FP_MAX_GROUPS, i0, s2, z2);
         const float zo = z2 + a_offset(i0 & 15);
         const float y0 = s2 * (cx.obuf[i0] - zo * x_g), y1 = s2 * (cx.obuf[i0 + 1] - zo * x_g);
-        const int ro = i0 / (H / G.n_ranks);
+        const int ro = p.hpr_shift >= 0 ? (i0 >> p.hpr_shift) : i0 / (H / G.n_ranks);
         stt2<SYS>(p.x2[ro] + (size_t)cmlp * H + i0, tagged_f(y0, t0 + 4), tagged_f(y1, t0 + 4));
     }
     __syncthreads();
@@ -876,7 +871,10 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         unsigned long long w[8];
         const unsigned long long* src = p.x2[G.rank] + o_first;
         poll_batch<SYS, 8>(p, cx, (nw - tid + FP_NT - 1) / FP_NT,
-                           [&](int e) { const int k = tid + e * FP_NT; return src + (size_t)(k / rs) * H + (k % rs); }, t0 + 4, 0x60000 | li, w);
+                           [&](int e) {
+                               const int k = tid + e * FP_NT, cq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
+                               return src + (size_t)cq * H + (k - cq * rs);
+                           }, t0 + 4, 0x60000 | li, w);
 #pragma unroll
         for (int e = 0; e < 8; ++e)
             if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
@@ -979,7 +977,12 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
         const long long blk = fused_unemb_block(G, c, round);
         if (blk < 0) break;
         // x'_j = scale[g(blk, j)] * x_j and Z = sum_j zp[g(blk, j)] * x'_j,  g(b, j) = ((b + j * Mb) mod Kb) mod entries
+        // (the groups repeat with period Kb along j: entry r of this round's table serves every j = r mod Kb)
         const int bmod = (int)(blk % Kb);
+        uint32_t* gtab = cx.un_sz + 64;
+        if (tid < Kb) gtab[tid] = cx.un_sz[((bmod + tid * mstep) % Kb) % n_alloc];
+        __syncthreads();
+        const bool kb_pow2 = (Kb & (Kb - 1)) == 0;
         float zacc = 0.0f, xacc = 0.0f;
         for (int ch = tid; ch < (H >> 3); ch += FP_NT) {
             const uint4 xv = *reinterpret_cast<const uint4*>(cx.hv + 8 * ch);
@@ -989,8 +992,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int j = 8 * ch + e;
-                const int gq = ((bmod + (j % Kb) * mstep) % Kb) % n_alloc;
-                const uint32_t sz = cx.un_sz[gq];
+                const uint32_t sz = gtab[kb_pow2 ? (j & (Kb - 1)) : (j % Kb)];
                 const __half xp = h_mul(__ushort_as_half((unsigned short)(sz & 0xffffu)), xh[e]);
                 oh[e] = xp;
                 zacc = fmaf(__half2float(__ushort_as_half((unsigned short)(sz >> 16))), __half2float(xp), zacc);
@@ -1090,7 +1092,7 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
     cx.rope_cs = reinterpret_cast<__half*>(misc + 2560);         // 256
     cx.wsum = reinterpret_cast<float*>(misc + 2816);             // 256
     cx.dsum = reinterpret_cast<double*>(misc + 3072);            // 128
-    cx.un_sz = reinterpret_cast<uint32_t*>(misc + 3200);         // 256
+    cx.un_sz = reinterpret_cast<uint32_t*>(misc + 5120);         // 512: groups in use | this round's table
     cx.argv = reinterpret_cast<float*>(misc + 3456);             // 64
     cx.argi = reinterpret_cast<int*>(misc + 3520);               // 64
     cx.s_dead = reinterpret_cast<int*>(misc + 3584);             // 16
@@ -1100,7 +1102,7 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
     cx.ring_cnt = reinterpret_cast<int*>(misc + 3840);           // FP_SLOTS * 4
     cx.ring_issued = reinterpret_cast<int*>(misc + 3968);
     cx.ldesc = reinterpret_cast<FLayerDesc*>(misc + 4096);       // 2 descriptors
-    static_assert(FP_SLOTS <= 16 && 4096 + 2 * sizeof(FLayerDesc) <= FP_MISC_BYTES, "misc area");
+    static_assert(FP_SLOTS <= 16 && 4096 + 2 * sizeof(FLayerDesc) <= 5120 && 5120 + 512 <= FP_MISC_BYTES, "misc area");
 
     const int tid = threadIdx.x, c = blockIdx.x;
     const FusedGeom& G = p.g;
@@ -1110,22 +1112,24 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
     // this CTA's share of every weight stream, in the order of consumption
     for (int i = tid; i < cx.n_seg; i += FP_NT) {
         const uint8_t* base = nullptr;
-        int wb = 0;
+        int wb = 0, ub = 1;
         if (i < 4 * p.n_layers) {
             const FGemvPlan& pl = p.plan[i & 3];
+            ub = pl.unit_bytes;
             if (c < pl.n_cta) {
                 wb = pl.warp_bytes;
                 base = p.layers[i >> 2].d.w[i & 3] + (size_t)c * F_NW * wb;
             }
         } else {
             const int round = i - 4 * p.n_layers;
+            ub = p.plan[F_UNEMB].unit_bytes;
             if (fused_unemb_block(G, c, round) >= 0) {
                 wb = p.plan[F_UNEMB].warp_bytes;
                 base = p.un_w + ((size_t)round * G.grid + c) * F_NW * wb;
             }
         }
         const unsigned long long b = reinterpret_cast<unsigned long long>(base);
-        cx.seg[i] = make_int4((int)(uint32_t)b, (int)(uint32_t)(b >> 32), wb, 0);
+        cx.seg[i] = make_int4((int)(uint32_t)b, (int)(uint32_t)(b >> 32), wb, ub);
     }
     if (tid == 0) {
         for (int s = 0; s < FP_SLOTS; ++s) {
@@ -1254,12 +1258,20 @@ __global__ void fused_repack_kernel(const FusedGeom g, const FGemvPlan pl, const
     out[wi] = fused_repack_word(g, pl, op, raw, out_dim, stream, warp, off);
 }
 
-// Fills the per-layer constant blocks from the descriptors (one block of FP_NT threads per layer).
-__global__ void fused_consts_kernel(FLayerConst* lc, const int4 n_alloc) {
+// Fills the per-layer constant blocks from the descriptors (one block of FP_NT threads per layer): entry b of matrix k
+// is the (scale, zero point) pair of its output block b, group = ((b mod (in_dim / 128)) mod entries).
+__global__ void fused_consts_kernel(FLayerConst* lc, const int4 n_alloc, const int4 kb, const int4 mb) {
     FLayerConst& L = lc[blockIdx.x];
-    const int tid = threadIdx.x, k = tid / FP_MAX_GROUPS, gq = tid % FP_MAX_GROUPS;
+    const int tid = threadIdx.x, k = tid / FP_MAX_GROUPS, b = tid % FP_MAX_GROUPS;
     const int na = k == 0 ? n_alloc.x : k == 1 ? n_alloc.y : k == 2 ? n_alloc.z : n_alloc.w;
-    L.sz[k][gq] = gq < na ? pack_h2(L.d.scale[k][gq], L.d.zp[k][gq]) : 0u;
+    const int kbk = k == 0 ? kb.x : k == 1 ? kb.y : k == 2 ? kb.z : kb.w;
+    const int mbk = k == 0 ? mb.x : k == 1 ? mb.y : k == 2 ? mb.z : mb.w;
+    uint32_t v = 0u;
+    if (b < mbk) {
+        const int gq = (b % kbk) % na;
+        v = pack_h2(L.d.scale[k][gq], L.d.zp[k][gq]);
+    }
+    L.sz[k][b] = v;
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------------------------
@@ -1270,15 +1282,26 @@ static bool make_plan(int n_cta, int n_mt, int n_ks, FGemvPlan* pl) {
         if (n_ks % wk) continue;
         const int ksw = n_ks / wk, rem = ksw % 4, mtw = n_mt / wm;
         if (rem != 0 && rem != 2) continue;
+        const int nq = ksw / 4;
         int tb = 0;
-        for (int t = 4; t >= 1; --t)
-            if (mtw % t == 0 && (rem == 0 || t % 2 == 0)) { tb = t; break; }   // 256-byte items come in pairs
+        for (int t = 4; t >= 1; --t)   // with a half group the whole block is one ring unit and must fit a slot
+            if (mtw % t == 0 && (rem == 0 || (t % 2 == 0 && t * (nq * 512 + rem * 128) <= F_UNIT))) { tb = t; break; }
         if (tb == 0) continue;
         if ((long long)wk * n_mt * 16 > FP_OBUF) continue;
         pl->n_cta = n_cta; pl->n_mt = n_mt; pl->n_ks = n_ks; pl->wk = wk; pl->tb = tb; pl->nb = mtw / tb;
-        pl->nq = ksw / 4; pl->rem = rem;
-        pl->warp_bytes = pl->nb * tb * (pl->nq * 512 + rem * 128);
-        pl->n_units = (pl->warp_bytes + F_UNIT - 1) / F_UNIT;
+        pl->nq = nq; pl->rem = rem;
+        pl->warp_bytes = pl->nb * tb * (nq * 512 + rem * 128);
+        if (rem) {
+            pl->gu = nq;
+            pl->unit_bytes = tb * (nq * 512 + rem * 128);
+        } else {
+            int gu = 1;
+            for (int c = 8; c >= 1; c >>= 1)
+                if (nq % c == 0 && c * tb * 512 <= F_UNIT) { gu = c; break; }
+            pl->gu = gu;
+            pl->unit_bytes = gu * tb * 512;
+        }
+        pl->n_units = pl->warp_bytes / pl->unit_bytes;
         return true;
     }
     return false;
@@ -1432,6 +1455,13 @@ int fused_create(const FusedCreate& a, FusedPass** out) {
     }
     P.n_layers = a.n_layers;
     P.eps = a.eps;
+    auto log2_exact = [](int v) {
+        int sh = 0;
+        while ((1 << sh) < v) ++sh;
+        return (1 << sh) == v ? sh : -1;
+    };
+    P.hpr_shift = log2_exact(g.H / g.n_ranks);
+    P.rs_shift = log2_exact(g.rs);
     P.n_rounds = a.unemb ? (g.n_blocks + g.n_ranks * g.grid - 1) / (g.n_ranks * g.grid) : 0;
     P.first_stage = a.emb ? 1 : 0;
     std::vector<FLayerConst> ld((size_t)a.n_layers);
@@ -1460,8 +1490,9 @@ int fused_create(const FusedCreate& a, FusedPass** out) {
         // pageable source: the copy is staged before the call returns
         if (cudaMemcpyAsync(d_layers, ld.data(), sizeof(FLayerConst) * ld.size(), cudaMemcpyHostToDevice, a.stream) != cudaSuccess)
             return bail(QW3_ERR_CUDA);
-        fused_consts_kernel<<<a.n_layers, FP_NT, 0, a.stream>>>(static_cast<FLayerConst*>(d_layers),
-                                                                make_int4(P.n_alloc[0], P.n_alloc[1], P.n_alloc[2], P.n_alloc[3]));
+        fused_consts_kernel<<<a.n_layers, FP_NT, 0, a.stream>>>(
+            static_cast<FLayerConst*>(d_layers), make_int4(P.n_alloc[0], P.n_alloc[1], P.n_alloc[2], P.n_alloc[3]),
+            make_int4(a.H / 128, a.H / 128, a.H / 128, a.I / 128), make_int4(3 * a.H / 128, a.H / 128, a.I / 128, a.H / 128));
         if (cudaGetLastError() != cudaSuccess) return bail(QW3_ERR_CUDA);
     }
     P.layers = static_cast<const FLayerConst*>(d_layers);
@@ -1582,7 +1613,7 @@ int qw3_fused_plan(const Qw3Config* cfg, int32_t n_ranks, int32_t rank, int32_t 
     const int32_t gv[16] = {g.H, g.I, g.heads, g.vocab, g.n_ranks, g.rank, g.heads_local, g.gs, g.n_act, g.rs, g.n1, g.n_blocks, g.grid, g.n_mlp, 0, 0};
     std::memcpy(geom_out, gv, sizeof(gv));
     for (int k = 0; k < F_NOPS; ++k) {
-        const int32_t pv[10] = {pl[k].n_cta, pl[k].n_mt, pl[k].n_ks, pl[k].wk, pl[k].tb, pl[k].nb, pl[k].nq, pl[k].rem, pl[k].warp_bytes, pl[k].n_units};
+        const int32_t pv[10] = {pl[k].n_cta, pl[k].n_mt, pl[k].n_ks, pl[k].wk, pl[k].tb, pl[k].nb, pl[k].nq, pl[k].rem, pl[k].warp_bytes, pl[k].unit_bytes};
         std::memcpy(plans_out + 10 * k, pv, sizeof(pv));
     }
     return QW3_OK;

@@ -5,7 +5,7 @@
 // cuBLAS walk it column-major (Inference.cu:1052-1065).  The on-disk files keep that layout (Inference.cu:780-900);
 // at load time each matrix is additionally rewritten, on the device, into the order in which the fused pass consumes
 // it: one byte stream per (CTA, warp), made of 512-byte items; the 16 warp streams of a CTA are interleaved in pieces of
-// F_UNIT bytes ([unit][warp][piece]) so that one bulk copy fetches the next piece of every warp.  An item is one m16n8k16 A-operand tile
+// whole k-groups ([unit][warp][piece]) so that one bulk copy fetches the next piece of every warp.  An item is one m16n8k16 A-operand tile
 // sequence: 16 outputs x 64 inputs, every lane owning one 16-byte piece = four 32-bit words = four k-steps, the eight
 // nibbles of a word sitting where one AND per register turns them into the fp16 A fragment.  (A trailing half group of
 // two k-steps makes a 256-byte item.)
@@ -31,7 +31,7 @@ constexpr int F_NW = 16;          // warps per CTA
 #ifndef QW3_F_UNIT
 #define QW3_F_UNIT 4096
 #endif
-constexpr int F_UNIT = QW3_F_UNIT;   // bytes of one warp's piece of a ring unit (a unit = 16 pieces = one bulk copy)
+constexpr int F_UNIT = QW3_F_UNIT;   // largest piece of one warp in a ring unit (a unit = 16 pieces = one bulk copy)
 
 enum FusedOp { F_QKV = 0, F_WO = 1, F_W1 = 2, F_W2 = 3, F_UNEMB = 4, F_NOPS = 5 };
 
@@ -43,7 +43,9 @@ struct FGemvPlan {
     int tb, nb;       // per warp: nb blocks of tb tiles
     int nq, rem;      // per warp: n_ks / wk = 4 * nq + rem, rem in {0, 2}
     int warp_bytes;   // bytes of one warp's stream = nb * tb * (nq * 512 + rem * 128)
-    int n_units;      // ring units of one warp's stream = ceil(warp_bytes / F_UNIT)
+    int gu;           // k-groups per ring unit (rem == 0; with a half group the whole block is one unit)
+    int unit_bytes;   // bytes of one warp's piece of a unit: gu * tb * 512, or the block's tb * (nq * 512 + rem * 128)
+    int n_units;      // ring units of one warp's stream = warp_bytes / unit_bytes
 };
 
 // Geometry every rank and CTA derives its slices from.
@@ -97,12 +99,11 @@ QW3_HD FWordPos fused_word_pos(const FGemvPlan& pl, int warp, int byte_off) {
 }
 
 // Where byte `stream_off` of a CTA's interleaved stream belongs: which warp, and which byte of that warp's own stream.
-// Unit u holds bytes [u * F_UNIT, min((u + 1) * F_UNIT, warp_bytes)) of every warp's stream, warp after warp.
+// Unit u holds bytes [u * unit_bytes, (u + 1) * unit_bytes) of every warp's stream, warp after warp.
 QW3_HD void fused_stream_locate(const FGemvPlan& pl, int stream_off, int& warp, int& warp_off) {
-    const int u = stream_off / (F_NW * F_UNIT), in_unit = stream_off % (F_NW * F_UNIT);
-    const int rest = pl.warp_bytes - u * F_UNIT, piece = rest < F_UNIT ? rest : F_UNIT;
-    warp = in_unit / piece;
-    warp_off = u * F_UNIT + in_unit % piece;
+    const int u = stream_off / (F_NW * pl.unit_bytes), in_unit = stream_off % (F_NW * pl.unit_bytes);
+    warp = in_unit / pl.unit_bytes;
+    warp_off = u * pl.unit_bytes + in_unit % pl.unit_bytes;
 }
 
 // The eight nibbles of a word: nibble n (bits 4n .. 4n+3) holds W[row][j] with

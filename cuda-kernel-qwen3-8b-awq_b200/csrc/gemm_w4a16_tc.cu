@@ -429,8 +429,6 @@ int qw3::gemm_launch(qw3_w4_t w, const void* d_x, int64_t rows, void* d_y, qw3_w
     p.epilogue = epilogue;
     p.err = ws_struct(ws)->err;
     p.a_lbo = 8192; p.a_sbo = 1024; p.a_kstep = 2048;
-    if (const char* e = std::getenv("QW3_GEMM_A_LBO")) p.a_lbo = std::atoi(e);
-    if (const char* e = std::getenv("QW3_GEMM_A_SBO")) p.a_sbo = std::atoi(e);
     CUtensorMap tmap_x;
     int rc;
     rc = encode_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d_x, (uint64_t)d->K, (uint64_t)rows, (uint64_t)d->K * 2, GM_BK,

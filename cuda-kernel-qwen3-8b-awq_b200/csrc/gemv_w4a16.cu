@@ -786,13 +786,40 @@ extern "C" int qw3_gemv_w4a16_noalloc(const void* d_packed, const void* d_scale,
     ws.err = reinterpret_cast<int32_t*>(base + NOALLOC_PARTIAL_BYTES + 512);
     ws.device = dev;
     ws.sm_count = nd->sm_count;
-    // The array keeps whatever the previous call left: the counters and the error word must start at
-    // zero (the partial sums are always written before they are read).
-    QW3_CUDA(cudaMemsetAsync(base + NOALLOC_PARTIAL_BYTES, 0, NOALLOC_TAIL_BYTES, st));
+    // The array keeps whatever the previous call left: the arrival counters must start at zero (the partial
+    // sums are always written before they are read).  The error word behind them is NOT cleared here: a bounded
+    // wait that gave up stays recorded until qw3_gemv_w4a16_noalloc_status reads it.
+    QW3_CUDA(cudaMemsetAsync(base + NOALLOC_PARTIAL_BYTES, 0, 512, st));
     Qw3GemvArgs a;
     std::memset(&a, 0, sizeof(a));
     a.d_x = d_x;
     a.d_y = d_y;
     a.epilogue = QW3_EPI_STORE;
     return gemv_launch(&d, &a, &ws, false, st);
+}
+
+// The error word of the fixed scratch: QW3_ERR_TIMEOUT when a bounded wait of an earlier qw3_gemv_w4a16_noalloc call
+// on this GPU gave up (its output is then void), QW3_OK otherwise.  Reads and clears the word; synchronises `stream`;
+// allocates nothing (the word is copied into a local variable).
+extern "C" int qw3_gemv_w4a16_noalloc_status(void* stream) {
+    int dev = 0;
+    QW3_CUDA(cudaGetDevice(&dev));
+    QW3_REQUIRE(dev >= 0 && dev < 64, "qw3_gemv_w4a16_noalloc_status: device index %d not supported", dev);
+    NoAllocDevice* nd = nullptr;
+    {
+        const int rc = noalloc_setup(dev, &nd);
+        if (rc != QW3_OK) return rc;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t* word = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(nd->base) + NOALLOC_PARTIAL_BYTES + 512);
+    int err = 0;
+    QW3_CUDA(cudaMemcpyAsync(&err, word, 4, cudaMemcpyDeviceToHost, st));
+    QW3_CUDA(cudaStreamSynchronize(st));
+    if (err != 0) {
+        QW3_CUDA(cudaMemsetAsync(word, 0, 4, st));
+        QW3_CUDA(cudaStreamSynchronize(st));
+        set_last_error("a bounded device-side wait of qw3_gemv_w4a16_noalloc gave up (device error word = 0x%x)", err);
+        return QW3_ERR_TIMEOUT;
+    }
+    return QW3_OK;
 }

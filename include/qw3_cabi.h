@@ -126,6 +126,12 @@ int qw3_gemv_w4a16(qw3_w4_t w, const Qw3GemvArgs* args, qw3_ws_t ws, void* strea
 int qw3_gemv_w4a16_noalloc(const void* d_packed, const void* d_scale, const void* d_zp, int64_t n_groups_alloc,
                            int64_t out_dim, int64_t in_dim, int zp_integral, const void* d_x, void* d_y,
                            void* stream);
+/* Companion of qw3_gemv_w4a16_noalloc (what qw3_ws_check is to a workspace): every wait inside the kernel is bounded,
+ * and one that gives up records a code in an error word of the fixed scratch instead of hanging the GPU; the call that
+ * launched the kernel has returned QW3_OK long before.  This reads and clears that word on the current device:
+ * QW3_ERR_TIMEOUT if a call since the last check gave up (its d_y is then void), QW3_OK otherwise.  Synchronises
+ * `stream`; allocates nothing either.  qw3_gemv_w4a16_noalloc itself never clears the word. */
+int qw3_gemv_w4a16_noalloc_status(void* stream);
 
 /* Tensor-core W4A16 contraction for `rows` activations (prefill / batched rows): Y[r][i] =
  * sum_j W[i + j*out_dim] * X[r][j], fp16 in, fp32 accumulate, fp16 out.  The reference has no
@@ -249,9 +255,13 @@ int qw3_layer_decode(qw3_handle h, int32_t layer, int32_t pos, void* host_hidden
  * exposes intermediate hidden states without any extra kernel. */
 int qw3_stage_hidden(qw3_handle h, int32_t stage, void* host_hidden_f16);
 
-/* Debug: global-timer value (ns) at which CTA 0 entered each operator of the last decode pass of a
- * stage, plus the end of the pass; needs QW3_TRACE set in the environment when the handle is made. */
+#ifdef QW3_TRACE
+/* Tracing builds of the library only (make EXTRA=-DQW3_TRACE; the shipped build holds no tracing code): global-timer
+ * stamps the pass kernels recorded during the last pass of a stage.  Fused pass: [CTA][layer][16] phase stamps of
+ * thread 0 (max_entries = number of values wanted, negative allowed).  Operator-list pass: the time CTA 0 entered each
+ * operator plus the end of the pass, or with max_entries < 0 the per-CTA event times [CTA][operator][8]. */
 int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entries, int32_t* n_entries);
+#endif
 
 /* One process per GPU (world > 1, n_stages == world, rank = this process's stage).  Every stage owns
  * a mailbox in its device memory; qw3_stage_export returns its 64-byte CUDA IPC handle, the caller

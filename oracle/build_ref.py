@@ -2,7 +2,7 @@
 infrastructure; see ref_wrap.cu).  Needs the reference checkout and nvcc; where either is missing the function
 returns None and the GPU tests that use the library skip.
 
-    python oracle/build_ref.py [path/to/reference]
+    python oracle/build_ref.py path/to/reference      (or QW3_REFERENCE_DIR=path/to/reference)
 
 The reference is one file, Inference.cu.  Only its first 292 lines (includes, constants, macros and the six
 kernels) compile with this toolkit; they are cut into a temporary file, compiled together with ref_wrap.cu, and
@@ -18,7 +18,11 @@ OUT = os.path.join(HERE, "_ref", "libref_kernels.so")
 PREFIX_LINES = 292   # up to, not including, readBinaryFileToDevice (Inference.cu:297)
 
 
-def build(reference_dir="/root/reference", force=False):
+def build(reference_dir=None, force=False):
+    """reference_dir: the reference checkout (default: $QW3_REFERENCE_DIR, else a directory `reference` beside this
+    repository).  Returns the library path, or None when neither the checkout nor a prebuilt library is there."""
+    if reference_dir is None:
+        reference_dir = os.environ.get("QW3_REFERENCE_DIR") or os.path.join(HERE, "..", "..", "reference")
     src = os.path.join(reference_dir, "Inference.cu")
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(src) or not os.path.exists(nvcc):

@@ -20,7 +20,7 @@ def _plan(pkg, cfg_kw, n_ranks=1, rank=0, grid=148):
     cabi.check(cabi.lib().qw3_fused_plan(C.byref(cfg), n_ranks, rank, grid, geom, plans), "qw3_fused_plan")
     names = ["H", "I", "heads", "vocab", "n_ranks", "rank", "heads_local", "gs", "n_act", "rs", "n1", "n_blocks", "grid", "n_mlp"]
     g = dict(zip(names, list(geom)))
-    pn = ["n_cta", "n_mt", "n_ks", "wk", "tb", "nb", "nq", "rem", "warp_bytes", "n_units"]
+    pn = ["n_cta", "n_mt", "n_ks", "wk", "tb", "nb", "nq", "rem", "warp_bytes", "unit_bytes"]
     return cfg, g, [dict(zip(pn, list(plans)[10 * k:10 * k + 10])) for k in range(5)]
 
 
@@ -34,6 +34,8 @@ def test_plan_of_the_full_model(pkg):
     for p in pl:
         assert p["n_mt"] == (16 // p["wk"]) * p["nb"] * p["tb"] and p["n_ks"] == p["wk"] * (4 * p["nq"] + p["rem"])
         assert p["rem"] in (0, 2) and (p["rem"] == 0 or p["tb"] % 2 == 0)
+        group = p["tb"] * 512
+        assert p["unit_bytes"] == (p["tb"] * (p["nq"] * 512 + p["rem"] * 128) if p["rem"] else p["unit_bytes"] // group * group)
 
 
 @pytest.mark.parametrize("n_ranks", [2, 4, 8])
@@ -80,18 +82,15 @@ def _k0(g, op, cta):
     return 0
 
 
-PIECE = 4096   # bytes of one warp's piece of a ring unit (F_UNIT of fused_plan.h)
-
-
 def _warp_streams(stream_words, p):
-    """The ring's view of a CTA's stream: unit after unit, a unit being [warp][piece]; returns the 16 per-warp streams."""
-    wb, out, at, u = p["warp_bytes"], [[] for _ in range(16)], 0, 0
-    while u * PIECE < wb:
-        piece = min(PIECE, wb - u * PIECE) // 4
+    """The ring's view of a CTA's stream: unit after unit, a unit being [warp][piece of unit_bytes] (whole k-groups);
+    returns the 16 per-warp streams."""
+    wb, ub, out, at = p["warp_bytes"], p["unit_bytes"], [[] for _ in range(16)], 0
+    assert wb % ub == 0 and ub <= 4096 and ub % 256 == 0
+    for _ in range(wb // ub):
         for warp in range(16):
-            out[warp].append(stream_words[at:at + piece])
-            at += piece
-        u += 1
+            out[warp].append(stream_words[at:at + ub // 4])
+            at += ub // 4
     assert at == stream_words.size
     return np.concatenate([np.concatenate(w) for w in out])
 

@@ -32,6 +32,7 @@ def _noalloc(ops, p, s, z, M, K, x, y):
 
 def test_noalloc_gemv_equals_workspace_gemv_on_two_calls_in_a_row(ops, orc, cuda):
     ws = ops.Workspace()
+    free_before = None
     for call, (M, K, seed) in enumerate([(4096, 4096, 31), (1536, 512, 32), (4096, 12288, 33)]):
         p, s, z = orc.gen_linear(seed, M, K)
         x = orc.gen_normal_f16(seed, orc.ACT, K)
@@ -40,14 +41,22 @@ def test_noalloc_gemv_equals_workspace_gemv_on_two_calls_in_a_row(ops, orc, cuda
         w = ops.W4Linear(pd, sd, zd, M, K)
         ops.gemv_w4a16(w, ws, ops.gemv_args(xd, y=want))
         got = torch.full((M,), 3.0, dtype=torch.float16, device=cuda)
+        torch.cuda.synchronize()
+        if call > 0:   # the first call may set the device up; from the second on the entry point must not allocate
+            free_before = torch.cuda.mem_get_info()[0]
         _noalloc(ops, pd, sd, zd, M, K, xd, got)
         torch.cuda.synchronize()
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] == free_before, "qw3_gemv_w4a16_noalloc changed the free device memory"
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"call {call}: {M}x{K}"
         # and the result is the oracle's, within the tolerance the GEMV tests use
         y32, _ = orc.gemm_w4a16(p, s, z, M, K, x)
         err = np.abs(got.cpu().numpy().astype(np.float32) - y32)
         assert (err <= 2e-2 * np.abs(y32) + 2e-2 * np.abs(y32).mean()).all()
     ws.check()
+    # no bounded wait gave up in any of the calls: the scratch's error word is clean
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert ops.cabi.lib().qw3_gemv_w4a16_noalloc_status(st) == ops.cabi.QW3_OK
 
 
 def test_noalloc_gemv_refuses_sizes_beyond_its_scratch(ops, cuda):
