@@ -321,11 +321,7 @@ def reference_method_token_us(torch, orc, weight_dir, n_layers_cycled=6, reps=6)
 
 def pass_only(pkg, orc, args):
     """Token passes of a model cut to --pass-layers layers (full-size matrices, small vocabulary unless asked
-    otherwise): the small case for profilers.  With QW3_TRACE=1 the engine records global-timer stamps inside
-    decode_pass_kernel; they are summarised per operator (CTA 0 entering each operator) and per phase (all
-    CTAs, one layer in the middle)."""
-    import ctypes as C
-    import numpy as np
+    otherwise): the small case for profilers (a 6-layer pass streams 503 MB per launch, four times the L2)."""
     L, V = args.pass_layers, args.pass_vocab
     cfg = dict(hidden=4096, inter=12288, heads=32, head_dim=128, layers=L, vocab=V, max_pos=args.prompt_len + args.steps + args.warmup + 8,
                rope_base=10000.0)
@@ -336,33 +332,10 @@ def pass_only(pkg, orc, args):
     inf = pkg.QWen3AWQInfer(wdir, **cfg)
     inf.generateResponse(prompt, args.warmup)
     inf.decode_more(args.steps)
-    out = {"kernel": "decode_pass_kernel", "layers": L, "vocab": V, "context": args.prompt_len + args.warmup,
-           "ms_per_token": inf.last_timing()[1] / args.steps}
-    if os.environ.get("QW3_TRACE"):
-        n_ops = 1 + 5 * L + 1
-        buf = (C.c_uint64 * (n_ops + 8))()
-        n = C.c_int32()
-        pkg.cabi.check(pkg.cabi.lib().qw3_debug_trace(inf._h, 0, buf, n_ops + 8, C.byref(n)), "qw3_debug_trace")
-        d = np.diff(np.array(buf[:n.value], dtype=np.float64)) / 1e3
-        lay = d[1:1 + 5 * L].reshape(L, 5)
-        out["op_us"] = {"embed": float(d[0]), "unembed_argmax": float(d[1 + 5 * L]), "layer": float(lay.sum(axis=1).mean()),
-                        **{k: float(v) for k, v in zip(["wqkv", "attention", "wo", "w1", "w2"], lay.mean(axis=0))}}
-        G = 148
-        buf2 = (C.c_uint64 * (256 * n_ops * 8))()
-        pkg.cabi.check(pkg.cabi.lib().qw3_debug_trace(inf._h, 0, buf2, -(256 * n_ops * 8), C.byref(n)), "qw3_debug_trace")
-        t = np.ctypeslib.as_array(buf2).reshape(256, n_ops, 8)[:G].astype(np.float64)
-        t[t == 0] = np.nan
-        names = ["enter", "input wait", "prologue", "units", "flush", "gather", "epilogue", "end"]
-        li = L // 2
-        phases = {}
-        for k, op in enumerate(["wqkv", "attention", "wo", "w1", "w2"]):
-            e = t[:, 1 + 5 * li + k, :]
-            e = e - np.nanmin(e[:, 0])
-            if op == "attention":   # its events: q polled, rows done, CTA merge, splits merged, ctx stored
-                e = e[::4]          # the CTAs that merge a head (split 0 of 4)
-            if True:   # median over CTAs of the time each phase ends, from the first CTA entering
-                phases[op] = {nm: float(np.nanmedian(e[:, j]) / 1e3) for j, nm in enumerate(names) if np.isfinite(e[:, j]).any()}
-        out["phase_end_us_median_over_ctas"] = phases
+    layer_bytes = L * (LAYER_PACKED + 1024) + V * 4096 // 2
+    ms = inf.last_timing()[1] / args.steps
+    out = {"kernel": "fused_pass_kernel", "layers": L, "vocab": V, "context": args.prompt_len + args.warmup, "ms_per_token": ms,
+           "packed_bytes_per_launch": layer_bytes, "GBps": layer_bytes / ms / 1e6}
     inf.close()
     return out
 
@@ -451,8 +424,7 @@ def main():
     ap.add_argument("--roofline-reps", type=int, default=6)
     ap.add_argument("--roofline-shape", default="12288x4096")
     ap.add_argument("--only-pass", action="store_true",
-                    help="run token passes of a model with --pass-layers layers (small case for profilers); with QW3_TRACE=1 in "
-                         "the environment also prints the per-operator and per-phase times of the pass kernel")
+                    help="run token passes of a model with --pass-layers layers (small case for profilers)")
     ap.add_argument("--pass-layers", type=int, default=6)
     ap.add_argument("--pass-vocab", type=int, default=2048)
     ap.add_argument("--only-gemm", action="store_true", help="batched-row sweep of the tensor-core W4A16 contraction")

@@ -175,6 +175,8 @@ struct FCtx {
     float* argv;        // [16]
     int* argi;          // [16]
     int* s_dead;
+    int* err;           // device error word of the launch
+    const FGemvPlan* plans;   // [F_NOPS] the operator plans, copied to shared memory for the out-of-line GEMV
     int* ring_cnt;      // [FP_SLOTS] warps that have consumed their piece of the unit in the slot
     int* ring_issued;   // units requested so far (only the issuing thread of the moment writes it)
     uint32_t bars;      // shared address of the ring barriers [FP_SLOTS]
@@ -184,8 +186,8 @@ struct FCtx {
     int n_seg;
 };
 
-__device__ __forceinline__ void fail(const FusedParams& p, const FCtx& cx, int code) {
-    atomicCAS(p.err, 0, code);
+__device__ __forceinline__ void fail(const FCtx& cx, int code) {
+    atomicCAS(cx.err, 0, code);
     *cx.s_dead = 1;
 }
 
@@ -211,7 +213,7 @@ __device__ __forceinline__ void poll_batch(const FusedParams& p, const FCtx& cx,
         }
         if (ok || *cx.s_dead != 0) break;
         if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
-            fail(p, cx, code);
+            fail(cx, code);
             break;
         }
     }
@@ -264,7 +266,7 @@ __device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, co
 }
 
 // Shared address of this warp's piece (of `piece` bytes) of the unit it consumes next, once the unit has landed.
-__device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FusedParams& p, const FCtx& cx, const int piece) {
+__device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FCtx& cx, const int piece) {
     const int warp = threadIdx.x >> 5, slot = r.uc % FP_SLOTS;
     uint32_t addr = smem_u32(cx.ring) + slot * (F_NW * F_UNIT) + warp * piece;
 #if !defined(QW3_FP_NOLOAD) && !defined(QW3_FP_NOWAIT)
@@ -275,7 +277,7 @@ __device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FusedPara
 #endif
     {
         if (*cx.s_dead == 0 && !mbar_wait(cx.bars + 8 * slot, (r.uc / FP_SLOTS) & 1)) {
-            if ((threadIdx.x & 31) == 0) fail(p, cx, 0x10000 | (r.uc & 0xffff));   // a weight unit never arrived
+            if ((threadIdx.x & 31) == 0) fail(cx, 0x10000 | (r.uc & 0xffff));   // a weight unit never arrived
         }
     }
     __syncwarp();
@@ -352,8 +354,7 @@ __device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0,
 // sum_j q[row][j] * x[j] of tile i of the block.  Tiles of a block are issued one after another per k-step, so TB
 // (2 * TB for narrow blocks) independent MMA chains are in flight.
 template <int TB>
-__device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, WarpRing& ring, const FGemvPlan& pl,
-                                          const uint32_t xs_addr, float* dst) {
+__device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const FGemvPlan& pl, const uint32_t xs_addr, float* dst) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nq = pl.nq, rem = pl.rem;
     const int upb = rem ? 1 : nq / pl.gu, ng = rem ? nq : pl.gu;   // units per block, full groups per unit
@@ -367,7 +368,7 @@ __device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, 
 #pragma unroll
                 for (int d = 0; d < 4; ++d) acc[i][h][d] = 0.0f;
         for (int uu = 0; uu < upb; ++uu) {
-            const uint32_t ubase = ring_wait(ring, p, cx, pl.unit_bytes);
+            const uint32_t ubase = ring_wait(ring, cx, pl.unit_bytes);
             uint32_t a = ubase + lane * 16;
             const uint32_t xq = xs_addr + uu * ng * 128;
             for (int gq = 0; gq < ng; ++gq) {
@@ -411,20 +412,41 @@ __device__ __forceinline__ void gemv_core(const FusedParams& p, const FCtx& cx, 
     }
 }
 
-// Runs this warp's share of an operator: warp (a, bk) of the plan; sums land in obuf[bk][tile * 16 + row].
-__device__ __forceinline__ void run_gemv(const FusedParams& p, const FCtx& cx, WarpRing& ring, const FGemvPlan& pl,
-                                         const __half* x_cta) {
+__device__ __forceinline__ FCtx carve_ctx(uint8_t* smem);
+
+// Runs this warp's share of operator `op`: warp (a, bk) of the plan; sums land in obuf[bk][tile * 16 + row].
+// ONE out-of-line copy serves the four operators of a layer and the unembedding (inlined at every call site the
+// loop was in the kernel twenty times, and a pass spent a sixth of its issue slots waiting for instructions).  The
+// function takes and returns the ring cursor in registers and finds everything else in shared memory, so nothing of
+// it lives in local memory.
+#ifdef QW3_FP_INLINE_GEMV
+__device__ __forceinline__
+#else
+__device__ __noinline__
+#endif
+int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const uint32_t x_cta_addr) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const FCtx cx = carve_ctx(smem);
+    WarpRing ring;
+    ring.uc = uc; ring.pseg = pseg; ring.pu = pu;
+    ring.policy = l2_policy_evict_first();
+    const FGemvPlan& pl = cx.plans[op];
     const int warp = threadIdx.x >> 5;
     const int a = warp / pl.wk, bk = warp % pl.wk;
     const int ksw = 4 * pl.nq + pl.rem;
-    const uint32_t xs_addr = smem_u32(x_cta) + bk * ksw * 32;
+    const uint32_t xs_addr = x_cta_addr + bk * ksw * 32;
     float* dst = cx.obuf + bk * (pl.n_mt * 16) + a * (pl.nb * pl.tb) * 16;
     switch (pl.tb) {
-        case 1: gemv_core<1>(p, cx, ring, pl, xs_addr, dst); break;
-        case 2: gemv_core<2>(p, cx, ring, pl, xs_addr, dst); break;
-        case 3: gemv_core<3>(p, cx, ring, pl, xs_addr, dst); break;
-        default: gemv_core<4>(p, cx, ring, pl, xs_addr, dst); break;
+        case 1: gemv_core<1>(cx, ring, pl, xs_addr, dst); break;
+        case 2: gemv_core<2>(cx, ring, pl, xs_addr, dst); break;
+        case 3: gemv_core<3>(cx, ring, pl, xs_addr, dst); break;
+        default: gemv_core<4>(cx, ring, pl, xs_addr, dst); break;
     }
+    return make_int3(ring.uc, ring.pseg, ring.pu);
+}
+__device__ __forceinline__ void run_gemv(WarpRing& ring, const int op, const __half* x_cta) {
+    const int3 r = gemv_entry(ring.uc, ring.pseg, ring.pu, op, smem_u32(x_cta));
+    ring.uc = r.x; ring.pseg = r.y; ring.pu = r.z;
 }
 __device__ __forceinline__ float sum_k_shares(const FCtx& cx, const FGemvPlan& pl, int i) {
     float s = 0.0f;
@@ -507,7 +529,7 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
         }
         if (ok || *cx.s_dead != 0) break;
         if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
-            fail(p, cx, 0x20000 | (tag & 0x1ff));   // the hidden state of this phase never arrived
+            fail(cx, 0x20000 | (tag & 0x1ff));   // the hidden state of this phase never arrived
             break;
         }
     }
@@ -611,7 +633,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         const long long o = (long long)(tile >> 3) * H + hglob * 128 + (tile & 7) * 16 + row;
         group_consts(lsz + F_QKV * FP_MAX_GROUPS, o, sc, zp);
     }
-    run_gemv(p, cx, ring, p.plan[F_QKV], cx.xs + r * hs);
+    run_gemv(ring, F_QKV, cx.xs + r * hs);
     __syncthreads();
     FP_STAMP(li, 2);
     if (tid < FP_QKV) {
@@ -791,7 +813,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
 
         // ---- Wo restricted to the head's 128 inputs, this CTA's share of the outputs (Inference.cu:1122-1141) ----------
         const FGemvPlan& plo = p.plan[F_WO];
-        run_gemv(p, cx, ring, plo, cx.ctx_s);
+        run_gemv(ring, F_WO, cx.ctx_s);
         __syncthreads();
         FP_STAMP(li, 6);
         const int n_out = plo.n_mt * 16;   // = hs
@@ -839,7 +861,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     gather_norm<SYS>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, cx.xs, -1, H, x_full, x_slice);
     FP_STAMP(li, 9);
     if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cmlp * n1 + tid, sc, zp);
-    run_gemv(p, cx, ring, p.plan[F_W1], cx.xs);
+    run_gemv(ring, F_W1, cx.xs);
     __syncthreads();
     float gv = 0.0f;
     if (tid < n1) {
@@ -851,7 +873,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     const float x_g = block_sum_f(cx, gv);   // its barriers also publish g_s and free obuf
     FP_STAMP(li, 10);
     // ---- W2 restricted to those n1 inputs, all outputs (Inference.cu:1198-1214) ------------------------------------------------
-    run_gemv(p, cx, ring, p.plan[F_W2], cx.g_s);
+    run_gemv(ring, F_W2, cx.g_s);
     __syncthreads();
     FP_STAMP(li, 11);
     for (int i0 = 2 * tid; i0 < H; i0 += 2 * FP_NT) {
@@ -923,7 +945,7 @@ __device__ __forceinline__ void l2_prefetch_pass(const FusedParams& p, const FCt
                 if (tid == 0) {
                     const long long t_begin = clock64();
                     while (!has_tag(ldt<SYS>(word), tag) && *cx.s_dead == 0) {
-                        if (clock64() - t_begin > FP_WAIT_PEER) { fail(p, cx, 0x90000 | li); break; }
+                        if (clock64() - t_begin > FP_WAIT_PEER) { fail(cx, 0x90000 | li); break; }
                         __nanosleep(200);
                     }
                 }
@@ -955,7 +977,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
             const long long t_begin = clock64();
             while (!has_tag(ldt<SYS>(p.hid[G.rank] + (H >> 1)), tag_in) && *cx.s_dead == 0) {
                 if (clock64() - t_begin > FP_WAIT_PEER) {
-                    fail(p, cx, 0x70000);
+                    fail(cx, 0x70000);
                     break;
                 }
                 __nanosleep(1000);
@@ -1006,7 +1028,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
 #else
         (void)xacc;
 #endif
-        run_gemv(p, cx, ring, pl, cx.xs);
+        run_gemv(ring, F_UNEMB, cx.xs);
         __syncthreads();
         if (tid < 128) {
             const __half hl = __float2half_rn(sum_k_shares(cx, pl, tid) - Z);   // fp16 logits, Inference.cu:1270
@@ -1055,7 +1077,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
                     ldt2<SYS>(p.xarg[G.rank] + 2 * (size_t)e, a, b);
                     if ((has_tag(a, tag) && has_tag(b, tag)) || *cx.s_dead != 0) break;
                     if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
-                        fail(p, cx, 0x80000);
+                        fail(cx, 0x80000);
                         break;
                     }
                 }
@@ -1074,9 +1096,9 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
     }
 }
 
-template <bool SYS>
-__global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
+// The shared-memory layout of the kernel (pointers only; the per-pass values tagbase / pos / n_seg are filled by the
+// kernel, n_seg also lives in shared memory for the out-of-line GEMV).
+__device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     FCtx cx;
     cx.ring = smem;
     cx.obuf = reinterpret_cast<float*>(smem + FP_OFF_OBUF);
@@ -1096,19 +1118,41 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
     cx.argv = reinterpret_cast<float*>(misc + 3456);             // 64
     cx.argi = reinterpret_cast<int*>(misc + 3520);               // 64
     cx.s_dead = reinterpret_cast<int*>(misc + 3584);             // 16
-    uint32_t* zero = reinterpret_cast<uint32_t*>(misc + 3616);   // 32 (16-byte aligned)
-    cx.zero_addr = smem_u32(zero);
+    cx.zero_addr = smem_u32(misc + 3616);                        // 32 zero bytes (16-byte aligned)
     cx.bars = smem_u32(misc + 3712);                             // FP_SLOTS * 8
     cx.ring_cnt = reinterpret_cast<int*>(misc + 3840);           // FP_SLOTS * 4
     cx.ring_issued = reinterpret_cast<int*>(misc + 3968);
     cx.ldesc = reinterpret_cast<FLayerDesc*>(misc + 4096);       // 2 descriptors
     static_assert(FP_SLOTS <= 16 && 4096 + 2 * sizeof(FLayerDesc) <= 5120 && 5120 + 512 <= FP_MISC_BYTES, "misc area");
 
+    cx.err = *reinterpret_cast<int**>(misc + 5632);                // written by the kernel before the first use
+    cx.n_seg = *reinterpret_cast<int*>(misc + 5640);
+    cx.plans = reinterpret_cast<const FGemvPlan*>(misc + 5648);   // F_NOPS plans
+    cx.tagbase = 0;
+    cx.pos = 0;
+    return cx;
+}
+
+template <bool SYS>
+__global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    {   // what the out-of-line GEMV reads from shared memory: error word, segment count, operator plans
+        uint8_t* misc0 = smem + FP_OFF_MISC;
+        if (threadIdx.x == 0) {
+            *reinterpret_cast<int**>(misc0 + 5632) = p.err;
+            *reinterpret_cast<int*>(misc0 + 5640) = 4 * p.n_layers + p.n_rounds;
+        }
+        static_assert(sizeof(FGemvPlan) % 4 == 0 && 5648 + F_NOPS * sizeof(FGemvPlan) <= FP_MISC_BYTES, "plans in the misc area");
+        for (int i = threadIdx.x; i < (int)(F_NOPS * sizeof(FGemvPlan) / 4); i += FP_NT)
+            reinterpret_cast<int*>(misc0 + 5648)[i] = reinterpret_cast<const int*>(p.plan)[i];
+        __syncthreads();
+    }
+    FCtx cx = carve_ctx(smem);
+    uint32_t* zero = reinterpret_cast<uint32_t*>(smem + FP_OFF_MISC + 3616);
     const int tid = threadIdx.x, c = blockIdx.x;
     const FusedGeom& G = p.g;
     const bool active = c < G.n_act;
     const int cglob = G.rank * G.n_act + c;
-    cx.n_seg = 4 * p.n_layers + p.n_rounds;
     // this CTA's share of every weight stream, in the order of consumption
     for (int i = tid; i < cx.n_seg; i += FP_NT) {
         const uint8_t* base = nullptr;
