@@ -19,13 +19,18 @@
 // Weights: every matrix is rewritten at load time (fused_plan.h) into per-(CTA, warp) byte streams in consumption
 // order.  Each warp owns FP_SLOTS ring slots of F_UNIT bytes and refills a slot with its own next unit (1-D bulk copy,
 // L2 evict-first) as soon as it has consumed it, across operator boundaries, since weights never depend on activations.
-// Inner loop: one 16-byte shared-memory load per lane yields four k-steps; `w & 0x000f000f`, `w & 0x00f000f0` and the
-// same on `w >> 8` ARE the fp16 A fragment of mma.sync.m16n8k16: a nibble in mantissa bits 0-3 of an fp16 with zero
-// exponent is the subnormal q * 2^-24 (bits 4-7: q * 2^-20), exactly.  So the tensor core accumulates
-// sum_j q_ij x_j in fp32 and the epilogue applies  y_i = scale_i * (2^24 * D_i - zp_i * sum_j x_j):  five integer
-// instructions and one MMA per eight weights.  This is algebraically the reference's (q - zp) * scale product
-// (Inference.cu:102-104) without its two fp16 roundings per weight; the bit-exact form stays in qw3_dequant_w4, in
-// the stand-alone GEMV and in the tensor-core GEMM, and the tests hold this kernel to the logits tolerance.
+// Inner loop: the integer tensor-core path.  One 16-byte shared-memory load per lane yields four words; `w & 0x0f0f0f0f`
+// and `w & 0xf0f0f0f0` of two words ARE the u8 A fragment of mma.sync.m16n8k32 (u8 x s8 -> s32): the low nibbles of a
+// word are four weights of row g, the high nibbles four weights of row g + 8 times 16.  The activations of the
+// operator are brought to fixed point once per CTA, X_j = rint(x_j * 2^sh) with |X_j| < 2^22 (fp16 values within 2^11
+// of the largest are exact, the others are off by at most 2^-23 of the largest), and split into three signed base-256
+// digits which sit in columns 0, 1, 2 of the B fragment.  So the tensor core accumulates sum_j q_ij X_j exactly, in
+// three s32 columns, and the epilogue applies  y_i = scale_i * (2^-sh * (65536 D_i0 + 256 D_i1 + D_i2) - zp_i * sum_j x_j):
+// two integer instructions per eight weights and one MMA per sixteen (the fp16 form of the same loop, nibbles as
+// subnormal fp16 into m16n8k16, needed five and two and ran half as fast: mma.sync issues at the same rate for both
+// shapes on this part).  This is algebraically the reference's (q - zp) * scale product (Inference.cu:102-104) without
+// its two fp16 roundings per weight; the bit-exact form stays in qw3_dequant_w4, in the stand-alone GEMV and in the
+// tensor-core GEMM, and the tests hold this kernel to the logits tolerance.
 // The unembedding's groups depend on the input index; there the scale is folded into the activations per block of
 // 128 outputs (x'_j = scale_g(b,j) * x_j) and the same loop runs.
 #include <cstdio>
@@ -54,7 +59,7 @@ constexpr int FP_QKV = 384;               // q, k, v of one head
 constexpr size_t FP_OFF_OBUF = (size_t)FP_SLOTS * F_NW * F_UNIT;
 constexpr size_t FP_OFF_HV = FP_OFF_OBUF + (size_t)FP_OBUF * 4;
 constexpr size_t FP_OFF_XS = FP_OFF_HV + (size_t)FP_MAX_H * 2;
-constexpr size_t FP_OFF_SEG = FP_OFF_XS + (size_t)FP_MAX_H * 2;
+constexpr size_t FP_OFF_SEG = FP_OFF_XS + (size_t)FP_MAX_H * 3;   // three digit planes of FP_MAX_H bytes
 constexpr size_t FP_OFF_LSZ = FP_OFF_SEG + (size_t)FP_MAX_SEG * 16;          // [2][4][FP_MAX_GROUPS] (scale, zero point) as floats
 constexpr size_t FP_OFF_MISC = FP_OFF_LSZ + (size_t)2 * 4 * FP_MAX_GROUPS * 8;
 constexpr size_t FP_MISC_BYTES = 8192;
@@ -160,13 +165,12 @@ struct FCtx {
     uint8_t* ring;
     float* obuf;
     __half* hv;
-    __half* xs;
+    uint8_t* xd;        // [3][FP_MAX_H] digits of the fixed-point activations of the operator about to run (plane c = digit c, most significant first)
+    float* xinv;        // 2^-sh of those activations
     int4* seg;          // {base lo, base hi, warp_bytes, unit_bytes} per weight segment of this CTA
     float2* lsz;        // [2][4][FP_MAX_GROUPS] (scale, zero point) of the layer's four matrices, two layers (current / next)
     FLayerDesc* ldesc;  // [2] descriptor of the current / next layer
     __half* qkv_s;      // [384] q, k, v of this CTA's head (after RoPE)
-    __half* ctx_s;      // [128]
-    __half* g_s;        // [n1] GeLU outputs
     __half* hmine;      // [rs] this CTA's part of the residual stream
     __half* rope_cs;    // [128] cos | sin of this position
     float* wsum;        // [64]
@@ -317,96 +321,107 @@ __device__ __forceinline__ uint2 lds64(uint32_t a) {
     asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
-__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-#ifdef QW3_FP_A_OFFSET
-// Variant kept for comparison: normal fp16 A values 1024 + q (bits 0-3) and 64 + q (bits 4-7); the epilogues then
-// subtract offset * sum(x) together with the zero point.
-constexpr uint32_t FP_OR_LO = 0x64006400u, FP_OR_HI = 0x54005400u;
-constexpr float FP_MULT_LO = 1.0f, FP_MULT_HI = 1.0f, FP_OFF_LO = 1024.0f, FP_OFF_HI = 64.0f;
-#else
-// The word's nibbles as subnormal fp16: bits 0-3 -> q * 2^-24 (rows g of a tile), bits 4-7 -> q * 2^-20 (rows g + 8).
-constexpr uint32_t FP_OR_LO = 0u, FP_OR_HI = 0u;
-constexpr float FP_MULT_LO = 16777216.0f, FP_MULT_HI = 1048576.0f, FP_OFF_LO = 0.0f, FP_OFF_HI = 0.0f;
-#endif
-// Offset the A values of output row `row16` (0..15 within its tile) carry (0 with subnormal A values).
-__device__ __forceinline__ float a_offset(int row16) { return (row16 & 8) ? FP_OFF_HI : FP_OFF_LO; }
-
-// One k-step: the word's eight nibbles as the A fragment.
-__device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0, uint32_t b1) {
+// Two words of a lane = one A fragment: low nibbles -> rows g, high nibbles -> rows g + 8 (sixteen-fold).
+__device__ __forceinline__ void mma_pair(int (&d)[4], uint32_t wa, uint32_t wb, uint32_t b0, uint32_t b1) {
 #ifdef QW3_FP_NOCOMPUTE
-    d[0] += __uint_as_float(w & b0 & b1);   // timing experiment: the weights only stream through (results are meaningless)
+    d[0] += (int)(wa & wb & b0 & b1);   // timing experiment: the weights only stream through (results are meaningless)
     return;
 #endif
-    const uint32_t u = w >> 8;
-    mma_f16(d, lop3_and_or(w, 0x000f000fu, FP_OR_LO), lop3_and_or(w, 0x00f000f0u, FP_OR_HI), lop3_and_or(u, 0x000f000fu, FP_OR_LO),
-            lop3_and_or(u, 0x00f000f0u, FP_OR_HI), b0, b1);
+    mma_u8s8(d, wa & 0x0f0f0f0fu, wa & 0xf0f0f0f0u, wb & 0x0f0f0f0fu, wb & 0xf0f0f0f0u, b0, b1);
 }
 
-// This warp's stream of one operator: nb blocks of TB tiles, each over nq groups of four k-steps (+ a half group when
+// ---- fixed-point activations ------------------------------------------------------------------------------------------------
+// bound >= max |x_j|  ->  up = 2^sh with |x_j| * 2^sh < 2^22, inv = 2^-sh.
+struct XScale { float up, inv; };
+__device__ __forceinline__ XScale xscale_for(float bound) {
+    int e = (int)((__float_as_uint(bound) >> 23) & 0xffu) - 126;   // bound < 2^e (normal floats; tiny bounds are clamped below)
+    int sh = 22 - e;
+    sh = max(-100, min(100, sh));
+    XScale r;
+    r.up = __uint_as_float((uint32_t)(sh + 127) << 23);
+    r.inv = __uint_as_float((uint32_t)(127 - sh) << 23);
+    return r;
+}
+__device__ __forceinline__ int xfix(__half x, const XScale& q) {
+    const int X = __float2int_rn(__half2float(x) * q.up);
+    return max(-(1 << 22), min(1 << 22, X));   // a non-finite activation must not leave the digit range
+}
+// X = 65536 h + 256 m + l with m, l in [-128, 127]; byte k of `pack` receives the digit.
+__device__ __forceinline__ void xdigits(int X, int k, uint32_t& ph, uint32_t& pm, uint32_t& pl) {
+    const int l = ((X + 128) & 255) - 128;
+    X = (X - l) >> 8;
+    const int m = ((X + 128) & 255) - 128;
+    const int h = (X - m) >> 8;
+    ph |= (uint32_t)(h & 255) << (8 * k);
+    pm |= (uint32_t)(m & 255) << (8 * k);
+    pl |= (uint32_t)(l & 255) << (8 * k);
+}
+
+// This warp's stream of one operator: nb blocks of TB tiles, each over nq groups of 64 inputs (+ a half group of 32 when
 // rem == 2).  The stream comes in ring units of whole groups (gu of them; a block with a half group is one unit), so
 // that one barrier wait is followed by straight-line code: every load of the unit can be issued ahead of its MMAs.
-// xs_addr: shared address of the fp16 activations of the warp's k-share.  dst[(block * TB + i) * 16 + row] receives
-// sum_j q[row][j] * x[j] of tile i of the block.  Tiles of a block are issued one after another per k-step, so TB
-// (2 * TB for narrow blocks) independent MMA chains are in flight.
+// xd_addr: shared address of the most significant digit plane at the warp's k-share.  dst[(block * TB + i) * 16 + row]
+// receives sum_j q[row][j] * x[j] of tile i of the block.  Tiles of a block are issued one after another per group, so
+// TB (2 * TB for narrow blocks) independent MMA chains are in flight.
 template <int TB>
-__device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const FGemvPlan& pl, const uint32_t xs_addr, float* dst) {
+__device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const FGemvPlan& pl, const uint32_t xd_addr, float* dst) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nq = pl.nq, rem = pl.rem;
     const int upb = rem ? 1 : nq / pl.gu, ng = rem ? nq : pl.gu;   // units per block, full groups per unit
     constexpr int NA = TB <= 2 ? 2 : 1;   // accumulators per tile: at least three independent chains in flight
+    // B fragment: column g of the MMA is digit plane g (columns 3-7 are zero); lane t holds 16 consecutive inputs of a group
+    const bool col = g < 3;
+    const uint32_t bbase = xd_addr + g * FP_MAX_H + t * 16, bhalf = xd_addr + g * FP_MAX_H + nq * 64 + t * 8;
+    const float inv = *cx.xinv;
     for (int b = 0; b < pl.nb; ++b) {
-        float acc[TB][NA][4];
+        int acc[TB][NA][4];
 #pragma unroll
         for (int i = 0; i < TB; ++i)
 #pragma unroll
             for (int h = 0; h < NA; ++h)
 #pragma unroll
-                for (int d = 0; d < 4; ++d) acc[i][h][d] = 0.0f;
+                for (int d = 0; d < 4; ++d) acc[i][h][d] = 0;
         for (int uu = 0; uu < upb; ++uu) {
             const uint32_t ubase = ring_wait(ring, cx, pl.unit_bytes);
             uint32_t a = ubase + lane * 16;
-            const uint32_t xq = xs_addr + uu * ng * 128;
+            const uint32_t xq = bbase + uu * ng * 64;
             for (int gq = 0; gq < ng; ++gq) {
-                // B fragment of the group: lanes 0-3 (column 0) hold the activations, the other columns are zero
-                const uint32_t ba = g == 0 ? xq + gq * 128 + t * 32 : cx.zero_addr;
-                const uint4 b03 = lds128(ba), b47 = lds128(ba + 16);
+                const uint4 bv = lds128(col ? xq + gq * 64 : cx.zero_addr);
                 uint4 w[TB];
 #pragma unroll
                 for (int i = 0; i < TB; ++i) w[i] = lds128(a + i * 512);
                 a += TB * 512;
 #pragma unroll
-                for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
+                for (int i = 0; i < TB; ++i) mma_pair(acc[i][0], w[i].x, w[i].y, bv.x, bv.y);
 #pragma unroll
-                for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
-#pragma unroll
-                for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].z, b47.x, b47.y);
-#pragma unroll
-                for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].w, b47.z, b47.w);
+                for (int i = 0; i < TB; ++i) mma_pair(acc[i][NA - 1], w[i].z, w[i].w, bv.z, bv.w);
             }
             if (rem == 2) {
-                const uint32_t ba = g == 0 ? xs_addr + nq * 128 + t * 16 : cx.zero_addr;
-                const uint4 b03 = lds128(ba);
+                const uint2 bv = lds64(col ? bhalf : cx.zero_addr);
                 const uint32_t h = ubase + nq * TB * 512 + lane * 8;
                 uint2 w[TB];
 #pragma unroll
                 for (int i = 0; i < TB; ++i) w[i] = lds64(h + i * 256);
 #pragma unroll
-                for (int i = 0; i < TB; ++i) mma_word(acc[i][0], w[i].x, b03.x, b03.y);
-#pragma unroll
-                for (int i = 0; i < TB; ++i) mma_word(acc[i][NA - 1], w[i].y, b03.z, b03.w);
+                for (int i = 0; i < TB; ++i) mma_pair(acc[i][0], w[i].x, w[i].y, bv.x, bv.y);
             }
             ring_release(ring, cx);
         }
-        if (t == 0) {
+        // D: lane t = 0 holds columns 0, 1 (digits 65536, 256) of rows g (d0, d1) and g + 8 (d2, d3), lane t = 1 column 2 (d0, d2)
 #pragma unroll
-            for (int i = 0; i < TB; ++i) {
-                dst[(b * TB + i) * 16 + g] = (NA == 2 ? acc[i][0][0] + acc[i][NA - 1][0] : acc[i][0][0]) * FP_MULT_LO;
-                dst[(b * TB + i) * 16 + g + 8] = (NA == 2 ? acc[i][0][2] + acc[i][NA - 1][2] : acc[i][0][2]) * FP_MULT_HI;
+        for (int i = 0; i < TB; ++i) {
+            int d[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) d[k] = NA == 2 ? acc[i][0][k] + acc[i][NA - 1][k] : acc[i][0][k];
+            const float lo_g = __shfl_down_sync(0xffffffffu, (float)d[0], 1), lo_g8 = __shfl_down_sync(0xffffffffu, (float)d[2], 1);
+            if (t == 0) {
+                dst[(b * TB + i) * 16 + g] = fmaf(65536.0f, (float)d[0], fmaf(256.0f, (float)d[1], lo_g)) * inv;
+                dst[(b * TB + i) * 16 + g + 8] = fmaf(65536.0f, (float)d[2], fmaf(256.0f, (float)d[3], lo_g8)) * (inv * 0.0625f);
             }
         }
     }
@@ -434,7 +449,7 @@ int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const 
     const int warp = threadIdx.x >> 5;
     const int a = warp / pl.wk, bk = warp % pl.wk;
     const int ksw = 4 * pl.nq + pl.rem;
-    const uint32_t xs_addr = x_cta_addr + bk * ksw * 32;
+    const uint32_t xs_addr = x_cta_addr + bk * ksw * 16;
     float* dst = cx.obuf + bk * (pl.n_mt * 16) + a * (pl.nb * pl.tb) * 16;
     switch (pl.tb) {
         case 1: gemv_core<1>(cx, ring, pl, xs_addr, dst); break;
@@ -444,7 +459,8 @@ int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const 
     }
     return make_int3(ring.uc, ring.pseg, ring.pu);
 }
-__device__ __forceinline__ void run_gemv(WarpRing& ring, const int op, const __half* x_cta) {
+// x_cta: the first input of the CTA within the digit planes (cx.xd + offset)
+__device__ __forceinline__ void run_gemv(WarpRing& ring, const int op, const uint8_t* x_cta) {
     const int3 r = gemv_entry(ring.uc, ring.pseg, ring.pu, op, smem_u32(x_cta));
     ring.uc = r.x; ring.pseg = r.y; ring.pu = r.z;
 }
@@ -499,13 +515,51 @@ __device__ __forceinline__ float block_sum_f(const FCtx& cx, float v) {   // all
     return s;
 }
 
+// Sum of v and maximum of a (a >= 0) over the CTA; all threads call.
+__device__ __forceinline__ void block_sum_max(const FCtx& cx, float v, float a, float& sum, float& amax) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, m);
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, m));
+    }
+    __syncthreads();
+    if (lane == 0) {
+        cx.wsum[warp] = v;
+        cx.wsum[F_NW + warp] = a;
+    }
+    __syncthreads();
+    sum = 0.0f;
+    amax = 0.0f;
+#pragma unroll
+    for (int w = 0; w < F_NW; ++w) {
+        sum += cx.wsum[w];
+        amax = fmaxf(amax, cx.wsum[F_NW + w]);
+    }
+}
+// A short activation vector (one element per thread, `n` of them) to the digit planes; a barrier must follow.
+__device__ __forceinline__ void quantise_own(const FCtx& cx, const __half v, const int n, const float amax) {
+    const int tid = threadIdx.x;
+    const XScale xq = xscale_for(amax);
+    if (tid < n) {
+        uint32_t ph = 0u, pm = 0u, pl = 0u;
+        xdigits(xfix(v, xq), 0, ph, pm, pl);
+        cx.xd[tid] = (uint8_t)ph;
+        cx.xd[FP_MAX_H + tid] = (uint8_t)pm;
+        cx.xd[2 * FP_MAX_H + tid] = (uint8_t)pl;
+    }
+    if (tid == 0) *cx.xinv = xq.inv;
+}
+
 // ---- gather of the hidden state + RMSNorm (rmsNormKernel, Inference.cu:111-145) --------------------------------------
-// Polls the H/2 tagged words of `hid`, normalises with `gamma` into `out` (shared memory).  x_full: sum of the
-// normalised vector; x_slice: sum over [slice * hs, (slice + 1) * hs) (hs a multiple of 128).
-template <bool SYS>
+// Polls the H/2 tagged words of `hid` and normalises with `gamma`.  QUANT: the result goes to the digit planes in fixed
+// point (the B operand of the operator that follows) and x_full / x_slice are the sums of those fixed-point values:
+// x_full over the whole vector, x_slice over [slice * hs, (slice + 1) * hs) (hs a multiple of 128).  Otherwise the fp16
+// result goes to `out` (shared memory) and `bound` receives an upper bound of its absolute values.
+template <bool SYS, bool QUANT>
 __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx, const unsigned long long* hid, const uint32_t tag,
                                             const __half* gamma, __half* out, const int slice, const int hs, float& x_full,
-                                            float& x_slice) {
+                                            float& x_slice, float& bound) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int H = p.g.H, nch = H >> 2;   // chunks of two words = four halves
     unsigned long long w[2][2] = {{0ull, 0ull}, {0ull, 0ull}};
@@ -534,26 +588,44 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
         }
     }
     double s = 0.0;
+    float amax = 0.0f;   // max |x_j * gamma_j|: with the norm's factor it bounds the result
 #pragma unroll
-    for (int e = 0; e < 2; ++e)
+    for (int e = 0; e < 2; ++e) {
+        const __half2* gh2 = reinterpret_cast<const __half2*>(&gm[e]);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {   // chunks past the end are zero
             const uint32_t pw = (uint32_t)w[e][k];
             const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw));
+            const float2 gf = __half22float2(gh2[k]);
             s += (double)(f.x * f.x);
             s += (double)(f.y * f.y);
+            amax = fmaxf(amax, fmaxf(fabsf(f.x * gf.x), fabsf(f.y * gf.y)));
         }
+    }
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) s += shfl_xor_double(s, m);
+    for (int m = 16; m > 0; m >>= 1) {
+        s += shfl_xor_double(s, m);
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    }
     __syncthreads();   // dsum / wsum of the phase before are no longer read
-    if (lane == 0) cx.dsum[warp] = s;
+    if (lane == 0) {
+        cx.dsum[warp] = s;
+        cx.wsum[2 * F_NW + warp] = amax;
+    }
     __syncthreads();
     double tot = cx.dsum[lane & (F_NW - 1)];
+    amax = cx.wsum[2 * F_NW + (lane & (F_NW - 1))];
 #pragma unroll
-    for (int m = 8; m > 0; m >>= 1) tot += shfl_xor_double(tot, m);
+    for (int m = 8; m > 0; m >>= 1) {
+        tot += shfl_xor_double(tot, m);
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    }
     const float mean_sq = __fdiv_rn((float)tot, (float)H);                          // Inference.cu:136
     const float denom = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, p.eps)));     // Inference.cu:137
     const __half nscale = __float2half_rn(denom);                                   // Inference.cu:138
+    // |fp16(fp16(x * nscale) * gamma)| <= |x * gamma| * nscale * (1 + 2^-11)^2 (+ half a subnormal step)
+    bound = amax * __half2float(nscale) * 1.002f + 1e-7f;
+    const XScale xq = xscale_for(bound);
     float ps[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -567,20 +639,36 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
             o[1] = h_mul(h_mul(__high2half(xa), nscale), gh[1]);
             o[2] = h_mul(h_mul(__low2half(xb), nscale), gh[2]);
             o[3] = h_mul(h_mul(__high2half(xb), nscale), gh[3]);
-            uint2 ov;
-            ov.x = pack_h2(o[0], o[1]);
-            ov.y = pack_h2(o[2], o[3]);
-            *reinterpret_cast<uint2*>(out + 4 * ch) = ov;
-            ps[e] = (__half2float(o[0]) + __half2float(o[1])) + (__half2float(o[2]) + __half2float(o[3]));
+            if (QUANT) {
+                uint32_t ph = 0u, pm = 0u, pl = 0u;
+                int sum = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int X = xfix(o[k], xq);
+                    xdigits(X, k, ph, pm, pl);
+                    sum += X;
+                }
+                *reinterpret_cast<uint32_t*>(cx.xd + 4 * ch) = ph;
+                *reinterpret_cast<uint32_t*>(cx.xd + FP_MAX_H + 4 * ch) = pm;
+                *reinterpret_cast<uint32_t*>(cx.xd + 2 * FP_MAX_H + 4 * ch) = pl;
+                ps[e] = (float)sum * xq.inv;
+            } else {
+                uint2 ov;
+                ov.x = pack_h2(o[0], o[1]);
+                ov.y = pack_h2(o[2], o[3]);
+                *reinterpret_cast<uint2*>(out + 4 * ch) = ov;
+                ps[e] = (__half2float(o[0]) + __half2float(o[1])) + (__half2float(o[2]) + __half2float(o[3]));
+            }
         }
     }
+    if (QUANT && tid == 0) *cx.xinv = xq.inv;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) ps[e] += __shfl_xor_sync(0xffffffffu, ps[e], m);
         if (lane == 0) cx.wsum[e * F_NW + warp] = ps[e];
     }
-    __syncthreads();   // `out` and the warp sums are visible
+    __syncthreads();   // the result and the warp sums are visible
     x_full = 0.0f;
     x_slice = 0.0f;
     const int lo = slice * hs, hi = lo + hs;
@@ -623,9 +711,9 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     const int o_first = rs * cglob;                              // this CTA's part of the residual stream
 
     // ---- RMSNorm + this CTA's K-slice of Wqkv for its head (Inference.cu:1036-1065) -----------------------------------
-    float x_full, x_slice;
+    float x_full, x_slice, x_bound;
     FP_STAMP(li, 0);
-    gather_norm<SYS>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, L.gamma, cx.xs, r, hs, x_full, x_slice);
+    gather_norm<SYS, true>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, L.gamma, nullptr, r, hs, x_full, x_slice, x_bound);
     FP_STAMP(li, 1);
     float sc = 0.0f, zp = 0.0f;
     if (tid < FP_QKV) {
@@ -633,12 +721,12 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         const long long o = (long long)(tile >> 3) * H + hglob * 128 + (tile & 7) * 16 + row;
         group_consts(lsz + F_QKV * FP_MAX_GROUPS, o, sc, zp);
     }
-    run_gemv(ring, F_QKV, cx.xs + r * hs);
+    run_gemv(ring, F_QKV, cx.xd + r * hs);
     __syncthreads();
     FP_STAMP(li, 2);
     if (tid < FP_QKV) {
         const float S = sum_k_shares(cx, p.plan[F_QKV], tid);
-        stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(sc * (S - (zp + a_offset(tid & 15)) * x_slice), t0));
+        stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(sc * (S - zp * x_slice), t0));
     }
     // ---- attention: cache rows of earlier positions are requested before q is known -----------------------------------
     const int len = pos + 1, chunk = (len + gs - 1) / gs;
@@ -802,18 +890,17 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
                 }
             }
         }
-        float cf = 0.0f;
-        if (tid < 128) {
-            const __half ch = __float2half_rn(O / Lsum);   // one rounding to fp16, Inference.cu:257-265
-            cx.ctx_s[tid] = ch;
-            cf = __half2float(ch);
-        }
-        const float x_o = block_sum_f(cx, cf);   // its barriers also publish ctx_s and free st
+        __half ch = __float2half_rn(0.0f);
+        if (tid < 128) ch = __float2half_rn(O / Lsum);   // one rounding to fp16, Inference.cu:257-265
+        float x_o, c_max;
+        block_sum_max(cx, __half2float(ch), fabsf(__half2float(ch)), x_o, c_max);   // its barriers also free st
+        quantise_own(cx, ch, 128, c_max);
+        __syncthreads();
         FP_STAMP(li, 5);
 
         // ---- Wo restricted to the head's 128 inputs, this CTA's share of the outputs (Inference.cu:1122-1141) ----------
         const FGemvPlan& plo = p.plan[F_WO];
-        run_gemv(ring, F_WO, cx.ctx_s);
+        run_gemv(ring, F_WO, cx.xd);
         __syncthreads();
         FP_STAMP(li, 6);
         const int n_out = plo.n_mt * 16;   // = hs
@@ -821,8 +908,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
             const long long o = (long long)r * hs + i0;
             float s2, z2;
             group_consts(lsz + F_WO * FP_MAX_GROUPS, o, s2, z2);
-            const float zo = z2 + a_offset(i0 & 15);   // i0 and i0 + 1 are rows of one half of a tile
-            const float y0 = s2 * (sum_k_shares(cx, plo, i0) - zo * x_o), y1 = s2 * (sum_k_shares(cx, plo, i0 + 1) - zo * x_o);
+            const float y0 = s2 * (sum_k_shares(cx, plo, i0) - z2 * x_o), y1 = s2 * (sum_k_shares(cx, plo, i0 + 1) - z2 * x_o);
             const int ro = p.hpr_shift >= 0 ? (int)(o >> p.hpr_shift) : (int)(o / (H / G.n_ranks));   // rank that owns these two elements
             stt2<SYS>(p.xo[ro] + (size_t)(hglob * gs + r) * n_out + i0, tagged_f(y0, t0 + 2), tagged_f(y1, t0 + 2));
         }
@@ -858,29 +944,26 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     if (c < G.n_mlp) {
     const int cmlp = G.rank * G.n_mlp + c;
     // ---- RMSNorm (same gamma) + this CTA's n1 outputs of W1 + GeLU (Inference.cu:1158-1197) ----------------------------------
-    gather_norm<SYS>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, cx.xs, -1, H, x_full, x_slice);
+    gather_norm<SYS, true>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, nullptr, -1, H, x_full, x_slice, x_bound);
     FP_STAMP(li, 9);
     if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cmlp * n1 + tid, sc, zp);
-    run_gemv(ring, F_W1, cx.xs);
+    run_gemv(ring, F_W1, cx.xd);
     __syncthreads();
-    float gv = 0.0f;
-    if (tid < n1) {
-        const float S = sum_k_shares(cx, p.plan[F_W1], tid);
-        const __half ge = gelu_h(__float2half_rn(sc * (S - (zp + a_offset(tid & 15)) * x_full)));
-        cx.g_s[tid] = ge;
-        gv = __half2float(ge);
-    }
-    const float x_g = block_sum_f(cx, gv);   // its barriers also publish g_s and free obuf
+    __half ge = __float2half_rn(0.0f);
+    if (tid < n1) ge = gelu_h(__float2half_rn(sc * (sum_k_shares(cx, p.plan[F_W1], tid) - zp * x_full)));
+    float x_g, g_max;
+    block_sum_max(cx, __half2float(ge), fabsf(__half2float(ge)), x_g, g_max);   // its barriers also free obuf
+    quantise_own(cx, ge, n1, g_max);
+    __syncthreads();
     FP_STAMP(li, 10);
     // ---- W2 restricted to those n1 inputs, all outputs (Inference.cu:1198-1214) ------------------------------------------------
-    run_gemv(ring, F_W2, cx.g_s);
+    run_gemv(ring, F_W2, cx.xd);
     __syncthreads();
     FP_STAMP(li, 11);
     for (int i0 = 2 * tid; i0 < H; i0 += 2 * FP_NT) {
         float s2, z2;
         group_consts(lsz + F_W2 * FP_MAX_GROUPS, i0, s2, z2);
-        const float zo = z2 + a_offset(i0 & 15);
-        const float y0 = s2 * (cx.obuf[i0] - zo * x_g), y1 = s2 * (cx.obuf[i0 + 1] - zo * x_g);
+        const float y0 = s2 * (cx.obuf[i0] - z2 * x_g), y1 = s2 * (cx.obuf[i0 + 1] - z2 * x_g);
         const int ro = p.hpr_shift >= 0 ? (i0 >> p.hpr_shift) : i0 / (H / G.n_ranks);
         stt2<SYS>(p.x2[ro] + (size_t)cmlp * H + i0, tagged_f(y0, t0 + 4), tagged_f(y1, t0 + 4));
     }
@@ -985,12 +1068,17 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
         }
         __syncthreads();
     }
-    float xf, xsl;
-    gather_norm<SYS>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, p.gamma_final, cx.hv, -1, H, xf, xsl);
+    float xf, xsl, hv_bound;
+    gather_norm<SYS, false>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, p.gamma_final, cx.hv, -1, H, xf, xsl, hv_bound);
     const int n_alloc = p.n_alloc[F_UNEMB];
     const int n_used = min(Kb, n_alloc);
     if (tid < n_used) cx.un_sz[tid] = pack_h2(p.un_scale[tid], p.un_zp[tid]);
     __syncthreads();
+    // |x'_j| = |fp16(scale * x_j)| <= largest |scale| * bound of x (+ rounding): one fixed-point scale serves every round
+    float smax = 0.0f;
+    for (int k = 0; k < n_used; ++k) smax = fmaxf(smax, fabsf(__half2float(__ushort_as_half((unsigned short)(cx.un_sz[k] & 0xffffu)))));
+    const XScale xq = xscale_for(hv_bound * smax * 1.001f + 1e-7f);
+    if (tid == 0) *cx.xinv = xq.inv;
     const FGemvPlan& pl = p.plan[F_UNEMB];
     const int mstep = Mb % Kb;
     float best = -INFINITY;
@@ -1005,30 +1093,25 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
         if (tid < Kb) gtab[tid] = cx.un_sz[((bmod + tid * mstep) % Kb) % n_alloc];
         __syncthreads();
         const bool kb_pow2 = (Kb & (Kb - 1)) == 0;
-        float zacc = 0.0f, xacc = 0.0f;
+        float zacc = 0.0f;
         for (int ch = tid; ch < (H >> 3); ch += FP_NT) {
             const uint4 xv = *reinterpret_cast<const uint4*>(cx.hv + 8 * ch);
             const __half* xh = reinterpret_cast<const __half*>(&xv);
-            uint4 ov;
-            __half* oh = reinterpret_cast<__half*>(&ov);
+            uint32_t ph[2] = {0u, 0u}, pm[2] = {0u, 0u}, pl[2] = {0u, 0u};
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int j = 8 * ch + e;
                 const uint32_t sz = gtab[kb_pow2 ? (j & (Kb - 1)) : (j % Kb)];
-                const __half xp = h_mul(__ushort_as_half((unsigned short)(sz & 0xffffu)), xh[e]);
-                oh[e] = xp;
-                zacc = fmaf(__half2float(__ushort_as_half((unsigned short)(sz >> 16))), __half2float(xp), zacc);
-                xacc += __half2float(xp);
+                const int X = xfix(h_mul(__ushort_as_half((unsigned short)(sz & 0xffffu)), xh[e]), xq);
+                xdigits(X, e & 3, ph[e >> 2], pm[e >> 2], pl[e >> 2]);
+                zacc = fmaf(__half2float(__ushort_as_half((unsigned short)(sz >> 16))), (float)X * xq.inv, zacc);
             }
-            *reinterpret_cast<uint4*>(cx.xs + 8 * ch) = ov;
+            *reinterpret_cast<uint2*>(cx.xd + 8 * ch) = make_uint2(ph[0], ph[1]);
+            *reinterpret_cast<uint2*>(cx.xd + FP_MAX_H + 8 * ch) = make_uint2(pm[0], pm[1]);
+            *reinterpret_cast<uint2*>(cx.xd + 2 * FP_MAX_H + 8 * ch) = make_uint2(pl[0], pl[1]);
         }
-        float Z = block_sum_f(cx, zacc);   // its barriers also publish xs
-#ifdef QW3_FP_A_OFFSET
-        Z += a_offset(tid & 15) * block_sum_f(cx, xacc);
-#else
-        (void)xacc;
-#endif
-        run_gemv(ring, F_UNEMB, cx.xs);
+        const float Z = block_sum_f(cx, zacc);   // its barriers also publish the digit planes
+        run_gemv(ring, F_UNEMB, cx.xd);
         __syncthreads();
         if (tid < 128) {
             const __half hl = __float2half_rn(sum_k_shares(cx, pl, tid) - Z);   // fp16 logits, Inference.cu:1270
@@ -1041,7 +1124,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
                 besti = (int)i;
             }
         }
-        __syncthreads();   // xs and obuf are rewritten by the next round
+        __syncthreads();   // the digit planes and obuf are rewritten by the next round
     }
     // winner of this CTA, then of all CTAs of all ranks
 #pragma unroll
@@ -1103,13 +1186,11 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.ring = smem;
     cx.obuf = reinterpret_cast<float*>(smem + FP_OFF_OBUF);
     cx.hv = reinterpret_cast<__half*>(smem + FP_OFF_HV);
-    cx.xs = reinterpret_cast<__half*>(smem + FP_OFF_XS);
+    cx.xd = smem + FP_OFF_XS;
     cx.seg = reinterpret_cast<int4*>(smem + FP_OFF_SEG);
     cx.lsz = reinterpret_cast<float2*>(smem + FP_OFF_LSZ);
     uint8_t* misc = smem + FP_OFF_MISC;
     cx.qkv_s = reinterpret_cast<__half*>(misc);                  // 768
-    cx.ctx_s = reinterpret_cast<__half*>(misc + 768);            // 256
-    cx.g_s = reinterpret_cast<__half*>(misc + 1024);             // 1024
     cx.hmine = reinterpret_cast<__half*>(misc + 2048);           // 512
     cx.rope_cs = reinterpret_cast<__half*>(misc + 2560);         // 256
     cx.wsum = reinterpret_cast<float*>(misc + 2816);             // 256
@@ -1118,6 +1199,7 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.argv = reinterpret_cast<float*>(misc + 3456);             // 64
     cx.argi = reinterpret_cast<int*>(misc + 3520);               // 64
     cx.s_dead = reinterpret_cast<int*>(misc + 3584);             // 16
+    cx.xinv = reinterpret_cast<float*>(misc + 3600);             // 16
     cx.zero_addr = smem_u32(misc + 3616);                        // 32 zero bytes (16-byte aligned)
     cx.bars = smem_u32(misc + 3712);                             // FP_SLOTS * 8
     cx.ring_cnt = reinterpret_cast<int*>(misc + 3840);           // FP_SLOTS * 4

@@ -5,10 +5,10 @@
 // cuBLAS walk it column-major (Inference.cu:1052-1065).  The on-disk files keep that layout (Inference.cu:780-900);
 // at load time each matrix is additionally rewritten, on the device, into the order in which the fused pass consumes
 // it: one byte stream per (CTA, warp), made of 512-byte items; the 16 warp streams of a CTA are interleaved in pieces of
-// whole k-groups ([unit][warp][piece]) so that one bulk copy fetches the next piece of every warp.  An item is one m16n8k16 A-operand tile
-// sequence: 16 outputs x 64 inputs, every lane owning one 16-byte piece = four 32-bit words = four k-steps, the eight
-// nibbles of a word sitting where one AND per register turns them into the fp16 A fragment.  (A trailing half group of
-// two k-steps makes a 256-byte item.)
+// whole k-groups ([unit][warp][piece]) so that one bulk copy fetches the next piece of every warp.  An item is the A operand of two
+// m16n8k32 integer MMAs: 16 outputs x 64 inputs, every lane owning one 16-byte piece = four 32-bit words, the eight
+// nibbles of a word sitting where one AND per register turns them into the u8 A fragment.  (A trailing half group of
+// 32 inputs makes a 256-byte item, one MMA.)
 //
 // A GEMV operator is cut twice.  Across CTAs: CTA c owns n_mt tiles of 16 outputs and n_ks k-steps of 16 inputs.
 // Across the 16 warps of a CTA: wm = 16 / wk warps along the tiles, wk warps along the k-steps; warp (a, bk) walks its
@@ -107,14 +107,17 @@ QW3_HD void fused_stream_locate(const FGemvPlan& pl, int stream_off, int& warp, 
 }
 
 // The eight nibbles of a word: nibble n (bits 4n .. 4n+3) holds W[row][j] with
-//   row = g + 8 * (n & 1)            (g = lane / 4: rows g of the tile come out of bits 0-3 / 8-11, rows g + 8 out of bits 4-7 / 12-15)
-//   j   = 16 * kstep + 4 * gsteps * t + 4 * s + 2 * ((n >> 1) & 1) + (n >> 2)      (t = lane % 4)
-// which is the m16n8k16 A fragment (a0: row g, k 2t..2t+1; a1: row g+8; a2: row g, k 2t+8..; a3: row g+8) when the B
-// fragment of lane t holds the activations 16*kstep + 4*gsteps*t + 4*s + {0,1} (b0) and + {2,3} (b1).
+//   row = g + 8 * (n & 1)            (g = lane / 4: the low nibble of every byte belongs to row g of the tile, the high one to row g + 8)
+//   j   = 16 * kstep + 4 * gsteps * t + 4 * s + (n >> 1)                           (t = lane % 4)
+// so that `w & 0x0f0f0f0f` and `w & 0xf0f0f0f0` of the words s = 0, 1 (and of s = 2, 3) of a lane are the u8 A fragment
+// of mma.sync.m16n8k32 (a0: row g, bytes k 4t..4t+3; a1: row g + 8; a2, a3: the same for k + 16) when the B fragment
+// of lane t holds, byte for byte, the inputs 16*kstep + 4*gsteps*t + 4*s + {0, 1, 2, 3}: lane t owns 4 * gsteps
+// consecutive inputs of the group.  (The MMA sums over all 32 k positions of a fragment, so which input sits at which
+// position is free as long as A and B agree.)
 QW3_HD void fused_nibble_src(const FWordPos& w, int n, int& row, int& j) {
     const int g = w.lane >> 2, t = w.lane & 3;
     row = g + 8 * (n & 1);
-    j = 16 * w.kstep + 4 * w.gsteps * t + 4 * w.s + 2 * ((n >> 1) & 1) + (n >> 2);
+    j = 16 * w.kstep + 4 * w.gsteps * t + 4 * w.s + (n >> 1);
 }
 
 // First output of tile `tile` of CTA `cta` (the tile covers 16 consecutive outputs), or -1 when the CTA has no such

@@ -117,14 +117,9 @@ def _consume(stream_words, p, g, op, cta, blk, x, y):
                     off += 32 * steps
                     for s in range(steps):
                         w = item[:, s].astype(np.int64)
-                        xb = q * 64 + 4 * steps * t + 4 * s                # B fragment: b0 = x[xb], x[xb+1]; b1 = x[xb+2], x[xb+3]
-                        u = w >> 8
-                        a0lo, a0hi = w & 0xF, (w >> 16) & 0xF              # w & 0x000f000f: rows g, k = 2t, 2t+1
-                        a1lo, a1hi = (w >> 4) & 0xF, (w >> 20) & 0xF       # w & 0x00f000f0: rows g + 8
-                        a2lo, a2hi = u & 0xF, (u >> 16) & 0xF              # (w >> 8) & 0x000f000f: rows g, k = 2t+8, 2t+9
-                        a3lo, a3hi = (u >> 4) & 0xF, (u >> 20) & 0xF       # rows g + 8
-                        lo = a0lo * xs[xb] + a0hi * xs[xb + 1] + a2lo * xs[xb + 2] + a2hi * xs[xb + 3]
-                        hi = a1lo * xs[xb] + a1hi * xs[xb + 1] + a3lo * xs[xb + 2] + a3hi * xs[xb + 3]
+                        xb = q * 64 + 4 * steps * t + 4 * s                # B fragment: byte k of this lane's register s = x[xb + k]
+                        lo = sum(((w >> (8 * k)) & 0xF) * xs[xb + k] for k in range(4))        # w & 0x0f0f0f0f: rows g
+                        hi = sum(((w >> (8 * k + 4)) & 0xF) * xs[xb + k] for k in range(4))    # w & 0xf0f0f0f0: rows g + 8 (x 16 in the MMA)
                         np.add.at(acc[i], gq, lo)
                         np.add.at(acc[i], gq + 8, hi)
             for i in range(p["tb"]):
