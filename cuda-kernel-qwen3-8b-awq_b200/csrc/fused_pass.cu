@@ -123,8 +123,17 @@ struct FusedParams {
             p.trace[((size_t)blockIdx.x * p.n_layers + (li)) * 16 + (k)] = t__;                       \
         }                                                                                            \
     } while (0)
+// Cycle stamps of the warps of CTA 0 inside the GEMV of operator `op` (tail of the trace buffer: [op][warp][8]).
+#define FP_WSTAMP(op, k)                                                                                   \
+    do {                                                                                                   \
+        extern __shared__ __align__(1024) uint8_t smem_w__[];                                              \
+        unsigned long long* tr__ = *reinterpret_cast<unsigned long long**>(smem_w__ + FP_OFF_MISC + 3680); \
+        if (tr__ != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0)                                 \
+            tr__[(op) * 128 + (threadIdx.x >> 5) * 8 + (k)] = (unsigned long long)clock64();               \
+    } while (0)
 #else
 #define FP_STAMP(li, k) do { } while (0)
+#define FP_WSTAMP(op, k) do { } while (0)
 #endif
 
 // ---- tagged words ------------------------------------------------------------------------------------------------
@@ -181,6 +190,7 @@ struct FCtx {
     int* s_dead;
     int* err;           // device error word of the launch
     const FGemvPlan* plans;   // [F_NOPS] the operator plans, copied to shared memory for the out-of-line GEMV
+    const int4* wplan;        // [F_NOPS][F_NW] per operator and warp: {byte offset of its k-share in a digit plane, float offset of its sums in obuf, units per block, groups per unit}
     int* ring_cnt;      // [FP_SLOTS] warps that have consumed their piece of the unit in the slot
     int* ring_issued;   // units requested so far (only the issuing thread of the moment writes it)
     uint32_t bars;      // shared address of the ring barriers [FP_SLOTS]
@@ -233,7 +243,6 @@ __device__ __forceinline__ void poll_batch(const FusedParams& p, const FCtx& cx,
 struct WarpRing {
     int uc;        // units consumed by this warp so far
     int pseg, pu;  // unit FP_SLOTS places ahead of uc: segment and unit within it (pseg == n_seg: past the end)
-    uint64_t policy;
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
@@ -266,7 +275,7 @@ __device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, co
 #endif
     *cx.ring_issued += 1;
     mbar_expect_tx(bar, F_NW * piece);
-    bulk_load(smem_u32(cx.ring) + slot * (F_NW * F_UNIT), base + (size_t)r.pu * (F_NW * piece), F_NW * piece, bar, r.policy);
+    bulk_load(smem_u32(cx.ring) + slot * (F_NW * F_UNIT), base + (size_t)r.pu * (F_NW * piece), F_NW * piece, bar, l2_policy_evict_first());
 }
 
 // Shared address of this warp's piece (of `piece` bytes) of the unit it consumes next, once the unit has landed.
@@ -369,10 +378,10 @@ __device__ __forceinline__ void xdigits(int X, int k, uint32_t& ph, uint32_t& pm
 // receives sum_j q[row][j] * x[j] of tile i of the block.  Tiles of a block are issued one after another per group, so
 // TB (2 * TB for narrow blocks) independent MMA chains are in flight.
 template <int TB>
-__device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const FGemvPlan& pl, const uint32_t xd_addr, float* dst) {
+__device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const FGemvPlan& pl, const uint32_t xd_addr, float* dst, const int op,
+                                          const int upb, const int ng) {   // units per block, full groups per unit
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nq = pl.nq, rem = pl.rem;
-    const int upb = rem ? 1 : nq / pl.gu, ng = rem ? nq : pl.gu;   // units per block, full groups per unit
     constexpr int NA = TB <= 2 ? 2 : 1;   // accumulators per tile: at least three independent chains in flight
     // B fragment: column g of the MMA is digit plane g (columns 3-7 are zero); lane t holds 16 consecutive inputs of a group
     const bool col = g < 3;
@@ -388,6 +397,7 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
                 for (int d = 0; d < 4; ++d) acc[i][h][d] = 0;
         for (int uu = 0; uu < upb; ++uu) {
             const uint32_t ubase = ring_wait(ring, cx, pl.unit_bytes);
+            if (b == 0 && uu == 0) FP_WSTAMP(op, 1);
             uint32_t a = ubase + lane * 16;
             const uint32_t xq = bbase + uu * ng * 64;
             for (int gq = 0; gq < ng; ++gq) {
@@ -410,7 +420,9 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
 #pragma unroll
                 for (int i = 0; i < TB; ++i) mma_pair(acc[i][0], w[i].x, w[i].y, bv.x, bv.y);
             }
+            FP_WSTAMP(op, 2);
             ring_release(ring, cx);
+            FP_WSTAMP(op, 3);
         }
         // D: lane t = 0 holds columns 0, 1 (digits 65536, 256) of rows g (d0, d1) and g + 8 (d2, d3), lane t = 1 column 2 (d0, d2)
 #pragma unroll
@@ -441,22 +453,23 @@ __device__ __noinline__
 #endif
 int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const uint32_t x_cta_addr) {
     extern __shared__ __align__(1024) uint8_t smem[];
+    FP_WSTAMP(op, 0);
     const FCtx cx = carve_ctx(smem);
     WarpRing ring;
     ring.uc = uc; ring.pseg = pseg; ring.pu = pu;
-    ring.policy = l2_policy_evict_first();
     const FGemvPlan& pl = cx.plans[op];
-    const int warp = threadIdx.x >> 5;
-    const int a = warp / pl.wk, bk = warp % pl.wk;
-    const int ksw = 4 * pl.nq + pl.rem;
-    const uint32_t xs_addr = x_cta_addr + bk * ksw * 16;
-    float* dst = cx.obuf + bk * (pl.n_mt * 16) + a * (pl.nb * pl.tb) * 16;
+    const int4 wp = cx.wplan[op * F_NW + (threadIdx.x >> 5)];
+    const uint32_t xs_addr = x_cta_addr + wp.x;
+    float* dst = cx.obuf + wp.y;
     switch (pl.tb) {
-        case 1: gemv_core<1>(cx, ring, pl, xs_addr, dst); break;
-        case 2: gemv_core<2>(cx, ring, pl, xs_addr, dst); break;
-        case 3: gemv_core<3>(cx, ring, pl, xs_addr, dst); break;
-        default: gemv_core<4>(cx, ring, pl, xs_addr, dst); break;
+#ifndef QW3_FP_TB34
+        case 1: gemv_core<1>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
+        case 2: gemv_core<2>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
+#endif
+        case 3: gemv_core<3>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
+        default: gemv_core<4>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
     }
+    FP_WSTAMP(op, 4);
     return make_int3(ring.uc, ring.pseg, ring.pu);
 }
 // x_cta: the first input of the CTA within the digit planes (cx.xd + offset)
@@ -1007,46 +1020,6 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     (void)lane; (void)warp;
 }
 
-#ifdef QW3_FP_L2PF
-// CTAs without a part in the layers pull the weight streams into L2 half a layer ahead of their consumers, so that the
-// consumers' ring loads are L2 hits: the first half of a layer (Wqkv, Wo) once the layer before has published its
-// attention output, the second half (W1, W2) once the layer itself has started.
-template <bool SYS>
-__device__ __forceinline__ void l2_prefetch_pass(const FusedParams& p, const FCtx& cx) {
-    const int tid = threadIdx.x;
-    const FusedGeom& G = p.g;
-    const int n_idle = G.grid - G.n_act, ic = blockIdx.x - G.n_act;
-    constexpr int CH = 4096;
-    for (int li = 0; li < p.n_layers; ++li) {
-        for (int half = 0; half < 2; ++half) {
-            // half 0 of layer li waits for hid[0] of layer li - 1 (phase 3), half 1 for the hidden state layer li starts from
-            uint32_t tag = 0u;
-            const unsigned long long* word = nullptr;
-            if (half == 0 && li > 0) { tag = cx.tagbase + 2 + 6 * (li - 1) + 3; word = p.hid[G.rank]; }
-            if (half == 1) { tag = li == 0 ? cx.tagbase + 1 : cx.tagbase + 2 + 6 * (li - 1) + 5; word = p.hid[G.rank] + (G.H >> 1); }
-            if (word != nullptr) {
-                if (tid == 0) {
-                    const long long t_begin = clock64();
-                    while (!has_tag(ldt<SYS>(word), tag) && *cx.s_dead == 0) {
-                        if (clock64() - t_begin > FP_WAIT_PEER) { fail(cx, 0x90000 | li); break; }
-                        __nanosleep(200);
-                    }
-                }
-                __syncthreads();
-            }
-            for (int k = 2 * half; k < 2 * half + 2; ++k) {
-                const uint8_t* base = p.layers[li].d.w[k];
-                const long long bytes = (long long)p.plan[k].n_cta * F_NW * p.plan[k].warp_bytes;
-                for (long long off = ((long long)ic * FP_NT + tid) * CH; off < bytes; off += (long long)n_idle * FP_NT * CH) {
-                    const unsigned sz = (unsigned)min((long long)CH, bytes - off);
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
-                }
-            }
-        }
-    }
-}
-#endif
-
 // ---- final norm + unembedding + arg-max (sampleNextToken, Inference.cu:1235-1292) ---------------------------------------------
 template <bool SYS>
 __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx, WarpRing& ring) {
@@ -1210,6 +1183,8 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.err = *reinterpret_cast<int**>(misc + 5632);                // written by the kernel before the first use
     cx.n_seg = *reinterpret_cast<int*>(misc + 5640);
     cx.plans = reinterpret_cast<const FGemvPlan*>(misc + 5648);   // F_NOPS plans
+    cx.wplan = reinterpret_cast<const int4*>(misc + 5888);        // F_NOPS * F_NW entries
+    static_assert(5648 + F_NOPS * sizeof(FGemvPlan) <= 5888 && 5888 + F_NOPS * F_NW * 16 <= FP_MISC_BYTES, "plans in the misc area");
     cx.tagbase = 0;
     cx.pos = 0;
     return cx;
@@ -1223,10 +1198,20 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         if (threadIdx.x == 0) {
             *reinterpret_cast<int**>(misc0 + 5632) = p.err;
             *reinterpret_cast<int*>(misc0 + 5640) = 4 * p.n_layers + p.n_rounds;
+#ifdef QW3_TRACE
+            *reinterpret_cast<unsigned long long**>(misc0 + 3680) = p.trace ? p.trace + (size_t)gridDim.x * p.n_layers * 16 : nullptr;
+#endif
         }
         static_assert(sizeof(FGemvPlan) % 4 == 0 && 5648 + F_NOPS * sizeof(FGemvPlan) <= FP_MISC_BYTES, "plans in the misc area");
         for (int i = threadIdx.x; i < (int)(F_NOPS * sizeof(FGemvPlan) / 4); i += FP_NT)
             reinterpret_cast<int*>(misc0 + 5648)[i] = reinterpret_cast<const int*>(p.plan)[i];
+        if (threadIdx.x < F_NOPS * F_NW) {   // what a warp derives from the plan, once instead of at every call
+            const FGemvPlan& pl = p.plan[threadIdx.x / F_NW];
+            const int warp = threadIdx.x % F_NW, a = warp / pl.wk, bk = warp % pl.wk;
+            reinterpret_cast<int4*>(misc0 + 5888)[threadIdx.x] =
+                make_int4(bk * (4 * pl.nq + pl.rem) * 16, bk * (pl.n_mt * 16) + a * (pl.nb * pl.tb) * 16, pl.rem ? 1 : pl.nq / pl.gu,
+                          pl.rem ? pl.nq : pl.gu);
+        }
         __syncthreads();
     }
     FCtx cx = carve_ctx(smem);
@@ -1281,7 +1266,6 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
 #endif
     WarpRing ring;
     ring.uc = 0; ring.pseg = 0; ring.pu = 0;
-    ring.policy = l2_policy_evict_first();
     for (int s = 0; s < FP_SLOTS; ++s) {   // prime the ring: thread 0 issues, every warp moves its cursor along
         if (ring_cursor_valid(ring, cx)) {
 #ifndef QW3_FP_NOLOAD
@@ -1334,7 +1318,6 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         }
     }
 #ifdef QW3_FP_L2PF
-    if (!active) l2_prefetch_pass<SYS>(p, cx);
 #endif
     if (p.n_rounds > 0) sample_pass<SYS>(p, cx, ring);
     // After a wait has given up, units may have been requested that nobody consumed: their copies must have landed
