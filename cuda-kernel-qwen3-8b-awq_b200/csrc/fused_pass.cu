@@ -44,7 +44,7 @@ namespace qw3 {
 
 constexpr int FP_NT = F_NW * 32;          // threads per CTA
 #ifndef QW3_FP_SLOTS
-#define QW3_FP_SLOTS 2
+#define QW3_FP_SLOTS 3
 #endif
 constexpr int FP_SLOTS = QW3_FP_SLOTS;    // ring units in flight
 constexpr int FP_MAX_H = 4096;            // largest hidden size (activation vectors kept in shared memory)
@@ -131,9 +131,18 @@ struct FusedParams {
         if (tr__ != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0)                                 \
             tr__[(op) * 128 + (threadIdx.x >> 5) * 8 + (k)] = (unsigned long long)clock64();               \
     } while (0)
+// Warp 0 of CTA 0: cycle stamps before / after the wait for unit `u` of operator `op` ([op][32][2] after the warp stamps).
+#define FP_USTAMP(op, u, k)                                                                                \
+    do {                                                                                                   \
+        extern __shared__ __align__(1024) uint8_t smem_w__[];                                              \
+        unsigned long long* tr__ = *reinterpret_cast<unsigned long long**>(smem_w__ + FP_OFF_MISC + 3680); \
+        if (tr__ != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && (u) < 32)                            \
+            tr__[640 + ((op) * 32 + (u)) * 2 + (k)] = (unsigned long long)clock64();                       \
+    } while (0)
 #else
 #define FP_STAMP(li, k) do { } while (0)
 #define FP_WSTAMP(op, k) do { } while (0)
+#define FP_USTAMP(op, u, k) do { } while (0)
 #endif
 
 // ---- tagged words ------------------------------------------------------------------------------------------------
@@ -307,7 +316,7 @@ __device__ __forceinline__ void ring_release(WarpRing& r, const FCtx& cx) {
 #ifndef QW3_FP_NOLOAD
     if ((threadIdx.x & 31) == 0) {
         uint32_t old;
-        asm volatile("atom.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(cx.ring_cnt + slot)) : "memory");
+        asm volatile("atom.release.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(cx.ring_cnt + slot)) : "memory");
         if (old == F_NW - 1) {
             cx.ring_cnt[slot] = 0;
             if (more && *cx.s_dead == 0) ring_issue(r, cx, slot);
@@ -318,16 +327,16 @@ __device__ __forceinline__ void ring_release(WarpRing& r, const FCtx& cx) {
     ++r.uc;
 }
 
-// Shared-memory loads of the weight stream and of the B fragments.  Not volatile: the compiler may schedule them
-// among the MMAs; the address they use is made to depend on the barrier wait (ring_wait), so none moves above it.
+// Shared-memory loads of the weight stream and of the B fragments.  Volatile, so that the compiler keeps them between
+// the wait for their unit and the count that releases it (both volatile); the MMAs are free to move.
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
-    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
     uint2 v;
-    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -387,6 +396,8 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
     const bool col = g < 3;
     const uint32_t bbase = xd_addr + g * FP_MAX_H + t * 16, bhalf = xd_addr + g * FP_MAX_H + nq * 64 + t * 8;
     const float inv = *cx.xinv;
+    uint32_t next_base = ring_wait(ring, cx, pl.unit_bytes);
+    FP_WSTAMP(op, 1);
     for (int b = 0; b < pl.nb; ++b) {
         int acc[TB][NA][4];
 #pragma unroll
@@ -396,8 +407,7 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
 #pragma unroll
                 for (int d = 0; d < 4; ++d) acc[i][h][d] = 0;
         for (int uu = 0; uu < upb; ++uu) {
-            const uint32_t ubase = ring_wait(ring, cx, pl.unit_bytes);
-            if (b == 0 && uu == 0) FP_WSTAMP(op, 1);
+            const uint32_t ubase = next_base;
             uint32_t a = ubase + lane * 16;
             const uint32_t xq = bbase + uu * ng * 64;
             for (int gq = 0; gq < ng; ++gq) {
@@ -406,6 +416,13 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
 #pragma unroll
                 for (int i = 0; i < TB; ++i) w[i] = lds128(a + i * 512);
                 a += TB * 512;
+                if (rem != 2 && gq + 1 == ng) {   // the unit's last loads are issued
+                    if (b == 0 && uu == 0) FP_WSTAMP(op, 2);
+                    ring_release(ring, cx);
+                    if (b == 0 && uu == 0) FP_WSTAMP(op, 3);
+                    if (uu + 1 < upb || b + 1 < pl.nb) next_base = ring_wait(ring, cx, pl.unit_bytes);
+                    if (b == 0 && uu == 0) FP_WSTAMP(op, 5);
+                }
 #pragma unroll
                 for (int i = 0; i < TB; ++i) mma_pair(acc[i][0], w[i].x, w[i].y, bv.x, bv.y);
 #pragma unroll
@@ -417,14 +434,14 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
                 uint2 w[TB];
 #pragma unroll
                 for (int i = 0; i < TB; ++i) w[i] = lds64(h + i * 256);
+                ring_release(ring, cx);
+                if (uu + 1 < upb || b + 1 < pl.nb) next_base = ring_wait(ring, cx, pl.unit_bytes);
 #pragma unroll
                 for (int i = 0; i < TB; ++i) mma_pair(acc[i][0], w[i].x, w[i].y, bv.x, bv.y);
             }
-            FP_WSTAMP(op, 2);
-            ring_release(ring, cx);
-            FP_WSTAMP(op, 3);
         }
         // D: lane t = 0 holds columns 0, 1 (digits 65536, 256) of rows g (d0, d1) and g + 8 (d2, d3), lane t = 1 column 2 (d0, d2)
+        if (b + 1 == pl.nb) FP_WSTAMP(op, 6);
 #pragma unroll
         for (int i = 0; i < TB; ++i) {
             int d[4];

@@ -29,7 +29,7 @@ namespace qw3 {
 
 constexpr int F_NW = 16;          // warps per CTA
 #ifndef QW3_F_UNIT
-#define QW3_F_UNIT 4096
+#define QW3_F_UNIT 3072
 #endif
 constexpr int F_UNIT = QW3_F_UNIT;   // largest piece of one warp in a ring unit (a unit = 16 pieces = one bulk copy)
 
