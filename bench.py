@@ -37,10 +37,10 @@ from __graft_entry__ import load_oracle, load_package  # noqa: E402
 
 METRIC = "batch-1 decode tokens/s (Qwen3-8B W4A16)"
 LAST_REF_GEMV_US = None
-# dram__bytes_read.sum + dram__bytes_write.sum of decode_pass_kernel over its algorithmic bytes, from the ncu
-# capture summarised in profiles/ (a 6-layer pass; traffic grows with the bytes streamed).
-NCU_TRAFFIC_RATIO = (509.30 + 4.82) / 507.6
-NCU_TRAFFIC_NOTE = ("dram read+write of an ncu capture of a 6-layer pass (514.1 MB for 507.6 MB algorithmic), scaled by bytes to the "
+# dram__bytes_read.sum + dram__bytes_write.sum of fused_pass_kernel over its algorithmic bytes, from the ncu
+# capture summarised in profiles/fused_pass_kernel_6layers_ncu.md (a 6-layer pass; traffic grows with the bytes streamed).
+NCU_TRAFFIC_RATIO = (509.34 + 13.53) / 507.52
+NCU_TRAFFIC_NOTE = ("dram read+write of an ncu capture of a 6-layer pass (522.9 MB for 507.5 MB algorithmic), scaled by bytes to the "
                     "36-layer launch")
 PROMPT_LEN = 128          # one GPU: prompt 128 + 20 new ids is the baseline's single-GPU configuration
 PROMPT_LEN_MULTI = 512    # several GPUs: prompt 512 + 128 new ids
