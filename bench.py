@@ -419,6 +419,8 @@ def main():
     ap.add_argument("--parallel", default="tp", choices=["pp", "tp"],
                     help="several GPUs: row-split of every matrix over the GPUs (default: the only form in which a second GPU's "
                          "bandwidth works on the same token) or the reference's layer pipeline")
+    ap.add_argument("--attn-split-min", type=int, default=0,
+                    help="fused pass: contexts longer than this are split over the CTAs of a head group (0: the engine's default)")
     ap.add_argument("--only-roofline", action="store_true", help="run only the dominant-kernel timing (small case for profilers)")
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)
@@ -499,14 +501,15 @@ def main():
     max_pos = args.prompt_len + W + (R + 2) * K + 8
     if world > 1 and tp:
         # one process per GPU, every matrix row-split over the GPUs; partial sums cross NVLink inside the pass kernel
-        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, world=world, rank=rank, tensor_parallel=1, device=[local] * 8)
+        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, world=world, rank=rank, tensor_parallel=1, device=[local] * 8,
+                                attn_split_min=args.attn_split_min)
         pipeline.connect_all(inf, dist)
     elif world > 1:
         # one process per GPU: this rank owns stage `rank`; hidden state and token id move by peer stores
         inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=world, world=world, rank=rank, device=list(range(world)))
         pipeline.connect_ring(inf, dist)
     else:
-        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)))
+        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)), attn_split_min=args.attn_split_min)
     barrier()
     ids_all = inf.generateResponse(prompt, W)              # prompt pass + W warm-up decode steps
     sampler = ClockSampler(local)

@@ -575,6 +575,7 @@ int qw3_config_default(Qw3Config* c) {
     c->hidden = 4096; c->inter = 12288; c->heads = 32; c->head_dim = 128; c->layers = 36; c->vocab = 151936;
     c->max_pos = 40960; c->eps = 1e-6f; c->rope_base = 10000.0f; c->sample_first = 0;
     c->n_stages = 1; c->rank = 0; c->world = 1; c->use_graph = 1; c->use_pdl = 1; c->keep_logits = 0; c->persistent = 2;
+    c->attn_split_min = 0;
     return QW3_OK;
 }
 
@@ -646,6 +647,7 @@ static int create_fused(qw3_engine* e, Stage& s) {
     std::memset(&a, 0, sizeof(a));
     a.H = c.hidden; a.I = c.inter; a.heads = c.heads; a.vocab = c.vocab; a.n_layers = n_layers; a.eps = c.eps; a.max_pos = c.max_pos;
     a.n_ranks = n_ranks; a.rank = rank; a.sm_count = ws->sm_count; a.device = s.device;
+    a.attn_split_min = c.attn_split_min > 0 ? c.attn_split_min : 32;
     a.layers = in.data();
     a.emb = first ? &emb : nullptr;
     a.unemb = last ? &unemb : nullptr;

@@ -23,6 +23,7 @@ struct FusedLayerIn {
 struct FusedCreate {
     int H, I, heads, vocab, n_layers;
     float eps;
+    int attn_split_min;        // contexts longer than this are split over the CTAs of a head group
     long long max_pos;
     int n_ranks, rank;         // row-split over GPUs (1, 0 otherwise)
     int sm_count, device;

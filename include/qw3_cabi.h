@@ -198,6 +198,9 @@ typedef struct Qw3Config {
                               1: one persistent kernel walking an operator list; 0: one launch per operator */
     int32_t tensor_parallel; /* with world > 1: 1 = every matrix row-split over the `world` GPUs instead of the layer pipeline (see
                                 qw3_tp_export); needs n_stages = 1, device[0] = this process's GPU, persistent = 2 */
+    int32_t attn_split_min;  /* fused pass: contexts longer than this many positions are split over the CTAs that share a head
+                                (an exchange between them merges the parts); shorter ones are run whole by each of them.
+                                0 = default (32; measured at 133, 517 and 1029 positions the split is the faster form) */
 } Qw3Config;
 
 typedef struct qw3_engine* qw3_handle;

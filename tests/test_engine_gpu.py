@@ -122,6 +122,13 @@ def test_small_model_every_step_and_hidden_probes(pkg, orc, cuda, small_dir, nam
     _check_steps_and_probes(pkg, orc, name, small_dir, SMALL, persistent, 10)
 
 
+def test_small_model_attention_split_over_the_head_group(pkg, orc, cuda, small_dir):
+    """The fused pass runs short contexts whole in every CTA of a head group and splits long ones over the group
+    (attn_split_min); the default keeps the small model's contexts whole, so this run forces the split from the fourth
+    position on: same ids, top-8 logits and hidden-state probes."""
+    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, attn_split_min=3), 2, 10)
+
+
 @pytest.mark.parametrize("persistent", [2, 1, 0])
 @pytest.mark.parametrize("n_stages", [2, 3, 4])
 def test_stage_split_does_not_change_tokens(pkg, orc, cuda, small_dir, n_stages, persistent):

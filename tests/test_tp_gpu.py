@@ -31,7 +31,10 @@ def _rank_main(rank, world, port, wdir, prompt, q, batched):
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
     try:
         torch.cuda.set_device(rank)
-        inf = pkg.QWen3AWQInfer(wdir, world=world, rank=rank, tensor_parallel=1, device=[rank], keep_logits=1, **SMALL)
+        # one case also splits the attention over the CTAs of a head group from the fourth position on (the default keeps
+        # contexts this short whole)
+        inf = pkg.QWen3AWQInfer(wdir, world=world, rank=rank, tensor_parallel=1, device=[rank], keep_logits=1,
+                                attn_split_min=3 if (world == 2 and not batched) else 0, **SMALL)
         pipeline.connect_all(inf, dist)
         inf.set_batched_prefill(bool(batched))
         ids = inf.generateResponse(prompt, 6)
