@@ -421,6 +421,7 @@ def main():
                          "bandwidth works on the same token) or the reference's layer pipeline")
     ap.add_argument("--attn-split-min", type=int, default=0,
                     help="fused pass: contexts longer than this are split over the CTAs of a head group (0: the engine's default)")
+    ap.add_argument("--no-cluster", action="store_true", help="fused pass: head groups exchange through global memory instead of a thread-block cluster")
     ap.add_argument("--only-roofline", action="store_true", help="run only the dominant-kernel timing (small case for profilers)")
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)
@@ -509,7 +510,8 @@ def main():
         inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=world, world=world, rank=rank, device=list(range(world)))
         pipeline.connect_ring(inf, dist)
     else:
-        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)), attn_split_min=args.attn_split_min)
+        inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)), attn_split_min=args.attn_split_min,
+                                no_cluster=1 if args.no_cluster else 0)
     barrier()
     ids_all = inf.generateResponse(prompt, W)              # prompt pass + W warm-up decode steps
     sampler = ClockSampler(local)

@@ -33,6 +33,7 @@
 // tensor-core GEMM, and the tests hold this kernel to the logits tolerance.
 // The unembedding's groups depend on the input index; there the scale is folded into the activations per block of
 // 128 outputs (x'_j = scale_g(b,j) * x_j) and the same loop runs.
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <vector>
@@ -63,7 +64,10 @@ constexpr size_t FP_OFF_SEG = FP_OFF_XS + (size_t)FP_MAX_H * 3;   // three digit
 constexpr size_t FP_OFF_LSZ = FP_OFF_SEG + (size_t)FP_MAX_SEG * 16;          // [2][4][FP_MAX_GROUPS] (scale, zero point) as floats
 constexpr size_t FP_OFF_MISC = FP_OFF_LSZ + (size_t)2 * 4 * FP_MAX_GROUPS * 8;
 constexpr size_t FP_MISC_BYTES = 8192;
-constexpr size_t FP_SMEM_BYTES = FP_OFF_MISC + FP_MISC_BYTES;
+constexpr int FP_CL_MAX = 4;              // largest head group that exchanges through distributed shared memory (one thread-block cluster)
+constexpr size_t FP_OFF_CL = FP_OFF_MISC + FP_MISC_BYTES;                    // xq_in [FP_CL_MAX][FP_QKV], xa_in [FP_CL_MAX][FP_ATT_STRIDE] floats, 2 barriers
+constexpr size_t FP_CL_BYTES = (size_t)FP_CL_MAX * (FP_QKV + FP_ATT_STRIDE) * 4 + 64;
+constexpr size_t FP_SMEM_BYTES = FP_OFF_CL + FP_CL_BYTES;
 
 struct FLayerDesc {
     const uint8_t* w[4];        // repacked Wqkv, Wo, W1, W2 of this rank
@@ -101,6 +105,7 @@ struct FusedParams {
     __half* hidden;               // residual stream between passes (plain)
     const int* d_pos; const int* d_token; const int* d_skip; const int* d_prompt; const int* d_gen;
     int decode;
+    int cluster;                  // 1: the gs CTAs of a head are one thread-block cluster and exchange through distributed shared memory
     const __half* cos_t; const __half* sin_t;
     long long max_pos;
     int* d_token_out;
@@ -186,6 +191,9 @@ struct FCtx {
     __half* hv;
     uint8_t* xd;        // [3][FP_MAX_H] digits of the fixed-point activations of the operator about to run (plane c = digit c, most significant first)
     float* xinv;        // 2^-sh of those activations
+    float* xq_in;       // [gs][FP_QKV] cluster exchange: slot r is written by CTA r of the head group (into every member's copy)
+    float* xa_in;       // [gs][FP_ATT_STRIDE]
+    uint32_t cl_bars;   // shared address of the two barriers of the cluster exchange (xq, xa)
     int4* seg;          // {base lo, base hi, warp_bytes, unit_bytes} per weight segment of this CTA
     float2* lsz;        // [2][4][FP_MAX_GROUPS] (scale, zero point) of the layer's four matrices, two layers (current / next)
     FLayerDesc* ldesc;  // [2] descriptor of the current / next layer
@@ -724,6 +732,40 @@ __device__ __forceinline__ void publish_hidden(const FusedParams& p, const FCtx&
     }
 }
 
+// ---- exchange inside a head group through distributed shared memory (the group is one thread-block cluster) --------------
+// A value goes into the same slot of every member's shared memory by an asynchronous store that also counts its bytes
+// off the member's barrier (st.async ... mbarrier::complete_tx), so no fence and no separate arrival follow: the first
+// form of this exchange (plain remote stores, then a release arrival per warp on every member's barrier) took a
+// microsecond longer than the tagged words in global memory it replaced.  A member arms its OWN barrier once per
+// layer with the bytes it expects, waits on it (one lane per warp polls, bounded) and reads its own shared memory.
+__device__ __forceinline__ uint32_t cl_map(uint32_t addr, int cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cl_store(const float* slot, float v, uint32_t bar, int gs) {
+    const uint32_t a = smem_u32(slot);
+    for (int q = 0; q < gs; ++q)
+        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                     ::"r"(cl_map(a, q)), "r"(__float_as_uint(v)), "r"(cl_map(bar, q)) : "memory");
+}
+__device__ __forceinline__ void cl_wait(const FCtx& cx, uint32_t bar, uint32_t parity, int code) {   // whole warps call
+    if ((threadIdx.x & 31) == 0) {
+        const long long t_begin = clock64();
+        for (;;) {
+            uint32_t ok;
+            asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok || *cx.s_dead != 0) break;
+            if (clock64() - t_begin > FP_WAIT_LOCAL) {
+                fail(cx, code);   // a member of the head group never delivered its part
+                break;
+            }
+        }
+    }
+    __syncwarp();
+}
+
 // ---- one decoder layer for the CTAs that run the layers (runOneLayer, Inference.cu:1029-1230) -----------------------------
 template <bool SYS>
 __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx, WarpRing& ring, const int li) {
@@ -757,7 +799,12 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     FP_STAMP(li, 2);
     if (tid < FP_QKV) {
         const float S = sum_k_shares(cx, p.plan[F_QKV], tid);
-        stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(sc * (S - zp * x_slice), t0));
+        const float part = sc * (S - zp * x_slice);
+        if (p.cluster) {
+            cl_store(cx.xq_in + r * FP_QKV + tid, part, cx.cl_bars, gs);
+        } else {
+            stt<false>(p.xq + (size_t)c * FP_QKV + tid, tagged_f(part, t0));
+        }
     }
     // ---- attention: cache rows of earlier positions are requested before q is known -----------------------------------
     // Very short contexts: every CTA of the head group runs over ALL positions and the exchange of the attention states
@@ -767,6 +814,10 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     const bool split = gs > 1 && len > p.attn_split_min;
     const int chunk = split ? (len + gs - 1) / gs : len;
     const int p0 = split ? r * chunk : 0, p1 = min(len, p0 + chunk);
+    if (p.cluster && tid == 0) {   // bytes the other members (and this CTA) will store into this CTA's slots in this layer
+        mbar_expect_tx(cx.cl_bars, (uint32_t)gs * FP_QKV * 4);
+        if (split) mbar_expect_tx(cx.cl_bars + 8, (uint32_t)gs * 130 * 4);
+    }
     const int grp = tid >> 4, sl = tid & 15;
     constexpr int NG = FP_NT / 16, UN = 2;
     const __half* kh = L.kc + (size_t)hglob * p.max_pos * 128 + sl * 8;
@@ -788,13 +839,18 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     // ---- group exchange: q, k, v of the head = ordered sum of the gs K-slices; RoPE; KV append (Inference.cu:1070-1103)
     if (tid < FP_QKV) {
         float v = 0.0f;
-        const unsigned long long* src = p.xq + (size_t)(h_l * gs) * FP_QKV + tid;
-        for (int r0 = 0; r0 < gs; r0 += 4) {
-            unsigned long long w[4];
-            poll_batch<false, 4>(p, cx, gs - r0, [&](int e) { return src + (size_t)(r0 + e) * FP_QKV; }, t0, 0x30000 | li, w);
+        if (p.cluster) {
+            cl_wait(cx, cx.cl_bars, li & 1, 0x30000 | li);
+            for (int r0 = 0; r0 < gs; ++r0) v += cx.xq_in[r0 * FP_QKV + tid];
+        } else {
+            const unsigned long long* src = p.xq + (size_t)(h_l * gs) * FP_QKV + tid;
+            for (int r0 = 0; r0 < gs; r0 += 4) {
+                unsigned long long w[4];
+                poll_batch<false, 4>(p, cx, gs - r0, [&](int e) { return src + (size_t)(r0 + e) * FP_QKV; }, t0, 0x30000 | li, w);
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (r0 + e < gs) v += payload_f(w[e]);
+                for (int e = 0; e < 4; ++e)
+                    if (r0 + e < gs) v += payload_f(w[e]);
+            }
         }
         const int tile = tid >> 4, row = tid & 15, sec = tile >> 3, d = (tile & 7) * 16 + row;
         __half me = __float2half_rn(v);                                                       // Inference.cu:1062 (fp16 store)
@@ -895,21 +951,37 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         FP_STAMP(li, 4);
         if (split) {
             // group exchange: every CTA of the head stores its state and merges all gs of them in CTA order
-            if (tid < 128) stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + tid, tagged_f(O, t0 + 1));
-            if (tid == 0) {
-                stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + 128, tagged_f(M, t0 + 1));
-                stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + 129, tagged_f(Lsum, t0 + 1));
-            }
-            __syncthreads();   // everybody has read st
-            if (tid < 130) {
-                const unsigned long long* src = p.xa + (size_t)(h_l * gs) * FP_ATT_STRIDE + tid;
-                for (int r0 = 0; r0 < gs; r0 += 4) {
-                    unsigned long long w[4];
-                    poll_batch<false, 4>(p, cx, gs - r0, [&](int e) { return src + (size_t)(r0 + e) * FP_ATT_STRIDE; }, t0 + 1,
-                                         0x40000 | li, w);
+            if (p.cluster) {
+                if (tid < 128) {
+                    cl_store(cx.xa_in + r * FP_ATT_STRIDE + tid, O, cx.cl_bars + 8, gs);
+                    if (tid == 0) {
+                        cl_store(cx.xa_in + r * FP_ATT_STRIDE + 128, M, cx.cl_bars + 8, gs);
+                        cl_store(cx.xa_in + r * FP_ATT_STRIDE + 129, Lsum, cx.cl_bars + 8, gs);
+                    }
+                }
+                __syncthreads();   // everybody has read st
+                if (tid < 160) {
+                    cl_wait(cx, cx.cl_bars + 8, li & 1, 0x40000 | li);
+                    if (tid < 130)
+                        for (int r0 = 0; r0 < gs; ++r0) st[r0 * FP_ATT_STRIDE + tid] = cx.xa_in[r0 * FP_ATT_STRIDE + tid];
+                }
+            } else {
+                if (tid < 128) stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + tid, tagged_f(O, t0 + 1));
+                if (tid == 0) {
+                    stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + 128, tagged_f(M, t0 + 1));
+                    stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + 129, tagged_f(Lsum, t0 + 1));
+                }
+                __syncthreads();   // everybody has read st
+                if (tid < 130) {
+                    const unsigned long long* src = p.xa + (size_t)(h_l * gs) * FP_ATT_STRIDE + tid;
+                    for (int r0 = 0; r0 < gs; r0 += 4) {
+                        unsigned long long w[4];
+                        poll_batch<false, 4>(p, cx, gs - r0, [&](int e) { return src + (size_t)(r0 + e) * FP_ATT_STRIDE; }, t0 + 1,
+                                             0x40000 | li, w);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        if (r0 + e < gs) st[(r0 + e) * FP_ATT_STRIDE + tid] = payload_f(w[e]);
+                        for (int e = 0; e < 4; ++e)
+                            if (r0 + e < gs) st[(r0 + e) * FP_ATT_STRIDE + tid] = payload_f(w[e]);
+                    }
                 }
             }
             __syncthreads();
@@ -1183,6 +1255,9 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.obuf = reinterpret_cast<float*>(smem + FP_OFF_OBUF);
     cx.hv = reinterpret_cast<__half*>(smem + FP_OFF_HV);
     cx.xd = smem + FP_OFF_XS;
+    cx.xq_in = reinterpret_cast<float*>(smem + FP_OFF_CL);
+    cx.xa_in = cx.xq_in + FP_CL_MAX * FP_QKV;
+    cx.cl_bars = smem_u32(smem + FP_OFF_CL + (size_t)FP_CL_MAX * (FP_QKV + FP_ATT_STRIDE) * 4);
     cx.seg = reinterpret_cast<int4*>(smem + FP_OFF_SEG);
     cx.lsz = reinterpret_cast<float2*>(smem + FP_OFF_LSZ);
     uint8_t* misc = smem + FP_OFF_MISC;
@@ -1272,9 +1347,20 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         }
         *cx.s_dead = 0;
         *cx.ring_issued = 0;
+        if (p.cluster) {   // one arrival per layer: this CTA arming the barrier with the bytes it expects
+            mbar_init(cx.cl_bars, 1);
+            mbar_init(cx.cl_bars + 8, 1);
+        }
         mbar_fence_init();
     }
     if (tid < 8) zero[tid] = 0u;
+#ifdef QW3_TRACE
+    if (tid == 0 && p.trace != nullptr && p.n_layers > 0) {   // which SM runs this CTA (slot 15 of its first layer's stamps)
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.trace[((size_t)blockIdx.x * p.n_layers) * 16 + 15] = smid;
+    }
+#endif
     cx.pos = __ldcg(p.d_pos);
     const int gen = p.d_gen != nullptr ? __ldcg(p.d_gen) : 0;
     cx.tagbase = (((uint32_t)gen & 0x3fu) << 26) | ((((uint32_t)cx.pos + 1u) & 0x1ffffu) << 9);
@@ -1283,6 +1369,10 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         cx.rope_cs[64 + tid] = p.sin_t[(size_t)cx.pos * 64 + tid];
     }
     __syncthreads();
+    if (p.cluster) {   // every member's barriers exist before anybody arrives on them (the only unbounded wait: it is the first thing every CTA does)
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
 #ifdef QW3_FP_FILL
     for (int i = tid; i < (int)(FP_OFF_OBUF / 4); i += FP_NT) reinterpret_cast<uint32_t*>(smem)[i] = (uint32_t)i * 2654435761u + 12345u * blockIdx.x;
     __syncthreads();
@@ -1561,6 +1651,26 @@ static void exchange_words(const FusedGeom& g, size_t (&w)[4]) {
     w[3] = 2 * (size_t)g.n_ranks * g.grid;
 }
 
+// Cooperative launch of `grid` CTAs; cluster > 0: in thread-block clusters of that many CTAs.
+static void fused_launch_config(int grid, int cluster, cudaStream_t st, cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr) {
+    *cfg = cudaLaunchConfig_t{};
+    cfg->gridDim = dim3(grid);
+    cfg->blockDim = dim3(FP_NT);
+    cfg->dynamicSmemBytes = FP_SMEM_BYTES;
+    cfg->stream = st;
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+    if (cluster > 0) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = cluster;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg->numAttrs = 2;
+    }
+}
+
 int fused_create(const FusedCreate& a, FusedPass** out) {
     FusedPass* f = new (std::nothrow) FusedPass();
     if (!f) return QW3_ERR_NOMEM;
@@ -1584,6 +1694,31 @@ int fused_create(const FusedCreate& a, FusedPass** out) {
     if (ce != cudaSuccess || nb < 1) {
         set_last_error("fused_pass_kernel does not fit on an SM (%zu bytes of shared memory): %s", FP_SMEM_BYTES, cudaGetErrorString(ce));
         return bail(QW3_ERR_CUDA);
+    }
+    // One GPU, head groups of 2 .. FP_CL_MAX CTAs: the group becomes a thread-block cluster and exchanges through
+    // distributed shared memory, when the device can hold enough clusters at once for the CTAs that run the layers.
+    // (The grid is then a multiple of the cluster size, so the plan is made again for that grid.)
+    if (g.n_ranks == 1 && g.gs >= 2 && g.gs <= FP_CL_MAX && !a.no_cluster) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[2];
+        fused_launch_config(a.sm_count - a.sm_count % g.gs, g.gs, a.stream, &cfg, attr);
+        int n_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, fused_pass_kernel<false>, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n_clusters = 0;
+        }
+        const int grid_c = std::min(a.sm_count - a.sm_count % g.gs, n_clusters * g.gs);
+        if (grid_c >= g.n_act) {
+            const int gs_before = g.gs;
+            FusedGeom g2;
+            FGemvPlan pl2[F_NOPS];
+            if (fused_plan(a.H, a.I, a.heads, a.vocab, a.n_layers, a.max_pos, a.n_ranks, a.rank, grid_c, &g2, pl2) && g2.gs == gs_before) {
+                P.g = g2;
+                for (int k = 0; k < F_NOPS; ++k) P.plan[k] = pl2[k];
+                f->grid = grid_c;
+                P.cluster = 1;
+            }
+        }
     }
     P.n_layers = a.n_layers;
     P.eps = a.eps;
@@ -1714,7 +1849,10 @@ int fused_launch(FusedPass* f, int decode, cudaStream_t st) {
     if (!decode) p.n_rounds = 0;   // prompt passes compute no logits (Inference.cu:1304-1343)
     void* args[] = {&p};
     const void* fn = f->sys ? reinterpret_cast<const void*>(fused_pass_kernel<true>) : reinterpret_cast<const void*>(fused_pass_kernel<false>);
-    QW3_CUDA(cudaLaunchCooperativeKernel(fn, dim3(f->grid), dim3(FP_NT), args, FP_SMEM_BYTES, st));
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    fused_launch_config(f->grid, p.cluster ? p.g.gs : 0, st, &cfg, attr);
+    QW3_CUDA(cudaLaunchKernelExC(&cfg, fn, args));
     return QW3_OK;
 }
 

@@ -24,6 +24,7 @@ struct FusedCreate {
     int H, I, heads, vocab, n_layers;
     float eps;
     int attn_split_min;        // contexts longer than this are split over the CTAs of a head group
+    int no_cluster;            // 1: head groups exchange through global memory even where a thread-block cluster could carry them
     long long max_pos;
     int n_ranks, rank;         // row-split over GPUs (1, 0 otherwise)
     int sm_count, device;

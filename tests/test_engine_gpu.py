@@ -129,6 +129,14 @@ def test_small_model_attention_split_over_the_head_group(pkg, orc, cuda, small_d
     _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, attn_split_min=3), 2, 10)
 
 
+def test_small_model_head_groups_without_cluster(pkg, orc, cuda, small_dir):
+    """On one GPU the CTAs of a head group exchange through distributed shared memory (one thread-block cluster per
+    group); no_cluster=1 keeps them on tagged words in global memory, the form the row split over GPUs uses: same
+    results, with the attention whole and split."""
+    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, no_cluster=1), 2, 10)
+    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, no_cluster=1, attn_split_min=3), 2, 10)
+
+
 @pytest.mark.parametrize("persistent", [2, 1, 0])
 @pytest.mark.parametrize("n_stages", [2, 3, 4])
 def test_stage_split_does_not_change_tokens(pkg, orc, cuda, small_dir, n_stages, persistent):
