@@ -163,6 +163,185 @@ attn_prefill_kernel(const __half* __restrict__ qkv, const __half* __restrict__ k
     ctx[(size_t)r * hidden + head * 128 + tid] = __float2half_rn(O / L);
 }
 
+// ---- the same attention on the tensor cores, tiled: 64 query rows x 64 cache rows at a time ------------------------------
+// grid (heads, ceil(R / 64)), 4 warps; warp w owns query rows 16w .. 16w+15 of the CTA's block.  A tile of 64 cache rows
+// of K and V (16 KB each) is shared by the 64 query rows instead of being read once per row from L2, which is what
+// made the row-per-CTA kernel take 1.8 of the 2.0 s of an 8 K prompt.  Per tile and warp: S = Q K^T by 64
+// mma.sync.m16n8k16 (fp16 operands, exact products, fp32 sums), online softmax in registers in the accumulator layout,
+// O += P V by 64 more with P as the A operand.  P goes in as TWO fp16 terms (P = hi + lo, lo the rounding error of hi),
+// so the probabilities keep 22 bits as in the fp32 arithmetic of the row kernel; V comes in through
+// ldmatrix.trans.  K / V tiles are double-buffered with cp.async; rows past the causal limit are zero-filled and masked.
+// (mma.sync, not tcgen05: an accumulator that the softmax rescales every tile has to live in registers.)
+constexpr int TA_ROWS = 64, TA_KEYS = 64, TA_THREADS = 128;
+constexpr int TA_LD = 136;                                   // halves per shared-memory row (272 B: ldmatrix rows 16-byte aligned, no bank conflicts)
+constexpr size_t TA_TILE = (size_t)TA_KEYS * TA_LD * 2;      // bytes of one K or V tile
+constexpr size_t TA_SMEM = (size_t)TA_ROWS * TA_LD * 2 + 4 * TA_TILE;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_h(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16 bytes global -> shared; `valid` false: the 16 bytes are zero-filled (the source is not read)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void split_hi_lo(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(a - hf.x, b - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+__global__ void __launch_bounds__(TA_THREADS)
+attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc, int hidden,
+                          long long max_pos, int pos0, int rows, __half* __restrict__ ctx) {
+    extern __shared__ __align__(128) uint8_t ta_smem[];
+    const int head = blockIdx.x, r0 = blockIdx.y * TA_ROWS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t q_s = smem_u32(ta_smem), kv_s = q_s + TA_ROWS * TA_LD * 2;   // kv_s + (2 * stage + {0: K, 1: V}) * TA_TILE
+    const int n_rows = min(TA_ROWS, rows - r0);
+    const int n_keys = pos0 + r0 + n_rows;                       // cache rows any query row of this block may see
+    const int n_tiles = (n_keys + TA_KEYS - 1) / TA_KEYS;
+    const __half* kh = kc + (size_t)head * max_pos * 128;
+    const __half* vh = vc + (size_t)head * max_pos * 128;
+    auto load_tile = [&](int tile, int stage) {
+        const int k0 = tile * TA_KEYS;
+        for (int i = tid; i < TA_KEYS * 16; i += TA_THREADS) {   // 16-byte pieces: 16 per cache row
+            const int row = i >> 4, piece = i & 15, key = k0 + row;
+            const bool ok = key < n_keys;
+            const size_t src = (size_t)(ok ? key : 0) * 128 + piece * 8;
+            const uint32_t dst = (uint32_t)(row * TA_LD + piece * 8) * 2;
+            cp_async16(kv_s + (2 * stage) * TA_TILE + dst, kh + src, ok);
+            cp_async16(kv_s + (2 * stage + 1) * TA_TILE + dst, vh + src, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(0, 0);
+    for (int i = tid; i < TA_ROWS * 16; i += TA_THREADS) {       // the block's q rows (after RoPE), zero past the last row
+        const int row = i >> 4, piece = i & 15;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows) v = *reinterpret_cast<const uint4*>(qkv + (size_t)(r0 + row) * 3 * hidden + head * 128 + piece * 8);
+        *reinterpret_cast<uint4*>(ta_smem + (size_t)(row * TA_LD + piece * 8) * 2) = v;
+    }
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int d = 0; d < 4; ++d) o[n][d] = 0.0f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;   // rows g and g + 8 of the warp's 16
+    const float scale = 1.0f / sqrtf(128.0f);                             // Inference.cu:218
+    const int pos_lo = pos0 + r0 + warp * 16 + g, pos_hi = pos_lo + 8;    // last cache row each of the two query rows sees
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        const int stage = tile & 1;
+        if (tile + 1 < n_tiles) {
+            load_tile(tile + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();   // the tile (and, the first time, the q rows) are in shared memory
+        const uint32_t k_s = kv_s + (2 * stage) * TA_TILE, v_s = k_s + TA_TILE;
+        // ---- S = Q K^T: 16 rows x 64 keys per warp
+        float sc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int d = 0; d < 4; ++d) sc[j][d] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(q_s + (uint32_t)((warp * 16 + (lane & 15)) * TA_LD + kk * 16 + 8 * (lane >> 4)) * 2, a0, a1, a2, a3);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {   // two key tiles per ldmatrix: (b0, b1) of tile j, then of tile j + 1
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(k_s + (uint32_t)((j * 8 + (lane & 7) + 8 * (lane >> 4)) * TA_LD + kk * 16 + 8 * ((lane >> 3) & 1)) * 2, b0, b1, b2, b3);
+                mma_h(sc[j], a0, a1, a2, a3, b0, b1);
+                mma_h(sc[j + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        // ---- scale, causal mask, online softmax (rows g: regs 0, 1; rows g + 8: regs 2, 3; keys 8j + 2t, + 1)
+        const int k0 = tile * TA_KEYS;
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                const int key = k0 + j * 8 + 2 * t + (d & 1);
+                const bool ok = key <= ((d & 2) ? pos_hi : pos_lo);
+                sc[j][d] = ok ? sc[j][d] * scale : -INFINITY;
+            }
+            mx_lo = fmaxf(mx_lo, fmaxf(sc[j][0], sc[j][1]));
+            mx_hi = fmaxf(mx_hi, fmaxf(sc[j][2], sc[j][3]));
+        }
+#pragma unroll
+        for (int msk = 1; msk <= 2; msk <<= 1) {
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, msk));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, msk));
+        }
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float c_lo = (m_lo == -INFINITY) ? 0.0f : expf(m_lo - mn_lo), c_hi = (m_hi == -INFINITY) ? 0.0f : expf(m_hi - mn_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        l_lo *= c_lo;
+        l_hi *= c_hi;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            o[n][0] *= c_lo; o[n][1] *= c_lo;
+            o[n][2] *= c_hi; o[n][3] *= c_hi;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {   // a row with nothing visible yet (only rows past the block's end) keeps p = 0
+            sc[j][0] = (mn_lo == -INFINITY) ? 0.0f : expf(sc[j][0] - mn_lo);
+            sc[j][1] = (mn_lo == -INFINITY) ? 0.0f : expf(sc[j][1] - mn_lo);
+            sc[j][2] = (mn_hi == -INFINITY) ? 0.0f : expf(sc[j][2] - mn_hi);
+            sc[j][3] = (mn_hi == -INFINITY) ? 0.0f : expf(sc[j][3] - mn_hi);
+            l_lo += sc[j][0] + sc[j][1];
+            l_hi += sc[j][2] + sc[j][3];
+        }
+        // ---- O += P V: P (16 x 64) as A operand, hi and lo terms; V through ldmatrix.trans
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {   // 16 keys: score tiles 2kk and 2kk + 1
+            uint32_t h0, h1, h2, h3, e0, e1, e2, e3;
+            split_hi_lo(sc[2 * kk][0], sc[2 * kk][1], h0, e0);
+            split_hi_lo(sc[2 * kk][2], sc[2 * kk][3], h1, e1);
+            split_hi_lo(sc[2 * kk + 1][0], sc[2 * kk + 1][1], h2, e2);
+            split_hi_lo(sc[2 * kk + 1][2], sc[2 * kk + 1][3], h3, e3);
+#pragma unroll
+            for (int n = 0; n < 16; n += 2) {   // two tiles of 8 dims per ldmatrix
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(v_s + (uint32_t)((kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * TA_LD + n * 8 + 8 * (lane >> 4)) * 2, b0, b1, b2, b3);
+                mma_h(o[n], h0, h1, h2, h3, b0, b1);
+                mma_h(o[n], e0, e1, e2, e3, b0, b1);
+                mma_h(o[n + 1], h0, h1, h2, h3, b2, b3);
+                mma_h(o[n + 1], e0, e1, e2, e3, b2, b3);
+            }
+        }
+        __syncthreads();   // everybody is done with this stage before the tile after next lands in it
+    }
+#pragma unroll
+    for (int msk = 1; msk <= 2; msk <<= 1) {
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, msk);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, msk);
+    }
+    const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+        if (row_lo < n_rows)
+            *reinterpret_cast<__half2*>(ctx + (size_t)(r0 + row_lo) * hidden + head * 128 + n * 8 + 2 * t) =
+                __floats2half2_rn(o[n][0] / l_lo, o[n][1] / l_lo);   // one rounding to fp16, Inference.cu:257-265
+        if (row_hi < n_rows)
+            *reinterpret_cast<__half2*>(ctx + (size_t)(r0 + row_hi) * hidden + head * 128 + n * 8 + 2 * t) =
+                __floats2half2_rn(o[n][2] / l_hi, o[n][3] / l_hi);
+    }
+}
+
 // The residual add (Inference.cu:1145-1156) and the GeLU (Inference.cu:271-279) of the block run in the epilogue of the
 // tensor-core contraction that produces their operand.
 
@@ -191,11 +370,35 @@ int rope_kv_rows_launch(void* qkv, void* kc, void* vc, const void* cos_t, const 
 }
 int attn_prefill_launch(const void* qkv, const void* kc, const void* vc, int heads, int hidden, long long max_pos, int pos0,
                         int rows, void* ctx, cudaStream_t st) {
-    attn_prefill_kernel<<<dim3(heads, rows), PF_THREADS, 0, st>>>(static_cast<const __half*>(qkv), static_cast<const __half*>(kc),
-                                                                  static_cast<const __half*>(vc), hidden, max_pos, pos0,
-                                                                  static_cast<__half*>(ctx));
+    if (rows >= 16) {   // blocks of rows: the tiled tensor-core kernel; a few rows: one CTA per row
+        static bool attr_set[64] = {};   // per device: the kernel's shared-memory limit is raised once
+        int dev = 0;
+        QW3_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) {
+            QW3_CUDA(cudaFuncSetAttribute(attn_prefill_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TA_SMEM));
+        } else if (!attr_set[dev]) {
+            QW3_CUDA(cudaFuncSetAttribute(attn_prefill_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TA_SMEM));
+            attr_set[dev] = true;
+        }
+        attn_prefill_tiled_kernel<<<dim3(heads, (rows + TA_ROWS - 1) / TA_ROWS), TA_THREADS, TA_SMEM, st>>>(
+            static_cast<const __half*>(qkv), static_cast<const __half*>(kc), static_cast<const __half*>(vc), hidden, max_pos, pos0,
+            rows, static_cast<__half*>(ctx));
+    } else {
+        attn_prefill_kernel<<<dim3(heads, rows), PF_THREADS, 0, st>>>(static_cast<const __half*>(qkv), static_cast<const __half*>(kc),
+                                                                      static_cast<const __half*>(vc), hidden, max_pos, pos0,
+                                                                      static_cast<__half*>(ctx));
+    }
     QW3_CUDA(cudaGetLastError());
     return QW3_OK;
 }
 
 }  // namespace qw3
+
+extern "C" int qw3_attn_prefill(const void* d_qkv, const void* d_k_cache, const void* d_v_cache, int32_t heads, int32_t head_dim,
+                                int64_t max_pos, int32_t pos0, int32_t rows, void* d_ctx, void* stream) {
+    QW3_REQUIRE(d_qkv && d_k_cache && d_v_cache && d_ctx, "qw3_attn_prefill: null pointer");
+    QW3_REQUIRE(head_dim == 128 && heads > 0, "qw3_attn_prefill: head_dim must be 128, heads positive");
+    QW3_REQUIRE(rows > 0 && pos0 >= 0 && (int64_t)pos0 + rows <= max_pos, "qw3_attn_prefill: rows out of range");
+    return qw3::attn_prefill_launch(d_qkv, d_k_cache, d_v_cache, heads, heads * 128, max_pos, pos0, rows, d_ctx,
+                                    static_cast<cudaStream_t>(stream));
+}

@@ -104,6 +104,14 @@ def attn_decode(q, k_cache, v_cache, heads, max_pos, pos, ws, d_pos=None):
     return ctx
 
 
+def attn_prefill(qkv, k_cache, v_cache, heads, max_pos, pos0, rows):
+    """Causal attention of a block of prompt rows (qkv: [rows][3 * heads * 128], q already rotated)."""
+    ctx = torch.empty(rows, heads * 128, dtype=torch.float16, device=qkv.device)
+    cabi.check(cabi.lib().qw3_attn_prefill(_ptr(qkv), _ptr(k_cache), _ptr(v_cache), heads, 128, max_pos, pos0, rows, _ptr(ctx),
+                                           _stream()), "qw3_attn_prefill")
+    return ctx
+
+
 def embed_gather_w4(packed, scale, zp, hidden, vocab, token, d_token=None):
     out = torch.empty(hidden, dtype=torch.float16, device=packed.device)
     cabi.check(cabi.lib().qw3_embed_gather_w4(_ptr(packed), _ptr(scale), _ptr(zp), scale.numel(), hidden, vocab,

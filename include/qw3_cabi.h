@@ -154,6 +154,14 @@ int qw3_attn_decode(const void* d_q, const void* d_k_cache, const void* d_v_cach
                     int32_t head_dim, int64_t max_pos, const int32_t* d_pos, int32_t pos,
                     void* d_ctx, qw3_ws_t ws, void* stream);
 
+/* The same attention for a block of `rows` consecutive prompt positions pos0 .. pos0 + rows - 1 (the batched prompt phase;
+ * the reference runs attentionKernel once per prompt token, Inference.cu:1304-1343): row r of d_qkv ([rows][3 * heads * 128]
+ * fp16, q in the first third, after RoPE) attends cache rows 0 .. pos0 + r, which must already hold the block's own k / v
+ * rows; d_ctx is [rows][heads * 128] fp16.  From 16 rows on a tiled tensor-core kernel runs (64 query rows share each tile
+ * of 64 cache rows), below that one CTA per row. */
+int qw3_attn_prefill(const void* d_qkv, const void* d_k_cache, const void* d_v_cache, int32_t heads, int32_t head_dim,
+                     int64_t max_pos, int32_t pos0, int32_t rows, void* d_ctx, void* stream);
+
 /* Embedding column gather straight from the packed [hidden][vocab] matrix (gather lambda,
  * Inference.cu:1310-1315).  Token from *d_token when it is not NULL, else `token`. */
 int qw3_embed_gather_w4(const void* d_packed, const void* d_scale, const void* d_zp, int64_t n_groups_alloc,

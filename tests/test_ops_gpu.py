@@ -50,6 +50,24 @@ def test_attention_decode(ops, orc, cuda, heads, max_pos, length):
     assert (d > 1).mean() < 0.01
 
 
+@pytest.mark.parametrize("heads,max_pos,pos0,rows", [(4, 256, 0, 64), (4, 600, 100, 37), (32, 1024, 256, 256), (2, 4096, 3000, 130),
+                                                     (4, 64, 3, 5), (3, 300, 0, 16), (2, 700, 511, 129)])
+def test_attention_prefill_block(ops, orc, cuda, heads, max_pos, pos0, rows):
+    """A block of prompt rows: row r must equal the oracle's attention of its q over cache rows 0 .. pos0 + r.  Blocks
+    that start inside a tile, end inside a row block, sit far from position 0, and blocks of a few rows (one CTA per row)."""
+    H = heads * 128
+    qkv = orc.gen_normal_f16(29, orc.ACT, rows * 3 * H).reshape(rows, 3 * H)
+    kc = orc.gen_normal_f16(29, orc.KV_K, heads * max_pos * 128)
+    vc = orc.gen_normal_f16(29, orc.KV_V, heads * max_pos * 128)
+    got = ops.attn_prefill(_to_dev(qkv, cuda), _to_dev(kc, cuda), _to_dev(vc, cuda), heads, max_pos, pos0, rows).cpu().numpy()
+    check = sorted(set([0, 1, 15, 16, 63, 64, rows // 2, rows - 2, rows - 1]) & set(range(rows)))
+    for r in check:
+        want = orc.attention(np.ascontiguousarray(qkv[r, :H]), kc, vc, heads, 128, max_pos, pos0 + r + 1)
+        err = np.abs(got[r].astype(np.float32) - want.astype(np.float32))
+        assert (err <= 2e-2 * np.abs(want.astype(np.float32)) + 2e-3).all(), r
+        assert (_ulp_diff(got[r], want) > 1).mean() < 0.01, r
+
+
 def test_embed_gather_bit_exact(ops, orc, cuda):
     H, V = 512, 4096 + 256
     p, s, z = orc.gen_linear(24, H, V, kind=orc.EMB)
