@@ -629,7 +629,7 @@ def main():
                        "note": f"host wall-clock of generateResponse(prompt of {len(prompt)} ids in host memory, {K} new ids back in host memory); "
                                "prompt in blocks of rows through the tensor-core contraction",
                        "token_loop": None if tp else {"value": K / gen["loop_s"], "wall_s": gen["loop_s"], "prompt_phase_ms": gen["loop_prompt_ms"],
-                                                      "note": "the same call with the reference's token-at-a-time prompt loop (the default flow)"}}
+                                                      "note": "the same call with the reference's token-at-a-time prompt loop (set_batched_prefill(False))"}}
         line = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": n_gpus, "steps": K, "warmup": W,
                 "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "w4a16 (int4 weights, fp16 activations, fp32 accumulation)", "data": "synthetic",

@@ -21,7 +21,7 @@ MAX_STAGES = 8
 EXPORTS = [
     "qw3_strerror", "qw3_last_error", "qw3_dequant_w4", "qw3_w4_create", "qw3_w4_destroy", "qw3_ws_create",
     "qw3_ws_destroy", "qw3_ws_set_pdl", "qw3_ws_check", "qw3_gemv_w4a16", "qw3_gemv_w4a16_noalloc", "qw3_gemv_w4a16_noalloc_status", "qw3_gemm_w4a16", "qw3_rmsnorm",
-    "qw3_rope_kv_append", "qw3_attn_decode", "qw3_attn_prefill", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
+    "qw3_rope_kv_append", "qw3_attn_decode", "qw3_attn_prefill", "qw3_handoff_wait", "qw3_embed_gather_w4", "qw3_argmax_f16", "qw3_config_default",
     "qw3_create", "qw3_destroy", "qw3_generate", "qw3_decode_more", "qw3_last_logits", "qw3_last_timing", "qw3_last_launches",
     "qw3_set_batched_prefill",
     "qw3_set_chained_decode",
@@ -96,6 +96,7 @@ def lib():
         "qw3_rope_kv_append": [vp, vp, vp, vp, vp, vp, i32, i32, i64, vp, i32, vp],
         "qw3_attn_decode": [vp, vp, vp, i32, i32, i64, vp, i32, vp, vp, vp],
         "qw3_attn_prefill": [vp, vp, vp, i32, i32, i64, i32, i32, vp, vp],
+        "qw3_handoff_wait": [vp, i32, i64, i32, vp, vp],
         "qw3_embed_gather_w4": [vp, vp, vp, i64, i64, i64, vp, i32, vp, vp],
         "qw3_argmax_f16": [vp, i64, vp, vp, vp],
         "qw3_config_default": [C.POINTER(Config)],

@@ -39,6 +39,7 @@ int step_tail_launch(int* d_pos, int* d_step, const int* d_token, int* d_out_ids
                      cudaStream_t st);
 const W4Desc* w4_desc(qw3_w4_t w);
 const Workspace* ws_struct(qw3_ws_t ws);
+int flag_wait_launch(const int* d_flag, int want, long long limit_clocks, int* err, int code, cudaStream_t st);
 // stage hand-off between processes (handoff.cu)
 size_t mailbox_bytes(int hidden);
 void* mailbox_linked_inbox(void* mb, int hidden);
@@ -150,7 +151,8 @@ struct qw3_engine {
     int msg_out = 0, msg_in = 0;        // hidden-state messages sent to the next stage / taken from the previous one
     int tok_out = 0, tok_in = 0;        // token messages (last stage -> first stage)
     int blk_out = 0, blk_in = 0;        // blocks of prompt rows (batched prompt phase)
-    bool batched_prefill = false;       // prompt in blocks of rows through the tensor-core contraction (qw3_set_batched_prefill)
+    int batched_prefill = -1;           // prompt in blocks of rows through the tensor-core contraction: 1 always, 0 never (the reference's
+                                        // token loop), -1 (default) from PF_AUTO_ROWS prompt tokens on (qw3_set_batched_prefill)
     int seq_len = 0;                    // token passes through the layers so far (next position)
     int sampled = 0;                    // ids sampled since the last prompt
     int gen = 0;                        // generate calls so far (one process per GPU: part of the cross-GPU tags)
@@ -451,6 +453,11 @@ static int handoff(qw3_engine* e, int from, int to, bool hidden, bool token) {
     QW3_CUDA(cudaSetDevice(a.device));
     QW3_CUDA(cudaStreamWaitEvent(a.stream, b.taken, 0));
     return QW3_OK;
+}
+
+constexpr int PF_AUTO_ROWS = 16;   // prompts at least this long take the batched prompt phase unless the caller chose
+static bool use_batched_prefill(const qw3_engine* e, int n_prompt) {
+    return e->batched_prefill > 0 || (e->batched_prefill < 0 && n_prompt >= PF_AUTO_ROWS);
 }
 
 // ---- batched prompt phase ---------------------------------------------------------------------------
@@ -945,7 +952,7 @@ static int generate_mp(qw3_engine* e, const int32_t* prompt, int32_t n_prompt, i
     if (s.d_gen) QW3_CUDA(cudaMemcpyAsync(s.d_gen, &e->gen, 4, cudaMemcpyHostToDevice, s.stream));
     if (first) QW3_CUDA(cudaMemcpyAsync(s.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s.stream));
     QW3_CUDA(cudaEventRecord(e->ev0, s.stream));
-    if (e->batched_prefill) {
+    if (use_batched_prefill(e, n_prompt)) {
         for (int t0 = 0; t0 < n_prompt; t0 += PF_BLOCK)
             QW3_TRY(prefill_block_mp(e, t0, n_prompt - t0 < PF_BLOCK ? n_prompt - t0 : PF_BLOCK));
     } else {
@@ -1040,7 +1047,7 @@ int qw3_generate(qw3_handle e, const int32_t* prompt, int32_t n_prompt, int32_t 
     QW3_CUDA(cudaSetDevice(s0.device));
     QW3_CUDA(cudaMemcpyAsync(s0.d_prompt, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s0.stream));
     QW3_CUDA(cudaEventRecord(e->ev0, s0.stream));
-    if (e->batched_prefill) {
+    if (use_batched_prefill(e, n_prompt)) {
         for (int t0 = 0; t0 < n_prompt; t0 += PF_BLOCK) QW3_TRY(prefill_block(e, t0, n_prompt - t0 < PF_BLOCK ? n_prompt - t0 : PF_BLOCK));
     } else {
         for (int t = 0; t < n_prompt; ++t) QW3_TRY(run_pass(e, false, true));        // Inference.cu:1304-1343
@@ -1092,7 +1099,7 @@ int qw3_last_logits(qw3_handle e, float* out_vocab) {
 
 int qw3_set_batched_prefill(qw3_handle e, int on) {
     QW3_REQUIRE(e, "qw3_set_batched_prefill: null handle");
-    e->batched_prefill = on != 0;   // one process per GPU: every stage must be set alike
+    e->batched_prefill = on < 0 ? -1 : (on != 0);   // one process per GPU: every stage must be set alike
     return QW3_OK;
 }
 
@@ -1251,6 +1258,12 @@ int qw3_stage_connect(qw3_handle e, const void* next_stage_handle_64B, const voi
         }
     }
     return QW3_OK;
+}
+
+int qw3_handoff_wait(const int32_t* d_flag, int32_t want, int64_t limit_clocks, int32_t code, qw3_ws_t ws, void* stream) {
+    QW3_REQUIRE(d_flag && ws, "qw3_handoff_wait: null pointer");
+    QW3_REQUIRE(limit_clocks > 0, "qw3_handoff_wait: the limit must be positive");
+    return flag_wait_launch(d_flag, want, limit_clocks, ws_struct(ws)->err, code, static_cast<cudaStream_t>(stream));
 }
 
 int qw3_tp_export(qw3_handle e, void* out_handle_64B) {

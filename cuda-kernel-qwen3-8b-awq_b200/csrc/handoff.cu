@@ -54,11 +54,12 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Bounded wait for *flag >= want.  Returns false after ~2^34 clocks.
-__device__ __forceinline__ bool wait_flag(const int* flag, int want) {
+// Bounded wait for *flag >= want.  Returns false after `limit` clocks (default ~2^34, about nine seconds).
+constexpr long long HANDOFF_WAIT_CLOCKS = 1ll << 34;
+__device__ __forceinline__ bool wait_flag(const int* flag, int want, long long limit = HANDOFF_WAIT_CLOCKS) {
     const long long t0 = clock64();
     while (ld_acquire_sys(flag) < want) {
-        if (clock64() - t0 > (1ll << 34)) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(64);
     }
     return true;
@@ -115,8 +116,8 @@ __global__ void token_recv_kernel(int* __restrict__ d_token, const Mailbox* my_m
 
 // Blocks of prompt rows: the rows move with a copy-engine copy between the two GPUs; these two one-thread kernels
 // around it carry the protocol (wait for the flag, bounded; publish the flag after the copy before it in the stream).
-__global__ void flag_wait_kernel(const int* flag, int want, int* err, int code) {
-    if (threadIdx.x == 0 && !wait_flag(flag, want)) atomicCAS(err, 0, code);
+__global__ void flag_wait_kernel(const int* flag, int want, int* err, int code, long long limit) {
+    if (threadIdx.x == 0 && !wait_flag(flag, want, limit)) atomicCAS(err, 0, code);
 }
 __global__ void flag_set_kernel(int* flag, int value) {
     if (threadIdx.x != 0) return;
@@ -126,7 +127,7 @@ __global__ void flag_set_kernel(int* flag, int value) {
 
 // Block `msg` (1, 2, ...) of `bytes` from `rows_src` into the next stage's block inbox.
 int block_send(const void* rows_src, size_t bytes, void* next_mb, const void* my_mb, int msg, int hidden, int* err, cudaStream_t st) {
-    flag_wait_kernel<<<1, 32, 0, st>>>(&static_cast<const Mailbox*>(my_mb)->blk_ack, msg - 2, err, 0x40004);
+    flag_wait_kernel<<<1, 32, 0, st>>>(&static_cast<const Mailbox*>(my_mb)->blk_ack, msg - 2, err, 0x40004, HANDOFF_WAIT_CLOCKS);
     QW3_CUDA(cudaGetLastError());
     QW3_CUDA(cudaMemcpyAsync(mailbox_block_inbox(next_mb, hidden, msg & 1), rows_src, bytes, cudaMemcpyDeviceToDevice, st));
     flag_set_kernel<<<1, 32, 0, st>>>(&static_cast<Mailbox*>(next_mb)->blk_flag, msg);
@@ -135,7 +136,7 @@ int block_send(const void* rows_src, size_t bytes, void* next_mb, const void* my
 }
 // Block `msg` out of this stage's block inbox into `rows_dst`, then the acknowledgement to the stage before.
 int block_recv(void* rows_dst, size_t bytes, void* my_mb, void* prev_mb, int msg, int hidden, int* err, cudaStream_t st) {
-    flag_wait_kernel<<<1, 32, 0, st>>>(&static_cast<const Mailbox*>(my_mb)->blk_flag, msg, err, 0x40005);
+    flag_wait_kernel<<<1, 32, 0, st>>>(&static_cast<const Mailbox*>(my_mb)->blk_flag, msg, err, 0x40005, HANDOFF_WAIT_CLOCKS);
     QW3_CUDA(cudaGetLastError());
     QW3_CUDA(cudaMemcpyAsync(rows_dst, mailbox_block_inbox(my_mb, hidden, msg & 1), bytes, cudaMemcpyDeviceToDevice, st));
     flag_set_kernel<<<1, 32, 0, st>>>(&static_cast<Mailbox*>(prev_mb)->blk_ack, msg);
@@ -162,6 +163,14 @@ int token_send(const int* d_token, void* first_mb, int msg, cudaStream_t st) {
 }
 int token_recv(int* d_token, const void* my_mb, int msg, int* err, cudaStream_t st) {
     token_recv_kernel<<<1, 32, 0, st>>>(d_token, static_cast<const Mailbox*>(my_mb), msg, err);
+    QW3_CUDA(cudaGetLastError());
+    return QW3_OK;
+}
+
+// Test hook: the protocol's wait kernel on a flag of the caller with a caller-chosen limit, so that a wait can be made to
+// run out in milliseconds (the flag is simply never set): the kernel returns, the error word carries `code`.
+int flag_wait_launch(const int* d_flag, int want, long long limit_clocks, int* err, int code, cudaStream_t st) {
+    flag_wait_kernel<<<1, 32, 0, st>>>(d_flag, want, err, code, limit_clocks);
     QW3_CUDA(cudaGetLastError());
     return QW3_OK;
 }

@@ -37,9 +37,9 @@ class QWen3AWQInfer:
         return [int(out[i]) for i in range(n_out.value)]
 
     def set_batched_prefill(self, on):
-        """Prompt in blocks of rows through the tensor-core contraction (True) or token by token as the
-        reference (False, the default)."""
-        cabi.check(self._lib.qw3_set_batched_prefill(self._h, 1 if on else 0), "qw3_set_batched_prefill")
+        """Prompt in blocks of rows through the tensor-core contraction (True), token by token as the reference
+        (False), or None: blocks for prompts of 16 tokens or more (the default of a new object)."""
+        cabi.check(self._lib.qw3_set_batched_prefill(self._h, -1 if on is None else (1 if on else 0)), "qw3_set_batched_prefill")
 
     def set_chained_decode(self, on):
         """One process per GPU: chain the stages inside the token-pass kernels from the second decode step on (True,

@@ -233,14 +233,15 @@ int qw3_generate(qw3_handle h, const int32_t* prompt, int32_t n_prompt, int32_t 
  * caller stream a long generation in pieces and lets a benchmark time decode steps alone. */
 int qw3_decode_more(qw3_handle h, int32_t max_new, int32_t* out_ids, int32_t* n_out);
 
-/* Prompt phase in blocks of up to 256 rows (on = 1) instead of token by token (on = 0, the default and the
- * reference's flow, Inference.cu:1304-1343): the four projections of a layer become the tensor-core
- * contraction of qw3_gemm_w4a16 over the block, with row versions of RMSNorm, RoPE + KV append, causal
- * attention, residual add and GeLU around them.  Per-element arithmetic is unchanged; the contractions sum
- * in a different fp32 order, so cache rows and the hidden state can differ from the token loop in the last
- * fp16 bit.  With one process per GPU (world > 1) the blocks travel from stage to stage through the mailboxes'
- * block inboxes (a peer copy between two flag kernels) and the stages overlap on successive blocks; every stage
- * must be set alike. */
+/* Prompt phase in blocks of up to 256 rows (on = 1) instead of token by token (on = 0, the reference's flow,
+ * Inference.cu:1304-1343); on = -1 (the default of a new handle) takes the blocks for prompts of 16 tokens or more and the
+ * token loop below that.  In a block the four projections of a layer become the tensor-core contraction of
+ * qw3_gemm_w4a16, with row versions of RMSNorm, RoPE + KV append, causal attention (tiled, on the tensor cores),
+ * residual add and GeLU around them.  Per-element arithmetic is unchanged; the contractions sum in a different fp32
+ * order, so cache rows and the hidden state can differ from the token loop in the last fp16 bit (the golden ids are
+ * reproduced either way).  With one process per GPU (world > 1) the blocks travel from stage to stage through the
+ * mailboxes' block inboxes (a peer copy between two flag kernels) and the stages overlap on successive blocks; every
+ * stage must be set alike. */
 int qw3_set_batched_prefill(qw3_handle h, int on);
 
 /* One process per GPU (world > 1): from the second decode step on the stages are chained inside the token-pass
@@ -287,6 +288,12 @@ int qw3_debug_trace(qw3_handle h, int32_t stage, uint64_t* out, int32_t max_entr
  * elsewhere). */
 int qw3_stage_export(qw3_handle h, void* out_handle_64B);
 int qw3_stage_connect(qw3_handle h, const void* next_stage_handle_64B, const void* prev_stage_handle_64B);
+
+/* The wait of the stage hand-off protocol (Inference.cu:1013-1023 has no such protocol: it relies on host synchronisation)
+ * as a stand-alone launch: one thread waits until *d_flag >= want, at most `limit_clocks` GPU clocks; when the wait runs
+ * out the kernel returns and stores `code` in the workspace's error word, which qw3_ws_check reports as QW3_ERR_TIMEOUT.
+ * The engine uses the same kernel with a limit of 2^34 clocks; this entry lets a host (or a test) choose a short one. */
+int qw3_handoff_wait(const int32_t* d_flag, int32_t want, int64_t limit_clocks, int32_t code, qw3_ws_t ws, void* stream);
 
 /* Row-split tensor parallelism (world > 1, tensor_parallel = 1): one process per GPU; every process loads the whole
  * weight directory, keeps its share of every matrix in the fused pass's layout (its heads of Wqkv / Wo and of the KV

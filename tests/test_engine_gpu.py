@@ -192,6 +192,7 @@ def test_full_model_tokens_match_golden(pkg, orc, cuda, full_dir):
     prompt = orc.gen_tokens(g["seed"], orc.TOKENS, g["n_prompt"], cfg.vocab)
     assert [int(t) for t in prompt[:8]] == g["prompt_head"]
     inf = pkg.QWen3AWQInfer(full_dir, keep_logits=1, **g["config"])
+    inf.set_batched_prefill(False)      # the reference's token loop (a new object would take blocks for this prompt length)
     got = inf.generateResponse(prompt, g["max_new"])
     logits = inf.last_logits()
     # the same run with the prompt as one block of 128 rows through the tensor-core contraction

@@ -92,3 +92,33 @@ def test_argmax_first_max_wins(ops, orc, cuda):
     logits[140000] = np.float16(2.0)   # tie between two maxima: the lower index
     assert int(ops.argmax_f16(_to_dev(logits, cuda), ws).item()) == 100000
     ws.check()
+
+
+def test_a_device_wait_that_runs_out_is_reported_and_leaves_the_gpu_usable(ops, orc, cuda):
+    """The hand-off protocol's wait kernel on a flag nobody sets, with a limit of about two milliseconds: the kernel
+    returns by itself, the workspace reports QW3_ERR_TIMEOUT with the code it was given, and the same workspace then
+    runs a GEMV correctly.  Nothing faults or hangs: the wait is bounded by design and this is its limit being reached."""
+    import ctypes as C
+    cabi = ops.cabi
+    ws = ops.Workspace()
+    flag = torch.zeros(4, dtype=torch.int32, device=cuda)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    cabi.check(cabi.lib().qw3_handoff_wait(C.c_void_p(flag.data_ptr()), 1, 4_000_000, 0x40005, ws.h, st), "qw3_handoff_wait")
+    with pytest.raises(cabi.Qw3Error) as e:
+        ws.check()
+    assert e.value.status == cabi.QW3_ERR_TIMEOUT and b"0x40005" in cabi.lib().qw3_last_error()
+    ws.check()   # the word was cleared by the failing check
+    # a flag that is already set: the same launch returns without an error
+    flag[0] = 3
+    cabi.check(cabi.lib().qw3_handoff_wait(C.c_void_p(flag.data_ptr()), 2, 4_000_000, 0x40005, ws.h, st), "qw3_handoff_wait")
+    ws.check()
+    M, K = 1536, 512
+    p, s, z = orc.gen_linear(41, M, K)
+    x = orc.gen_normal_f16(41, orc.ACT, K)
+    w = ops.W4Linear(_to_dev(p, cuda), _to_dev(s, cuda), _to_dev(z, cuda), M, K)
+    y = torch.zeros(M, dtype=torch.float16, device=cuda)
+    ops.gemv_w4a16(w, ws, ops.gemv_args(_to_dev(x, cuda), y=y))
+    ws.check()
+    y32, _ = orc.gemm_w4a16(p, s, z, M, K, x)
+    err = np.abs(y.cpu().numpy().astype(np.float32) - y32)
+    assert (err <= 2e-2 * np.abs(y32) + 2e-2 * np.abs(y32).mean()).all()
