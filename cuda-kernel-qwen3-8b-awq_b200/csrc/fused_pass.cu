@@ -164,6 +164,13 @@ __device__ __forceinline__ void ldt2(const unsigned long long* p, unsigned long 
     if (SYS) asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
     else asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
+// Four adjacent words by one 32-byte load (the address is 32-byte aligned).  Every word is still checked by its own tag:
+// nothing here relies on the four arriving together.
+template <bool SYS>
+__device__ __forceinline__ void ldt4(const unsigned long long* p, unsigned long long (&w)[4]) {
+    if (SYS) asm volatile("ld.relaxed.sys.global.v4.b64 {%0, %1, %2, %3}, [%4];" : "=l"(w[0]), "=l"(w[1]), "=l"(w[2]), "=l"(w[3]) : "l"(p) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.v4.b64 {%0, %1, %2, %3}, [%4];" : "=l"(w[0]), "=l"(w[1]), "=l"(w[2]), "=l"(w[3]) : "l"(p) : "memory");
+}
 template <bool SYS>
 __device__ __forceinline__ void stt(unsigned long long* p, unsigned long long a) {
     if (SYS) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
@@ -240,6 +247,58 @@ __device__ __forceinline__ void poll_batch(const FusedParams& p, const FCtx& cx,
             if (!have[e]) {
                 w[e] = ldt<SYS>(addr(e));
                 have[e] = has_tag(w[e], tag);
+            }
+            ok = ok && have[e];
+        }
+        if (ok || *cx.s_dead != 0) break;
+        if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
+            fail(cx, code);
+            break;
+        }
+    }
+}
+
+// The same for PAIRS of adjacent words (one 16-byte load each): addr(e) is the first word of pair e, 16-byte aligned.
+template <bool SYS, int NB, typename AddrFn>
+__device__ __forceinline__ void poll_pairs(const FusedParams& p, const FCtx& cx, const int n_valid, AddrFn addr, const uint32_t tag,
+                                           const int code, unsigned long long (&w)[NB][2]) {
+    const long long t_begin = clock64();
+    bool have[NB];
+#pragma unroll
+    for (int e = 0; e < NB; ++e) have[e] = e >= n_valid;
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int e = 0; e < NB; ++e) {
+            if (!have[e]) {
+                ldt2<SYS>(addr(e), w[e][0], w[e][1]);
+                have[e] = has_tag(w[e][0], tag) && has_tag(w[e][1], tag);
+            }
+            ok = ok && have[e];
+        }
+        if (ok || *cx.s_dead != 0) break;
+        if (clock64() - t_begin > (SYS ? FP_WAIT_PEER : FP_WAIT_LOCAL)) {
+            fail(cx, code);
+            break;
+        }
+    }
+}
+
+// The same for groups of FOUR adjacent words (one 32-byte load each): addr(e) is 32-byte aligned.
+template <bool SYS, int NB, typename AddrFn>
+__device__ __forceinline__ void poll_quads(const FusedParams& p, const FCtx& cx, const int n_valid, AddrFn addr, const uint32_t tag,
+                                           const int code, unsigned long long (&w)[NB][4]) {
+    const long long t_begin = clock64();
+    bool have[NB];
+#pragma unroll
+    for (int e = 0; e < NB; ++e) have[e] = e >= n_valid;
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int e = 0; e < NB; ++e) {
+            if (!have[e]) {
+                ldt4<SYS>(addr(e), w[e]);
+                have[e] = has_tag(w[e][0], tag) && has_tag(w[e][1], tag) && has_tag(w[e][2], tag) && has_tag(w[e][3], tag);
             }
             ok = ok && have[e];
         }
@@ -1024,18 +1083,19 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         // ---- ordered sum over the heads for this CTA's rs outputs + residual (Inference.cu:1145-1156) ----------------------
         {
             const int r_src = o_first / n_out, off = o_first % n_out;
-            const int nw = G.heads * rs;
-            unsigned long long w[8];
+            const int np = (G.heads * rs) >> 1;   // pairs of adjacent words: rs is even and a contributor's rs words are contiguous
+            unsigned long long w[4][2];
             const unsigned long long* src = p.xo[G.rank] + (size_t)r_src * n_out + off;
-            poll_batch<SYS, 8>(p, cx, (nw - tid + FP_NT - 1) / FP_NT,
+            poll_pairs<SYS, 4>(p, cx, (np - tid + FP_NT - 1) / FP_NT,
                                [&](int e) {
-                                   const int k = tid + e * FP_NT, hq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
+                                   const int k = 2 * (tid + e * FP_NT), hq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
                                    return src + (size_t)hq * gs * n_out + (k - hq * rs);
                                }, t0 + 2,
                                0x50000 | li, w);
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
+            for (int e = 0; e < 4; ++e)
+                if (tid + e * FP_NT < np)
+                    *reinterpret_cast<float2*>(cx.obuf + 2 * (tid + e * FP_NT)) = make_float2(payload_f(w[e][0]), payload_f(w[e][1]));
         }
         __syncthreads();
         FP_STAMP(li, 7);
@@ -1080,17 +1140,33 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     }
     // ---- ordered sum over all contributors for this CTA's rs outputs + residual (Inference.cu:1217-1228) ----------------------
     const int ncontrib = G.n_ranks * G.n_mlp, nw = ncontrib * rs;
-    {
-        unsigned long long w[8];
+    if ((rs & 3) == 0) {   // a contributor's rs words are contiguous: four at a time
+        const int nq4 = nw >> 2;
+        unsigned long long w[2][4];
         const unsigned long long* src = p.x2[G.rank] + o_first;
-        poll_batch<SYS, 8>(p, cx, (nw - tid + FP_NT - 1) / FP_NT,
+        poll_quads<SYS, 2>(p, cx, (nq4 - tid + FP_NT - 1) / FP_NT,
                            [&](int e) {
-                               const int k = tid + e * FP_NT, cq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
+                               const int k = 4 * (tid + e * FP_NT), cq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
                                return src + (size_t)cq * H + (k - cq * rs);
                            }, t0 + 4, 0x60000 | li, w);
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-            if (tid + e * FP_NT < nw) cx.obuf[tid + e * FP_NT] = payload_f(w[e]);
+        for (int e = 0; e < 2; ++e)
+            if (tid + e * FP_NT < nq4)
+                *reinterpret_cast<float4*>(cx.obuf + 4 * (tid + e * FP_NT)) =
+                    make_float4(payload_f(w[e][0]), payload_f(w[e][1]), payload_f(w[e][2]), payload_f(w[e][3]));
+    } else {
+        const int np = nw >> 1;
+        unsigned long long w[4][2];
+        const unsigned long long* src = p.x2[G.rank] + o_first;
+        poll_pairs<SYS, 4>(p, cx, (np - tid + FP_NT - 1) / FP_NT,
+                           [&](int e) {
+                               const int k = 2 * (tid + e * FP_NT), cq = p.rs_shift >= 0 ? k >> p.rs_shift : k / rs;
+                               return src + (size_t)cq * H + (k - cq * rs);
+                           }, t0 + 4, 0x60000 | li, w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (tid + e * FP_NT < np)
+                *reinterpret_cast<float2*>(cx.obuf + 2 * (tid + e * FP_NT)) = make_float2(payload_f(w[e][0]), payload_f(w[e][1]));
     }
     __syncthreads();
     FP_STAMP(li, 12);
