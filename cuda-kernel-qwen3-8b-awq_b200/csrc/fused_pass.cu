@@ -208,6 +208,7 @@ struct FCtx {
     __half* hmine;      // [rs] this CTA's part of the residual stream
     __half* rope_cs;    // [128] cos | sin of this position
     float* wsum;        // [64]
+    float* bsm;         // [2][2 * F_NW] scratch rows of block_sum_max
     double* dsum;       // [16]
     uint32_t* un_sz;    // [<= 64] scale | zp pairs of the unembedding groups in use
     float* argv;        // [16]
@@ -613,26 +614,27 @@ __device__ __forceinline__ float block_sum_f(const FCtx& cx, float v) {   // all
     return s;
 }
 
-// Sum of v and maximum of a (a >= 0) over the CTA; all threads call.
-__device__ __forceinline__ void block_sum_max(const FCtx& cx, float v, float a, float& sum, float& amax) {
+// Sum of v and maximum of a (a >= 0) over the CTA; all threads call.  `which` (0 / 1) names one of two scratch rows: the
+// two calls of a layer alternate, and a row's readers of the layer before are many barriers away, so ONE barrier does.
+__device__ __forceinline__ void block_sum_max(const FCtx& cx, const int which, float v, float a, float& sum, float& amax) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) {
         v += __shfl_xor_sync(0xffffffffu, v, m);
         a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, m));
     }
-    __syncthreads();
+    float* row = cx.bsm + which * 2 * F_NW;
     if (lane == 0) {
-        cx.wsum[warp] = v;
-        cx.wsum[F_NW + warp] = a;
+        row[warp] = v;
+        row[F_NW + warp] = a;
     }
     __syncthreads();
     sum = 0.0f;
     amax = 0.0f;
 #pragma unroll
     for (int w = 0; w < F_NW; ++w) {
-        sum += cx.wsum[w];
-        amax = fmaxf(amax, cx.wsum[F_NW + w]);
+        sum += row[w];
+        amax = fmaxf(amax, row[F_NW + w]);
     }
 }
 // A short activation vector (one element per thread, `n` of them) to the digit planes; a barrier must follow.
@@ -1060,7 +1062,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         __half ch = __float2half_rn(0.0f);
         if (tid < 128) ch = __float2half_rn(O / Lsum);   // one rounding to fp16, Inference.cu:257-265
         float x_o, c_max;
-        block_sum_max(cx, __half2float(ch), fabsf(__half2float(ch)), x_o, c_max);   // its barriers also free st
+        block_sum_max(cx, 0, __half2float(ch), fabsf(__half2float(ch)), x_o, c_max);   // its barrier also frees st
         quantise_own(cx, ch, 128, c_max);
         __syncthreads();
         FP_STAMP(li, 5);
@@ -1104,7 +1106,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
             for (int hg = 0; hg < G.heads; ++hg) v += cx.obuf[hg * rs + tid];
             cx.hmine[tid] = h_add(cx.hmine[tid], __float2half_rn(v));   // fp16 store of the GEMV, then __hadd
         }
-        __syncthreads();
+        if (rs <= 32) __syncwarp(); else __syncthreads();   // writers and readers of hmine are the first rs threads
         publish_hidden<SYS>(p, cx, 0, t0 + 3, cglob);
         FP_STAMP(li, 8);
     }
@@ -1120,7 +1122,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     __half ge = __float2half_rn(0.0f);
     if (tid < n1) ge = gelu_h(__float2half_rn(sc * (sum_k_shares(cx, p.plan[F_W1], tid) - zp * x_full)));
     float x_g, g_max;
-    block_sum_max(cx, __half2float(ge), fabsf(__half2float(ge)), x_g, g_max);   // its barriers also free obuf
+    block_sum_max(cx, 1, __half2float(ge), fabsf(__half2float(ge)), x_g, g_max);   // its barrier also frees obuf
     quantise_own(cx, ge, n1, g_max);
     __syncthreads();
     FP_STAMP(li, 10);
@@ -1138,6 +1140,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     __syncthreads();
     FP_STAMP(li, 14);
     }
+    layer_commit(cx, (li + 1) & 1, lp);   // the next layer's constants: visible after the barriers below, last read a layer ago
     // ---- ordered sum over all contributors for this CTA's rs outputs + residual (Inference.cu:1217-1228) ----------------------
     const int ncontrib = G.n_ranks * G.n_mlp, nw = ncontrib * rs;
     if ((rs & 3) == 0) {   // a contributor's rs words are contiguous: four at a time
@@ -1183,10 +1186,8 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         for (int q = 1; q < parts; ++q) v += cx.obuf[nw + q * rs + tid];
         cx.hmine[tid] = h_add(cx.hmine[tid], __float2half_rn(v));
     }
-    __syncthreads();
+    if (rs <= 32) __syncwarp(); else __syncthreads();
     publish_hidden<SYS>(p, cx, 1, t0 + 5, cglob);
-    layer_commit(cx, (li + 1) & 1, lp);
-    __syncthreads();
     FP_STAMP(li, 13);
     (void)lane; (void)warp;
 }
@@ -1358,6 +1359,8 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.n_seg = *reinterpret_cast<int*>(misc + 5640);
     cx.plans = reinterpret_cast<const FGemvPlan*>(misc + 5648);   // F_NOPS plans
     cx.wplan = reinterpret_cast<const int4*>(misc + 5888);        // F_NOPS * F_NW entries
+    cx.bsm = reinterpret_cast<float*>(misc + 5888 + F_NOPS * F_NW * 16);
+    static_assert(5888 + F_NOPS * F_NW * 16 + 4 * F_NW * 4 <= FP_MISC_BYTES, "scratch rows in the misc area");
     static_assert(5648 + F_NOPS * sizeof(FGemvPlan) <= 5888 && 5888 + F_NOPS * F_NW * 16 <= FP_MISC_BYTES, "plans in the misc area");
     cx.tagbase = 0;
     cx.pos = 0;
