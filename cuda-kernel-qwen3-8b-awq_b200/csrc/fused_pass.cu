@@ -209,6 +209,7 @@ struct FCtx {
     __half* rope_cs;    // [128] cos | sin of this position
     float* wsum;        // [64]
     float* bsm;         // [2][2 * F_NW] scratch rows of block_sum_max
+    float* gsm;         // [2][3 * F_NW] scratch rows of gather_norm (with dsum [2][F_NW])
     double* dsum;       // [16]
     uint32_t* un_sz;    // [<= 64] scale | zp pairs of the unembedding groups in use
     float* argv;        // [16]
@@ -659,8 +660,10 @@ __device__ __forceinline__ void quantise_own(const FCtx& cx, const __half v, con
 template <bool SYS, bool QUANT>
 __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx, const unsigned long long* hid, const uint32_t tag,
                                             const __half* gamma, __half* out, const int slice, const int hs, float& x_full,
-                                            float& x_slice, float& bound) {
+                                            float& x_slice, float& bound, const int which) {   // which (0 / 1): scratch row; successive calls alternate
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* const row = cx.gsm + which * 3 * F_NW;   // [2 * F_NW] sums, [F_NW] maxima
+    double* const drow = cx.dsum + which * F_NW;
     const int H = p.g.H, nch = H >> 2;   // chunks of two words = four halves
     unsigned long long w[2][2] = {{0ull, 0ull}, {0ull, 0ull}};
     uint2 gm[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
@@ -707,14 +710,13 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
         s += shfl_xor_double(s, m);
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
     }
-    __syncthreads();   // dsum / wsum of the phase before are no longer read
-    if (lane == 0) {
-        cx.dsum[warp] = s;
-        cx.wsum[2 * F_NW + warp] = amax;
+    if (lane == 0) {   // (the row's readers of two calls ago are many barriers away)
+        drow[warp] = s;
+        row[2 * F_NW + warp] = amax;
     }
     __syncthreads();
-    double tot = cx.dsum[lane & (F_NW - 1)];
-    amax = cx.wsum[2 * F_NW + (lane & (F_NW - 1))];
+    double tot = drow[lane & (F_NW - 1)];
+    amax = row[2 * F_NW + (lane & (F_NW - 1))];
 #pragma unroll
     for (int m = 8; m > 0; m >>= 1) {
         tot += shfl_xor_double(tot, m);
@@ -766,7 +768,7 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
     for (int e = 0; e < 2; ++e) {
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) ps[e] += __shfl_xor_sync(0xffffffffu, ps[e], m);
-        if (lane == 0) cx.wsum[e * F_NW + warp] = ps[e];
+        if (lane == 0) row[e * F_NW + warp] = ps[e];
     }
     __syncthreads();   // the result and the warp sums are visible
     x_full = 0.0f;
@@ -774,7 +776,7 @@ __device__ __forceinline__ void gather_norm(const FusedParams& p, const FCtx& cx
     const int lo = slice * hs, hi = lo + hs;
 #pragma unroll
     for (int k = 0; k < 2 * F_NW; ++k) {
-        const float v = cx.wsum[k];
+        const float v = row[k];
         x_full += v;
         const int first = 4 * ((k & (F_NW - 1)) * 32 + (k / F_NW) * FP_NT);   // first element of that warp's row of chunks
         if (first >= lo && first < hi) x_slice += v;                           // (slice < 0: the range is empty)
@@ -847,7 +849,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     // ---- RMSNorm + this CTA's K-slice of Wqkv for its head (Inference.cu:1036-1065) -----------------------------------
     float x_full, x_slice, x_bound;
     FP_STAMP(li, 0);
-    gather_norm<SYS, true>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, L.gamma, nullptr, r, hs, x_full, x_slice, x_bound);
+    gather_norm<SYS, true>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, L.gamma, nullptr, r, hs, x_full, x_slice, x_bound, 0);
     FP_STAMP(li, 1);
     float sc = 0.0f, zp = 0.0f;
     if (tid < FP_QKV) {
@@ -1012,20 +1014,17 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
         FP_STAMP(li, 4);
         if (split) {
             // group exchange: every CTA of the head stores its state and merges all gs of them in CTA order
-            if (p.cluster) {
+            const float* sts = st;   // the gs states to merge
+            if (p.cluster) {         // they arrive in this CTA's own shared memory: the four warps that merge wait for them, no CTA barrier
                 if (tid < 128) {
                     cl_store(cx.xa_in + r * FP_ATT_STRIDE + tid, O, cx.cl_bars + 8, gs);
                     if (tid == 0) {
                         cl_store(cx.xa_in + r * FP_ATT_STRIDE + 128, M, cx.cl_bars + 8, gs);
                         cl_store(cx.xa_in + r * FP_ATT_STRIDE + 129, Lsum, cx.cl_bars + 8, gs);
                     }
-                }
-                __syncthreads();   // everybody has read st
-                if (tid < 160) {
                     cl_wait(cx, cx.cl_bars + 8, li & 1, 0x40000 | li);
-                    if (tid < 130)
-                        for (int r0 = 0; r0 < gs; ++r0) st[r0 * FP_ATT_STRIDE + tid] = cx.xa_in[r0 * FP_ATT_STRIDE + tid];
                 }
+                sts = cx.xa_in;
             } else {
                 if (tid < 128) stt<false>(p.xa + (size_t)c * FP_ATT_STRIDE + tid, tagged_f(O, t0 + 1));
                 if (tid == 0) {
@@ -1044,18 +1043,18 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
                             if (r0 + e < gs) st[(r0 + e) * FP_ATT_STRIDE + tid] = payload_f(w[e]);
                     }
                 }
+                __syncthreads();
             }
-            __syncthreads();
             if (tid < 128) {
                 M = -INFINITY;
-                for (int q = 0; q < gs; ++q) M = fmaxf(M, st[q * FP_ATT_STRIDE + 128]);
+                for (int q = 0; q < gs; ++q) M = fmaxf(M, sts[q * FP_ATT_STRIDE + 128]);
                 Lsum = 0.0f;
                 O = 0.0f;
                 for (int q = 0; q < gs; ++q) {
-                    const float mq = st[q * FP_ATT_STRIDE + 128];
+                    const float mq = sts[q * FP_ATT_STRIDE + 128];
                     const float w = (mq == -INFINITY) ? 0.0f : expf(mq - M);
-                    Lsum += st[q * FP_ATT_STRIDE + 129] * w;
-                    O += st[q * FP_ATT_STRIDE + tid] * w;
+                    Lsum += sts[q * FP_ATT_STRIDE + 129] * w;
+                    O += sts[q * FP_ATT_STRIDE + tid] * w;
                 }
             }
         }
@@ -1081,8 +1080,11 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
             const int ro = p.hpr_shift >= 0 ? (int)(o >> p.hpr_shift) : (int)(o / (H / G.n_ranks));   // rank that owns these two elements
             stt2<SYS>(p.xo[ro] + (size_t)(hglob * gs + r) * n_out + i0, tagged_f(y0, t0 + 2), tagged_f(y1, t0 + 2));
         }
-        __syncthreads();   // obuf is free again
         // ---- ordered sum over the heads for this CTA's rs outputs + residual (Inference.cu:1145-1156) ----------------------
+        // The gathered words go to the end of obuf; where that does not overlap Wo's sums no barrier is needed in between.
+        const int xo_at = (plo.wk * n_out + G.heads * rs <= FP_OBUF) ? FP_OBUF - G.heads * rs : 0;
+        if (xo_at == 0) __syncthreads();   // obuf is free again
+        float* const xo_s = cx.obuf + xo_at;
         {
             const int r_src = o_first / n_out, off = o_first % n_out;
             const int np = (G.heads * rs) >> 1;   // pairs of adjacent words: rs is even and a contributor's rs words are contiguous
@@ -1097,13 +1099,13 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
 #pragma unroll
             for (int e = 0; e < 4; ++e)
                 if (tid + e * FP_NT < np)
-                    *reinterpret_cast<float2*>(cx.obuf + 2 * (tid + e * FP_NT)) = make_float2(payload_f(w[e][0]), payload_f(w[e][1]));
+                    *reinterpret_cast<float2*>(xo_s + 2 * (tid + e * FP_NT)) = make_float2(payload_f(w[e][0]), payload_f(w[e][1]));
         }
         __syncthreads();
         FP_STAMP(li, 7);
         if (tid < rs) {
             float v = 0.0f;
-            for (int hg = 0; hg < G.heads; ++hg) v += cx.obuf[hg * rs + tid];
+            for (int hg = 0; hg < G.heads; ++hg) v += xo_s[hg * rs + tid];
             cx.hmine[tid] = h_add(cx.hmine[tid], __float2half_rn(v));   // fp16 store of the GEMV, then __hadd
         }
         if (rs <= 32) __syncwarp(); else __syncthreads();   // writers and readers of hmine are the first rs threads
@@ -1114,7 +1116,7 @@ __device__ __forceinline__ void layer_pass(const FusedParams& p, const FCtx& cx,
     if (c < G.n_mlp) {
     const int cmlp = G.rank * G.n_mlp + c;
     // ---- RMSNorm (same gamma) + this CTA's n1 outputs of W1 + GeLU (Inference.cu:1158-1197) ----------------------------------
-    gather_norm<SYS, true>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, nullptr, -1, H, x_full, x_slice, x_bound);
+    gather_norm<SYS, true>(p, cx, p.hid[G.rank], t0 + 3, L.gamma, nullptr, -1, H, x_full, x_slice, x_bound, 1);
     FP_STAMP(li, 9);
     if (tid < n1) group_consts(lsz + F_W1 * FP_MAX_GROUPS, (long long)cmlp * n1 + tid, sc, zp);
     run_gemv(ring, F_W1, cx.xd);
@@ -1214,7 +1216,7 @@ __device__ __forceinline__ void sample_pass(const FusedParams& p, const FCtx& cx
         __syncthreads();
     }
     float xf, xsl, hv_bound;
-    gather_norm<SYS, false>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, p.gamma_final, cx.hv, -1, H, xf, xsl, hv_bound);
+    gather_norm<SYS, false>(p, cx, p.hid[G.rank] + (H >> 1), tag_in, p.gamma_final, cx.hv, -1, H, xf, xsl, hv_bound, 0);
     const int n_alloc = p.n_alloc[F_UNEMB];
     const int n_used = min(Kb, n_alloc);
     if (tid < n_used) cx.un_sz[tid] = pack_h2(p.un_scale[tid], p.un_zp[tid]);
@@ -1342,7 +1344,7 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.hmine = reinterpret_cast<__half*>(misc + 2048);           // 512
     cx.rope_cs = reinterpret_cast<__half*>(misc + 2560);         // 256
     cx.wsum = reinterpret_cast<float*>(misc + 2816);             // 256
-    cx.dsum = reinterpret_cast<double*>(misc + 3072);            // 128
+    cx.dsum = reinterpret_cast<double*>(misc + 3072);            // 256: two rows of F_NW
     cx.un_sz = reinterpret_cast<uint32_t*>(misc + 5120);         // 512: groups in use | this round's table
     cx.argv = reinterpret_cast<float*>(misc + 3456);             // 64
     cx.argi = reinterpret_cast<int*>(misc + 3520);               // 64
@@ -1360,7 +1362,8 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem) {
     cx.plans = reinterpret_cast<const FGemvPlan*>(misc + 5648);   // F_NOPS plans
     cx.wplan = reinterpret_cast<const int4*>(misc + 5888);        // F_NOPS * F_NW entries
     cx.bsm = reinterpret_cast<float*>(misc + 5888 + F_NOPS * F_NW * 16);
-    static_assert(5888 + F_NOPS * F_NW * 16 + 4 * F_NW * 4 <= FP_MISC_BYTES, "scratch rows in the misc area");
+    cx.gsm = cx.bsm + 4 * F_NW;
+    static_assert(5888 + F_NOPS * F_NW * 16 + (4 + 6) * F_NW * 4 <= FP_MISC_BYTES, "scratch rows in the misc area");
     static_assert(5648 + F_NOPS * sizeof(FGemvPlan) <= 5888 && 5888 + F_NOPS * F_NW * 16 <= FP_MISC_BYTES, "plans in the misc area");
     cx.tagbase = 0;
     cx.pos = 0;
