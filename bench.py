@@ -39,8 +39,8 @@ METRIC = "batch-1 decode tokens/s (Qwen3-8B W4A16)"
 LAST_REF_GEMV_US = None
 # dram__bytes_read.sum + dram__bytes_write.sum of fused_pass_kernel over its algorithmic bytes, from the ncu
 # capture summarised in profiles/fused_pass_kernel_6layers_ncu.md (a 6-layer pass; traffic grows with the bytes streamed).
-NCU_TRAFFIC_RATIO = (509.34 + 13.53) / 507.52
-NCU_TRAFFIC_NOTE = ("dram read+write of an ncu capture of a 6-layer pass (522.9 MB for 507.5 MB algorithmic), scaled by bytes to the "
+NCU_TRAFFIC_RATIO = (509.26 + 16.55) / 507.52
+NCU_TRAFFIC_NOTE = ("dram read+write of an ncu capture of a 6-layer pass (525.8 MB for 507.5 MB algorithmic), scaled by bytes to the "
                     "36-layer launch")
 PROMPT_LEN = 128          # one GPU: prompt 128 + 20 new ids is the baseline's single-GPU configuration
 PROMPT_LEN_MULTI = 512    # several GPUs: prompt 512 + 128 new ids
@@ -329,13 +329,13 @@ def pass_only(pkg, orc, args):
     if not os.path.exists(os.path.join(wdir, "unembed_zp.bin")):
         orc.write_weight_dir(orc.default_config(**cfg), SEED, wdir)
     prompt = [int(t) for t in orc.gen_tokens(SEED, orc.TOKENS, args.prompt_len, V)]
-    inf = pkg.QWen3AWQInfer(wdir, **cfg)
+    inf = pkg.QWen3AWQInfer(wdir, no_cluster=1 if args.no_cluster else 0, **cfg)
     inf.generateResponse(prompt, args.warmup)
     inf.decode_more(args.steps)
     layer_bytes = L * (LAYER_PACKED + 1024) + V * 4096 // 2
     ms = inf.last_timing()[1] / args.steps
     out = {"kernel": "fused_pass_kernel", "layers": L, "vocab": V, "context": args.prompt_len + args.warmup, "ms_per_token": ms,
-           "packed_bytes_per_launch": layer_bytes, "GBps": layer_bytes / ms / 1e6}
+           "packed_bytes_per_launch": layer_bytes, "GBps": layer_bytes / ms / 1e6, "cluster": not args.no_cluster}
     inf.close()
     return out
 
