@@ -329,7 +329,7 @@ def pass_only(pkg, orc, args):
     if not os.path.exists(os.path.join(wdir, "unembed_zp.bin")):
         orc.write_weight_dir(orc.default_config(**cfg), SEED, wdir)
     prompt = [int(t) for t in orc.gen_tokens(SEED, orc.TOKENS, args.prompt_len, V)]
-    inf = pkg.QWen3AWQInfer(wdir, no_cluster=1 if args.no_cluster else 0, **cfg)
+    inf = pkg.QWen3AWQInfer(wdir, cluster=0 if args.no_cluster else 1, **cfg)
     inf.generateResponse(prompt, args.warmup)
     inf.decode_more(args.steps)
     layer_bytes = L * (LAYER_PACKED + 1024) + V * 4096 // 2
@@ -421,7 +421,9 @@ def main():
                          "bandwidth works on the same token) or the reference's layer pipeline")
     ap.add_argument("--attn-split-min", type=int, default=0,
                     help="fused pass: contexts longer than this are split over the CTAs of a head group (0: the engine's default)")
-    ap.add_argument("--no-cluster", action="store_true", help="fused pass: head groups exchange through global memory instead of a thread-block cluster")
+    ap.add_argument("--no-cluster", action="store_true", help="fused pass: head groups exchange through global memory instead of a thread-block cluster (the library's default; "
+                         "the bench turns clusters on unless this is given; needed under Nsight Compute, which terminates a process that "
+                         "launches the cooperative cluster form)")
     ap.add_argument("--only-roofline", action="store_true", help="run only the dominant-kernel timing (small case for profilers)")
     ap.add_argument("--roofline-mats", type=int, default=36)
     ap.add_argument("--roofline-reps", type=int, default=6)
@@ -511,7 +513,7 @@ def main():
         pipeline.connect_ring(inf, dist)
     else:
         inf = pkg.QWen3AWQInfer(wdir, max_pos=max_pos, n_stages=n_gpus, device=list(range(n_gpus)), attn_split_min=args.attn_split_min,
-                                no_cluster=1 if args.no_cluster else 0)
+                                cluster=0 if args.no_cluster else 1)
     barrier()
     ids_all = inf.generateResponse(prompt, W)              # prompt pass + W warm-up decode steps
     sampler = ClockSampler(local)
@@ -634,7 +636,10 @@ def main():
                 "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "w4a16 (int4 weights, fp16 activations, fp32 accumulation)", "data": "synthetic",
                 "config": {"workload": workload_string(args), "parallelism": par,
-                           "l2": "3.3 GB of weights streamed per step (inputs larger than L2)"},
+                           "l2": "3.3 GB of weights streamed per step (inputs larger than L2)",
+                           "head_groups": ("global memory" if (n_gpus > 1 or args.no_cluster) else
+                                           "thread-block clusters (Qw3Config.cluster = 1)")},
+                "dtype_note": "the fused pass accumulates exactly in s32 on the integer tensor cores (fixed-point activations), fp32 in its epilogues",
                 "timed_regions": {"repeats": R, "steps_each": K, "ms": region_ms, "median_ms": decode_ms,
                                   "spread": (max(region_ms) - min(region_ms)) / decode_ms},
                 **check,

@@ -50,7 +50,7 @@ class Config(C.Structure):
                 ("first_layer", C.c_int32 * (MAX_STAGES + 1)), ("device", C.c_int32 * MAX_STAGES),
                 ("rank", C.c_int32), ("world", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32),
                 ("keep_logits", C.c_int32), ("persistent", C.c_int32), ("tensor_parallel", C.c_int32),
-                ("attn_split_min", C.c_int32), ("no_cluster", C.c_int32)]
+                ("attn_split_min", C.c_int32), ("cluster", C.c_int32)]
 
 
 def build(force=False, verbose=False):

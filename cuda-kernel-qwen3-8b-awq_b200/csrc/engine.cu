@@ -656,7 +656,7 @@ static int create_fused(qw3_engine* e, Stage& s) {
     a.H = c.hidden; a.I = c.inter; a.heads = c.heads; a.vocab = c.vocab; a.n_layers = n_layers; a.eps = c.eps; a.max_pos = c.max_pos;
     a.n_ranks = n_ranks; a.rank = rank; a.sm_count = ws->sm_count; a.device = s.device;
     a.attn_split_min = c.attn_split_min > 0 ? c.attn_split_min : 32;
-    a.no_cluster = c.no_cluster != 0;
+    a.no_cluster = c.cluster == 0;
     a.layers = in.data();
     a.emb = first ? &emb : nullptr;
     a.unemb = last ? &unemb : nullptr;

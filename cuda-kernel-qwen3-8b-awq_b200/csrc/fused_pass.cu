@@ -106,6 +106,7 @@ struct FusedParams {
     const int* d_pos; const int* d_token; const int* d_skip; const int* d_prompt; const int* d_gen;
     int decode;
     int cluster;                  // 1: the gs CTAs of a head are one thread-block cluster and exchange through distributed shared memory
+    int dry;                      // 1: the launch only proves that the configuration can be launched (every CTA returns after the cluster barrier)
     const __half* cos_t; const __half* sin_t;
     long long max_pos;
     int* d_token_out;
@@ -1455,6 +1456,7 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
+    if (p.dry) return;
 #ifdef QW3_FP_FILL
     for (int i = tid; i < (int)(FP_OFF_OBUF / 4); i += FP_NT) reinterpret_cast<uint32_t*>(smem)[i] = (uint32_t)i * 2654435761u + 12345u * blockIdx.x;
     __syncthreads();
@@ -1899,6 +1901,23 @@ int fused_create(const FusedCreate& a, FusedPass** out) {
     }
 #endif
     f->sys = g.n_ranks > 1;
+    if (P.cluster) {
+        // Occupancy said the clusters fit; a launch that does nothing proves it (a profiler, or another client of the GPU,
+        // can leave too few SMs for co-resident clusters).  If it is refused the same grid runs without clusters: the head
+        // groups then exchange through global memory, as they do when the matrices are row-split over GPUs.
+        FusedParams q = P;
+        q.dry = 1;
+        void* args[] = {&q};
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[2];
+        fused_launch_config(f->grid, g.gs, a.stream, &cfg, attr);
+        cudaError_t le = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(fused_pass_kernel<false>), args);
+        if (le == cudaSuccess) le = cudaStreamSynchronize(a.stream);
+        if (le != cudaSuccess) {
+            (void)cudaGetLastError();
+            P.cluster = 0;
+        }
+    }
     *out = f;
     return QW3_OK;
 }

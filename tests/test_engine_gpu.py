@@ -129,12 +129,12 @@ def test_small_model_attention_split_over_the_head_group(pkg, orc, cuda, small_d
     _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, attn_split_min=3), 2, 10)
 
 
-def test_small_model_head_groups_without_cluster(pkg, orc, cuda, small_dir):
-    """On one GPU the CTAs of a head group exchange through distributed shared memory (one thread-block cluster per
-    group); no_cluster=1 keeps them on tagged words in global memory, the form the row split over GPUs uses: same
-    results, with the attention whole and split."""
-    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, no_cluster=1), 2, 10)
-    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, no_cluster=1, attn_split_min=3), 2, 10)
+def test_small_model_head_groups_as_clusters(pkg, orc, cuda, small_dir):
+    """cluster=1: on one GPU the CTAs of a head group form a thread-block cluster and exchange through distributed
+    shared memory instead of tagged words in global memory (the default, and the form the row split over GPUs uses):
+    same results, with the attention whole and split."""
+    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, cluster=1), 2, 10)
+    _check_steps_and_probes(pkg, orc, "small_model", small_dir, dict(SMALL, cluster=1, attn_split_min=3), 2, 10)
 
 
 @pytest.mark.parametrize("persistent", [2, 1, 0])
@@ -214,6 +214,11 @@ def test_full_model_every_step_and_hidden_probes(pkg, orc, cuda, full_dir, persi
     """The 36-layer model step by step: ids, top-8 logits of every step, hidden state after layers 0, 17 and 35 at the
     last prompt position and at decode step 19."""
     _check_steps_and_probes(pkg, orc, "full_model", full_dir, GOLDEN["full_model"]["config"], persistent, 24)
+
+
+def test_full_model_head_groups_as_clusters(pkg, orc, cuda, full_dir):
+    """The same 24 steps and probes with the head groups as thread-block clusters (what bench.py runs on one GPU)."""
+    _check_steps_and_probes(pkg, orc, "full_model", full_dir, dict(GOLDEN["full_model"]["config"], cluster=1), 2, 24)
 
 
 def test_errors_are_status_codes(pkg, orc, cuda, small_dir, tmp_path):
