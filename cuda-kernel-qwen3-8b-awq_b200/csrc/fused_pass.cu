@@ -17,8 +17,11 @@
 // the same words are stored into every GPU's copy of the exchange buffers over NVLink and polled locally.
 //
 // Weights: every matrix is rewritten at load time (fused_plan.h) into per-(CTA, warp) byte streams in consumption
-// order.  Each warp owns FP_SLOTS ring slots of F_UNIT bytes and refills a slot with its own next unit (1-D bulk copy,
-// L2 evict-first) as soon as it has consumed it, across operator boundaries, since weights never depend on activations.
+// order, the 16 warp streams of a CTA interleaved in units.  A ring of FP_SLOTS slots per CTA holds the units in flight:
+// one 1-D bulk copy (L2 evict-first) per unit; a warp counts itself off a unit once its last loads of it are issued and
+// the sixteenth warp refills the slot, across operator boundaries, since weights never depend on activations.
+// On one GPU the CTAs of a head can form a thread-block cluster (FusedParams::cluster): the two exchanges inside the
+// group then go through distributed shared memory instead of global memory.
 // Inner loop: the integer tensor-core path.  One 16-byte shared-memory load per lane yields four words; `w & 0x0f0f0f0f`
 // and `w & 0xf0f0f0f0` of two words ARE the u8 A fragment of mma.sync.m16n8k32 (u8 x s8 -> s32): the low nibbles of a
 // word are four weights of row g, the high nibbles four weights of row g + 8 times 16.  The activations of the
@@ -347,12 +350,10 @@ __device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, co
     const uint8_t* base = reinterpret_cast<const uint8_t*>(((unsigned long long)(uint32_t)sg.y << 32) | (uint32_t)sg.x);
     const int piece = sg.w;
     const uint32_t bar = cx.bars + 8 * slot;
-    // The slot was read with ordinary loads whose values have all been consumed (every warp counted itself off after
-    // its last MMA on the piece), so the bulk write cannot overtake them; no proxy fence is needed for this
-    // read-then-overwrite order, and one here would wait for the copies still in flight into the other slots.
-#ifdef QW3_FP_FENCE
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
+    // The slot was read with ordinary loads that have all completed (every warp counted itself off with a release
+    // operation after issuing its last loads of the piece), so the bulk write cannot overtake them; no proxy fence is
+    // needed for this read-then-overwrite order, and one here would wait for the copies still in flight into the
+    // other slots (measured: no difference in results, slower).
     *cx.ring_issued += 1;
     mbar_expect_tx(bar, F_NW * piece);
     bulk_load(smem_u32(cx.ring) + slot * (F_NW * F_UNIT), base + (size_t)r.pu * (F_NW * piece), F_NW * piece, bar, l2_policy_evict_first());
@@ -362,13 +363,10 @@ __device__ __forceinline__ void ring_issue(const WarpRing& r, const FCtx& cx, co
 __device__ __forceinline__ uint32_t ring_wait(const WarpRing& r, const FCtx& cx, const int piece) {
     const int warp = threadIdx.x >> 5, slot = r.uc % FP_SLOTS;
     uint32_t addr = smem_u32(cx.ring) + slot * (F_NW * F_UNIT) + warp * piece;
-#if !defined(QW3_FP_NOLOAD) && !defined(QW3_FP_NOWAIT)
+#ifndef QW3_FP_NOLOAD
     // One lane polls the barrier (barrier operations of a CTA are served one at a time: 512 threads polling cost more
     // than the piece's arithmetic); the warp barrier hands the observation, and the memory order it implies, to the others.
-#ifndef QW3_FP_ALLWAIT
-    if ((threadIdx.x & 31) == 0)
-#endif
-    {
+    if ((threadIdx.x & 31) == 0) {
         if (*cx.s_dead == 0 && !mbar_wait(cx.bars + 8 * slot, (r.uc / FP_SLOTS) & 1)) {
             if ((threadIdx.x & 31) == 0) fail(cx, 0x10000 | (r.uc & 0xffff));   // a weight unit never arrived
         }
@@ -534,12 +532,7 @@ __device__ __forceinline__ FCtx carve_ctx(uint8_t* smem);
 // loop was in the kernel twenty times, and a pass spent a sixth of its issue slots waiting for instructions).  The
 // function takes and returns the ring cursor in registers and finds everything else in shared memory, so nothing of
 // it lives in local memory.
-#ifdef QW3_FP_INLINE_GEMV
-__device__ __forceinline__
-#else
-__device__ __noinline__
-#endif
-int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const uint32_t x_cta_addr) {
+__device__ __noinline__ int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const uint32_t x_cta_addr) {
     extern __shared__ __align__(1024) uint8_t smem[];
     FP_WSTAMP(op, 0);
     const FCtx cx = carve_ctx(smem);
@@ -550,10 +543,8 @@ int3 gemv_entry(const int uc, const int pseg, const int pu, const int op, const 
     const uint32_t xs_addr = x_cta_addr + wp.x;
     float* dst = cx.obuf + wp.y;
     switch (pl.tb) {
-#ifndef QW3_FP_TB34
         case 1: gemv_core<1>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
         case 2: gemv_core<2>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
-#endif
         case 3: gemv_core<3>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
         default: gemv_core<4>(cx, ring, pl, xs_addr, dst, op, wp.z, wp.w); break;
     }
@@ -1457,10 +1448,6 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     if (p.dry) return;
-#ifdef QW3_FP_FILL
-    for (int i = tid; i < (int)(FP_OFF_OBUF / 4); i += FP_NT) reinterpret_cast<uint32_t*>(smem)[i] = (uint32_t)i * 2654435761u + 12345u * blockIdx.x;
-    __syncthreads();
-#endif
     WarpRing ring;
     ring.uc = 0; ring.pseg = 0; ring.pu = 0;
     for (int s = 0; s < FP_SLOTS; ++s) {   // prime the ring: thread 0 issues, every warp moves its cursor along
@@ -1514,8 +1501,6 @@ __global__ void __launch_bounds__(FP_NT, 1) fused_pass_kernel(const FusedParams 
             }
         }
     }
-#ifdef QW3_FP_L2PF
-#endif
     if (p.n_rounds > 0) sample_pass<SYS>(p, cx, ring);
     // After a wait has given up, units may have been requested that nobody consumed: their copies must have landed
     // before the CTA gives up its shared memory (bounded; a normal pass has none outstanding).
