@@ -7,6 +7,7 @@ import multiprocessing as mp
 import os
 import socket
 
+import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
@@ -30,15 +31,16 @@ def _rank_main(rank, world, port, wdir, prompt, q, sample_first, chained):
     try:
         torch.cuda.set_device(rank)
         inf = pkg.QWen3AWQInfer(wdir, n_stages=world, world=world, rank=rank, device=list(range(world)),
-                                sample_first=sample_first, **SMALL)
+                                sample_first=sample_first, keep_logits=1 if rank == world - 1 else 0, **SMALL)
         pipeline.connect_ring(inf, dist)
         inf.set_chained_decode(bool(chained))
         dist.barrier()
         ids = inf.generateResponse(prompt, 6)
         more = inf.decode_more(4)
+        logits = inf.last_logits() if rank == world - 1 else None   # of the tenth step, on the stage that samples
         dist.barrier()
         ids = pipeline.broadcast_ids(ids + more if rank == world - 1 else [], 10, dist)
-        q.put((rank, ids))
+        q.put((rank, ids, logits))
         inf.close()
     finally:
         dist.destroy_process_group()
@@ -66,7 +68,7 @@ def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_f
     for p in procs:
         p.start()
     try:
-        got = sorted(q.get(timeout=300) for _ in range(world))
+        got = sorted((q.get(timeout=300) for _ in range(world)), key=lambda t: t[0])
         for p in procs:
             p.join(timeout=120)
             assert p.exitcode == 0
@@ -75,8 +77,13 @@ def test_one_process_per_gpu_matches_golden(orc, cuda, tmp_path, world, sample_f
             if p.is_alive():
                 p.terminate()
                 p.join()
-    for rank, ids in got:
+    g = golden["small_model_sample_first" if sample_first else "small_model"]
+    for rank, ids, logits in got:
         assert ids == want, (rank, ids, want)
+        if rank == world - 1:   # not the ids only: the last step's eight largest logits of the oracle, within the logits tolerance
+            top = np.array(g["last_logits_top8_idx"])
+            ref = np.array(g["last_logits_top8"], np.float32)
+            assert (np.abs(logits[top] - ref) <= 2e-2 * np.abs(ref) + 2e-2 * np.abs(ref).mean()).all()
 
 
 def _rank_main_batched(rank, world, port, wdir, prompt, q, max_pos):
