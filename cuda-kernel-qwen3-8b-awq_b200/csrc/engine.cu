@@ -464,8 +464,8 @@ static bool use_batched_prefill(const qw3_engine* e, int n_prompt) {
 // A block of `rows` prompt tokens at positions pos0.. goes through every stage together: the projections are
 // the tensor-core contraction, the rest the row kernels of prefill.cu.  Same per-element arithmetic as the
 // token-at-a-time loop (Inference.cu:1304-1343); the contractions sum in a different fp32 order.
-constexpr int PF_BLOCK = 1024;  // also the rows a block inbox of the mailbox holds (handoff.cu); the contraction reaches 0.4 of its
-                                // tensor bound at 256 rows and 0.6 at 1024 and more
+constexpr int PF_BLOCK = 2048;  // also the rows a block inbox of the mailbox holds (handoff.cu); the contraction reaches 0.4 of its
+                                // tensor bound at 256 rows and 0.6 at 2048
 
 static int prefill_alloc(qw3_engine* e, Stage& s) {
     if (s.pf_h) return QW3_OK;

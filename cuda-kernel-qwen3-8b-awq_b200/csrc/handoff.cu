@@ -35,7 +35,7 @@ struct Mailbox {
 };
 static_assert(sizeof(Mailbox) == 256, "mailbox header is 256 bytes");
 
-constexpr int MB_BLOCK_ROWS = 1024;  // largest block of prompt rows handed over at once (PF_BLOCK of the engine)
+constexpr int MB_BLOCK_ROWS = 2048;  // largest block of prompt rows handed over at once (PF_BLOCK of the engine)
 size_t mailbox_bytes(int hidden) {
     return sizeof(Mailbox) + (size_t)2 * hidden * 2 + (size_t)(hidden / 2) * 8 + (size_t)2 * MB_BLOCK_ROWS * hidden * 2;
 }

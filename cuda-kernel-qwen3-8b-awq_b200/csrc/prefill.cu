@@ -163,16 +163,16 @@ attn_prefill_kernel(const __half* __restrict__ qkv, const __half* __restrict__ k
     ctx[(size_t)r * hidden + head * 128 + tid] = __float2half_rn(O / L);
 }
 
-// ---- the same attention on the tensor cores, tiled: 64 query rows x 64 cache rows at a time ------------------------------
-// grid (heads, ceil(R / 64)), 4 warps; warp w owns query rows 16w .. 16w+15 of the CTA's block.  A tile of 64 cache rows
-// of K and V (16 KB each) is shared by the 64 query rows instead of being read once per row from L2, which is what
-// made the row-per-CTA kernel take 1.8 of the 2.0 s of an 8 K prompt.  Per tile and warp: S = Q K^T by 64
+// ---- the same attention on the tensor cores, tiled: 64 query rows x 32 cache rows at a time ------------------------------
+// grid (heads, ceil(R / 64)), 4 warps; warp w owns query rows 16w .. 16w+15 of the CTA's block.  A tile of 32 cache rows
+// of K and V (8 KB each) is shared by the 64 query rows instead of being read once per row from L2, which is what
+// made the row-per-CTA kernel take 1.8 of the 2.0 s of an 8 K prompt.  Per tile and warp: S = Q K^T by 32
 // mma.sync.m16n8k16 (fp16 operands, exact products, fp32 sums), online softmax in registers in the accumulator layout,
-// O += P V by 64 more with P as the A operand.  P goes in as TWO fp16 terms (P = hi + lo, lo the rounding error of hi),
+// O += P V by 32 more (twice) with P as the A operand.  P goes in as TWO fp16 terms (P = hi + lo, lo the rounding error of hi),
 // so the probabilities keep 22 bits as in the fp32 arithmetic of the row kernel; V comes in through
 // ldmatrix.trans.  K / V tiles are double-buffered with cp.async; rows past the causal limit are zero-filled and masked.
 // (mma.sync, not tcgen05: an accumulator that the softmax rescales every tile has to live in registers.)
-constexpr int TA_ROWS = 64, TA_KEYS = 64, TA_THREADS = 128;
+constexpr int TA_ROWS = 64, TA_KEYS = 32, TA_THREADS = 128, TA_NJ = TA_KEYS / 8;   // (64-key tiles: 8 % slower at 8 K rows, 16-key tiles 20 %)
 constexpr int TA_LD = 136;                                   // halves per shared-memory row (272 B: ldmatrix rows 16-byte aligned, no bank conflicts)
 constexpr size_t TA_TILE = (size_t)TA_KEYS * TA_LD * 2;      // bytes of one K or V tile
 constexpr size_t TA_SMEM = (size_t)TA_ROWS * TA_LD * 2 + 4 * TA_TILE;
@@ -199,11 +199,11 @@ __device__ __forceinline__ void split_hi_lo(float a, float b, uint32_t& hi, uint
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-__global__ void __launch_bounds__(TA_THREADS)
+__global__ void __launch_bounds__(TA_THREADS, 4)   // 52 KB of shared memory and 128 registers: four CTAs per SM
 attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restrict__ kc, const __half* __restrict__ vc, int hidden,
                           long long max_pos, int pos0, int rows, __half* __restrict__ ctx) {
     extern __shared__ __align__(128) uint8_t ta_smem[];
-    const int head = blockIdx.x, r0 = blockIdx.y * TA_ROWS;
+    const int head = blockIdx.x, r0 = (gridDim.y - 1 - blockIdx.y) * TA_ROWS;   // the row blocks with the most cache rows start first
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const uint32_t q_s = smem_u32(ta_smem), kv_s = q_s + TA_ROWS * TA_LD * 2;   // kv_s + (2 * stage + {0: K, 1: V}) * TA_TILE
     const int n_rows = min(TA_ROWS, rows - r0);
@@ -249,9 +249,9 @@ attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restri
         __syncthreads();   // the tile (and, the first time, the q rows) are in shared memory
         const uint32_t k_s = kv_s + (2 * stage) * TA_TILE, v_s = k_s + TA_TILE;
         // ---- S = Q K^T: 16 rows x 64 keys per warp
-        float sc[8][4];
+        float sc[TA_NJ][4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < TA_NJ; ++j)
 #pragma unroll
             for (int d = 0; d < 4; ++d) sc[j][d] = 0.0f;
 #pragma unroll
@@ -259,7 +259,7 @@ attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restri
             uint32_t a0, a1, a2, a3;
             ldsm_x4(q_s + (uint32_t)((warp * 16 + (lane & 15)) * TA_LD + kk * 16 + 8 * (lane >> 4)) * 2, a0, a1, a2, a3);
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) {   // two key tiles per ldmatrix: (b0, b1) of tile j, then of tile j + 1
+            for (int j = 0; j < TA_NJ; j += 2) {   // two key tiles per ldmatrix: (b0, b1) of tile j, then of tile j + 1
                 uint32_t b0, b1, b2, b3;
                 ldsm_x4(k_s + (uint32_t)((j * 8 + (lane & 7) + 8 * (lane >> 4)) * TA_LD + kk * 16 + 8 * ((lane >> 3) & 1)) * 2, b0, b1, b2, b3);
                 mma_h(sc[j], a0, a1, a2, a3, b0, b1);
@@ -270,7 +270,7 @@ attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restri
         const int k0 = tile * TA_KEYS;
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < TA_NJ; ++j) {
 #pragma unroll
             for (int d = 0; d < 4; ++d) {
                 const int key = k0 + j * 8 + 2 * t + (d & 1);
@@ -297,7 +297,7 @@ attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restri
             o[n][2] *= c_hi; o[n][3] *= c_hi;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {   // a row with nothing visible yet (only rows past the block's end) keeps p = 0
+        for (int j = 0; j < TA_NJ; ++j) {   // a row with nothing visible yet (only rows past the block's end) keeps p = 0
             sc[j][0] = (mn_lo == -INFINITY) ? 0.0f : expf(sc[j][0] - mn_lo);
             sc[j][1] = (mn_lo == -INFINITY) ? 0.0f : expf(sc[j][1] - mn_lo);
             sc[j][2] = (mn_hi == -INFINITY) ? 0.0f : expf(sc[j][2] - mn_hi);
@@ -307,7 +307,7 @@ attn_prefill_tiled_kernel(const __half* __restrict__ qkv, const __half* __restri
         }
         // ---- O += P V: P (16 x 64) as A operand, hi and lo terms; V through ldmatrix.trans
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {   // 16 keys: score tiles 2kk and 2kk + 1
+        for (int kk = 0; kk < TA_KEYS / 16; ++kk) {   // 16 keys: score tiles 2kk and 2kk + 1
             uint32_t h0, h1, h2, h3, e0, e1, e2, e3;
             split_hi_lo(sc[2 * kk][0], sc[2 * kk][1], h0, e0);
             split_hi_lo(sc[2 * kk][2], sc[2 * kk][3], h1, e1);

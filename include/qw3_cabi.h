@@ -235,7 +235,7 @@ int qw3_generate(qw3_handle h, const int32_t* prompt, int32_t n_prompt, int32_t 
  * caller stream a long generation in pieces and lets a benchmark time decode steps alone. */
 int qw3_decode_more(qw3_handle h, int32_t max_new, int32_t* out_ids, int32_t* n_out);
 
-/* Prompt phase in blocks of up to 1024 rows (on = 1) instead of token by token (on = 0, the reference's flow,
+/* Prompt phase in blocks of up to 2048 rows (on = 1) instead of token by token (on = 0, the reference's flow,
  * Inference.cu:1304-1343); on = -1 (the default of a new handle) takes the blocks for prompts of 16 tokens or more and the
  * token loop below that.  In a block the four projections of a layer become the tensor-core contraction of
  * qw3_gemm_w4a16, with row versions of RMSNorm, RoPE + KV append, causal attention (tiled, on the tensor cores),

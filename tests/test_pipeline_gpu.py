@@ -117,9 +117,9 @@ def _rank_main_batched(rank, world, port, wdir, prompt, q, max_pos):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,n_prompt", [(2, 6), (2, 2600), (4, 2600)])
+@pytest.mark.parametrize("world,n_prompt", [(2, 6), (2, 5000), (4, 5000)])
 def test_one_process_per_gpu_batched_prompt(pkg, orc, cuda, tmp_path, world, n_prompt):
-    """Prompt in blocks of up to 1024 rows handed from stage to stage through the mailboxes' block inboxes (2600 rows:
+    """Prompt in blocks of up to 2048 rows handed from stage to stage through the mailboxes' block inboxes (5000 rows:
     three blocks over two acknowledged slots): same ids as the single-GPU run with the same blocks."""
     import torch
     if torch.cuda.device_count() < world:
