@@ -460,7 +460,8 @@ __device__ __forceinline__ void gemv_core(const FCtx& cx, WarpRing& ring, const 
                                           const int upb, const int ng) {   // units per block, full groups per unit
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nq = pl.nq, rem = pl.rem;
-    constexpr int NA = TB <= 2 ? 2 : 1;   // accumulators per tile: at least three independent chains in flight
+    constexpr int NA = TB <= 3 ? 2 : 1;   // accumulators per tile: the two MMAs of a group never wait for each other (six chains at
+                                          // TB = 3: 2.5 % in tokens/s over one accumulator; at TB = 4 the second set costs registers: slower)
     // B fragment: column g of the MMA is digit plane g (columns 3-7 are zero); lane t holds 16 consecutive inputs of a group
     const bool col = g < 3;
     const uint32_t bbase = xd_addr + g * FP_MAX_H + t * 16, bhalf = xd_addr + g * FP_MAX_H + nq * 64 + t * 8;
