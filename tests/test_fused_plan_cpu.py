@@ -38,6 +38,16 @@ def test_plan_of_the_full_model(pkg):
         assert p["unit_bytes"] == (p["tb"] * (p["nq"] * 512 + p["rem"] * 128) if p["rem"] else p["unit_bytes"] // group * group)
 
 
+def test_plan_of_the_full_model_in_clusters(pkg):
+    """With the head groups as thread-block clusters of four CTAs only 33 clusters are co-resident on the part: the grid
+    is 132 CTAs.  Same work split for the layers; the 1187 blocks of the unembedding then take nine full rounds."""
+    _, g148, pl148 = _plan(pkg, dict(max_pos=40960))
+    _, g, pl = _plan(pkg, dict(max_pos=40960), grid=132)
+    assert (g["gs"], g["n_act"], g["rs"], g["n1"], g["grid"]) == (4, 128, 32, 96, 132)
+    assert pl[:4] == pl148[:4]
+    assert -(-g["n_blocks"] // 132) == 9 and 9 * 132 - g["n_blocks"] == 1
+
+
 @pytest.mark.parametrize("n_ranks", [2, 4, 8])
 def test_plan_of_the_full_model_row_split(pkg, n_ranks):
     """Every matrix row-split over 2, 4 and 8 GPUs: all 128 CTAs of a GPU share its heads, the bytes divide by the GPUs."""
