@@ -70,3 +70,75 @@ def test_multiprocess_handle_requires_matching_stage_count(pkg, tmp_path):
     assert cabi.lib().qw3_create(str(tmp_path).encode(), C.byref(cfg), C.byref(h)) == cabi.QW3_ERR_ARG
     assert cabi.lib().qw3_stage_export(None, None) == cabi.QW3_ERR_ARG
     assert cabi.lib().qw3_stage_connect(None, None, None) == cabi.QW3_ERR_ARG
+
+
+class _FakeTpLib:
+    """Stands in for the C library in connect_all: hands out a handle that names its rank, records what is connected."""
+    def __init__(self, rank):
+        self.rank, self.connected = rank, None
+
+    def qw3_tp_export(self, h, buf):
+        for i in range(64):
+            buf[i] = self.rank + 1
+        return 0
+
+    def qw3_tp_connect(self, h, flat):
+        self.connected = bytes(flat)
+        return 0
+
+
+def _tp_rank_main(rank, world, port, q):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import torch.distributed as dist
+    from conftest import load_package
+    pkg = load_package()
+    import importlib
+    pipeline = importlib.import_module("qw3awq_b200.pipeline")
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        fake = _FakeTpLib(rank)
+        pkg.cabi.lib = lambda: fake                      # connect_all goes through cabi.lib()
+
+        class Infer:
+            _h = None
+        pipeline.connect_all(Infer(), dist)
+        q.put((rank, fake.connected))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_split_wiring_two_gloo_ranks():
+    """connect_all hands qw3_tp_connect the handles of ALL ranks, rank-major, 64 bytes each (the rank's own included),
+    and every rank gets the same table."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world = 2
+    procs = [ctx.Process(target=_tp_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        got = sorted(q.get(timeout=120) for _ in range(world))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join()
+    table = bytes([1]) * 64 + bytes([2]) * 64
+    assert got == [(0, table), (1, table)]
+    assert pkg_null_checks()
+
+
+def pkg_null_checks():
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from conftest import load_package
+    cabi = load_package().cabi
+    return cabi.lib().qw3_tp_export(None, None) == cabi.QW3_ERR_ARG and cabi.lib().qw3_tp_connect(None, None) == cabi.QW3_ERR_ARG
